@@ -1,0 +1,182 @@
+/*
+ * ruda_b200.h — C ABI of libruda_b200.so, the NVIDIA B200 (sm_100a) backend for the dense-transformer
+ * hot path of rust-ascend.
+ *
+ * Every entry point names the reference interface it stands in for (file:line inside the
+ * rust-ascend repository).  A Rust FFI crate binds these symbols one to one; the signatures use only
+ * plain pointers, integers and the POD structs below.
+ *
+ * Conventions (kept from the reference):
+ *   - every function returns an rb_status; 0 is success.  The message of the last failure on the
+ *     calling thread is returned by rb_last_error().  Status codes mirror the variants of
+ *     CannError (rust-ascend-driver/src/lib.rs:18-40); validation failures are RB_INVALID_TENSOR.
+ *   - one context per process and device (rust-ascend-driver/src/tensor/runtime/mod.rs:424-435).
+ *   - launches are enqueue-only on the context's stream; a failed launch is pushed on a sticky list
+ *     that the next rb_read / rb_sync reports as RB_SERVER_UNHEALTHY (runtime/mod.rs:645-661).
+ *     rb_options.synchronous = 1 restores the reference's launch-then-synchronise behaviour.
+ *   - tensors must be contiguous row-major unless a function says otherwise; outputs may not overlap
+ *     inputs (rust-ascend-driver/src/tensor/runtime/worker.rs:418-453).
+ *   - there is no CPU fallback: an unsupported dtype, layout or shape is an error (src/backend.rs:43-45).
+ */
+#ifndef RUDA_B200_H
+#define RUDA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define RB_API
+#else
+#define RB_API __attribute__((visibility("default")))
+#endif
+
+/* CannError variants, rust-ascend-driver/src/lib.rs:18-40. */
+typedef enum rb_status {
+    RB_OK = 0,
+    RB_LIBRARY = 1,          /* CannError::Library: a shared library could not be loaded        */
+    RB_SYMBOL = 2,           /* CannError::Symbol                                               */
+    RB_STATUS = 3,           /* CannError::Status{operation,code}: a CUDA / NCCL call failed    */
+    RB_INVALID_DEVICE = 4,   /* CannError::InvalidDevice                                        */
+    RB_INVALID_TENSOR = 5,   /* CannError::InvalidTensor(message)                               */
+    RB_NULL_HANDLE = 6,      /* CannError::NullHandle                                           */
+    RB_COMPLETION = 7,       /* CannError::Completion{operation,launch_code,sync_code}          */
+    RB_SERVER_UNHEALTHY = 8  /* ServerError::ServerUnhealthy{errors}, runtime/mod.rs:645-661    */
+} rb_status;
+
+/* ruda_core::tensor::DType values used on this path (runtime/hccl.rs:97-111 lists the same set). */
+typedef enum rb_dtype { RB_F32 = 0, RB_F16 = 1, RB_BF16 = 2, RB_I32 = 3, RB_I64 = 4, RB_U8 = 5 } rb_dtype;
+
+/* Transpose, rust-ascend-driver/src/tensor/deepgemm/plan.rs. */
+typedef enum rb_transpose { RB_NO_TRANSPOSE = 0, RB_TRANSPOSE = 1 } rb_transpose;
+
+/* RotaryLayout, rust-ascend-compiler/src/ascend/rotary_programs.rs:5-6. */
+typedef enum rb_rotary_layout { RB_ROTARY_INTERLEAVED = 0, RB_ROTARY_SPLIT_HALF = 1 } rb_rotary_layout;
+
+/* Epilogue fused into the GEMM store.  The reference GEMM stores the identity only
+ * (rust-ascend-kernels/src/kernel.rs:2); bias and SiLU*up are separate passes there
+ * (affine_programs.rs:31-36, programs.rs:25,41). */
+typedef enum rb_epilogue { RB_EPILOGUE_NONE = 0, RB_EPILOGUE_BIAS = 1, RB_EPILOGUE_SWIGLU = 2 } rb_epilogue;
+
+/* HcclReduceOp, rust-ascend-driver/src/tensor/runtime/hccl.rs. */
+typedef enum rb_reduce_op { RB_SUM = 0, RB_PROD = 1, RB_MAX = 2, RB_MIN = 3 } rb_reduce_op;
+
+/* Attention output layout: [B,H,M,Dv] is the reference's (src/nn/attention.rs:49-67); [B,M,H,Dv]
+ * feeds the output projection without a transpose. */
+typedef enum rb_attention_layout { RB_LAYOUT_BHMD = 0, RB_LAYOUT_BMHD = 1 } rb_attention_layout;
+
+/* RuntimeOptions, rust-ascend-driver/src/tensor/runtime/mod.rs:93-115. */
+typedef struct rb_options {
+    int32_t device;        /* CUDA ordinal (RuntimeOptions::device)                              */
+    int32_t synchronous;   /* 1: synchronise the stream after every launch, as the reference does */
+    uint64_t reserved[4];
+} rb_options;
+
+/* TensorBuffer{handle,shape,strides,dtype} (ruda_runtime; used throughout runtime/mod.rs:147-436).
+ * handle is a storage id from rb_alloc / rb_import; offset is the byte offset of element 0
+ * (Binding offset_start, runtime/mod.rs:629-644); strides are in elements. */
+typedef struct rb_tensor {
+    uint64_t handle;
+    uint64_t offset;
+    uint32_t dtype;
+    uint32_t rank;
+    uint64_t shape[8];
+    uint64_t strides[8];
+} rb_tensor;
+
+/* KernelStats / ProgramStats, deepgemm/mod.rs:16 and common_ir/mod.rs:12. */
+typedef struct rb_stats {
+    uint64_t launches;
+    uint64_t synchronizations;
+    uint64_t empty_calls;
+    uint64_t bytes_in_use;
+    uint64_t allocations;
+} rb_stats;
+
+typedef struct rb_ctx rb_ctx;
+
+/* ---- context, storage, server ------------------------------------------------------------------ */
+/* AscendRuntime::initialize_exclusive, runtime/mod.rs:424-435: once per process; a second call fails. */
+RB_API int32_t rb_init_exclusive(const rb_options* options, rb_ctx** out);
+/* Drops the process context (the reference keeps its worker for the process lifetime; tests need this). */
+RB_API int32_t rb_shutdown(rb_ctx* ctx);
+RB_API const char* rb_last_error(void);
+/* Device properties, runtime/mod.rs:544-595: name, SM count, memory bytes. */
+RB_API int32_t rb_device_properties(rb_ctx* ctx, char* name, size_t name_bytes, int32_t* sm_count, uint64_t* memory_bytes);
+
+/* AscendStorage::alloc / dealloc, runtime/mod.rs:501-515.  Alignment is 256 B (the reference's is 32);
+ * zero-byte requests still own a minimal allocation (tensor/mod.rs:106-111).  rb_free synchronises first. */
+RB_API int32_t rb_alloc(rb_ctx* ctx, uint64_t bytes, uint64_t* handle);
+RB_API int32_t rb_free(rb_ctx* ctx, uint64_t handle);
+/* Registers caller-owned device memory (for example a torch tensor) as a non-owning storage handle. */
+RB_API int32_t rb_import(rb_ctx* ctx, void* device_pointer, uint64_t bytes, uint64_t* handle);
+/* AscendStorage::get, runtime/mod.rs:494-500: resolves a handle to its device address and size. */
+RB_API int32_t rb_resource(rb_ctx* ctx, uint64_t handle, void** device_pointer, uint64_t* bytes);
+/* AscendServer::write / read, runtime/mod.rs:767-845.  write is asynchronous from pinned memory;
+ * read synchronises and raises the sticky errors first. */
+RB_API int32_t rb_write(rb_ctx* ctx, uint64_t handle, uint64_t offset, const void* host, uint64_t bytes);
+RB_API int32_t rb_read(rb_ctx* ctx, uint64_t handle, uint64_t offset, void* host, uint64_t bytes);
+RB_API int32_t rb_memset(rb_ctx* ctx, uint64_t handle, uint64_t offset, int32_t value, uint64_t bytes);
+/* AscendServer::sync / flush, runtime/mod.rs:840-856. */
+RB_API int32_t rb_sync(rb_ctx* ctx);
+/* Drains the sticky error list into buf (newline separated); *count receives how many were pending. */
+RB_API int32_t rb_take_errors(rb_ctx* ctx, char* buf, size_t buf_bytes, uint32_t* count);
+/* AscendServer::memory_usage and the launch counters. */
+RB_API int32_t rb_get_stats(rb_ctx* ctx, rb_stats* out);
+/* Pinned host staging memory for rb_write / rb_read. */
+RB_API int32_t rb_host_alloc(rb_ctx* ctx, uint64_t bytes, void** host);
+RB_API int32_t rb_host_free(rb_ctx* ctx, void* host);
+/* AscendServer::start_profile / end_profile, runtime/mod.rs:857-873, on CUDA events of the context's
+ * stream.  rb_profile_end synchronises and returns the elapsed device milliseconds. */
+RB_API int32_t rb_profile_begin(rb_ctx* ctx);
+RB_API int32_t rb_profile_end(rb_ctx* ctx, float* milliseconds);
+/* The context's CUDA stream as a cudaStream_t, for callers that share it with other libraries. */
+RB_API int32_t rb_stream(rb_ctx* ctx, void** stream);
+
+/* ---- row programs (FP32 math; storage F32 or BF16) --------------------------------------------- */
+/* AscendRuntime::rms_norm, runtime/mod.rs:405-408 -> normalization.rs:153-166, IR row_programs.rs:144-151.
+ * y = (x * rsqrt(mean(x^2) + eps)) * w over the last axis; rstd [rows] FP32 may be NULL. */
+RB_API int32_t rb_rms_norm(rb_ctx* ctx, const rb_tensor* x, const rb_tensor* weight, double epsilon,
+                           const rb_tensor* y, const rb_tensor* rstd);
+/* Runtime::layer_norm, runtime/mod.rs:442-448 -> normalization.rs:116-132, IR row_programs.rs:164-177.
+ * bias may be NULL (zeros); mean / rstd [rows] FP32 may be NULL. */
+RB_API int32_t rb_layer_norm(rb_ctx* ctx, const rb_tensor* x, const rb_tensor* weight, const rb_tensor* bias,
+                             double epsilon, const rb_tensor* y, const rb_tensor* mean, const rb_tensor* rstd);
+/* AscendRuntime::softmax / log_softmax, runtime/mod.rs:322-329 -> rows.rs:52-64, IR row_programs.rs:135-143. */
+RB_API int32_t rb_softmax(rb_ctx* ctx, const rb_tensor* x, int32_t logarithmic, const rb_tensor* y);
+/* AscendRuntime::sum_last / mean_last / max_last, runtime/mod.rs:286-303 (op: 0 sum, 1 mean, 2 max). */
+RB_API int32_t rb_reduce_last(rb_ctx* ctx, const rb_tensor* x, int32_t op, const rb_tensor* y);
+
+/* ---- element maps ------------------------------------------------------------------------------- */
+/* AscendRuntime::silu_mul, runtime/mod.rs:282-284 -> elementwise.rs:13-19, IR programs.rs:25,41. */
+RB_API int32_t rb_silu_mul(rb_ctx* ctx, const rb_tensor* gate, const rb_tensor* up, const rb_tensor* y);
+/* AscendRuntime::bias_add, runtime/mod.rs:179-181 -> affine.rs:10-22, IR affine_programs.rs:16-38.
+ * y = (x [+ residual]) + bias[col], in that order; residual may be NULL. */
+RB_API int32_t rb_bias_add(rb_ctx* ctx, const rb_tensor* x, const rb_tensor* bias, const rb_tensor* residual,
+                           const rb_tensor* y);
+/* Plain element-wise sum of two equal-shaped tensors (MapProgram::Add, programs.rs:34). */
+RB_API int32_t rb_add(rb_ctx* ctx, const rb_tensor* a, const rb_tensor* b, const rb_tensor* y);
+/* AscendRuntime::rotary / rotary_backward, runtime/mod.rs:259-268 -> rotary.rs:15-30, IR rotary_programs.rs:47-97. */
+RB_API int32_t rb_rotary(rb_ctx* ctx, const rb_tensor* x, const rb_tensor* cos, const rb_tensor* sin,
+                         int32_t layout, int32_t backward, const rb_tensor* y);
+/* AscendRuntime::rotary_prefix, runtime/mod.rs:215-221 -> rotary.rs:31-48, IR rotary_programs.rs:101-156.
+ * Tables have the rank of x, last axis width/2, other axes 1 or equal; columns >= width keep their bits. */
+RB_API int32_t rb_rotary_prefix(rb_ctx* ctx, const rb_tensor* x, const rb_tensor* cos, const rb_tensor* sin,
+                                uint32_t width, int32_t layout, int32_t backward, const rb_tensor* y);
+/* AscendRuntime::repeat_kv_heads, runtime/mod.rs:209 -> heads.rs:21-28, IR heads_programs.rs:43-55. */
+RB_API int32_t rb_repeat_kv_heads(rb_ctx* ctx, const rb_tensor* x, uint32_t query_heads, const rb_tensor* y);
+/* AscendRuntime::causal_mask, runtime/mod.rs:206 -> mask.rs:5-15, IR mask_programs.rs:19-39.
+ * out is FP32 [batch, queries, keys]. */
+RB_API int32_t rb_causal_mask(rb_ctx* ctx, uint64_t query_start, uint64_t key_start, const rb_tensor* out);
+/* AscendRuntime::cast / cast_into, runtime/mod.rs:271-279 -> conversion.rs:21-45 (F32 <-> BF16 <-> F16, RNE). */
+RB_API int32_t rb_cast(rb_ctx* ctx, const rb_tensor* x, const rb_tensor* y);
+/* AscendRuntime::embedding, runtime/mod.rs:231-233 -> indexing.rs:33-37: out[i,:] = table[ids[i],:]. */
+RB_API int32_t rb_embedding(rb_ctx* ctx, const rb_tensor* table, const rb_tensor* ids, const rb_tensor* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RUDA_B200_H */

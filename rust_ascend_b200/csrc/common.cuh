@@ -1,0 +1,78 @@
+// Shared host-side plumbing of libruda_b200: the process context, storage table, sticky errors,
+// tensor validation and the launch epilogue.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "ruda_b200.h"
+
+namespace rb {
+
+void set_error(const char* fmt, ...);
+int32_t fail(rb_status code, const char* fmt, ...);
+
+struct Storage {
+    void* ptr = nullptr;
+    uint64_t bytes = 0;
+    bool owned = false;
+};
+
+}  // namespace rb
+
+struct rb_ctx {
+    int device = 0;
+    bool synchronous = false;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t profile_start = nullptr, profile_stop = nullptr;
+    std::mutex lock;
+    std::unordered_map<uint64_t, rb::Storage> storage;
+    uint64_t next_handle = 1;
+    std::vector<std::string> sticky;   // failures raised by the next read / sync
+    bool poisoned = false;             // set after a failed launch or synchronisation
+    rb_stats stats{};
+    int sm_count = 0;
+    size_t smem_optin = 0;
+    void* workspace = nullptr;         // lazily grown scratch owned by the context
+    uint64_t workspace_bytes = 0;
+    void* gemm_state = nullptr;        // tensor-map cache owned by the GEMM translation unit
+    void* attention_state = nullptr;
+};
+
+namespace rb {
+
+size_t dtype_size(uint32_t dtype);
+const char* dtype_name(uint32_t dtype);
+uint64_t elements(const rb_tensor* t);
+bool contiguous(const rb_tensor* t);
+
+// Resolves a tensor to its device address after the checks the reference performs before a launch:
+// known handle, contiguous layout, byte range inside the storage, 16-byte alignment.
+int32_t resolve(rb_ctx* ctx, const rb_tensor* t, const char* what, void** out, bool allow_null = false);
+// Rejects an output that overlaps an input in device memory.
+int32_t no_overlap(const void* out, uint64_t out_bytes, const void* in, uint64_t in_bytes, const char* what);
+bool same_shape(const rb_tensor* a, const rb_tensor* b);
+// Rows and width of a last-axis operation.
+void rows_width(const rb_tensor* t, uint64_t* rows, uint64_t* width);
+
+// Called after every kernel launch: records launch failures on the sticky list, counts the launch
+// and synchronises when the context runs in the reference's synchronous mode.
+int32_t after_launch(rb_ctx* ctx, const char* operation);
+int32_t ensure_workspace(rb_ctx* ctx, uint64_t bytes);
+int32_t check_ctx(rb_ctx* ctx);
+int32_t empty_call(rb_ctx* ctx);
+
+}  // namespace rb
+
+#define RB_TRY(expr) do { int32_t _s = (expr); if (_s != RB_OK) return _s; } while (0)
+#define RB_CUDA(ctx, op, expr) do { cudaError_t _e = (expr); if (_e != cudaSuccess) \
+    return rb::fail(RB_STATUS, "%s failed with CUDA status %d (%s)", op, (int)_e, cudaGetErrorString(_e)); } while (0)

@@ -1,0 +1,453 @@
+"""Host-side mirror of rust-ascend's runtime boundary (rust-ascend-driver/src/tensor/runtime/mod.rs).
+
+`B200Runtime` keeps the associated-function style of `AscendRuntime` (runtime/mod.rs:146-436): every
+operator takes the `ComputeClient` first, `TensorBuffer` arguments after it, and returns new
+`TensorBuffer`s or raises a `B200Error` whose subclass mirrors the `CannError` variant
+(rust-ascend-driver/src/lib.rs:18-40).  All arithmetic happens in libruda_b200.so; nothing here
+computes on the host.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import enum
+from dataclasses import dataclass, field
+
+import numpy as np
+
+from . import _lib
+from ._lib import rb_options, rb_stats, rb_tensor
+
+
+class DType(enum.IntEnum):
+    F32 = 0
+    F16 = 1
+    BF16 = 2
+    I32 = 3
+    I64 = 4
+    U8 = 5
+
+    @property
+    def size(self) -> int:
+        return {0: 4, 1: 2, 2: 2, 3: 4, 4: 8, 5: 1}[int(self)]
+
+    @property
+    def numpy(self):
+        """Host carrier type: BF16 travels as its 16-bit pattern."""
+        return {0: np.float32, 1: np.float16, 2: np.uint16, 3: np.int32, 4: np.int64, 5: np.uint8}[int(self)]
+
+
+class Transpose(enum.IntEnum):
+    No = 0
+    Yes = 1
+
+
+class RotaryLayout(enum.IntEnum):
+    Interleaved = 0
+    SplitHalf = 1
+
+
+class B200Error(RuntimeError):
+    """Base of the CannError mirror; `.status` is the rb_status code."""
+    status = 0
+
+
+class LibraryError(B200Error): status = 1
+class SymbolError(B200Error): status = 2
+class StatusError(B200Error): status = 3
+class InvalidDevice(B200Error): status = 4
+class InvalidTensor(B200Error): status = 5
+class NullHandle(B200Error): status = 6
+class CompletionError(B200Error): status = 7
+class ServerUnhealthy(B200Error): status = 8
+
+
+_ERRORS = {c.status: c for c in (LibraryError, SymbolError, StatusError, InvalidDevice, InvalidTensor, NullHandle,
+                                 CompletionError, ServerUnhealthy)}
+
+
+def _check(code: int) -> None:
+    if code != 0:
+        message = _lib.load().rb_last_error().decode("utf-8", "replace")
+        raise _ERRORS.get(code, B200Error)(message)
+
+
+@dataclass
+class RuntimeOptions:
+    """RuntimeOptions (runtime/mod.rs:93-115) reduced to what a CUDA device needs."""
+    device: int = 0
+    synchronous: bool = False
+
+
+@dataclass(frozen=True)
+class B200Device:
+    """AscendDevice (runtime/mod.rs:117-140)."""
+    ordinal: int = 0
+
+
+def _contiguous_strides(shape) -> tuple:
+    strides, s = [], 1
+    for d in reversed(shape):
+        strides.append(s)
+        s *= d
+    return tuple(reversed(strides))
+
+
+@dataclass
+class TensorBuffer:
+    """TensorBuffer{handle, shape, strides, dtype} (ruda_runtime); strides in elements."""
+    handle: int
+    shape: tuple
+    dtype: DType
+    strides: tuple = field(default=None)
+    offset: int = 0
+
+    def __post_init__(self):
+        self.shape = tuple(int(d) for d in self.shape)
+        if self.strides is None:
+            self.strides = _contiguous_strides(self.shape)
+        self.dtype = DType(self.dtype)
+
+    @property
+    def elements(self) -> int:
+        n = 1
+        for d in self.shape:
+            n *= d
+        return n
+
+    @property
+    def nbytes(self) -> int:
+        return self.elements * self.dtype.size
+
+    def reshape(self, shape) -> "TensorBuffer":
+        shape = tuple(int(d) for d in shape)
+        n = 1
+        for d in shape:
+            n *= d
+        if n != self.elements:
+            raise InvalidTensor("reshape must keep the element count")
+        return TensorBuffer(self.handle, shape, self.dtype, None, self.offset)
+
+    def _c(self) -> rb_tensor:
+        if not 1 <= len(self.shape) <= 8:
+            raise InvalidTensor("tensor rank must be within 1..8")
+        t = rb_tensor()
+        t.handle, t.offset, t.dtype, t.rank = self.handle, self.offset, int(self.dtype), len(self.shape)
+        for i, (d, s) in enumerate(zip(self.shape, self.strides)):
+            t.shape[i], t.strides[i] = d, s
+        return t
+
+
+def _ref(t: TensorBuffer | None):
+    return None if t is None else C.byref(t._c())
+
+
+class ComputeClient:
+    """ComputeClient<AscendRuntime> as the operators see it: storage, transfers, sync and counters
+    (AscendStorage runtime/mod.rs:485-517, AscendServer runtime/mod.rs:767-877)."""
+
+    def __init__(self, ctx, device: B200Device):
+        self._ctx = ctx
+        self.device = device
+        self._lib = _lib.load()
+
+    # -- storage ---------------------------------------------------------------------------------
+    def empty(self, size: int) -> int:
+        h = C.c_uint64()
+        _check(self._lib.rb_alloc(self._ctx, C.c_uint64(size), C.byref(h)))
+        return h.value
+
+    def create_from_slice(self, data) -> int:
+        """Allocate and upload bytes (or any C-contiguous array)."""
+        arr = np.ascontiguousarray(data) if not isinstance(data, (bytes, bytearray, memoryview)) else np.frombuffer(data, dtype=np.uint8)
+        h = self.empty(arr.nbytes)
+        if arr.nbytes:
+            _check(self._lib.rb_write(self._ctx, C.c_uint64(h), C.c_uint64(0), arr.ctypes.data_as(C.c_void_p), C.c_uint64(arr.nbytes)))
+            _check(self._lib.rb_sync(self._ctx))  # the source array may be pageable and short-lived
+        return h
+
+    def free(self, handle: int) -> None:
+        _check(self._lib.rb_free(self._ctx, C.c_uint64(handle)))
+
+    def import_pointer(self, device_pointer: int, size: int) -> int:
+        h = C.c_uint64()
+        _check(self._lib.rb_import(self._ctx, C.c_void_p(device_pointer), C.c_uint64(size), C.byref(h)))
+        return h.value
+
+    def resource(self, handle: int):
+        p, n = C.c_void_p(), C.c_uint64()
+        _check(self._lib.rb_resource(self._ctx, C.c_uint64(handle), C.byref(p), C.byref(n)))
+        return p.value, n.value
+
+    # -- transfers -------------------------------------------------------------------------------
+    def write(self, handle: int, host: np.ndarray, offset: int = 0) -> None:
+        """Asynchronous upload; `host` should be pinned (see `pinned`) and must outlive the copy."""
+        _check(self._lib.rb_write(self._ctx, C.c_uint64(handle), C.c_uint64(offset), host.ctypes.data_as(C.c_void_p), C.c_uint64(host.nbytes)))
+
+    def read_into(self, handle: int, host: np.ndarray, offset: int = 0) -> None:
+        _check(self._lib.rb_read(self._ctx, C.c_uint64(handle), C.c_uint64(offset), host.ctypes.data_as(C.c_void_p), C.c_uint64(host.nbytes)))
+
+    def read_one(self, handle: int) -> bytes:
+        _, size = self.resource(handle)
+        out = np.empty(size, dtype=np.uint8)
+        self.read_into(handle, out)
+        return out.tobytes()
+
+    def read(self, t: TensorBuffer) -> np.ndarray:
+        """Contiguous tensors only, like AscendServer::read (runtime/mod.rs:926-943)."""
+        if tuple(t.strides) != _contiguous_strides(t.shape) and t.elements > 1:
+            raise InvalidTensor("UnsupportedStrides: read requires a contiguous tensor")
+        out = np.empty(t.shape, dtype=t.dtype.numpy)
+        self.read_into(t.handle, out, t.offset)
+        return out
+
+    def upload(self, array, dtype: DType | None = None) -> TensorBuffer:
+        """Upload a host array as a new contiguous tensor.  BF16 takes uint16 bit patterns."""
+        arr = np.ascontiguousarray(array)
+        if dtype is None:
+            dtype = {np.dtype(np.float32): DType.F32, np.dtype(np.float16): DType.F16, np.dtype(np.uint16): DType.BF16,
+                     np.dtype(np.int32): DType.I32, np.dtype(np.int64): DType.I64, np.dtype(np.uint8): DType.U8}[arr.dtype]
+        if arr.dtype != np.dtype(DType(dtype).numpy):
+            raise InvalidTensor(f"host array dtype {arr.dtype} does not carry {DType(dtype).name}")
+        return TensorBuffer(self.create_from_slice(arr), arr.shape if arr.ndim else (1,), dtype)
+
+    def tensor(self, shape, dtype: DType) -> TensorBuffer:
+        shape = tuple(int(d) for d in shape)
+        n = 1
+        for d in shape:
+            n *= d
+        return TensorBuffer(self.empty(n * DType(dtype).size), shape, dtype)
+
+    def pinned(self, shape, dtype) -> np.ndarray:
+        """Page-locked host array for asynchronous rb_write / rb_read."""
+        dt = np.dtype(dtype)
+        n = int(np.prod(shape)) * dt.itemsize
+        p = C.c_void_p()
+        _check(self._lib.rb_host_alloc(self._ctx, C.c_uint64(n), C.byref(p)))
+        buf = (C.c_uint8 * max(n, 1)).from_address(p.value)
+        arr = np.frombuffer(buf, dtype=dt, count=int(np.prod(shape))).reshape(shape)
+        return arr
+
+    def memset(self, t: TensorBuffer, value: int = 0) -> None:
+        _check(self._lib.rb_memset(self._ctx, C.c_uint64(t.handle), C.c_uint64(t.offset), C.c_int32(value), C.c_uint64(t.nbytes)))
+
+    # -- server ----------------------------------------------------------------------------------
+    def sync(self) -> None:
+        _check(self._lib.rb_sync(self._ctx))
+
+    flush = sync
+
+    def take_errors(self) -> list[str]:
+        buf = C.create_string_buffer(4096)
+        n = C.c_uint32()
+        _check(self._lib.rb_take_errors(self._ctx, buf, C.c_size_t(4096), C.byref(n)))
+        return [s for s in buf.value.decode().split("\n") if s]
+
+    def stats(self) -> dict:
+        s = rb_stats()
+        _check(self._lib.rb_get_stats(self._ctx, C.byref(s)))
+        return {k: getattr(s, k) for k, _ in rb_stats._fields_}
+
+    memory_usage = stats
+
+    def start_profile(self) -> None:
+        _check(self._lib.rb_profile_begin(self._ctx))
+
+    def end_profile(self) -> float:
+        ms = C.c_float()
+        _check(self._lib.rb_profile_end(self._ctx, C.byref(ms)))
+        return ms.value
+
+    def properties(self) -> dict:
+        name = C.create_string_buffer(128)
+        sm, mem = C.c_int32(), C.c_uint64()
+        _check(self._lib.rb_device_properties(self._ctx, name, C.c_size_t(128), C.byref(sm), C.byref(mem)))
+        return {"name": name.value.decode(), "sm_count": sm.value, "memory_bytes": mem.value}
+
+
+class B200Runtime:
+    """Mirror of AscendRuntime's associated functions (runtime/mod.rs:146-436)."""
+
+    _ctx = None
+    _device: B200Device | None = None
+
+    # -- lifetime --------------------------------------------------------------------------------
+    @classmethod
+    def initialize_exclusive(cls, options: RuntimeOptions | None = None) -> B200Device:
+        """Once per process; a second call is an error (runtime/mod.rs:424-435)."""
+        options = options or RuntimeOptions()
+        o = rb_options(device=options.device, synchronous=int(options.synchronous))
+        ctx = C.c_void_p()
+        _check(_lib.load().rb_init_exclusive(C.byref(o), C.byref(ctx)))
+        cls._ctx, cls._device = ctx, B200Device(options.device)
+        return cls._device
+
+    @classmethod
+    def client(cls, device: B200Device) -> ComputeClient:
+        if cls._ctx is None or device != cls._device:
+            raise InvalidDevice("call B200Runtime.initialize_exclusive before B200Runtime.client")
+        return ComputeClient(cls._ctx, device)
+
+    @classmethod
+    def shutdown(cls) -> None:
+        if cls._ctx is not None:
+            _check(_lib.load().rb_shutdown(cls._ctx))
+            cls._ctx = cls._device = None
+
+    # -- helpers ---------------------------------------------------------------------------------
+    @staticmethod
+    def _rows(t: TensorBuffer) -> int:
+        n = 1
+        for d in t.shape[:-1]:
+            n *= d
+        return n
+
+    # -- row programs ----------------------------------------------------------------------------
+    @staticmethod
+    def rms_norm(client: ComputeClient, input: TensorBuffer, weight: TensorBuffer, epsilon: float, out_dtype: DType | None = None):
+        """[output, rstd] (runtime/mod.rs:405-408)."""
+        out = client.tensor(input.shape, out_dtype if out_dtype is not None else input.dtype)
+        rstd = client.tensor((B200Runtime._rows(input),), DType.F32)
+        _check(client._lib.rb_rms_norm(client._ctx, _ref(input), _ref(weight), C.c_double(epsilon), _ref(out), _ref(rstd)))
+        return [out, rstd]
+
+    @staticmethod
+    def layer_norm(client: ComputeClient, input: TensorBuffer, weight: TensorBuffer, bias: TensorBuffer | None, epsilon: float):
+        """[output, mean, rstd] (runtime/mod.rs:442-448)."""
+        out = client.tensor(input.shape, input.dtype)
+        rows = B200Runtime._rows(input)
+        mean, rstd = client.tensor((rows,), DType.F32), client.tensor((rows,), DType.F32)
+        _check(client._lib.rb_layer_norm(client._ctx, _ref(input), _ref(weight), _ref(bias), C.c_double(epsilon), _ref(out), _ref(mean), _ref(rstd)))
+        return [out, mean, rstd]
+
+    @staticmethod
+    def softmax(client: ComputeClient, input: TensorBuffer) -> TensorBuffer:
+        """runtime/mod.rs:322-324."""
+        out = client.tensor(input.shape, input.dtype)
+        _check(client._lib.rb_softmax(client._ctx, _ref(input), C.c_int32(0), _ref(out)))
+        return out
+
+    @staticmethod
+    def log_softmax(client: ComputeClient, input: TensorBuffer) -> TensorBuffer:
+        """runtime/mod.rs:327-329."""
+        out = client.tensor(input.shape, input.dtype)
+        _check(client._lib.rb_softmax(client._ctx, _ref(input), C.c_int32(1), _ref(out)))
+        return out
+
+    @staticmethod
+    def _reduce(client, input, op):
+        out = client.tensor(input.shape[:-1] + (1,), DType.F32)
+        _check(client._lib.rb_reduce_last(client._ctx, _ref(input), C.c_int32(op), _ref(out)))
+        return out
+
+    @staticmethod
+    def sum_last(client, input):
+        """runtime/mod.rs:286-289."""
+        return B200Runtime._reduce(client, input, 0)
+
+    @staticmethod
+    def mean_last(client, input):
+        """runtime/mod.rs:292-294."""
+        return B200Runtime._reduce(client, input, 1)
+
+    @staticmethod
+    def max_last(client, input):
+        """runtime/mod.rs:297-299."""
+        return B200Runtime._reduce(client, input, 2)
+
+    # -- element maps ----------------------------------------------------------------------------
+    @staticmethod
+    def silu_mul(client, gate: TensorBuffer, up: TensorBuffer) -> TensorBuffer:
+        """runtime/mod.rs:282-284."""
+        out = client.tensor(gate.shape, gate.dtype)
+        _check(client._lib.rb_silu_mul(client._ctx, _ref(gate), _ref(up), _ref(out)))
+        return out
+
+    @staticmethod
+    def bias_add(client, input: TensorBuffer, bias: TensorBuffer, residual: TensorBuffer | None = None) -> TensorBuffer:
+        """runtime/mod.rs:179-181."""
+        out = client.tensor(input.shape, input.dtype)
+        _check(client._lib.rb_bias_add(client._ctx, _ref(input), _ref(bias), _ref(residual), _ref(out)))
+        return out
+
+    @staticmethod
+    def add(client, a: TensorBuffer, b: TensorBuffer, out: TensorBuffer | None = None) -> TensorBuffer:
+        out = out or client.tensor(a.shape, a.dtype)
+        _check(client._lib.rb_add(client._ctx, _ref(a), _ref(b), _ref(out)))
+        return out
+
+    @staticmethod
+    def rotary(client, input, cos, sin, layout: RotaryLayout) -> TensorBuffer:
+        """runtime/mod.rs:259-262."""
+        out = client.tensor(input.shape, input.dtype)
+        _check(client._lib.rb_rotary(client._ctx, _ref(input), _ref(cos), _ref(sin), C.c_int32(int(layout)), C.c_int32(0), _ref(out)))
+        return out
+
+    @staticmethod
+    def rotary_backward(client, grad, cos, sin, layout: RotaryLayout) -> TensorBuffer:
+        """runtime/mod.rs:265-268."""
+        out = client.tensor(grad.shape, grad.dtype)
+        _check(client._lib.rb_rotary(client._ctx, _ref(grad), _ref(cos), _ref(sin), C.c_int32(int(layout)), C.c_int32(1), _ref(out)))
+        return out
+
+    @staticmethod
+    def rotary_prefix(client, input, cos, sin, width: int, layout: RotaryLayout) -> TensorBuffer:
+        """runtime/mod.rs:215-217."""
+        out = client.tensor(input.shape, input.dtype)
+        _check(client._lib.rb_rotary_prefix(client._ctx, _ref(input), _ref(cos), _ref(sin), C.c_uint32(width), C.c_int32(int(layout)), C.c_int32(0), _ref(out)))
+        return out
+
+    @staticmethod
+    def rotary_prefix_backward(client, grad, cos, sin, width: int, layout: RotaryLayout) -> TensorBuffer:
+        """runtime/mod.rs:219-221."""
+        out = client.tensor(grad.shape, grad.dtype)
+        _check(client._lib.rb_rotary_prefix(client._ctx, _ref(grad), _ref(cos), _ref(sin), C.c_uint32(width), C.c_int32(int(layout)), C.c_int32(1), _ref(out)))
+        return out
+
+    @staticmethod
+    def repeat_kv_heads(client, input: TensorBuffer, query_heads: int) -> TensorBuffer:
+        """runtime/mod.rs:209."""
+        if len(input.shape) != 4:
+            raise InvalidTensor("KV repetition requires [B,Hkv,N,D]")
+        b, _, n, d = input.shape
+        out = client.tensor((b, query_heads, n, d), input.dtype)
+        _check(client._lib.rb_repeat_kv_heads(client._ctx, _ref(input), C.c_uint32(query_heads), _ref(out)))
+        return out
+
+    @staticmethod
+    def causal_mask(client, batch: int, queries: int, keys: int, query_start: int, key_start: int) -> TensorBuffer:
+        """CausalMaskSpec{batch,queries,keys,query_start,key_start} (runtime/mod.rs:206)."""
+        out = client.tensor((batch, queries, keys), DType.F32)
+        _check(client._lib.rb_causal_mask(client._ctx, C.c_uint64(query_start), C.c_uint64(key_start), _ref(out)))
+        return out
+
+    @staticmethod
+    def cast(client, input: TensorBuffer, dtype: DType) -> TensorBuffer:
+        """runtime/mod.rs:271-274."""
+        out = client.tensor(input.shape, dtype)
+        _check(client._lib.rb_cast(client._ctx, _ref(input), _ref(out)))
+        return out
+
+    @staticmethod
+    def cast_into(client, input: TensorBuffer, output: TensorBuffer) -> None:
+        """runtime/mod.rs:277-279."""
+        _check(client._lib.rb_cast(client._ctx, _ref(input), _ref(output)))
+
+    @staticmethod
+    def embedding(client, weight: TensorBuffer, indices: TensorBuffer) -> TensorBuffer:
+        """runtime/mod.rs:231-233."""
+        out = client.tensor(indices.shape + (weight.shape[1],), weight.dtype)
+        _check(client._lib.rb_embedding(client._ctx, _ref(weight), _ref(indices), _ref(out)))
+        return out
+
+
+# ---- host-side BF16 carriers (bit patterns in uint16) ---------------------------------------------
+def f32_to_bf16_bits(x) -> np.ndarray:
+    """Round-to-nearest-even FP32 -> BF16 bit patterns; NaN/Inf keep their upper half."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    special = (u & 0x7F800000) == 0x7F800000
+    r = (u + 0x7FFF + ((u >> 16) & 1)) >> 16
+    return np.where(special, u >> 16, r).astype(np.uint16)
+
+
+def bf16_bits_to_f32(bits) -> np.ndarray:
+    return (np.ascontiguousarray(bits, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)

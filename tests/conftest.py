@@ -18,3 +18,12 @@ def oracle():
     import oracle as orc
     orc.build()
     return orc
+
+
+@pytest.fixture(scope="session")
+def client():
+    """One process-wide runtime context, as the reference allows exactly one (runtime/mod.rs:424-435)."""
+    from rust_ascend_b200 import B200Runtime, RuntimeOptions
+    if B200Runtime._ctx is None:
+        B200Runtime.initialize_exclusive(RuntimeOptions(device=0))
+    return B200Runtime.client(B200Runtime._device)
