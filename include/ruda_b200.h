@@ -176,6 +176,17 @@ RB_API int32_t rb_cast(rb_ctx* ctx, const rb_tensor* x, const rb_tensor* y);
 /* AscendRuntime::embedding, runtime/mod.rs:231-233 -> indexing.rs:33-37: out[i,:] = table[ids[i],:]. */
 RB_API int32_t rb_embedding(rb_ctx* ctx, const rb_tensor* table, const rb_tensor* ids, const rb_tensor* out);
 
+/* ---- BF16 matrix programs (tcgen05 tensor cores, FP32 accumulation) ------------------------------ */
+/* AscendRuntime::gemm / gemm_into, runtime/mod.rs:346-355 -> matrix.rs:47-59 -> GemmSpec deepgemm/plan.rs:49-80;
+ * device program rust-ascend-kernels/src/kernel.rs:11-76.  out = op(A) op(B): contiguous BF16 operands, rank 2
+ * or equal-batch rank 3, M/N/K positive multiples of 16, out BF16 or FP32.  With transpose_b = 1 and B = W[N,K]
+ * this is Linear, Y = X W^T (src/nn.rs:77-79).  The epilogue runs in FP32 before the output rounding:
+ *   RB_EPILOGUE_BIAS   + bias[N] (FP32 or BF16)                      (bias_add, affine_programs.rs:31-36)
+ *   RB_EPILOGUE_SWIGLU out = SiLU(op(A) op(B)) * (op(A) op(b_up))    (swiglu, src/nn/feed_forward.rs:39-41)
+ * bias / b_up are NULL unless their epilogue is selected. */
+RB_API int32_t rb_gemm(rb_ctx* ctx, const rb_tensor* a, const rb_tensor* b, int32_t transpose_a, int32_t transpose_b,
+                       const rb_tensor* bias, const rb_tensor* b_up, int32_t epilogue, const rb_tensor* out);
+
 #ifdef __cplusplus
 }
 #endif

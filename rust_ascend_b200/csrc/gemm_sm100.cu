@@ -1,0 +1,384 @@
+// BF16 GEMM with FP32 accumulation on Blackwell tensor cores (tcgen05 + TMEM), fed by a multi-stage TMA ring.
+//
+// Replaces the reference's generated matrix program (rust-ascend-kernels/src/kernel.rs:11-76, persistent
+// scheduler scheduler.rs:5-79, tile constants layout.rs:4-12) and its runtime entry points
+// (rust-ascend-driver/src/tensor/runtime/matrix.rs:47-59).  The contract is the reference's
+// (deepgemm/plan.rs:49-80): contiguous row-major BF16 operands, rank 2 or equal-batch rank 3, M/N/K positive
+// multiples of 16, all four transpose combinations, BF16 or FP32 output.
+//
+// Design: one persistent CTA per SM walks output tiles of 128 x BN in a grouped raster.  Warp 0 is the TMA
+// producer, warp 1 issues tcgen05.mma (UMMA 128 x BN x 16, operands K-major in 128-byte-swizzled shared
+// memory), warps 2..5 are the epilogue.  Two TMEM accumulators let the epilogue of tile i overlap the
+// main loop of tile i+1.  The epilogue is fused: identity, + bias[n], or SiLU(gate)*up where the gate and
+// up projections are accumulated side by side in one UMMA of N = BN from two weight matrices.
+// Operands that are not K-major (A transposed, B not transposed) are first rewritten K-major by a tiled
+// transpose kernel; the hot Linear layout (X [M,K], W [N,K]) needs no rewrite.
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace {
+
+using namespace sm100;
+using bf = __nv_bfloat16;
+
+constexpr int BM = 128;      // UMMA M (TMEM lanes)
+constexpr int BK = 64;       // K per stage: 64 BF16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int GROUP_M = 8;   // raster group height in tiles
+constexpr int THREADS = 192;
+
+struct GemmParams {
+    uint32_t m, n, k, batches;      // n = output columns
+    uint32_t tiles_m, tiles_n;
+    uint32_t epilogue;              // rb_epilogue
+    uint32_t out_f32;               // 1: FP32 output, 0: BF16
+    uint32_t bias_bf16;             // bias storage: 1 BF16, 0 FP32
+    void* out;
+    const void* bias;
+    uint32_t* status;               // device status word: non-zero when a bounded wait expired
+};
+
+template <int BN> struct Config {
+    static constexpr int STAGES = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int TMEM_COLS = 2 * BN;
+};
+
+__device__ __forceinline__ void tile_coords(uint32_t t, const GemmParams& p, uint32_t& batch, uint32_t& tm, uint32_t& tn) {
+    uint32_t per_batch = p.tiles_m * p.tiles_n;
+    batch = t / per_batch; t -= batch * per_batch;
+    uint32_t group_size = GROUP_M * p.tiles_n;
+    uint32_t group = t / group_size, first_m = group * GROUP_M;
+    uint32_t rows = p.tiles_m - first_m < GROUP_M ? p.tiles_m - first_m : GROUP_M;
+    uint32_t r = t - group * group_size;
+    tm = first_m + r % rows; tn = r / rows;
+}
+
+__device__ __forceinline__ float bias_at(const GemmParams& p, uint32_t col) {
+    return p.bias_bf16 ? __bfloat162float(static_cast<const bf*>(p.bias)[col]) : static_cast<const float*>(p.bias)[col];
+}
+
+template <int BN>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const __grid_constant__ CUtensorMap map_b2, const GemmParams p) {
+    using C = Config<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+    uint64_t* empty_bar = full_bar + C::STAGES;
+    uint64_t* tmem_full = empty_bar + C::STAGES;
+    uint64_t* tmem_empty = tmem_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    volatile uint32_t* abort_word = tmem_slot + 1;
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool swiglu = p.epilogue == RB_EPILOGUE_SWIGLU;
+    const uint32_t bn_out = swiglu ? BN / 2 : BN;
+    const uint32_t num_kb = (p.k + BK - 1) / BK;
+    const uint32_t num_tiles = p.tiles_m * p.tiles_n * p.batches;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], 128); }
+        *abort_word = 0;
+        fence_barrier_init();
+        prefetch_tmap(&map_a); prefetch_tmap(&map_b); if (swiglu) prefetch_tmap(&map_b2);
+    }
+    if (warp == 1) { tmem_alloc(tmem_slot, C::TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (elect_one()) {
+            uint32_t stage = 0, phase = 0, armed = 0, armed_parity = 0;
+            bool ok = true;
+            for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+                uint32_t batch, tm, tn; tile_coords(t, p, batch, tm, tn);
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_word))) break;
+                    uint8_t* sa = smem + stage * C::STAGE_BYTES; uint8_t* sb = sa + C::A_BYTES;
+                    mbar_expect_tx(&full_bar[stage], C::STAGE_BYTES);
+                    armed |= 1u << stage; armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
+                    tma_load_3d(sa, &map_a, &full_bar[stage], (int32_t)(kb * BK), (int32_t)(tm * BM), (int32_t)batch);
+                    if (swiglu) {
+                        tma_load_3d(sb, &map_b, &full_bar[stage], (int32_t)(kb * BK), (int32_t)(tn * (BN / 2)), (int32_t)batch);
+                        tma_load_3d(sb + C::B_BYTES / 2, &map_b2, &full_bar[stage], (int32_t)(kb * BK), (int32_t)(tn * (BN / 2)), (int32_t)batch);
+                    } else {
+                        tma_load_3d(sb, &map_b, &full_bar[stage], (int32_t)(kb * BK), (int32_t)(tn * BN), (int32_t)batch);
+                    }
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (!ok) {
+                // A wait expired somewhere: let the copies this thread issued land before the CTA retires.
+                for (int s = 0; s < C::STAGES; ++s)
+                    if (armed & (1u << s))
+                        for (uint32_t i = 0; i < (1u << 20) && !mbar_try_wait(&full_bar[s], (armed_parity >> s) & 1u); ++i) {}
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (elect_one()) {
+            const uint32_t idesc = make_idesc_bf16(BM, BN);
+            uint32_t stage = 0, phase = 0, iter = 0;
+            bool ok = true;
+            for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++iter) {
+                const uint32_t acc = iter & 1, acc_phase = (iter >> 1) & 1;
+                if (!(ok = mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_word))) break;
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + acc * BN;
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    if (!(ok = mbar_wait(&full_bar[stage], phase, abort_word))) break;
+                    tc_fence_after();
+                    uint8_t* sa = smem + stage * C::STAGE_BYTES;
+                    const uint64_t da = make_kmajor_sw128_desc(smem_u32(sa)), db = make_kmajor_sw128_desc(smem_u32(sa + C::A_BYTES));
+#pragma unroll
+                    for (uint32_t k = 0; k < BK / UMMA_K; ++k)
+                        umma_bf16_ss(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);  // +32 bytes per K step
+                    umma_commit(&empty_bar[stage]);
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (ok) umma_commit(&tmem_full[acc]);
+            }
+        }
+    } else {
+        // ---------------- epilogue: 4 warps, one TMEM lane (= output row) per thread ----------------
+        const uint32_t quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 are the ones this warp may read
+        uint32_t iter = 0;
+        bool ok = true;
+        for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++iter) {
+            const uint32_t acc = iter & 1, acc_phase = (iter >> 1) & 1;
+            uint32_t batch, tm, tn; tile_coords(t, p, batch, tm, tn);
+            if (!(ok = mbar_wait(&tmem_full[acc], acc_phase, abort_word))) break;
+            tc_fence_after();
+            const uint32_t row = tm * BM + quarter * 32 + lane;
+            const uint32_t col0 = tn * bn_out;
+            const uint32_t taddr = tmem_base + acc * BN + ((quarter * 32) << 16);
+            const size_t out_off = ((size_t)batch * p.m + row) * p.n;
+            for (uint32_t c = 0; c < bn_out; c += 32) {
+                if (col0 + c >= p.n) break;  // warp-uniform
+                uint32_t r[32];
+                tmem_ld_32x32(taddr + c, r);
+                float v[32];
+                if (swiglu) {
+                    uint32_t u[32];
+                    tmem_ld_32x32(taddr + BN / 2 + c, u);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        float g = __uint_as_float(r[j]);
+                        float s = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-g)));
+                        v[j] = __fmul_rn(__fmul_rn(g, s), __uint_as_float(u[j]));
+                    }
+                } else {
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                    if (p.epilogue == RB_EPILOGUE_BIAS) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) if (col0 + c + j < p.n) v[j] = __fadd_rn(v[j], bias_at(p, col0 + c + j));
+                    }
+                }
+                if (row < p.m) {
+                    if (p.out_f32) {
+                        float* o = static_cast<float*>(p.out) + out_off + col0 + c;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4)
+                            if (col0 + c + j < p.n) *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    } else {
+                        bf* o = static_cast<bf*>(p.out) + out_off + col0 + c;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            if (col0 + c + j < p.n) {
+                                __nv_bfloat162 q0 = __floats2bfloat162_rn(v[j], v[j + 1]), q1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+                                __nv_bfloat162 q2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), q3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+                                uint4 w;
+                                w.x = *reinterpret_cast<uint32_t*>(&q0); w.y = *reinterpret_cast<uint32_t*>(&q1);
+                                w.z = *reinterpret_cast<uint32_t*>(&q2); w.w = *reinterpret_cast<uint32_t*>(&q3);
+                                *reinterpret_cast<uint4*>(o + j) = w;
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(&tmem_empty[acc]);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_word) atomicExch(p.status, 1u);
+    if (warp == 1) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem_base, C::TMEM_COLS); }
+}
+
+// Batched BF16 transpose [batches, R, C] -> [batches, C, R] through a padded shared-memory tile.
+__global__ void __launch_bounds__(256) transpose_bf16_kernel(const uint16_t* in, uint16_t* out, uint32_t rows, uint32_t cols) {
+    __shared__ uint16_t tile[64][66];
+    const size_t base = (size_t)blockIdx.z * rows * cols;
+    const uint32_t r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+    for (uint32_t i = threadIdx.x; i < 64 * 64; i += 256) {
+        uint32_t r = i / 64, c = i % 64;
+        if (r0 + r < rows && c0 + c < cols) tile[r][c] = in[base + (size_t)(r0 + r) * cols + c0 + c];
+    }
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < 64 * 64; i += 256) {
+        uint32_t c = i / 64, r = i % 64;
+        if (r0 + r < rows && c0 + c < cols) out[base + (size_t)(c0 + c) * rows + r0 + r] = tile[r][c];
+    }
+}
+
+struct GemmState { uint32_t* status = nullptr; bool attrs_set = false; };
+
+template <int BN>
+int32_t launch(rb_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2, GemmParams& p) {
+    using C = Config<BN>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+        if (e != cudaSuccess) return rb::fail(RB_STATUS, "cudaFuncSetAttribute(GEMM) failed with CUDA status %d (%s)", (int)e, cudaGetErrorString(e));
+        configured = true;
+    }
+    uint32_t tiles = p.tiles_m * p.tiles_n * p.batches;
+    uint32_t grid = tiles < (uint32_t)ctx->sm_count ? tiles : (uint32_t)ctx->sm_count;
+    gemm_bf16_kernel<BN><<<grid, THREADS, C::SMEM_BYTES, ctx->stream>>>(ma, mb, mb2, p);
+    return rb::after_launch(ctx, "gemm");
+}
+
+bool make_operand_map(CUtensorMap* map, const void* base, uint64_t batches, uint64_t rows, uint64_t k, uint32_t box_rows) {
+    uint64_t dims[3] = {k, rows, batches};
+    uint64_t strides[2] = {k * 2, rows * k * 2};
+    uint32_t box[3] = {BK, box_rows, 1};
+    return encode_bf16_map(map, base, 3, dims, strides, box, true);
+}
+
+}  // namespace
+
+using namespace rb;
+
+namespace rb {
+
+// Device status word shared by the tensor-core kernels; non-zero after a bounded wait expired.
+int32_t kernel_status_word(rb_ctx* ctx, uint32_t** out) {
+    GemmState* st = static_cast<GemmState*>(ctx->gemm_state);
+    if (!st) { st = new GemmState(); ctx->gemm_state = st; }
+    if (!st->status) {
+        cudaError_t e = cudaMalloc(&st->status, 256);
+        if (e == cudaSuccess) e = cudaMemset(st->status, 0, 256);
+        if (e != cudaSuccess) return fail(RB_STATUS, "status word allocation failed with CUDA status %d", (int)e);
+    }
+    *out = st->status;
+    return RB_OK;
+}
+
+// Reads the status word after the stream has drained; a non-zero value becomes a sticky error.
+int32_t poll_kernel_status(rb_ctx* ctx) {
+    GemmState* st = static_cast<GemmState*>(ctx->gemm_state);
+    if (!st || !st->status) return RB_OK;
+    uint32_t h = 0;
+    if (cudaMemcpy(&h, st->status, sizeof(h), cudaMemcpyDeviceToHost) != cudaSuccess) return RB_OK;
+    if (h) {
+        cudaMemset(st->status, 0, sizeof(h));
+        std::lock_guard<std::mutex> g(ctx->lock);
+        ctx->sticky.emplace_back("a tensor-core kernel gave up on a bounded barrier wait (status word = 1); its output is invalid");
+    }
+    return RB_OK;
+}
+
+// C[batches, m, n] = A_k[batches, m, k] * B_k[batches, n, k]^T with both operands already K-major.
+int32_t gemm_kmajor(rb_ctx* ctx, const void* a, const void* b, const void* b_up, uint32_t batches, uint32_t m, uint32_t n, uint32_t k,
+                    int epilogue, const void* bias, bool bias_bf16, void* out, bool out_f32) {
+    GemmParams p{};
+    p.m = m; p.n = n; p.k = k; p.batches = batches; p.epilogue = (uint32_t)epilogue; p.out_f32 = out_f32; p.bias_bf16 = bias_bf16;
+    p.out = out; p.bias = bias;
+    RB_TRY(kernel_status_word(ctx, &p.status));
+    const bool swiglu = epilogue == RB_EPILOGUE_SWIGLU;
+    // Tile width: the widest accumulator that does not leave most of the tile empty.
+    int bn = n > 128 || swiglu ? 256 : (n > 64 ? 128 : 64);
+    if (swiglu && n <= 64) bn = 128;
+    const uint32_t bn_out = swiglu ? bn / 2 : bn;
+    p.tiles_m = (m + BM - 1) / BM; p.tiles_n = (n + bn_out - 1) / bn_out;
+    CUtensorMap ma, mb, mb2;
+    if (!make_operand_map(&ma, a, batches, m, k, BM) || !make_operand_map(&mb, b, batches, n, k, bn_out) ||
+        !make_operand_map(&mb2, swiglu ? b_up : b, batches, n, k, bn_out))
+        return fail(RB_STATUS, "cuTensorMapEncodeTiled failed for a GEMM operand (m=%u n=%u k=%u)", m, n, k);
+    if (bn == 256) return launch<256>(ctx, ma, mb, mb2, p);
+    if (bn == 128) return launch<128>(ctx, ma, mb, mb2, p);
+    return launch<64>(ctx, ma, mb, mb2, p);
+}
+
+}  // namespace rb
+
+namespace {
+
+int32_t matrix_dims(const rb_tensor* t, const char* what, uint64_t* batches, uint64_t* rows, uint64_t* cols) {
+    if (t->rank != 2 && t->rank != 3) return fail(RB_INVALID_TENSOR, "%s: GEMM operands are rank 2 or equal-batch rank 3", what);
+    *batches = t->rank == 3 ? t->shape[0] : 1; *rows = t->shape[t->rank - 2]; *cols = t->shape[t->rank - 1];
+    return RB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t rb_gemm(rb_ctx* ctx, const rb_tensor* a, const rb_tensor* b, int32_t transpose_a, int32_t transpose_b,
+                const rb_tensor* bias, const rb_tensor* b_up, int32_t epilogue, const rb_tensor* out) {
+    RB_TRY(check_ctx(ctx));
+    void *pa, *pb, *pbias = nullptr, *pup = nullptr, *po;
+    RB_TRY(resolve(ctx, a, "GEMM A", &pa)); RB_TRY(resolve(ctx, b, "GEMM B", &pb)); RB_TRY(resolve(ctx, out, "GEMM output", &po));
+    if (a->dtype != RB_BF16 || b->dtype != RB_BF16) return fail(RB_INVALID_TENSOR, "native GEMM requires BF16 operands");
+    if (out->dtype != RB_BF16 && out->dtype != RB_F32) return fail(RB_INVALID_TENSOR, "GEMM output must be BF16 or FP32");
+    uint64_t ba, ra, ca, bb, rbw, cb, bo, ro, co;
+    RB_TRY(matrix_dims(a, "GEMM A", &ba, &ra, &ca)); RB_TRY(matrix_dims(b, "GEMM B", &bb, &rbw, &cb)); RB_TRY(matrix_dims(out, "GEMM output", &bo, &ro, &co));
+    const uint64_t m = transpose_a ? ca : ra, k = transpose_a ? ra : ca;
+    const uint64_t n = transpose_b ? rbw : cb, kb = transpose_b ? cb : rbw;
+    if (a->rank != b->rank || a->rank != out->rank || ba != bb || ba != bo || k != kb || ro != m || co != n)
+        return fail(RB_INVALID_TENSOR, "GEMM shapes do not agree: A gives M=%llu K=%llu, B gives N=%llu K=%llu, output is %llux%llu",
+                    (unsigned long long)m, (unsigned long long)k, (unsigned long long)n, (unsigned long long)kb, (unsigned long long)ro, (unsigned long long)co);
+    if (m == 0 || n == 0 || k == 0 || m % 16 || n % 16 || k % 16 || m > 0x7fffffffull || n > 0x7fffffffull || k > 0x7fffffffull)
+        return fail(RB_INVALID_TENSOR, "GEMM M/N/K must be positive multiples of 16 within INT32_MAX");
+    if (ba == 0 || ba > 4096) return fail(RB_INVALID_TENSOR, "GEMM batch count must be within 1..4096");
+    if (epilogue != RB_EPILOGUE_NONE && epilogue != RB_EPILOGUE_BIAS && epilogue != RB_EPILOGUE_SWIGLU) return fail(RB_INVALID_TENSOR, "unknown GEMM epilogue");
+    if (epilogue == RB_EPILOGUE_BIAS) {
+        RB_TRY(resolve(ctx, bias, "GEMM bias", &pbias));
+        if (elements(bias) != n || (bias->dtype != RB_F32 && bias->dtype != RB_BF16)) return fail(RB_INVALID_TENSOR, "GEMM bias must hold N FP32 or BF16 values");
+    }
+    if (epilogue == RB_EPILOGUE_SWIGLU) {
+        RB_TRY(resolve(ctx, b_up, "GEMM up weight", &pup));
+        if (!same_shape(b, b_up) || b_up->dtype != RB_BF16) return fail(RB_INVALID_TENSOR, "SwiGLU epilogue needs an up weight with the gate weight's shape and dtype");
+    }
+    const uint64_t a_bytes = ba * m * k * 2, b_bytes = ba * n * k * 2, o_bytes = ba * m * n * dtype_size(out->dtype);
+    RB_TRY(no_overlap(po, o_bytes, pa, a_bytes, "GEMM")); RB_TRY(no_overlap(po, o_bytes, pb, b_bytes, "GEMM"));
+    if (pup) RB_TRY(no_overlap(po, o_bytes, pup, b_bytes, "GEMM"));
+    // Operands that are not K-major are rewritten K-major in the context workspace.
+    const bool fix_a = transpose_a != 0, fix_b = transpose_b == 0;
+    uint64_t need = (fix_a ? a_bytes : 0) + (fix_b ? b_bytes * (pup ? 2 : 1) : 0);
+    if (need) RB_TRY(ensure_workspace(ctx, need + 1024));
+    uint8_t* ws = static_cast<uint8_t*>(ctx->workspace) + 256;  // the first 256 bytes hold small flags
+    const void *ka = pa, *kbp = pb, *kup = pup;
+    if (fix_a) {  // stored [K, M] -> [M, K]
+        dim3 grid((unsigned)((m + 63) / 64), (unsigned)((k + 63) / 64), (unsigned)ba);
+        transpose_bf16_kernel<<<grid, 256, 0, ctx->stream>>>((const uint16_t*)pa, (uint16_t*)ws, (uint32_t)k, (uint32_t)m);
+        RB_TRY(after_launch(ctx, "gemm operand transpose")); ka = ws; ws += a_bytes;
+    }
+    if (fix_b) {  // stored [K, N] -> [N, K]
+        dim3 grid((unsigned)((n + 63) / 64), (unsigned)((k + 63) / 64), (unsigned)ba);
+        transpose_bf16_kernel<<<grid, 256, 0, ctx->stream>>>((const uint16_t*)pb, (uint16_t*)ws, (uint32_t)k, (uint32_t)n);
+        RB_TRY(after_launch(ctx, "gemm operand transpose")); kbp = ws; ws += b_bytes;
+        if (pup) {
+            transpose_bf16_kernel<<<grid, 256, 0, ctx->stream>>>((const uint16_t*)pup, (uint16_t*)ws, (uint32_t)k, (uint32_t)n);
+            RB_TRY(after_launch(ctx, "gemm operand transpose")); kup = ws;
+        }
+    }
+    return gemm_kmajor(ctx, ka, kbp, kup, (uint32_t)ba, (uint32_t)m, (uint32_t)n, (uint32_t)k, epilogue, pbias,
+                       bias && bias->dtype == RB_BF16, po, out->dtype == RB_F32);
+}
+
+}  // extern "C"

@@ -284,6 +284,8 @@ int32_t rb_sync(rb_ctx* ctx) {
         std::lock_guard<std::mutex> g(ctx->lock);
         char msg[200]; snprintf(msg, sizeof(msg), "stream synchronisation failed with CUDA status %d (%s)", (int)e, cudaGetErrorString(e));
         ctx->sticky.emplace_back(msg);
+    } else {
+        poll_kernel_status(ctx);
     }
     return raise_sticky(ctx);
 }

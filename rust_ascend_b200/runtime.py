@@ -440,6 +440,56 @@ class B200Runtime:
         return out
 
 
+    # -- BF16 matrix programs --------------------------------------------------------------------
+    @staticmethod
+    def _gemm_shape(a: TensorBuffer, b: TensorBuffer, ta: Transpose, tb: Transpose):
+        if len(a.shape) not in (2, 3) or len(a.shape) != len(b.shape):
+            raise InvalidTensor("GEMM operands are rank 2 or equal-batch rank 3")
+        m = a.shape[-1] if ta else a.shape[-2]
+        n = b.shape[-2] if tb else b.shape[-1]
+        return tuple(a.shape[:-2]) + (m, n)
+
+    @staticmethod
+    def gemm_into(client, a: TensorBuffer, b: TensorBuffer, ta: Transpose, tb: Transpose, out: TensorBuffer,
+                  bias: TensorBuffer | None = None, b_up: TensorBuffer | None = None) -> None:
+        """runtime/mod.rs:352-355; `bias` / `b_up` select the fused epilogues of the B200 kernel."""
+        epilogue = 2 if b_up is not None else (1 if bias is not None else 0)
+        _check(client._lib.rb_gemm(client._ctx, _ref(a), _ref(b), C.c_int32(int(ta)), C.c_int32(int(tb)), _ref(bias), _ref(b_up),
+                                   C.c_int32(epilogue), _ref(out)))
+
+    @staticmethod
+    def gemm(client, a: TensorBuffer, b: TensorBuffer, ta: Transpose, tb: Transpose, dtype: DType,
+             bias: TensorBuffer | None = None, b_up: TensorBuffer | None = None) -> TensorBuffer:
+        """runtime/mod.rs:346-349: BF16 operands, BF16 or FP32 result."""
+        out = client.tensor(B200Runtime._gemm_shape(a, b, ta, tb), dtype)
+        B200Runtime.gemm_into(client, a, b, ta, tb, out, bias, b_up)
+        return out
+
+    @staticmethod
+    def gemm_bf16_fp32(client, a: TensorBuffer, b: TensorBuffer, ta: Transpose, tb: Transpose):
+        """[FP32 output, saved BF16 A, saved BF16 B] from FP32 operands: Cast, Cast, GEMM
+        (runtime/mod.rs:422-425 -> matrix.rs:84-93)."""
+        if a.dtype != DType.F32 or b.dtype != DType.F32:
+            raise InvalidTensor("gemm_bf16_fp32 requires FP32 inputs")
+        a16, b16 = B200Runtime.cast(client, a, DType.BF16), B200Runtime.cast(client, b, DType.BF16)
+        return [B200Runtime.gemm(client, a16, b16, ta, tb, DType.F32), a16, b16]
+
+    @staticmethod
+    def linear_bf16_fp32(client, input: TensorBuffer, weight: TensorBuffer):
+        """Y = bf16(X) bf16(W)^T with FP32 X [M,K], W [N,K]; returns [Y, X_bf16, W_bf16]
+        (runtime/mod.rs:367-370 -> matrix.rs:129-133)."""
+        if len(input.shape) != 2 or len(weight.shape) != 2:
+            raise InvalidTensor("linear requires rank-2 X[M,K] and W[N,K]")
+        return B200Runtime.gemm_bf16_fp32(client, input, weight, Transpose.No, Transpose.Yes)
+
+    @staticmethod
+    def linear_frozen_bf16_fp32(client, input: TensorBuffer, weight: TensorBuffer) -> TensorBuffer:
+        """FP32 X times a fixed BF16 W^T, FP32 result, no weight copy (runtime/mod.rs:383-385 -> matrix.rs:147-159)."""
+        if input.dtype != DType.F32 or weight.dtype != DType.BF16:
+            raise InvalidTensor("frozen linear requires FP32 input and BF16 weight storage")
+        return B200Runtime.gemm(client, B200Runtime.cast(client, input, DType.BF16), weight, Transpose.No, Transpose.Yes, DType.F32)
+
+
 # ---- host-side BF16 carriers (bit patterns in uint16) ---------------------------------------------
 def f32_to_bf16_bits(x) -> np.ndarray:
     """Round-to-nearest-even FP32 -> BF16 bit patterns; NaN/Inf keep their upper half."""

@@ -1,0 +1,170 @@
+"""GPU parity (through the C ABI): tcgen05 BF16 GEMM against the CPU oracle and the reference's GEMM vectors.
+Tolerance (BF16 path): max abs error <= 2e-2 and mean relative error <= 1e-2 against the FP32-accumulated
+oracle; the reference's own small vectors are held to their stated tolerances."""
+import numpy as np
+import pytest
+
+import vectors as V
+from rust_ascend_b200 import B200Runtime as RT
+from rust_ascend_b200 import DType, InvalidTensor, Transpose
+from rust_ascend_b200.runtime import bf16_bits_to_f32, f32_to_bf16_bits
+
+pytestmark = pytest.mark.gpu
+T = {False: Transpose.No, True: Transpose.Yes}
+
+
+def up16(client, x):
+    return client.upload(f32_to_bf16_bits(x))
+
+
+def read(client, t):
+    a = client.read(t)
+    return bf16_bits_to_f32(a) if t.dtype == DType.BF16 else a
+
+
+def bf16_tolerance(got, want):
+    got = got.astype(np.float64); want = want.astype(np.float64)
+    assert np.all(np.isfinite(got))
+    err = np.abs(got - want)
+    # 2e-2 absolute covers half a BF16 ulp up to |y| < 8; beyond that the bound is half an ulp, 2^-8 relative.
+    assert err.max() <= max(2e-2, 2.0 ** -8 * np.abs(want).max()), f"max abs {err.max()}"
+    assert (err.sum() / max(np.abs(want).sum(), 1e-30)) <= 1e-2
+
+
+@pytest.mark.parametrize("ta", [False, True])
+@pytest.mark.parametrize("tb", [False, True])
+@pytest.mark.parametrize("out_bf16", [False, True])
+@pytest.mark.parametrize("batches,m,n,k", [(1, 80, 96, 144), (3, 16, 32, 16)])
+def test_reference_kernel_vectors(client, oracle, ta, tb, out_bf16, batches, m, n, k):
+    # rust-ascend-kernels/src/tests.rs:89-132, tolerance 1e-4.
+    a, b, d = V.gemm_kernel_case(batches, m, n, k, ta, tb)
+    if batches == 1:
+        a, b, d = a[0], b[0], d[0]
+    out = RT.gemm(client, up16(client, a), up16(client, b), T[ta], T[tb], DType.BF16 if out_bf16 else DType.F32)
+    got = read(client, out)
+    want = oracle.gemm_bf16(a, b, ta, tb, out_bf16)
+    assert np.abs(got.astype(np.float64) - want).max() < 1e-4
+    assert np.abs(got.astype(np.float64) - (V.bf16_f64(d.astype(np.float32)) if out_bf16 else d)).max() < 1e-4
+
+
+@pytest.mark.parametrize("batches", [1, 2])
+@pytest.mark.parametrize("ta", [False, True])
+@pytest.mark.parametrize("tb", [False, True])
+@pytest.mark.parametrize("dtype", [DType.BF16, DType.F32])
+def test_reference_runtime_vectors_and_reuse(client, batches, ta, tb, dtype):
+    # examples/matrix_runtime.rs:50-77: gemm, then gemm_into the same output.
+    a, b, d = V.gemm_runtime_case(batches, ta, tb)
+    if batches == 1:
+        a, b, d = a[0], b[0], d[0]
+    da, db = up16(client, a), up16(client, b)
+    out = RT.gemm(client, da, db, T[ta], T[tb], dtype)
+    assert out.shape == d.shape
+    rel = 4e-3 if dtype == DType.BF16 else 5e-4
+    assert np.all(np.abs(read(client, out) - d) <= 5e-4 + rel * np.abs(d))
+    client.memset(out, 0xFF)
+    RT.gemm_into(client, da, db, T[ta], T[tb], out)
+    assert np.all(np.abs(read(client, out) - d) <= 5e-4 + rel * np.abs(d))
+
+
+@pytest.mark.parametrize("m,n,k", [(16, 32, 16), (32, 48, 32)])
+def test_linear_bf16_fp32_contract(client, m, n, k):
+    # examples/linear_tensor.rs:24-50: FP32 in, FP32 out, BF16 snapshots returned.
+    x, w, y = V.linear_case(m, n, k)
+    out, x16, w16 = RT.linear_bf16_fp32(client, client.upload(x), client.upload(w))
+    assert out.dtype == DType.F32 and out.shape == (m, n) and x16.dtype == DType.BF16 and w16.shape == (n, k)
+    assert np.all(np.abs(client.read(out) - y) <= 5e-4 + 5e-4 * np.abs(y))
+    np.testing.assert_array_equal(client.read(x16), f32_to_bf16_bits(x))
+    frozen = RT.linear_frozen_bf16_fp32(client, client.upload(x), up16(client, w))
+    np.testing.assert_array_equal(client.read(frozen), client.read(out))
+
+
+@pytest.mark.parametrize("m,n,k,seed", [(128, 256, 64, 0), (256, 512, 512, 1), (384, 1024, 1040, 2), (1024, 4096, 4096, 3),
+                                        (144, 272, 208, 4), (2048, 176, 96, 5), (16, 16, 16, 6), (4096, 64, 4096, 7)])
+def test_linear_random_against_oracle(client, oracle, m, n, k, seed):
+    rng = np.random.default_rng(seed)
+    x = bf16_bits_to_f32(f32_to_bf16_bits(rng.standard_normal((m, k), dtype=np.float32)))
+    w = bf16_bits_to_f32(f32_to_bf16_bits(rng.standard_normal((n, k), dtype=np.float32) * 0.02))
+    got32 = read(client, RT.gemm(client, up16(client, x), up16(client, w), Transpose.No, Transpose.Yes, DType.F32))
+    want = oracle.linear(x, w)
+    assert np.abs(got32 - want).max() <= 1e-4 * max(1.0, np.abs(want).max())  # FP32 accumulate, order only
+    got16 = read(client, RT.gemm(client, up16(client, x), up16(client, w), Transpose.No, Transpose.Yes, DType.BF16))
+    bf16_tolerance(got16, want)
+
+
+def test_batched_random(client, oracle):
+    rng = np.random.default_rng(21)
+    a = bf16_bits_to_f32(f32_to_bf16_bits(rng.standard_normal((5, 272, 192), dtype=np.float32)))
+    b = bf16_bits_to_f32(f32_to_bf16_bits(rng.standard_normal((5, 192, 144), dtype=np.float32)))
+    got = read(client, RT.gemm(client, up16(client, a), up16(client, b), Transpose.No, Transpose.No, DType.F32))
+    assert np.abs(got - oracle.gemm_bf16(a, b, False, False, False)).max() <= 2e-4
+
+
+@pytest.mark.parametrize("bias_dtype", [DType.F32, DType.BF16])
+def test_bias_epilogue(client, oracle, bias_dtype):
+    rng = np.random.default_rng(8)
+    m, n, k = 272, 528, 320
+    x = bf16_bits_to_f32(f32_to_bf16_bits(rng.standard_normal((m, k), dtype=np.float32)))
+    w = bf16_bits_to_f32(f32_to_bf16_bits(rng.standard_normal((n, k), dtype=np.float32) * 0.02))
+    bias = (rng.standard_normal(n) * 0.02).astype(np.float32)
+    if bias_dtype == DType.BF16:
+        bias = bf16_bits_to_f32(f32_to_bf16_bits(bias)); tb = up16(client, bias)
+    else:
+        tb = client.upload(bias)
+    got = read(client, RT.gemm(client, up16(client, x), up16(client, w), Transpose.No, Transpose.Yes, DType.F32, bias=tb))
+    assert np.abs(got - oracle.linear(x, w, bias=bias)).max() <= 1e-4
+    got16 = read(client, RT.gemm(client, up16(client, x), up16(client, w), Transpose.No, Transpose.Yes, DType.BF16, bias=tb))
+    bf16_tolerance(got16, oracle.linear(x, w, bias=bias))
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (272, 528, 320), (512, 11008 // 8, 1024), (16, 16, 16)])
+def test_swiglu_epilogue(client, oracle, m, n, k):
+    rng = np.random.default_rng(m + n)
+    x = bf16_bits_to_f32(f32_to_bf16_bits(rng.standard_normal((m, k), dtype=np.float32)))
+    wg = bf16_bits_to_f32(f32_to_bf16_bits(rng.standard_normal((n, k), dtype=np.float32) * 0.05))
+    wu = bf16_bits_to_f32(f32_to_bf16_bits(rng.standard_normal((n, k), dtype=np.float32) * 0.05))
+    got = read(client, RT.gemm(client, up16(client, x), up16(client, wg), Transpose.No, Transpose.Yes, DType.F32, b_up=up16(client, wu)))
+    want = oracle.linear(x, wg, w_up=wu)
+    assert np.abs(got - want).max() <= 2e-4 * max(1.0, np.abs(want).max())
+    got16 = read(client, RT.gemm(client, up16(client, x), up16(client, wg), Transpose.No, Transpose.Yes, DType.BF16, b_up=up16(client, wu)))
+    bf16_tolerance(got16, want)
+
+
+def test_swiglu_zero_gate_gives_zero(client):
+    # examples/swiglu_tensor.rs:22-40.
+    width = 16
+    x = (((np.arange(width * width) % 7).astype(np.float32) - 3.0) * 0.125).reshape(width, width)
+    up = np.eye(width, dtype=np.float32) * 0.5
+    got = read(client, RT.gemm(client, up16(client, x), up16(client, np.zeros((width, width), np.float32)), Transpose.No, Transpose.Yes,
+                               DType.F32, b_up=up16(client, up)))
+    np.testing.assert_array_equal(got, np.zeros((width, width), np.float32))
+
+
+def test_full_size_linearity_property(client):
+    # Config-2 size: (X1+X2) W^T == X1 W^T + X2 W^T when the sums are exact in BF16 (small integers).
+    rng = np.random.default_rng(2)
+    m = n = k = 4096
+    x1 = rng.integers(-4, 5, size=(m, k)).astype(np.float32); x2 = rng.integers(-4, 5, size=(m, k)).astype(np.float32)
+    w = rng.integers(-2, 3, size=(n, k)).astype(np.float32)
+    tw = up16(client, w)
+    y1 = client.read(RT.gemm(client, up16(client, x1), tw, Transpose.No, Transpose.Yes, DType.F32))
+    y2 = client.read(RT.gemm(client, up16(client, x2), tw, Transpose.No, Transpose.Yes, DType.F32))
+    y12 = client.read(RT.gemm(client, up16(client, x1 + x2), tw, Transpose.No, Transpose.Yes, DType.F32))
+    np.testing.assert_array_equal(y12, y1 + y2)  # all values are integers below 2^24: exact in FP32
+    rows = rng.integers(0, m, 8)
+    np.testing.assert_array_equal(y1[rows], x1[rows].astype(np.float64) @ w.astype(np.float64).T)
+
+
+def test_domain_errors(client):
+    a = up16(client, np.zeros((32, 48), np.float32)); b = up16(client, np.zeros((64, 48), np.float32))
+    with pytest.raises(InvalidTensor, match="multiples of 16"):
+        RT.gemm(client, up16(client, np.zeros((24, 48), np.float32)), b, Transpose.No, Transpose.Yes, DType.F32)
+    with pytest.raises(InvalidTensor, match="agree"):
+        RT.gemm(client, a, b, Transpose.No, Transpose.No, DType.F32)
+    with pytest.raises(InvalidTensor, match="BF16 operands"):
+        RT.gemm(client, client.upload(np.zeros((32, 48), np.float32)), b, Transpose.No, Transpose.Yes, DType.F32)
+    out = client.tensor((32, 64), DType.F32)
+    alias = type(out)(a.handle, (32, 24), DType.F32)
+    with pytest.raises(InvalidTensor):
+        RT.gemm_into(client, a, b, Transpose.No, Transpose.Yes, alias)
+    with pytest.raises(InvalidTensor, match="FP32 inputs"):
+        RT.gemm_bf16_fp32(client, a, b, Transpose.No, Transpose.Yes)
