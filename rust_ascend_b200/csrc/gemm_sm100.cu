@@ -43,7 +43,8 @@ template <int BN> struct Config {
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int BIAS_BYTES = 4 * 2 * 256 * 4;  // per epilogue warp: two staged bias rows, one per accumulator in flight
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + BIAS_BYTES;
     static constexpr int TMEM_COLS = 2 * BN;
 };
 
@@ -74,6 +75,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     uint64_t* tmem_empty = tmem_full + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
     volatile uint32_t* abort_word = tmem_slot + 1;
+    float* bias_smem = reinterpret_cast<float*>(smem + C::STAGES * C::STAGE_BYTES + 256);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool swiglu = p.epilogue == RB_EPILOGUE_SWIGLU;
@@ -156,7 +158,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++iter) {
             const uint32_t acc = iter & 1, acc_phase = (iter >> 1) & 1;
             uint32_t batch, tm, tn; tile_coords(t, p, batch, tm, tn);
-            if (!(ok = mbar_wait(&tmem_full[acc], acc_phase, abort_word))) break;
+            float* sbias = bias_smem + (quarter * 2 + acc) * 256;
+            if (p.epilogue == RB_EPILOGUE_BIAS) {
+                // Each warp stages this tile's bias row for itself (warp-level sync only, so no CTA barrier can
+                // be left waiting if a bounded wait expires).
+                for (uint32_t j = lane; j < bn_out; j += 32) sbias[j] = tn * bn_out + j < p.n ? bias_at(p, tn * bn_out + j) : 0.f;
+                __syncwarp();
+            }
+            ok = mbar_wait(&tmem_full[acc], acc_phase, abort_word);
+            if (!(ok = __all_sync(0xffffffffu, ok))) break;  // keep the warp converged
             tc_fence_after();
             const uint32_t row = tm * BM + quarter * 32 + lane;
             const uint32_t col0 = tn * bn_out;
@@ -183,7 +193,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
                     if (p.epilogue == RB_EPILOGUE_BIAS) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) if (col0 + c + j < p.n) v[j] = __fadd_rn(v[j], bias_at(p, col0 + c + j));
+                        for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], sbias[c + j]);
                     }
                 }
                 if (row < p.m) {
