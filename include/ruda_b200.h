@@ -187,6 +187,23 @@ RB_API int32_t rb_embedding(rb_ctx* ctx, const rb_tensor* table, const rb_tensor
 RB_API int32_t rb_gemm(rb_ctx* ctx, const rb_tensor* a, const rb_tensor* b, int32_t transpose_a, int32_t transpose_b,
                        const rb_tensor* bias, const rb_tensor* b_up, int32_t epilogue, const rb_tensor* out);
 
+/* ---- attention --------------------------------------------------------------------------------------- */
+/* nn::scaled_dot_product_attention_bf16_fp32 / causal_attention / grouped_query_attention /
+ * causal_grouped_query_attention, src/nn/attention.rs:10,33,49,69 (domain checks :81-104); the reference composes
+ * them from causal_mask (runtime/mod.rs:206), repeat_kv_heads (:209), two BF16 GEMMs and softmax.
+ * q [B,Hq,M,D], k [B,Hkv,N,D], v [B,Hkv,N,Dv] as rank-4 tensors whose last axis is contiguous (other strides may
+ * describe a [B,S,H,D] buffer); out is contiguous [B,Hq,M,Dv] (RB_LAYOUT_BHMD) or [B,M,Hq,Dv] (RB_LAYOUT_BMHD).
+ * O = softmax(scale * bf16(Q) bf16(K)^T + mask) bf16(V); with causal != 0 key k of the block is hidden from query q
+ * iff key_start + k > query_start + q (mask_programs.rs:30-37).  additive_mask is NULL or FP32 [B,Hq,M,N].
+ * cos / sin (NULL, or FP32 [positions, 64]) apply the rotary encoding of rotary_programs.rs:63-93 to Q and K before
+ * the product: key n uses table row n, query i uses row i + (query_start - key_start).
+ * BF16 tensors with D = Dv = 128, no additive mask and a positive scale run on the tensor-core kernel (nothing is
+ * materialised); other shapes run a general kernel that follows the reference's materialised algorithm. */
+RB_API int32_t rb_attention(rb_ctx* ctx, const rb_tensor* q, const rb_tensor* k, const rb_tensor* v, const rb_tensor* additive_mask,
+                            float scale, int32_t causal, uint64_t query_start, uint64_t key_start,
+                            const rb_tensor* cos, const rb_tensor* sin, int32_t rotary_layout, int32_t out_layout,
+                            const rb_tensor* out);
+
 #ifdef __cplusplus
 }
 #endif

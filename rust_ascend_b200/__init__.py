@@ -5,6 +5,7 @@ libruda_b200.so (hand-written sm_100a CUDA kernels behind a C ABI).
 TensorBuffer, RuntimeOptions, CannError); `nn` mirrors src/nn.rs and src/nn/*.rs; `distributed`
 mirrors src/distributed.rs with NCCL in place of HCCL.
 """
+from . import nn
 from .runtime import (B200Device, B200Error, B200Runtime, ComputeClient, DType, InvalidTensor, RotaryLayout,
                       RuntimeOptions, ServerUnhealthy, TensorBuffer, Transpose)
 

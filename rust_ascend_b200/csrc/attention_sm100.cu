@@ -1,0 +1,539 @@
+// Flash-style attention forward on Blackwell tensor cores (tcgen05 + TMEM), head dim 128, BF16 in/out.
+//
+// Stands in for the reference's composed attention (src/nn/attention.rs:10-80): S = scale * bf16(Q) bf16(K)^T,
+// causal predicate key_start+k > query_start+q (mask_programs.rs:30-37), softmax in FP32, O = bf16(P) bf16(V),
+// grouped-query mapping kv_head = q_head / (Hq/Hkv) (heads_programs.rs:48-52).  Nothing is materialised: no
+// score matrix, no mask tensor, no repeated KV heads.
+//
+// One CTA owns 256 query rows of one (batch, head) as two 128-row tiles that ping-pong on the tensor core:
+//   warps 0-3 / 4-7  softmax of tile 0 / tile 1: one query row per thread, running max and sum in FP32,
+//                    exp2 with the scale folded in, P written back to TMEM as BF16 over the scores
+//   warp 8           TMA producer: Q once, then K and V tiles of 128 keys through two 2-stage rings
+//   warp 9           issues tcgen05.mma:  S_t = Q_t K^T (operands in shared memory),  O_t += P_t V (P from TMEM,
+//                    V consumed as stored, Dv-contiguous)
+// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_t aliases the first 64 columns of S_t.
+// The running maximum is only refreshed when it grows by more than 2^8 (the accumulator and the sum are then
+// rescaled), so most key blocks need no pass over O.
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace {
+
+using namespace sm100;
+using bf = __nv_bfloat16;
+
+constexpr int D = 128;            // head dim (Q/K) and value dim
+constexpr int TQ = 128;           // query rows per tile
+constexpr int TK = 128;           // keys per block
+constexpr int KV_STAGES = 2;
+constexpr int THREADS = 320;
+constexpr int TILE_BYTES = 128 * D * 2;       // 32 KiB: one [128 x 128] BF16 tile = two 64-wide swizzle slabs
+constexpr int SLAB_BYTES = 128 * 64 * 2;      // 16 KiB
+constexpr int SMEM_BYTES = 2 * TILE_BYTES + 2 * KV_STAGES * TILE_BYTES + 1024 + 256;
+
+struct AttnParams {
+    uint32_t B, Hq, Hkv, M, N;
+    float scale_log2;             // scale * log2(e)
+    int32_t causal;
+    int64_t delta;                // query_start - key_start (saturated): key k is masked iff k > q + delta
+    bf* out; uint64_t o_stride_b, o_stride_h, o_stride_m;   // elements
+    uint32_t* status;
+};
+
+__device__ __forceinline__ float ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    uint32_t r; asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo)); return r;
+}
+
+// Number of key blocks tile rows [row0, row_end) must visit.
+__device__ __forceinline__ uint32_t blocks_for(const AttnParams& p, uint32_t row0, uint32_t row_end) {
+    if (row0 >= p.M) return 0;
+    uint32_t all = (p.N + TK - 1) / TK;
+    if (!p.causal) return all;
+    int64_t last_q = (int64_t)(row_end < p.M ? row_end : p.M) - 1 + p.delta;  // largest visible key index
+    if (last_q < 0) return 0;
+    int64_t need = last_q / TK + 1;
+    return need < (int64_t)all ? (uint32_t)need : all;
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                     const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sq = smem;                                   // [2 tiles][2 slabs][128][64]
+    uint8_t* sk = smem + 2 * TILE_BYTES;                  // [stages][2 slabs][128 keys][64 d]
+    uint8_t* sv = sk + KV_STAGES * TILE_BYTES;            // [stages][2 slabs][128 keys][64 dv]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sv + KV_STAGES * TILE_BYTES);
+    uint64_t* q_full = bars;                    // [1]
+    uint64_t* k_full = bars + 1;                // [stages]
+    uint64_t* k_empty = k_full + KV_STAGES;
+    uint64_t* v_full = k_empty + KV_STAGES;
+    uint64_t* v_empty = v_full + KV_STAGES;
+    uint64_t* s_full = v_empty + KV_STAGES;     // [2 tiles]
+    uint64_t* p_full = s_full + 2;              // [2 tiles]
+    uint64_t* o_full = p_full + 2;              // [2 tiles]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
+    volatile uint32_t* abort_word = tmem_slot + 1;
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // Heaviest query blocks first: under a causal mask the last rows see the most keys.
+    const uint32_t qb = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const uint32_t kvh = h / (p.Hq / p.Hkv);
+    const uint32_t row0 = qb * 2 * TQ;
+    const uint32_t n_blocks[2] = {blocks_for(p, row0, row0 + TQ), blocks_for(p, row0 + TQ, row0 + 2 * TQ)};
+    const uint32_t n_max = n_blocks[0] > n_blocks[1] ? n_blocks[0] : n_blocks[1];
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
+        for (int t = 0; t < 2; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 128); mbar_init(&o_full[t], 1); }
+        *abort_word = 0;
+        fence_barrier_init();
+        prefetch_tmap(&map_q); prefetch_tmap(&map_k); prefetch_tmap(&map_v);
+    }
+    if (warp == 9) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 8) {
+        // ---------------- TMA producer ----------------
+        if (elect_one()) {
+            bool ok = true;
+            mbar_expect_tx(q_full, 2 * TILE_BYTES);
+            for (int t = 0; t < 2; ++t)
+                for (int s = 0; s < 2; ++s)
+                    tma_load_4d(sq + t * TILE_BYTES + s * SLAB_BYTES, &map_q, q_full, s * 64, (int32_t)(row0 + t * TQ), (int32_t)h, (int32_t)b);
+            uint32_t issued_k = 0, issued_v = 0;
+            for (uint32_t j = 0; ok && j < n_max; ++j) {
+                const uint32_t st = j % KV_STAGES, ph = (j / KV_STAGES) & 1;
+                if (!(ok = mbar_wait(&k_empty[st], ph ^ 1, abort_word))) break;
+                mbar_expect_tx(&k_full[st], TILE_BYTES); issued_k = j + 1;
+                for (int s = 0; s < 2; ++s)
+                    tma_load_4d(sk + st * TILE_BYTES + s * SLAB_BYTES, &map_k, &k_full[st], s * 64, (int32_t)(j * TK), (int32_t)kvh, (int32_t)b);
+                if (!(ok = mbar_wait(&v_empty[st], ph ^ 1, abort_word))) break;
+                mbar_expect_tx(&v_full[st], TILE_BYTES); issued_v = j + 1;
+                for (int s = 0; s < 2; ++s)
+                    tma_load_4d(sv + st * TILE_BYTES + s * SLAB_BYTES, &map_v, &v_full[st], s * 64, (int32_t)(j * TK), (int32_t)kvh, (int32_t)b);
+            }
+            if (!ok) {
+                // A wait expired: give the copies already issued a bounded time to land before the CTA retires.
+                for (uint32_t i = 0; i < (1u << 20) && !mbar_try_wait(q_full, 0); ++i) {}
+                for (uint32_t j = issued_k > KV_STAGES ? issued_k - KV_STAGES : 0; j < issued_k; ++j)
+                    for (uint32_t i = 0; i < (1u << 20) && !mbar_try_wait(&k_full[j % KV_STAGES], (j / KV_STAGES) & 1); ++i) {}
+                for (uint32_t j = issued_v > KV_STAGES ? issued_v - KV_STAGES : 0; j < issued_v; ++j)
+                    for (uint32_t i = 0; i < (1u << 20) && !mbar_try_wait(&v_full[j % KV_STAGES], (j / KV_STAGES) & 1); ++i) {}
+            }
+        }
+    } else if (warp == 9) {
+        // ---------------- MMA issuer ----------------
+        if (elect_one()) {
+            const uint32_t idesc_qk = make_idesc_bf16(TQ, TK, 0, 0);   // A = Q (K-major), B = K tile (K-major)
+            const uint32_t idesc_pv = make_idesc_bf16(TQ, D, 0, 1);    // A = P (TMEM), B = V tile, Dv-contiguous (MN-major)
+            bool ok = mbar_wait(q_full, 0, abort_word);
+            auto issue_s = [&](uint32_t t, uint32_t j) {
+                const uint32_t st = j % KV_STAGES;
+                const uint32_t qa = smem_u32(sq + t * TILE_BYTES), ka = smem_u32(sk + st * TILE_BYTES);
+#pragma unroll
+                for (uint32_t kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t off = (kk >> 2) * SLAB_BYTES + (kk & 3) * 32;  // 16 head-dim elements per step
+                    umma_bf16_ss(tmem_base + t * TK, make_kmajor_sw128_desc(qa + off), make_kmajor_sw128_desc(ka + off), idesc_qk, kk != 0);
+                }
+                umma_commit(&s_full[t]);
+            };
+            if (ok && n_max > 0) {
+                ok = mbar_wait(&k_full[0], 0, abort_word);
+                if (ok) {
+                    tc_fence_after();
+                    for (uint32_t t = 0; t < 2; ++t) if (n_blocks[t] > 0) issue_s(t, 0);
+                    umma_commit(&k_empty[0]);
+                }
+            }
+            for (uint32_t j = 0; ok && j < n_max; ++j) {
+                const uint32_t st = j % KV_STAGES, ph = (j / KV_STAGES) & 1;
+                for (uint32_t t = 0; ok && t < 2; ++t) {
+                    if (j >= n_blocks[t]) continue;
+                    if (!(ok = mbar_wait(&p_full[t], j & 1, abort_word))) break;
+                    if (!(ok = mbar_wait(&v_full[st], ph, abort_word))) break;
+                    tc_fence_after();
+                    const uint32_t va = smem_u32(sv + st * TILE_BYTES);
+#pragma unroll
+                    for (uint32_t kk = 0; kk < TK / 16; ++kk)   // 16 keys per step: 8 TMEM columns of packed BF16 pairs
+                        umma_bf16_ts(tmem_base + 256 + t * D, tmem_base + t * TK + kk * 8,
+                                     make_mnmajor_sw128_desc(va + kk * 2048, SLAB_BYTES), idesc_pv, (j | kk) != 0);
+                    const bool last_user = (t == 1) || (j >= n_blocks[1]);
+                    if (last_user) umma_commit(&v_empty[st]);
+                    if (j + 1 < n_blocks[t]) {
+                        const uint32_t st1 = (j + 1) % KV_STAGES, ph1 = ((j + 1) / KV_STAGES) & 1;
+                        if (!(ok = mbar_wait(&k_full[st1], ph1, abort_word))) break;
+                        tc_fence_after();
+                        issue_s(t, j + 1);
+                        const bool last_k_user = (t == 1) || (j + 1 >= n_blocks[1]);
+                        if (last_k_user) umma_commit(&k_empty[st1]);
+                    } else {
+                        umma_commit(&o_full[t]);
+                    }
+                }
+            }
+        }
+    } else {
+        // ---------------- softmax + epilogue: warps 0-3 own tile 0, warps 4-7 own tile 1 ----------------
+        const uint32_t t = warp >> 2, quarter = warp & 3;
+        const uint32_t row_in_tile = quarter * 32 + lane;
+        const uint32_t row = row0 + t * TQ + row_in_tile;          // query index inside the sequence
+        const uint32_t lane_base = (quarter * 32) << 16;
+        const uint32_t tmem_s = tmem_base + t * TK + lane_base;
+        const uint32_t tmem_o = tmem_base + 256 + t * D + lane_base;
+        const uint32_t nb = n_blocks[t];
+        const int64_t q_limit = (int64_t)row + p.delta;            // keys with index > q_limit are masked (causal)
+        float m_used = 0.f, l = 0.f;
+        bool ok = true;
+        for (uint32_t j = 0; j < nb; ++j) {
+            ok = mbar_wait(&s_full[t], j & 1, abort_word);
+            if (!(ok = __all_sync(0xffffffffu, ok))) break;
+            tc_fence_after();
+            const uint32_t k0 = j * TK;
+            const bool partial = k0 + TK > p.N;
+            const bool diagonal = p.causal && (int64_t)(k0 + TK - 1) > (int64_t)(row0 + t * TQ) + p.delta;  // warp-uniform
+            int32_t visible = TK;   // keys of this block the row may see
+            if (partial || diagonal) {
+                int64_t limit = (int64_t)p.N - 1;
+                if (p.causal && q_limit < limit) limit = q_limit;
+                const int64_t v64 = limit - (int64_t)k0 + 1;
+                visible = (int32_t)(v64 > TK ? TK : (v64 < 0 ? 0 : v64));
+            }
+            // Pass 1 over the scores in TMEM: row maximum (the scale is positive on this path).
+            const float sc = p.scale_log2;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_s + c * 32, r);
+                tmem_wait_ld();
+                if (partial || diagonal) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) if (c * 32 + i < visible) mx = fmaxf(mx, __uint_as_float(r[i]));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+                }
+            }
+            float m_blk = mx * sc;                      // -inf when every key of the block is masked for this row
+            if (!(m_blk > -INFINITY)) m_blk = -INFINITY;
+            // Refresh the reference maximum only when it grew by more than 8 (a factor 256 in P).
+            const bool first = j == 0;
+            const bool grow = first ? true : (m_blk > m_used + 8.f);
+            if (__any_sync(0xffffffffu, grow)) {
+                float m_new = first ? (m_blk > -INFINITY ? m_blk : 0.f) : (grow ? m_blk : m_used);
+                if (!first) {
+                    const float alpha = ex2(m_used - m_new);   // 1 for lanes that keep their maximum
+                    l *= alpha;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t r[32];
+                        tmem_ld_32x32(tmem_o + c * 32, r);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                        tmem_st_32x32(tmem_o + c * 32, r);
+                    }
+                    tmem_wait_st();
+                }
+                m_used = m_new;
+            }
+            // Pass 2: P = exp2(s*scale*log2e - m) as BF16 pairs, written over the scores already consumed
+            // (words 16c..16c+15 land in columns that chunk c or an earlier chunk has read).
+            float sum = 0.f;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[32], packed[16];
+                tmem_ld_32x32(tmem_s + c * 32, r);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float p0 = ex2(__fmaf_rn(__uint_as_float(r[i]), sc, -m_used)), p1 = ex2(__fmaf_rn(__uint_as_float(r[i + 1]), sc, -m_used));
+                    if (partial || diagonal) { if (c * 32 + i >= visible) p0 = 0.f; if (c * 32 + i + 1 >= visible) p1 = 0.f; }
+                    sum += p0 + p1;
+                    packed[i >> 1] = pack_bf16(p0, p1);
+                }
+                tmem_st_32x16(tmem_s + c * 16, packed);
+            }
+            l += sum;
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(&p_full[t]);
+        }
+        if (ok && row0 + t * TQ < p.M) {
+            bf* o = p.out + (uint64_t)b * p.o_stride_b + (uint64_t)h * p.o_stride_h + (uint64_t)row * p.o_stride_m;
+            if (nb == 0) {
+                // No visible key for this tile: the reference's softmax over an empty set has no value; write zeros.
+                if (row < p.M) for (int i = 0; i < D / 8; ++i) reinterpret_cast<uint4*>(o)[i] = make_uint4(0, 0, 0, 0);
+            } else {
+                ok = mbar_wait(&o_full[t], 0, abort_word);
+                ok = __all_sync(0xffffffffu, ok);
+                if (ok) {
+                    tc_fence_after();
+                    const float inv = l > 0.f ? __fdiv_rn(1.0f, l) : 0.f;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t r[32];
+                        tmem_ld_32x32(tmem_o + c * 32, r);
+                        tmem_wait_ld();
+                        if (row < p.M) {
+#pragma unroll
+                            for (int i = 0; i < 32; i += 8) {
+                                uint4 w;
+                                w.x = pack_bf16(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+                                w.y = pack_bf16(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+                                w.z = pack_bf16(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+                                w.w = pack_bf16(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+                                *reinterpret_cast<uint4*>(o + c * 32 + i) = w;
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_word) atomicExch(p.status, 2u);
+    if (warp == 9) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+// Rotary encoding of a BF16 [B,H,S,128] tensor (any strides with a contiguous last axis) into a contiguous
+// [B,H,S,128] buffer, SplitHalf or Interleaved, FP32 math with the reference's operation order
+// (rotary_programs.rs:63-93); tables are FP32 [positions, 64], row = sequence index + position_offset.
+__global__ void __launch_bounds__(256) rope_bf16_kernel(const bf* x, uint64_t sb, uint64_t sh, uint64_t ss, const float* cs, const float* sn,
+                                                       bf* y, uint32_t H, uint32_t S, uint64_t total_rows, uint32_t position_offset, int layout) {
+    // one thread per 8 pairs: 8 rows of the table, 16 input values
+    const uint64_t idx = (uint64_t)blockIdx.x * 256 + threadIdx.x;
+    const uint64_t rowi = idx / 8; const uint32_t g = (uint32_t)(idx % 8);
+    if (rowi >= total_rows) return;
+    const uint32_t s = (uint32_t)(rowi % S); const uint64_t bh = rowi / S; const uint32_t hh = (uint32_t)(bh % H); const uint64_t bb = bh / H;
+    const bf* xr = x + bb * sb + hh * sh + (uint64_t)s * ss;
+    bf* yr = y + rowi * D;
+    const float* c = cs + (uint64_t)(s + position_offset) * 64 + g * 8;
+    const float* sv = sn + (uint64_t)(s + position_offset) * 64 + g * 8;
+    float a[8], bq[8];
+    if (layout == RB_ROTARY_SPLIT_HALF) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { a[i] = __bfloat162float(xr[g * 8 + i]); bq[i] = __bfloat162float(xr[64 + g * 8 + i]); }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { a[i] = __bfloat162float(xr[(g * 8 + i) * 2]); bq[i] = __bfloat162float(xr[(g * 8 + i) * 2 + 1]); }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        // first of the pair: x*cos + (pair*sin)*(-1); second: x*cos + (pair*sin)*(+1)
+        const float ya = __fadd_rn(__fmul_rn(a[i], c[i]), __fmul_rn(__fmul_rn(bq[i], sv[i]), -1.0f));
+        const float yb = __fadd_rn(__fmul_rn(bq[i], c[i]), __fmul_rn(__fmul_rn(a[i], sv[i]), 1.0f));
+        if (layout == RB_ROTARY_SPLIT_HALF) { yr[g * 8 + i] = __float2bfloat16_rn(ya); yr[64 + g * 8 + i] = __float2bfloat16_rn(yb); }
+        else { yr[(g * 8 + i) * 2] = __float2bfloat16_rn(ya); yr[(g * 8 + i) * 2 + 1] = __float2bfloat16_rn(yb); }
+    }
+}
+
+// General attention for shapes the tensor-core kernel does not take (head dims other than 128, FP32 storage,
+// additive masks).  One CTA per query row; it follows the reference's materialised algorithm literally:
+// scores in FP32 from BF16-rounded operands, + mask, row softmax by division, P rounded to BF16, P V in FP32.
+template <typename T>
+__global__ void __launch_bounds__(128) attention_rows_kernel(const T* q, const T* k, const T* v, const float* mask, T* out,
+                                                            uint32_t Hq, uint32_t Hkv, uint32_t M, uint32_t N, uint32_t Dq, uint32_t Dv,
+                                                            float scale, int causal, int64_t delta,
+                                                            uint64_t o_stride_b, uint64_t o_stride_h, uint64_t o_stride_m) {
+    extern __shared__ float sc[];   // [N] scores, then probabilities
+    __shared__ float red[4];
+    __shared__ float qs[256];
+    const uint64_t r = blockIdx.x;  // flat (b, h, i)
+    const uint32_t i = (uint32_t)(r % M); const uint64_t bh = r / M; const uint32_t h = (uint32_t)(bh % Hq); const uint64_t b = bh / Hq;
+    const uint32_t kvh = h / (Hq / Hkv);
+    auto ldf = [](const T* ptr, uint64_t idx) -> float {
+        if constexpr (sizeof(T) == 4) return __bfloat162float(__float2bfloat16_rn(ptr[idx]));  // BF16-rounded operand
+        else return __bfloat162float(ptr[idx]);
+    };
+    const T* qr = q + r * Dq; const T* kb = k + (b * Hkv + kvh) * (uint64_t)N * Dq; const T* vb = v + (b * Hkv + kvh) * (uint64_t)N * Dv;
+    for (uint32_t c = threadIdx.x; c < Dq; c += 128) qs[c] = ldf(qr, c);
+    __syncthreads();
+    float mx = -INFINITY;
+    for (uint32_t j = threadIdx.x; j < N; j += 128) {
+        float acc = 0.f;
+        for (uint32_t c = 0; c < Dq; ++c) acc = __fmaf_rn(qs[c], ldf(kb, (uint64_t)j * Dq + c), acc);
+        float s = __fmul_rn(acc, scale);
+        if (mask) s = __fadd_rn(s, mask[r * N + j]);
+        if (causal && (int64_t)j > (int64_t)i + delta) s = -INFINITY;
+        sc[j] = s; mx = fmaxf(mx, s);
+    }
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    mx = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    __syncthreads();
+    float sum = 0.f;
+    for (uint32_t j = threadIdx.x; j < N; j += 128) { float e = expf(__fsub_rn(sc[j], mx)); sc[j] = e; sum += e; }
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sum;
+    __syncthreads();
+    sum = (red[0] + red[1]) + (red[2] + red[3]);
+    for (uint32_t j = threadIdx.x; j < N; j += 128) sc[j] = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(sc[j], sum)));
+    __syncthreads();
+    T* o = out + b * o_stride_b + (uint64_t)h * o_stride_h + (uint64_t)i * o_stride_m;
+    for (uint32_t c = threadIdx.x; c < Dv; c += 128) {
+        float acc = 0.f;
+        for (uint32_t j = 0; j < N; ++j) acc = __fmaf_rn(sc[j], ldf(vb, (uint64_t)j * Dv + c), acc);
+        if constexpr (sizeof(T) == 4) o[c] = acc; else o[c] = __float2bfloat16_rn(acc);
+    }
+}
+
+bool make_qkv_map(CUtensorMap* map, const void* base, const rb_tensor* t) {
+    // logical [B, H, S, 128] with element strides; TMA dims innermost first: {d, s, h, b}
+    uint64_t dims[4] = {t->shape[3], t->shape[2], t->shape[1], t->shape[0]};
+    uint64_t strides[3] = {t->strides[2] * 2, t->strides[1] * 2, t->strides[0] * 2};
+    uint32_t box[4] = {64, 128, 1, 1};
+    return encode_bf16_map(map, base, 4, dims, strides, box, true);
+}
+
+// Address and validity of a rank-4 tensor whose last axis is contiguous and whose other strides are multiples
+// of 8 elements (16 bytes for BF16); the byte range reached through the strides must lie inside the storage.
+int32_t resolve_strided4(rb_ctx* ctx, const rb_tensor* t, const char* what, void** out) {
+    *out = nullptr;
+    if (!t) return rb::fail(RB_INVALID_TENSOR, "%s: missing tensor", what);
+    if (t->rank != 4) return rb::fail(RB_INVALID_TENSOR, "%s: attention tensors are rank 4 [B,H,S,D]", what);
+    size_t es = rb::dtype_size(t->dtype);
+    if (!es) return rb::fail(RB_INVALID_TENSOR, "%s: unsupported dtype", what);
+    if (t->shape[3] > 1 && t->strides[3] != 1) return rb::fail(RB_INVALID_TENSOR, "%s: the last axis must be contiguous", what);
+    uint64_t span = 1;
+    for (int i = 0; i < 4; ++i) {
+        if (t->shape[i] == 0) { span = 0; break; }
+        span += (t->shape[i] - 1) * t->strides[i];
+    }
+    void* base; uint64_t bytes;
+    if (rb_resource(ctx, t->handle, &base, &bytes) != RB_OK) return RB_NULL_HANDLE;
+    if (t->offset > bytes || span * es > bytes - t->offset) return rb::fail(RB_INVALID_TENSOR, "%s: strides reach outside the storage", what);
+    char* ptr = (char*)base + t->offset;
+    if (((uintptr_t)ptr & 15u) != 0) return rb::fail(RB_INVALID_TENSOR, "%s: device address must be 16-byte aligned", what);
+    *out = ptr;
+    return RB_OK;
+}
+
+bool is_contiguous4(const rb_tensor* t) { return rb::contiguous(t); }
+
+}  // namespace
+
+using namespace rb;
+
+extern "C" {
+
+int32_t rb_attention(rb_ctx* ctx, const rb_tensor* q, const rb_tensor* k, const rb_tensor* v, const rb_tensor* additive_mask,
+                     float scale, int32_t causal, uint64_t query_start, uint64_t key_start,
+                     const rb_tensor* cos, const rb_tensor* sin, int32_t rotary_layout, int32_t out_layout, const rb_tensor* out) {
+    RB_TRY(check_ctx(ctx));
+    void *pq, *pk, *pv, *po, *pm = nullptr, *pc = nullptr, *ps = nullptr;
+    RB_TRY(resolve_strided4(ctx, q, "attention Q", &pq)); RB_TRY(resolve_strided4(ctx, k, "attention K", &pk));
+    RB_TRY(resolve_strided4(ctx, v, "attention V", &pv)); RB_TRY(resolve(ctx, out, "attention output", &po));
+    const uint64_t B = q->shape[0], Hq = q->shape[1], M = q->shape[2], Dq = q->shape[3];
+    const uint64_t Hkv = k->shape[1], N = k->shape[2], Dv = v->shape[3];
+    // Domain of src/nn/attention.rs:81-104.
+    if (Hq == 0 || Hkv == 0 || Hq % Hkv != 0 || k->shape[0] != B || v->shape[0] != B || v->shape[1] != Hkv || k->shape[3] != Dq || v->shape[2] != N)
+        return fail(RB_INVALID_TENSOR, "GQA requires matching batches, positive divisible Q/KV heads and matching K/V lengths and Q/K widths");
+    const uint64_t flat = B * Hq;
+    if (flat == 0 || flat > 4096 || M == 0 || Dq == 0 || Dv == 0 || M % 16 || Dq % 16 || Dv % 16 || N == 0 || N % 32 || N > 0x7fffffffull ||
+        M > 0x7fffffffull || !(scale - scale == 0.0f) || flat * M * N > 0xffffffffull)
+        return fail(RB_INVALID_TENSOR, "attention requires matching batches/contractions, aligned positive matrix dimensions, positive N divisible by 32 "
+                                       "within INT32_MAX, a finite FP32 scale and scores within u32");
+    if (q->dtype != k->dtype || q->dtype != v->dtype || q->dtype != out->dtype || (q->dtype != RB_BF16 && q->dtype != RB_F32))
+        return fail(RB_INVALID_TENSOR, "attention requires Q/K/V and the output in one dtype, BF16 or FP32");
+    if (causal && (query_start + (M - 1) < query_start || key_start + (N - 1) < key_start)) return fail(RB_INVALID_TENSOR, "causal absolute position overflow");
+    if (out->rank != 4) return fail(RB_INVALID_TENSOR, "attention output is rank 4");
+    const bool bmhd = out_layout == RB_LAYOUT_BMHD;
+    const uint64_t want[4] = {B, bmhd ? M : Hq, bmhd ? Hq : M, Dv};
+    for (int i = 0; i < 4; ++i) if (out->shape[i] != want[i]) return fail(RB_INVALID_TENSOR, "attention output shape does not match the requested layout");
+    const uint64_t o_stride_b = Hq * M * Dv, o_stride_h = bmhd ? Dv : M * Dv, o_stride_m = bmhd ? Hq * Dv : Dv;
+    if (additive_mask) {
+        RB_TRY(resolve(ctx, additive_mask, "attention mask", &pm));
+        if (additive_mask->dtype != RB_F32 || elements(additive_mask) != flat * M * N) return fail(RB_INVALID_TENSOR, "attention additive mask must be FP32 [B,Hq,M,N]");
+    }
+    const bool rope = cos != nullptr || sin != nullptr;
+    int64_t delta;
+    {
+        const uint64_t cap = 1ull << 40;
+        if (query_start >= key_start) delta = (int64_t)(query_start - key_start < cap ? query_start - key_start : cap);
+        else delta = -(int64_t)(key_start - query_start < cap ? key_start - query_start : cap);
+    }
+    if (rope) {
+        if (!cos || !sin) return fail(RB_INVALID_TENSOR, "fused rotary needs both tables");
+        RB_TRY(resolve(ctx, cos, "attention cos table", &pc)); RB_TRY(resolve(ctx, sin, "attention sin table", &ps));
+        const int64_t q_off = delta;
+        if (cos->dtype != RB_F32 || sin->dtype != RB_F32 || !same_shape(cos, sin) || cos->shape[cos->rank - 1] != 64 || Dq != 128 || q->dtype != RB_BF16 ||
+            q_off < 0 || elements(cos) / 64 < N || elements(cos) / 64 < M + (uint64_t)q_off)
+            return fail(RB_INVALID_TENSOR, "fused rotary needs BF16 head dim 128 and FP32 tables [positions >= max(N, M + query_start - key_start), 64]");
+        if (rotary_layout != RB_ROTARY_SPLIT_HALF && rotary_layout != RB_ROTARY_INTERLEAVED) return fail(RB_INVALID_TENSOR, "unknown rotary layout");
+    }
+
+    const bool fast = q->dtype == RB_BF16 && Dq == 128 && Dv == 128 && !additive_mask && scale > 0.0f;
+    if (!fast) {
+        if (rope) return fail(RB_INVALID_TENSOR, "fused rotary is only available on the BF16 head-dim-128 path");
+        if (!is_contiguous4(q) || !is_contiguous4(k) || !is_contiguous4(v)) return fail(RB_INVALID_TENSOR, "general attention path requires contiguous [B,H,S,D] tensors");
+        if (Dq > 256) return fail(RB_INVALID_TENSOR, "general attention path supports head dims up to 256");
+        const size_t smem = N * sizeof(float);
+        if (smem > 200 * 1024) return fail(RB_INVALID_TENSOR, "general attention path supports up to 51200 keys; use BF16 head dim 128 for longer sequences");
+        const uint64_t rows = flat * M;
+        if (q->dtype == RB_F32) {
+            static bool set32 = false;
+            if (!set32) { cudaFuncSetAttribute(attention_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); set32 = true; }
+            attention_rows_kernel<float><<<(unsigned)rows, 128, smem, ctx->stream>>>((const float*)pq, (const float*)pk, (const float*)pv, (const float*)pm, (float*)po,
+                (uint32_t)Hq, (uint32_t)Hkv, (uint32_t)M, (uint32_t)N, (uint32_t)Dq, (uint32_t)Dv, scale, causal, delta, o_stride_b, o_stride_h, o_stride_m);
+        } else {
+            static bool set16 = false;
+            if (!set16) { cudaFuncSetAttribute(attention_rows_kernel<bf>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); set16 = true; }
+            attention_rows_kernel<bf><<<(unsigned)rows, 128, smem, ctx->stream>>>((const bf*)pq, (const bf*)pk, (const bf*)pv, (const float*)pm, (bf*)po,
+                (uint32_t)Hq, (uint32_t)Hkv, (uint32_t)M, (uint32_t)N, (uint32_t)Dq, (uint32_t)Dv, scale, causal, delta, o_stride_b, o_stride_h, o_stride_m);
+        }
+        return after_launch(ctx, "attention (general path)");
+    }
+
+    // ---- tensor-core path ----
+    rb_tensor qt = *q, kt = *k;
+    if (rope) {
+        // K is rotated once per KV head and Q once per query head into the context workspace; doing it inside the
+        // attention CTAs would repeat the K rotation for every query head of the group and every query block.
+        const uint64_t qn = flat * M * 128, kn = B * Hkv * N * 128;
+        RB_TRY(ensure_workspace(ctx, 1024 + (qn + kn) * 2));
+        bf* wq = reinterpret_cast<bf*>(static_cast<uint8_t*>(ctx->workspace) + 1024); bf* wk = wq + qn;
+        const uint32_t q_off = (uint32_t)delta;
+        rope_bf16_kernel<<<(unsigned)((flat * M * 8 + 255) / 256), 256, 0, ctx->stream>>>((const bf*)pq, q->strides[0], q->strides[1], q->strides[2], (const float*)pc,
+            (const float*)ps, wq, (uint32_t)Hq, (uint32_t)M, flat * M, q_off, rotary_layout);
+        RB_TRY(after_launch(ctx, "attention rotary(Q)"));
+        rope_bf16_kernel<<<(unsigned)((B * Hkv * N * 8 + 255) / 256), 256, 0, ctx->stream>>>((const bf*)pk, k->strides[0], k->strides[1], k->strides[2], (const float*)pc,
+            (const float*)ps, wk, (uint32_t)Hkv, (uint32_t)N, B * Hkv * N, 0, rotary_layout);
+        RB_TRY(after_launch(ctx, "attention rotary(K)"));
+        pq = wq; pk = wk;
+        qt.strides[0] = Hq * M * 128; qt.strides[1] = M * 128; qt.strides[2] = 128; qt.strides[3] = 1;
+        kt.strides[0] = Hkv * N * 128; kt.strides[1] = N * 128; kt.strides[2] = 128; kt.strides[3] = 1;
+    }
+    const rb_tensor* operands[3] = {&qt, &kt, v};
+    for (const rb_tensor* t : operands)
+        for (int i = 0; i < 3; ++i)
+            if (t->strides[i] % 8 != 0) return fail(RB_INVALID_TENSOR, "attention strides must be multiples of 8 elements");
+    AttnParams p{};
+    p.B = (uint32_t)B; p.Hq = (uint32_t)Hq; p.Hkv = (uint32_t)Hkv; p.M = (uint32_t)M; p.N = (uint32_t)N;
+    p.scale_log2 = scale * 1.4426950408889634f; p.causal = causal ? 1 : 0; p.delta = causal ? delta : 0;
+    p.out = (bf*)po; p.o_stride_b = o_stride_b; p.o_stride_h = o_stride_h; p.o_stride_m = o_stride_m;
+    RB_TRY(kernel_status_word(ctx, &p.status));
+    CUtensorMap mq, mk, mv;
+    if (!make_qkv_map(&mq, pq, &qt) || !make_qkv_map(&mk, pk, &kt) || !make_qkv_map(&mv, pv, v))
+        return fail(RB_STATUS, "cuTensorMapEncodeTiled failed for an attention operand");
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return fail(RB_STATUS, "cudaFuncSetAttribute(attention) failed with CUDA status %d (%s)", (int)e, cudaGetErrorString(e));
+        configured = true;
+    }
+    dim3 grid((unsigned)((M + 2 * TQ - 1) / (2 * TQ)), (unsigned)Hq, (unsigned)B);
+    attention_fwd_kernel<<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(mq, mk, mv, p);
+    return after_launch(ctx, "attention");
+}
+
+}  // extern "C"

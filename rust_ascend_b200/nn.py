@@ -1,0 +1,174 @@
+"""Mirror of `rust_ascend::nn` (src/nn.rs and src/nn/*.rs): explicit native operators on tensors.
+
+The reference's functions are generic over RUDA `Tensor<B, D>`; here a `Tensor` is a `TensorBuffer` bound to
+its `ComputeClient`.  Names, argument order, shape/dtype rules and error behaviour follow the reference; the
+work is done by libruda_b200.so through `B200Runtime`.  Forward contracts only: the reference's autodiff
+registration (`Backward` impls, src/nn.rs:209-232) needs RUDA and is outside this package.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+
+from .runtime import (B200Runtime as RT, ComputeClient, DType, InvalidTensor, RotaryLayout, TensorBuffer, Transpose)
+
+
+@dataclass
+class Tensor:
+    client: ComputeClient
+    buffer: TensorBuffer
+
+    @classmethod
+    def from_data(cls, client: ComputeClient, data, dtype: DType | None = None) -> "Tensor":
+        return cls(client, client.upload(np.asarray(data), dtype))
+
+    def dims(self):
+        return list(self.buffer.shape)
+
+    def dtype(self) -> DType:
+        return self.buffer.dtype
+
+    def into_data(self) -> np.ndarray:
+        return self.client.read(self.buffer)
+
+    def reshape(self, shape) -> "Tensor":
+        return Tensor(self.client, self.buffer.reshape(shape))
+
+
+def _same_client(*tensors):
+    client = tensors[0].client
+    for t in tensors[1:]:
+        if t is not None and t.client is not client:
+            raise InvalidTensor("tensors must live on the same device and execution queue")  # src/nn.rs:180-187
+    return client
+
+
+def _wrap(client, buffer):
+    return Tensor(client, buffer)
+
+
+def matmul_bf16_fp32(a: Tensor, b: Tensor, ta: Transpose = Transpose.No, tb: Transpose = Transpose.No) -> Tensor:
+    """FP32 operands, BF16 compute, FP32 result (src/nn.rs:55-72)."""
+    c = _same_client(a, b)
+    return _wrap(c, RT.gemm_bf16_fp32(c, a.buffer, b.buffer, ta, tb)[0])
+
+
+def linear_bf16_fp32(input: Tensor, weight: Tensor) -> Tensor:
+    """Y = X W^T, W stored [N,K] (src/nn.rs:73-88)."""
+    c = _same_client(input, weight)
+    return _wrap(c, RT.linear_bf16_fp32(c, input.buffer, weight.buffer)[0])
+
+
+def rms_norm(input: Tensor, weight: Tensor, epsilon: float) -> Tensor:
+    """src/nn.rs:165-174."""
+    c = _same_client(input, weight)
+    return _wrap(c, RT.rms_norm(c, input.buffer, weight.buffer, epsilon)[0])
+
+
+def softmax(input: Tensor) -> Tensor:
+    """src/nn.rs:101-110."""
+    return _wrap(input.client, RT.softmax(input.client, input.buffer))
+
+
+def log_softmax(input: Tensor) -> Tensor:
+    """src/nn.rs:111-120."""
+    return _wrap(input.client, RT.log_softmax(input.client, input.buffer))
+
+
+def sum_last(input: Tensor) -> Tensor:
+    return _wrap(input.client, RT.sum_last(input.client, input.buffer))
+
+
+def mean_last(input: Tensor) -> Tensor:
+    return _wrap(input.client, RT.mean_last(input.client, input.buffer))
+
+
+def silu_mul(gate: Tensor, up: Tensor) -> Tensor:
+    """src/nn.rs:121-135."""
+    c = _same_client(gate, up)
+    return _wrap(c, RT.silu_mul(c, gate.buffer, up.buffer))
+
+
+def swiglu_bf16_fp32(input: Tensor, gate: Tensor, up: Tensor, down: Tensor) -> Tensor:
+    """(SiLU(X Wg^T) * (X Wu^T)) Wd^T with FP32 storage (src/nn/feed_forward.rs:28-42).  The gate/up pair runs as
+    one tensor-core GEMM whose epilogue applies SiLU*up; the hidden activation is kept in FP32 as in the reference."""
+    c = _same_client(input, gate, up, down)
+    m, k = input.dims()
+    hidden, gk = gate.dims()
+    n, dh = down.dims()
+    if gk != k or up.dims() != [hidden, k] or dh != hidden or any(s == 0 or s % 16 for s in (m, n, k, hidden)):
+        raise InvalidTensor("SwiGLU requires aligned X[M,K], gate/up[H,K] and down[N,H]")
+    if any(t.dtype() != DType.F32 for t in (input, gate, up, down)):
+        raise InvalidTensor("SwiGLU requires FP32 input and weights on the same device")
+    x16 = RT.cast(c, input.buffer, DType.BF16)
+    h = RT.gemm(c, x16, RT.cast(c, gate.buffer, DType.BF16), Transpose.No, Transpose.Yes, DType.F32, b_up=RT.cast(c, up.buffer, DType.BF16))
+    return _wrap(c, RT.linear_bf16_fp32(c, h, down.buffer)[0])
+
+
+def rotary(input: Tensor, cos: Tensor, sin: Tensor, layout: RotaryLayout) -> Tensor:
+    """src/nn/rotary.rs:19-30."""
+    c = _same_client(input, cos, sin)
+    return _wrap(c, RT.rotary(c, input.buffer, cos.buffer, sin.buffer, layout))
+
+
+def rotary_prefix(input: Tensor, cos: Tensor, sin: Tensor, width: int, layout: RotaryLayout) -> Tensor:
+    """src/nn/rotary.rs:32-45."""
+    c = _same_client(input, cos, sin)
+    return _wrap(c, RT.rotary_prefix(c, input.buffer, cos.buffer, sin.buffer, width, layout))
+
+
+def repeat_kv_heads(input: Tensor, query_heads: int) -> Tensor:
+    """src/nn/heads.rs:11-25."""
+    return _wrap(input.client, RT.repeat_kv_heads(input.client, input.buffer, query_heads))
+
+
+def causal_mask(client: ComputeClient, shape, query_start: int, key_start: int) -> Tensor:
+    """FP32 [B,Q,K] mask (src/nn/mask.rs:12-25)."""
+    b, q, k = shape
+    return _wrap(client, RT.causal_mask(client, b, q, k, query_start, key_start))
+
+
+def _attention(query, key, value, scale, mask, causal, query_start, key_start):
+    c = _same_client(query, key, value, mask)
+    rank3 = len(query.dims()) == 3
+    q, k, v = query.buffer, key.buffer, value.buffer
+    m = None if mask is None else mask.buffer
+    if rank3:
+        q, k, v = (t.reshape((t.shape[0], 1) + t.shape[1:]) for t in (q, k, v))
+        m = None if m is None else m.reshape((m.shape[0], 1) + m.shape[1:])
+    if any(t.dtype != DType.F32 for t in (q, k, v)):
+        raise InvalidTensor("attention requires FP32 Q/K/V on the same device")
+    out = RT.attention(c, q, k, v, scale, mask=m, causal=causal, query_start=query_start, key_start=key_start)
+    return _wrap(c, out.reshape((out.shape[0],) + out.shape[2:]) if rank3 else out)
+
+
+def scaled_dot_product_attention_bf16_fp32(query: Tensor, key: Tensor, value: Tensor, scale: float,
+                                           additive_mask: Tensor | None = None) -> Tensor:
+    """Q[B,M,D], K[B,N,D], V[B,N,Dv] FP32 (src/nn/attention.rs:10-29)."""
+    if len(query.dims()) != 3:
+        raise InvalidTensor("scaled_dot_product_attention takes rank-3 tensors")
+    return _attention(query, key, value, scale, additive_mask, False, 0, 0)
+
+
+def causal_attention_bf16_fp32(query: Tensor, key: Tensor, value: Tensor, scale: float, query_start: int, key_start: int) -> Tensor:
+    """src/nn/attention.rs:33-45."""
+    if len(query.dims()) != 3:
+        raise InvalidTensor("causal_attention takes rank-3 tensors")
+    return _attention(query, key, value, scale, None, True, query_start, key_start)
+
+
+def grouped_query_attention_bf16_fp32(query: Tensor, key: Tensor, value: Tensor, scale: float,
+                                      additive_mask: Tensor | None = None) -> Tensor:
+    """Q[B,Hq,M,D], K[B,Hkv,N,D], V[B,Hkv,N,Dv] FP32 (src/nn/attention.rs:49-67)."""
+    if len(query.dims()) != 4:
+        raise InvalidTensor("grouped_query_attention takes rank-4 tensors")
+    return _attention(query, key, value, scale, additive_mask, False, 0, 0)
+
+
+def causal_grouped_query_attention_bf16_fp32(query: Tensor, key: Tensor, value: Tensor, scale: float, query_start: int,
+                                             key_start: int) -> Tensor:
+    """src/nn/attention.rs:69-80."""
+    if len(query.dims()) != 4:
+        raise InvalidTensor("causal_grouped_query_attention takes rank-4 tensors")
+    return _attention(query, key, value, scale, None, True, query_start, key_start)

@@ -490,6 +490,25 @@ class B200Runtime:
         return B200Runtime.gemm(client, B200Runtime.cast(client, input, DType.BF16), weight, Transpose.No, Transpose.Yes, DType.F32)
 
 
+    # -- attention -------------------------------------------------------------------------------
+    @staticmethod
+    def attention(client, q: TensorBuffer, k: TensorBuffer, v: TensorBuffer, scale: float, mask: TensorBuffer | None = None,
+                  causal: bool = False, query_start: int = 0, key_start: int = 0, cos: TensorBuffer | None = None,
+                  sin: TensorBuffer | None = None, rotary_layout: RotaryLayout = RotaryLayout.SplitHalf,
+                  bmhd_output: bool = False, out: TensorBuffer | None = None) -> TensorBuffer:
+        """Fused attention for q [B,Hq,M,D], k [B,Hkv,N,D], v [B,Hkv,N,Dv] (src/nn/attention.rs:10-80).
+        Returns [B,Hq,M,Dv], or [B,M,Hq,Dv] when `bmhd_output`."""
+        if len(q.shape) != 4 or len(v.shape) != 4:
+            raise InvalidTensor("attention tensors are rank 4 [B,H,S,D]")
+        b, hq, m, _ = q.shape
+        dv = v.shape[3]
+        out = out or client.tensor((b, m, hq, dv) if bmhd_output else (b, hq, m, dv), q.dtype)
+        _check(client._lib.rb_attention(client._ctx, _ref(q), _ref(k), _ref(v), _ref(mask), C.c_float(scale), C.c_int32(int(causal)),
+                                        C.c_uint64(query_start), C.c_uint64(key_start), _ref(cos), _ref(sin), C.c_int32(int(rotary_layout)),
+                                        C.c_int32(1 if bmhd_output else 0), _ref(out)))
+        return out
+
+
 # ---- host-side BF16 carriers (bit patterns in uint16) ---------------------------------------------
 def f32_to_bf16_bits(x) -> np.ndarray:
     """Round-to-nearest-even FP32 -> BF16 bit patterns; NaN/Inf keep their upper half."""
