@@ -187,6 +187,21 @@ RB_API int32_t rb_embedding(rb_ctx* ctx, const rb_tensor* table, const rb_tensor
 RB_API int32_t rb_gemm(rb_ctx* ctx, const rb_tensor* a, const rb_tensor* b, int32_t transpose_a, int32_t transpose_b,
                        const rb_tensor* bias, const rb_tensor* b_up, int32_t epilogue, const rb_tensor* out);
 
+/* rb_gemm without any device allocation.  It has no counterpart in the reference (whose GEMM provider allocates
+ * through ComputeStorage); it exists for hosts that must not call cudaMalloc once they are running: servers with a
+ * memory budget fixed at start-up, real-time loops that cannot take the device-wide synchronisation cudaMalloc and
+ * cudaFree imply, processes that have handed the rest of the device memory to another pool.
+ * Same operand contract as rb_gemm with the identity epilogue.  The scratch rb_gemm would allocate (the K-major
+ * rewrite of an operand given as A[K,M] or B[K,N], and the kernel's status word) lives in a 16 MiB + 256 B array
+ * inside the library image, held by every GPU that loads the library until the process exits.  Limit: the operands
+ * that need a rewrite may take at most 16 MiB together (A[M,K] with B[N,K] needs none); larger ones are rejected with
+ * RB_INVALID_TENSOR.  The context's device must be current on the calling thread.  The first call on a device
+ * resolves the array's address (cudaGetSymbolAddress); make that first call before any stream capture begins.
+ * Every call shares the one array: calls that overlap on the GPU (other streams, other threads) race on it.  The
+ * call drains the context's stream before it returns, so that an expired kernel wait is reported by this call. */
+RB_API int32_t rb_gemm_no_alloc(rb_ctx* ctx, const rb_tensor* a, const rb_tensor* b, int32_t transpose_a, int32_t transpose_b,
+                                const rb_tensor* out);
+
 /* ---- attention --------------------------------------------------------------------------------------- */
 /* nn::scaled_dot_product_attention_bf16_fp32 / causal_attention / grouped_query_attention /
  * causal_grouped_query_attention, src/nn/attention.rs:10,33,49,69 (domain checks :81-104); the reference composes

@@ -392,3 +392,94 @@ int32_t rb_gemm(rb_ctx* ctx, const rb_tensor* a, const rb_tensor* b, int32_t tra
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------------
+// Allocation-free GEMM entry point.
+//
+// Some hosts of this library may not allocate device memory once they are running: an inference server whose
+// memory budget is fixed and audited at start-up, a real-time loop that cannot afford the device-wide
+// synchronisation hidden in cudaMalloc/cudaFree, or a process that hands all remaining memory to another pool
+// and would simply get an out-of-memory error.  rb_gemm needs scratch memory in two places (the K-major rewrite
+// of an operand stored the other way round, and the status word the kernel raises when a bounded wait expires)
+// and takes both from cudaMalloc.  rb_gemm_no_alloc takes them from the array below instead, which is part of
+// the loaded module: every GPU that loads the library holds these 16 MiB + 256 B until the process exits.
+// ---------------------------------------------------------------------------------------------------------
+#define RB_NO_ALLOC_SCRATCH_BYTES (16ull << 20)
+static __device__ __align__(256) uint8_t g_no_alloc_scratch[256 + RB_NO_ALLOC_SCRATCH_BYTES];
+// Device address of g_no_alloc_scratch per CUDA ordinal.  In host code the array's name is only a stand-in
+// for the symbol, not an address a kernel can use; the real address comes from cudaGetSymbolAddress.
+static uint8_t* g_no_alloc_scratch_address[64] = {};
+
+extern "C" int32_t rb_gemm_no_alloc(rb_ctx* ctx, const rb_tensor* a, const rb_tensor* b, int32_t transpose_a, int32_t transpose_b,
+                                    const rb_tensor* out) {
+    RB_TRY(check_ctx(ctx));
+    int current = -1;
+    RB_CUDA(ctx, "cudaGetDevice", cudaGetDevice(&current));
+    if (current != ctx->device || current < 0 || current >= 64)
+        return fail(RB_INVALID_DEVICE, "rb_gemm_no_alloc: make the context's device (%d) current on the calling thread (current is %d)", ctx->device, current);
+    // One-time set-up per device, with that device current: resolve the symbol to its device address.
+    if (!g_no_alloc_scratch_address[current]) {
+        void* address = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&address, g_no_alloc_scratch);
+        if (e != cudaSuccess || !address)
+            return fail(RB_STATUS, "rb_gemm_no_alloc: cudaGetSymbolAddress failed with CUDA status %d (%s)", (int)e, cudaGetErrorString(e));
+        g_no_alloc_scratch_address[current] = static_cast<uint8_t*>(address);
+    }
+    uint8_t* scratch = g_no_alloc_scratch_address[current];
+
+    void *pa, *pb, *po;
+    RB_TRY(resolve(ctx, a, "GEMM A", &pa)); RB_TRY(resolve(ctx, b, "GEMM B", &pb)); RB_TRY(resolve(ctx, out, "GEMM output", &po));
+    if (a->dtype != RB_BF16 || b->dtype != RB_BF16) return fail(RB_INVALID_TENSOR, "native GEMM requires BF16 operands");
+    if (out->dtype != RB_BF16 && out->dtype != RB_F32) return fail(RB_INVALID_TENSOR, "GEMM output must be BF16 or FP32");
+    uint64_t ba, ra, ca, bb, rbw, cb, bo, ro, co;
+    RB_TRY(matrix_dims(a, "GEMM A", &ba, &ra, &ca)); RB_TRY(matrix_dims(b, "GEMM B", &bb, &rbw, &cb)); RB_TRY(matrix_dims(out, "GEMM output", &bo, &ro, &co));
+    const uint64_t m = transpose_a ? ca : ra, k = transpose_a ? ra : ca;
+    const uint64_t n = transpose_b ? rbw : cb, kb = transpose_b ? cb : rbw;
+    if (a->rank != b->rank || a->rank != out->rank || ba != bb || ba != bo || k != kb || ro != m || co != n)
+        return fail(RB_INVALID_TENSOR, "GEMM shapes do not agree");
+    if (m == 0 || n == 0 || k == 0 || m % 16 || n % 16 || k % 16 || m > 0x7fffffffull || n > 0x7fffffffull || k > 0x7fffffffull)
+        return fail(RB_INVALID_TENSOR, "GEMM M/N/K must be positive multiples of 16 within INT32_MAX");
+    if (ba == 0 || ba > 4096) return fail(RB_INVALID_TENSOR, "GEMM batch count must be within 1..4096");
+    const uint64_t a_bytes = ba * m * k * 2, b_bytes = ba * n * k * 2, o_bytes = ba * m * n * dtype_size(out->dtype);
+    RB_TRY(no_overlap(po, o_bytes, pa, a_bytes, "GEMM")); RB_TRY(no_overlap(po, o_bytes, pb, b_bytes, "GEMM"));
+    const bool fix_a = transpose_a != 0, fix_b = transpose_b == 0;
+    const uint64_t need = (fix_a ? a_bytes : 0) + (fix_b ? b_bytes : 0);
+    if (need > RB_NO_ALLOC_SCRATCH_BYTES)
+        return fail(RB_INVALID_TENSOR, "rb_gemm_no_alloc: the operands stored against the K-major layout need %llu bytes of scratch, the built-in "
+                    "array holds %llu; use rb_gemm, or store A as [M,K] and B as [N,K]", (unsigned long long)need, (unsigned long long)RB_NO_ALLOC_SCRATCH_BYTES);
+
+    // The array keeps whatever the previous call left in it.  Only the status word must start at zero; the
+    // operand rewrites below overwrite every byte they later read.
+    uint32_t* status = reinterpret_cast<uint32_t*>(scratch);
+    RB_CUDA(ctx, "cudaMemsetAsync", cudaMemsetAsync(status, 0, 256, ctx->stream));
+    uint8_t* ws = scratch + 256;
+    const void *ka = pa, *kbp = pb;
+    if (fix_a) {
+        dim3 grid((unsigned)((m + 63) / 64), (unsigned)((k + 63) / 64), (unsigned)ba);
+        transpose_bf16_kernel<<<grid, 256, 0, ctx->stream>>>((const uint16_t*)pa, (uint16_t*)ws, (uint32_t)k, (uint32_t)m);
+        RB_TRY(after_launch(ctx, "gemm operand transpose")); ka = ws; ws += a_bytes;
+    }
+    if (fix_b) {
+        dim3 grid((unsigned)((n + 63) / 64), (unsigned)((k + 63) / 64), (unsigned)ba);
+        transpose_bf16_kernel<<<grid, 256, 0, ctx->stream>>>((const uint16_t*)pb, (uint16_t*)ws, (uint32_t)k, (uint32_t)n);
+        RB_TRY(after_launch(ctx, "gemm operand transpose")); kbp = ws;
+    }
+    GemmParams p{};
+    p.m = (uint32_t)m; p.n = (uint32_t)n; p.k = (uint32_t)k; p.batches = (uint32_t)ba; p.epilogue = RB_EPILOGUE_NONE;
+    p.out_f32 = out->dtype == RB_F32; p.out = po; p.status = status;
+    const int bn = n > 128 ? 256 : (n > 64 ? 128 : 64);
+    p.tiles_m = (p.m + BM - 1) / BM; p.tiles_n = (p.n + bn - 1) / bn;
+    CUtensorMap ma, mb;
+    if (!make_operand_map(&ma, ka, ba, m, k, BM) || !make_operand_map(&mb, kbp, ba, n, k, (uint32_t)bn))
+        return fail(RB_STATUS, "cuTensorMapEncodeTiled failed for a GEMM operand");
+    int32_t launched = bn == 256 ? launch<256>(ctx, ma, mb, mb, p) : (bn == 128 ? launch<128>(ctx, ma, mb, mb, p) : launch<64>(ctx, ma, mb, mb, p));
+    RB_TRY(launched);
+    // Report an expired wait without any state outside the array: drain the stream and read the status word.
+    ctx->stats.synchronizations++;
+    cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) { ctx->poisoned = true; return fail(RB_COMPLETION, "rb_gemm_no_alloc: completion failed with CUDA status %d (%s)", (int)e, cudaGetErrorString(e)); }
+    uint32_t raised = 0;
+    RB_CUDA(ctx, "cudaMemcpy(status)", cudaMemcpy(&raised, status, sizeof(raised), cudaMemcpyDeviceToHost));
+    if (raised) return fail(RB_COMPLETION, "rb_gemm_no_alloc: the kernel gave up on a bounded barrier wait; the output is invalid");
+    return RB_OK;
+}

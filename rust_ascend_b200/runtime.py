@@ -466,6 +466,13 @@ class B200Runtime:
         return out
 
     @staticmethod
+    def gemm_no_alloc(client, a: TensorBuffer, b: TensorBuffer, ta: Transpose, tb: Transpose, out: TensorBuffer) -> None:
+        """rb_gemm_no_alloc: GEMM into `out` that takes its scratch from a fixed array inside the library instead of
+        cudaMalloc, for hosts that may not allocate device memory while running.  Operands stored against the K-major
+        layout may need at most 16 MiB of rewrite space; the call returns after the stream has drained."""
+        _check(client._lib.rb_gemm_no_alloc(client._ctx, _ref(a), _ref(b), C.c_int32(int(ta)), C.c_int32(int(tb)), _ref(out)))
+
+    @staticmethod
     def gemm_bf16_fp32(client, a: TensorBuffer, b: TensorBuffer, ta: Transpose, tb: Transpose):
         """[FP32 output, saved BF16 A, saved BF16 B] from FP32 operands: Cast, Cast, GEMM
         (runtime/mod.rs:422-425 -> matrix.rs:84-93)."""
