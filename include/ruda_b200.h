@@ -159,6 +159,8 @@ RB_API int32_t rb_bias_add(rb_ctx* ctx, const rb_tensor* x, const rb_tensor* bia
                            const rb_tensor* y);
 /* Plain element-wise sum of two equal-shaped tensors (MapProgram::Add, programs.rs:34). */
 RB_API int32_t rb_add(rb_ctx* ctx, const rb_tensor* a, const rb_tensor* b, const rb_tensor* y);
+/* Division by a scalar, in place allowed: the Mean step after a Sum collective (src/distributed.rs:150-154,267-271). */
+RB_API int32_t rb_div_scalar(rb_ctx* ctx, const rb_tensor* x, float divisor, const rb_tensor* y);
 /* AscendRuntime::rotary / rotary_backward, runtime/mod.rs:259-268 -> rotary.rs:15-30, IR rotary_programs.rs:47-97. */
 RB_API int32_t rb_rotary(rb_ctx* ctx, const rb_tensor* x, const rb_tensor* cos, const rb_tensor* sin,
                          int32_t layout, int32_t backward, const rb_tensor* y);
@@ -218,6 +220,30 @@ RB_API int32_t rb_attention(rb_ctx* ctx, const rb_tensor* q, const rb_tensor* k,
                             float scale, int32_t causal, uint64_t query_start, uint64_t key_start,
                             const rb_tensor* cos, const rb_tensor* sin, int32_t rotary_layout, int32_t out_layout,
                             const rb_tensor* out);
+
+/* ---- collectives: NCCL over NVLink 5 / NVSwitch in place of HCCL ----------------------------------------------- */
+typedef struct rb_comm rb_comm;
+/* HcclGetRootInfo, runtime/hccl.rs:340-357: rank 0 creates the 128-byte id (ncclUniqueId) that the control plane
+ * hands to every rank (src/distributed.rs:74-110).  The NCCL library is loaded with dlopen (RUDA_NCCL_LIBRARY or
+ * libnccl.so.2), as the reference loads libhccl.so (runtime/hccl.rs:79-85). */
+RB_API int32_t rb_comm_unique_id(uint8_t* id_128_bytes);
+/* HcclCommInitRootInfo, runtime/hccl.rs:133-197: one communicator per process and device. */
+RB_API int32_t rb_comm_init(rb_ctx* ctx, const uint8_t* id_128_bytes, uint32_t rank, uint32_t world_size, rb_comm** out);
+/* Entry drop, runtime/hccl.rs:119-131: drains, destroys; aborts and leaks if the work cannot be drained. */
+RB_API int32_t rb_comm_destroy(rb_comm* comm);
+/* HcclCommunicator::rank / world_size, runtime/hccl.rs:435-443. */
+RB_API int32_t rb_comm_info(rb_comm* comm, uint32_t* rank, uint32_t* world_size, int32_t* nccl_version);
+/* HcclCommunicator::all_reduce, runtime/hccl.rs:452-460 (sum/prod/max/min over F32/F16/BF16/I32/I64).  in == out is
+ * allowed.  deferred_fence != 0 lets later compute on the context's stream run while the collective is in flight;
+ * rb_comm_fence then orders the compute stream after every collective issued so far. */
+RB_API int32_t rb_all_reduce(rb_comm* comm, const rb_tensor* in, int32_t op, const rb_tensor* out, int32_t deferred_fence);
+RB_API int32_t rb_comm_fence(rb_comm* comm);
+/* HcclCommunicator::broadcast, runtime/hccl.rs:444-451. */
+RB_API int32_t rb_broadcast(rb_comm* comm, const rb_tensor* in, uint32_t root, const rb_tensor* out);
+/* HcclCommunicator::all_gather, runtime/hccl.rs:461-466: rank-ordered concatenation along the leading axis. */
+RB_API int32_t rb_all_gather(rb_comm* comm, const rb_tensor* in, const rb_tensor* out);
+/* HcclCommunicator::reduce_scatter, runtime/hccl.rs:467-473: this rank's equal leading-axis shard of the reduction. */
+RB_API int32_t rb_reduce_scatter(rb_comm* comm, const rb_tensor* in, int32_t op, const rb_tensor* out);
 
 #ifdef __cplusplus
 }

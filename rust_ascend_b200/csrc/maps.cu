@@ -124,6 +124,12 @@ __global__ void __launch_bounds__(256) causal_mask_kernel(uint32_t* out, uint64_
     }
 }
 
+template <typename T>
+__global__ void __launch_bounds__(256) div_scalar_kernel(const T* x, T* y, uint64_t n, float divisor) {
+    uint64_t stride = (uint64_t)gridDim.x * 256;
+    for (uint64_t i = (uint64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += stride) st(y, i, __fdiv_rn(ld(x, i), divisor));
+}
+
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(256) cast_kernel(const TI* x, TO* y, uint64_t n) {
     uint64_t stride = (uint64_t)gridDim.x * 256;
@@ -304,6 +310,20 @@ int32_t rb_cast(rb_ctx* ctx, const rb_tensor* x, const rb_tensor* y) {
     RB_CAST(__half, RB_F16, bf, RB_BF16) RB_CAST(bf, RB_BF16, __half, RB_F16) RB_CAST(__half, RB_F16, __half, RB_F16)
 #undef RB_CAST
     return fail(RB_INVALID_TENSOR, "cast supports FP32, FP16 and BF16");
+}
+
+int32_t rb_div_scalar(rb_ctx* ctx, const rb_tensor* x, float divisor, const rb_tensor* y) {
+    RB_TRY(check_ctx(ctx));
+    void *px, *py;
+    RB_TRY(resolve(ctx, x, "div_scalar input", &px)); RB_TRY(resolve(ctx, y, "div_scalar output", &py));
+    if (!same_shape(x, y) || x->dtype != y->dtype) return fail(RB_INVALID_TENSOR, "div_scalar keeps shape and dtype");
+    uint64_t n = elements(x);
+    if (n == 0) return empty_call(ctx);
+    if (x->dtype == RB_F32) div_scalar_kernel<float><<<grid_for(ctx, n), 256, 0, ctx->stream>>>((const float*)px, (float*)py, n, divisor);
+    else if (x->dtype == RB_BF16) div_scalar_kernel<bf><<<grid_for(ctx, n), 256, 0, ctx->stream>>>((const bf*)px, (bf*)py, n, divisor);
+    else if (x->dtype == RB_F16) div_scalar_kernel<__half><<<grid_for(ctx, n), 256, 0, ctx->stream>>>((const __half*)px, (__half*)py, n, divisor);
+    else return fail(RB_INVALID_TENSOR, "div_scalar supports FP32, FP16 and BF16");
+    return after_launch(ctx, "div_scalar");
 }
 
 int32_t rb_embedding(rb_ctx* ctx, const rb_tensor* table, const rb_tensor* ids, const rb_tensor* out) {
