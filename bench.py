@@ -210,6 +210,7 @@ def run_ours(args):
     e2e_s = max_over_ranks(dist, (time.perf_counter() - t0) / e2e_steps)
     e2e_value = world * FLOPS_PER_STEP / e2e_s / 1e12
 
+    extra = {} if args.no_extras else extras(client, RT, pk, args, rank, world, dist)
     if rank != 0:
         return
     kernel_tflops = FLOPS_PER_STEP / (ms_per_step * 1e-3) / 1e12
@@ -232,19 +233,26 @@ def run_ours(args):
     if world == 1 and not args.no_cpu_baseline:
         import oracle as orc
         orc.build()
-        rate, _ = cpu_linear_rate(orc, 16)
+        rate, _ = cpu_linear_rate(orc, 64)
         rows = int(max(16, min(M, rate * 1e12 * 12.0 / (2.0 * N * K))))
-        rate, dt = cpu_linear_rate(orc, rows)
-        line["cpu_baseline"] = {"value": rate, "unit": "TFLOP/s", "cores": orc.threads(), "kind": "port",
-                                "sample": f"{rows} of {M} rows of the same Linear, {dt:.1f} s, oracle port (f64 accumulate, OpenMP)"}
-    line["extras"] = extras(client, RT, pk, args) if world == 1 and not args.no_extras else {}
+        reps, spent, rates = 0, 0.0, []
+        while spent < 10.0 and reps < 16:   # bounded: about 10-30 s of CPU work
+            rate, dt = cpu_linear_rate(orc, rows)
+            rates.append(rate); spent += dt; reps += 1
+        line["cpu_baseline"] = {"value": float(np.median(rates)), "unit": "TFLOP/s", "cores": orc.threads(), "kind": "port",
+                                "sample": f"{rows} of {M} rows of the same Linear, {reps} repetitions, {spent:.1f} s, oracle port (f64 accumulate, OpenMP)"}
+    line["extras"] = extra
     print(json.dumps(line))
 
 
-def extras(client, RT, pk, args):
+def extras(client, RT, pk, args, rank, world, dist):
     """Secondary kernels of the same hot path, each against its own roofline (reported, not the headline)."""
     from rust_ascend_b200 import DType
     out = {}
+    out["tp_decoder"] = decoder_extra(client, pk, rank, world, dist)
+    if world > 1:
+        return out
+    out.update(attention_extra(client, RT, pk))
     rows, width = 4096, 4096
     rng = np.random.default_rng(0)
     sets = []
@@ -276,6 +284,102 @@ def extras(client, RT, pk, args):
     return out
 
 
+def attention_extra(client, RT, pk):
+    """Causal attention at configs 3 and 4 (flops = the causal half, 2*B*H*S^2*D)."""
+    from rust_ascend_b200 import DType
+    from rust_ascend_b200.runtime import f32_to_bf16_bits
+    out = {}
+    rng = np.random.default_rng(3)
+    for name, (b, hq, hkv, s) in {"attention_causal_b4_h32_s2048_d128": (4, 32, 32, 2048),
+                                   "attention_causal_gqa_b2_h32_kv8_s4096_d128": (2, 32, 8, 4096)}.items():
+        sets = []
+        for _ in range(3):  # 3 x (Q,K,V,O) > 126 MB L2
+            mk = lambda h: client.upload(f32_to_bf16_bits(rng.standard_normal((b, h, s, 128), dtype=np.float32)))
+            sets.append((mk(hq), mk(hkv), mk(hkv), client.tensor((b, s, hq, 128), DType.BF16)))
+        run = lambda i: RT.attention(client, sets[i % 3][0], sets[i % 3][1], sets[i % 3][2], 128 ** -0.5, causal=True, bmhd_output=True, out=sets[i % 3][3])
+        for i in range(5):
+            run(i)
+        client.sync()
+        client.start_profile()
+        for i in range(30):
+            run(i)
+        ms = client.end_profile() / 30
+        tf = 2 * b * hq * s * s * 128 / (ms * 1e-3) / 1e12
+        out[name] = {"value": tf, "unit": "TFLOP/s", "us": ms * 1e3,
+                     "roofline": {"bound": "tensor", "achieved": tf, "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": tf / pk["bf16_tflops"],
+                                  "peak_kind": "burst of " + pk["source"]}}
+        for st in sets:
+            for t in st:
+                client.free(t.handle)
+    return out
+
+
+def decoder_extra(client, pk, rank, world, dist):
+    """Config 5: Llama-style stack, 8 layers, T = 8 x 2048, tensor-parallel over `world` GPUs with NCCL all-reduces."""
+    from rust_ascend_b200.decoder import LlamaConfig, TensorParallelDecoder
+    comm = None
+    if world > 1:
+        from rust_ascend_b200.distributed import NcclCommunicator, TorchControl
+        comm = NcclCommunicator.initialize(TorchControl(), client)
+    cfg = LlamaConfig()
+    chunks = 1 if world == 1 else 4
+    model = TensorParallelDecoder(client, cfg, 8, 2048, comm=comm, rank=rank, world=world, chunks=chunks)
+    tokens = np.random.default_rng(5).integers(0, cfg.vocab, size=(8, 2048)).astype(np.int32)
+    model.forward(tokens)
+    for _ in range(2):
+        model.forward()
+    client.sync()
+    if dist is not None:
+        dist.barrier()
+    steps = 8
+    client.start_profile()
+    for _ in range(steps):
+        model.forward()
+    ms = max_over_ranks(dist, client.end_profile() / steps)
+    tf = cfg.flops(8 * 2048, 2048) / (ms * 1e-3) / 1e12
+    return {"value": tf, "unit": "TFLOP/s (whole job)", "ms_per_forward": ms, "n_gpus": world, "row_chunks": chunks,
+            "launches_per_forward": model.launches_per_forward, "all_reduces_per_forward": 16 if world > 1 else 0,
+            "config": "8 layers, hidden 4096, 32q/8kv heads, ffn 14336, vocab 32000, batch 8 x seq 2048, BF16",
+            "frac_of_sustained_peak_per_gpu": tf / world / pk["bf16_tflops_sustained"]}
+
+
+def run_single_kernel(args):
+    """`--kernel NAME`: W + K launches of one kernel of the path on its bench workload and a one-line JSON with the
+    CUDA-event time per launch.  This is the command the ncu captures under profiles/ run."""
+    from rust_ascend_b200 import B200Runtime as RT
+    from rust_ascend_b200 import DType, RuntimeOptions, Transpose
+    from rust_ascend_b200.runtime import f32_to_bf16_bits
+    import ctypes as C
+    from rust_ascend_b200.runtime import _check, _ref
+    client = RT.client(RT.initialize_exclusive(RuntimeOptions(device=0)))
+    rng = np.random.default_rng(0)
+    bf = lambda *shape, scale=1.0: client.upload(f32_to_bf16_bits(rng.standard_normal(shape, dtype=np.float32) * np.float32(scale)))
+    if args.kernel == "gemm":
+        sets = [(bf(M, K), bf(N, K, scale=0.02), client.upload((rng.standard_normal(N) * 0.02).astype(np.float32)), client.tensor((M, N), DType.BF16)) for _ in range(SETS)]
+        run = lambda i: RT.gemm_into(client, sets[i % SETS][0], sets[i % SETS][1], Transpose.No, Transpose.Yes, sets[i % SETS][3], bias=sets[i % SETS][2])
+        work, unit = FLOPS_PER_STEP, "TFLOP/s"
+    elif args.kernel == "attention":
+        b, h, s = 4, 32, 2048
+        sets = [(bf(b, h, s, 128), bf(b, h, s, 128), bf(b, h, s, 128), client.tensor((b, s, h, 128), DType.BF16)) for _ in range(3)]
+        run = lambda i: RT.attention(client, sets[i % 3][0], sets[i % 3][1], sets[i % 3][2], 128 ** -0.5, causal=True, bmhd_output=True, out=sets[i % 3][3])
+        work, unit = 2 * b * h * s * s * 128, "TFLOP/s"
+    else:
+        rows = width = 4096
+        sets = [(client.upload(rng.standard_normal((rows, width), dtype=np.float32)), client.upload(rng.uniform(0.5, 1.5, width).astype(np.float32)),
+                 client.tensor((rows, width), DType.F32), client.tensor((rows,), DType.F32)) for _ in range(6)]
+        run = lambda i: _check(client._lib.rb_rms_norm(client._ctx, _ref(sets[i % 6][0]), _ref(sets[i % 6][1]), C.c_double(1e-6), _ref(sets[i % 6][2]), _ref(sets[i % 6][3])))
+        work, unit = 2 * rows * width * 4 + width * 4 + rows * 4, "GB/s"
+    for i in range(args.warmup):
+        run(i)
+    client.sync()
+    client.start_profile()
+    for i in range(args.steps):
+        run(i)
+    ms = client.end_profile() / args.steps
+    rate = work / (ms * 1e-3) / (1e12 if unit == "TFLOP/s" else 1e9)
+    print(json.dumps({"kernel": args.kernel, "us_per_launch": ms * 1e3, "value": rate, "unit": unit, "steps": args.steps, "warmup": args.warmup}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -284,9 +388,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true")
+    ap.add_argument("--kernel", default=None, choices=["gemm", "attention", "rms_norm"], help="time one kernel alone (profiling helper)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    if args.impl == "reference":
+    if args.kernel:
+        run_single_kernel(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
