@@ -11,6 +11,7 @@
 //   warp 8           TMA producer: Q once, then K and V tiles of 128 keys through two 2-stage rings
 //   warp 9           issues tcgen05.mma:  S_t = Q_t K^T (operands in shared memory),  O_t += P_t V (P from TMEM,
 //                    V consumed as stored, Dv-contiguous)
+//   warps 10-11      idle; they only donate their registers to the softmax warps (setmaxnreg)
 // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_t aliases the first 64 columns of S_t.
 // The running maximum is only refreshed when it grows by more than 2^8 (the accumulator and the sum are then
 // rescaled), so most key blocks need no pass over O.
@@ -26,7 +27,7 @@ constexpr int D = 128;            // head dim (Q/K) and value dim
 constexpr int TQ = 128;           // query rows per tile
 constexpr int TK = 128;           // keys per block
 constexpr int KV_STAGES = 2;
-constexpr int THREADS = 320;
+constexpr int THREADS = 384;   // warps 0-7 softmax, 8 TMA, 9 MMA, 10-11 only donate registers
 constexpr int TILE_BYTES = 128 * D * 2;       // 32 KiB: one [128 x 128] BF16 tile = two 64-wide swizzle slabs
 constexpr int SLAB_BYTES = 128 * 64 * 2;      // 16 KiB
 constexpr int SMEM_BYTES = 2 * TILE_BYTES + 2 * KV_STAGES * TILE_BYTES + 1024 + 256;
@@ -54,6 +55,92 @@ __device__ __forceinline__ uint32_t blocks_for(const AttnParams& p, uint32_t row
     if (last_q < 0) return 0;
     int64_t need = last_q / TK + 1;
     return need < (int64_t)all ? (uint32_t)need : all;
+}
+
+
+// Packed FP32 pairs (fma.rn.f32x2 / add.rn.f32x2) and the three-input max halve the issue slots of the softmax.
+__device__ __forceinline__ uint64_t pack2(uint32_t lo, uint32_t hi) { uint64_t r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi)); return r; }
+__device__ __forceinline__ uint64_t pack2f(float lo, float hi) { uint64_t r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi)); return r; }
+__device__ __forceinline__ void unpack2f(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) { uint64_t d; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c)); return d; }
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) { uint64_t d; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
+__device__ __forceinline__ float max3(float a, float b, float c) { float d; asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c)); return d; }
+
+// One key block of the online softmax for one query row (= one thread, one TMEM lane).  The 128 scores are read
+// from TMEM once (four loads in flight, one wait) and stay in registers; P = exp2(s*scale*log2e - m) goes back to
+// TMEM as BF16 pairs over the scores already consumed.  MASKED is false for blocks entirely below the causal
+// diagonal and inside the key range, so their inner loops carry no predicates.
+template <bool MASKED>
+__device__ __forceinline__ void softmax_block(uint32_t tmem_s, uint32_t tmem_o, float sc, int32_t visible, bool first, float& m_used, float& l) {
+    uint32_t r0[32], r1[32], r2[32], r3[32];
+    tmem_ld_32x32(tmem_s, r0); tmem_ld_32x32(tmem_s + 32, r1); tmem_ld_32x32(tmem_s + 64, r2); tmem_ld_32x32(tmem_s + 96, r3);
+    tmem_wait_ld();
+    float mx;
+    if (MASKED) {
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#define RB_ROWMAX(R, BASE) _Pragma("unroll") for (int i = 0; i < 32; ++i) { if (BASE + i < visible) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(R[i])); }
+        RB_ROWMAX(r0, 0) RB_ROWMAX(r1, 32) RB_ROWMAX(r2, 64) RB_ROWMAX(r3, 96)
+#undef RB_ROWMAX
+        mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+    } else {
+        // four independent chains of three-input maxima: 64 instructions, dependent depth 16
+        float m4[4] = {__uint_as_float(r0[0]), __uint_as_float(r1[0]), __uint_as_float(r2[0]), __uint_as_float(r3[0])};
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+            m4[0] = max3(m4[0], __uint_as_float(r0[i]), __uint_as_float(r0[i + 1]));
+            m4[1] = max3(m4[1], __uint_as_float(r1[i]), __uint_as_float(r1[i + 1]));
+            m4[2] = max3(m4[2], __uint_as_float(r2[i]), __uint_as_float(r2[i + 1]));
+            m4[3] = max3(m4[3], __uint_as_float(r3[i]), __uint_as_float(r3[i + 1]));
+        }
+        mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+    }
+    float m_blk = mx * sc;                      // -inf when every key of the block is masked for this row
+    if (!(m_blk > -INFINITY)) m_blk = -INFINITY;
+    // Refresh the reference maximum only when it grew by more than 8 (a factor 256 in P).
+    const bool grow = first ? true : (m_blk > m_used + 8.f);
+    if (__any_sync(0xffffffffu, grow)) {
+        const float m_new = first ? (m_blk > -INFINITY ? m_blk : 0.f) : (grow ? m_blk : m_used);
+        if (!first) {
+            const float alpha = ex2(m_used - m_new);   // 1 for lanes that keep their maximum
+            l *= alpha;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t o[32];
+                tmem_ld_32x32(tmem_o + c * 32, o);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                tmem_st_32x32(tmem_o + c * 32, o);
+            }
+            tmem_wait_st();
+        }
+        m_used = m_new;
+    }
+    const float neg_m = -m_used;
+    if (MASKED) {
+        float sum0 = 0.f, sum1 = 0.f;
+#define RB_EXP(R, BASE) { uint32_t packed[16]; _Pragma("unroll") for (int i = 0; i < 32; i += 2) { \
+            float p0 = ex2(__fmaf_rn(__uint_as_float(R[i]), sc, neg_m)), p1 = ex2(__fmaf_rn(__uint_as_float(R[i + 1]), sc, neg_m)); \
+            if (BASE + i >= visible) p0 = 0.f; if (BASE + i + 1 >= visible) p1 = 0.f; \
+            sum0 += p0; sum1 += p1; packed[i >> 1] = pack_bf16(p0, p1); } \
+            tmem_st_32x16(tmem_s + BASE / 2, packed); }
+        RB_EXP(r0, 0) RB_EXP(r1, 32) RB_EXP(r2, 64) RB_EXP(r3, 96)
+#undef RB_EXP
+        l += sum0 + sum1;
+    } else {
+        const uint64_t sc2 = pack2f(sc, sc), nm2 = pack2f(neg_m, neg_m);
+        uint64_t acc_a = pack2f(0.f, 0.f), acc_b = acc_a;
+#define RB_EXP2(R, BASE) { uint32_t packed[16]; _Pragma("unroll") for (int i = 0; i < 32; i += 2) { \
+            float x0, x1; unpack2f(fma2(pack2(R[i], R[i + 1]), sc2, nm2), x0, x1); \
+            const float p0 = ex2(x0), p1 = ex2(x1); \
+            if (i & 2) acc_b = add2(acc_b, pack2f(p0, p1)); else acc_a = add2(acc_a, pack2f(p0, p1)); \
+            packed[i >> 1] = pack_bf16(p0, p1); } \
+            tmem_st_32x16(tmem_s + BASE / 2, packed); }
+        RB_EXP2(r0, 0) RB_EXP2(r1, 32) RB_EXP2(r2, 64) RB_EXP2(r3, 96)
+#undef RB_EXP2
+        float s0, s1; unpack2f(add2(acc_a, acc_b), s0, s1);
+        l += s0 + s1;
+    }
 }
 
 __global__ void __launch_bounds__(THREADS, 1)
@@ -98,7 +185,10 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    // Register budget: the two softmax warpgroups keep a whole score row in registers, the third warpgroup
+    // (TMA, MMA and two idle warps) needs almost none.  256*224 + 128*56 = 64512 registers.
     if (warp == 8) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
         // ---------------- TMA producer ----------------
         if (elect_one()) {
             bool ok = true;
@@ -128,6 +218,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             }
         }
     } else if (warp == 9) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
         // ---------------- MMA issuer ----------------
         if (elect_one()) {
             const uint32_t idesc_qk = make_idesc_bf16(TQ, TK, 0, 0);   // A = Q (K-major), B = K tile (K-major)
@@ -178,7 +269,10 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 }
             }
         }
+    } else if (warp >= 10) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
         // ---------------- softmax + epilogue: warps 0-3 own tile 0, warps 4-7 own tile 1 ----------------
         const uint32_t t = warp >> 2, quarter = warp & 3;
         const uint32_t row_in_tile = quarter * 32 + lane;
@@ -204,63 +298,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 const int64_t v64 = limit - (int64_t)k0 + 1;
                 visible = (int32_t)(v64 > TK ? TK : (v64 < 0 ? 0 : v64));
             }
-            // Pass 1 over the scores in TMEM: row maximum (the scale is positive on this path).
-            const float sc = p.scale_log2;
-            float mx = -INFINITY;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                tmem_ld_32x32(tmem_s + c * 32, r);
-                tmem_wait_ld();
-                if (partial || diagonal) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) if (c * 32 + i < visible) mx = fmaxf(mx, __uint_as_float(r[i]));
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
-                }
-            }
-            float m_blk = mx * sc;                      // -inf when every key of the block is masked for this row
-            if (!(m_blk > -INFINITY)) m_blk = -INFINITY;
-            // Refresh the reference maximum only when it grew by more than 8 (a factor 256 in P).
-            const bool first = j == 0;
-            const bool grow = first ? true : (m_blk > m_used + 8.f);
-            if (__any_sync(0xffffffffu, grow)) {
-                float m_new = first ? (m_blk > -INFINITY ? m_blk : 0.f) : (grow ? m_blk : m_used);
-                if (!first) {
-                    const float alpha = ex2(m_used - m_new);   // 1 for lanes that keep their maximum
-                    l *= alpha;
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        uint32_t r[32];
-                        tmem_ld_32x32(tmem_o + c * 32, r);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                        tmem_st_32x32(tmem_o + c * 32, r);
-                    }
-                    tmem_wait_st();
-                }
-                m_used = m_new;
-            }
-            // Pass 2: P = exp2(s*scale*log2e - m) as BF16 pairs, written over the scores already consumed
-            // (words 16c..16c+15 land in columns that chunk c or an earlier chunk has read).
-            float sum = 0.f;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t r[32], packed[16];
-                tmem_ld_32x32(tmem_s + c * 32, r);
-                tmem_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float p0 = ex2(__fmaf_rn(__uint_as_float(r[i]), sc, -m_used)), p1 = ex2(__fmaf_rn(__uint_as_float(r[i + 1]), sc, -m_used));
-                    if (partial || diagonal) { if (c * 32 + i >= visible) p0 = 0.f; if (c * 32 + i + 1 >= visible) p1 = 0.f; }
-                    sum += p0 + p1;
-                    packed[i >> 1] = pack_bf16(p0, p1);
-                }
-                tmem_st_32x16(tmem_s + c * 16, packed);
-            }
-            l += sum;
+            if (partial || diagonal) softmax_block<true>(tmem_s, tmem_o, p.scale_log2, visible, j == 0, m_used, l);
+            else softmax_block<false>(tmem_s, tmem_o, p.scale_log2, visible, j == 0, m_used, l);
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(&p_full[t]);

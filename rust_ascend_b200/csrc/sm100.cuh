@@ -36,6 +36,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
                  : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
+// Non-blocking probe of a phase (no hardware suspend): for threads that serve several barriers by polling.
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
 // Every wait is bounded: after `WAIT_LIMIT` polls the waiter raises the CTA's abort word and returns
 // false; every role polls that word and leaves its loop, so a lost signal ends the kernel with an error
 // status instead of hanging the GPU.
