@@ -133,6 +133,17 @@ RB_API int32_t rb_host_free(rb_ctx* ctx, void* host);
  * stream.  rb_profile_end synchronises and returns the elapsed device milliseconds. */
 RB_API int32_t rb_profile_begin(rb_ctx* ctx);
 RB_API int32_t rb_profile_end(rb_ctx* ctx, float* milliseconds);
+/* Caps the number of SMs the persistent GEMM occupies (0 = all), leaving the rest to a collective that runs beside
+ * it.  No counterpart in the reference, whose collectives and kernels never overlap (runtime/hccl.rs:290-305). */
+RB_API int32_t rb_set_sm_limit(rb_ctx* ctx, int32_t sm_limit);
+/* Records everything enqueued on the context between begin and end (kernels, copies, collectives with their
+ * cross-stream fences) into a CUDA graph, and replays it with one launch.  The reference launches and synchronises
+ * kernel by kernel (worker.rs:92-103); replay removes the per-launch host cost of a fixed step.  No entry point that
+ * synchronises or allocates (rb_read, rb_sync, rb_alloc, first use of a kernel) may be called while recording. */
+RB_API int32_t rb_graph_begin(rb_ctx* ctx);
+RB_API int32_t rb_graph_end(rb_ctx* ctx, uint64_t* graph);
+RB_API int32_t rb_graph_launch(rb_ctx* ctx, uint64_t graph);
+RB_API int32_t rb_graph_destroy(rb_ctx* ctx, uint64_t graph);
 /* The context's CUDA stream as a cudaStream_t, for callers that share it with other libraries. */
 RB_API int32_t rb_stream(rb_ctx* ctx, void** stream);
 
@@ -141,6 +152,11 @@ RB_API int32_t rb_stream(rb_ctx* ctx, void** stream);
  * y = (x * rsqrt(mean(x^2) + eps)) * w over the last axis; rstd [rows] FP32 may be NULL. */
 RB_API int32_t rb_rms_norm(rb_ctx* ctx, const rb_tensor* x, const rb_tensor* weight, double epsilon,
                            const rb_tensor* y, const rb_tensor* rstd);
+/* Residual update fused into the norm that follows it: x_out = x + delta (rounded to x's storage type; x_out may be
+ * x itself), y = rms_norm(x_out).  Equals bias_add's residual sum (affine_programs.rs:31-36, MapProgram::Add
+ * programs.rs:34) followed by AscendRuntime::rms_norm (runtime/mod.rs:405-408) with one pass over memory less. */
+RB_API int32_t rb_add_rms_norm(rb_ctx* ctx, const rb_tensor* x, const rb_tensor* delta, const rb_tensor* weight, double epsilon,
+                               const rb_tensor* x_out, const rb_tensor* y);
 /* Runtime::layer_norm, runtime/mod.rs:442-448 -> normalization.rs:116-132, IR row_programs.rs:164-177.
  * bias may be NULL (zeros); mean / rstd [rows] FP32 may be NULL. */
 RB_API int32_t rb_layer_norm(rb_ctx* ctx, const rb_tensor* x, const rb_tensor* weight, const rb_tensor* bias,
@@ -238,6 +254,11 @@ RB_API int32_t rb_comm_info(rb_comm* comm, uint32_t* rank, uint32_t* world_size,
  * rb_comm_fence then orders the compute stream after every collective issued so far. */
 RB_API int32_t rb_all_reduce(rb_comm* comm, const rb_tensor* in, int32_t op, const rb_tensor* out, int32_t deferred_fence);
 RB_API int32_t rb_comm_fence(rb_comm* comm);
+/* Finer fences for deferred collectives: rb_comm_ticket returns the sequence number of the latest collective issued
+ * on this communicator, rb_comm_wait_ticket orders the compute stream after that one collective only (the reference
+ * synchronises after every collective, runtime/hccl.rs:290-305; these calls let independent row blocks overlap). */
+RB_API int32_t rb_comm_ticket(rb_comm* comm, uint64_t* ticket);
+RB_API int32_t rb_comm_wait_ticket(rb_comm* comm, uint64_t ticket);
 /* HcclCommunicator::broadcast, runtime/hccl.rs:444-451. */
 RB_API int32_t rb_broadcast(rb_comm* comm, const rb_tensor* in, uint32_t root, const rb_tensor* out);
 /* HcclCommunicator::all_gather, runtime/hccl.rs:461-466: rank-ordered concatenation along the leading axis. */

@@ -20,6 +20,7 @@ struct NcclApi {
     void* library = nullptr;
     ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
     ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommInitRankConfig)(ncclComm_t*, int, ncclUniqueId, int, ncclConfig_t*) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
     ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t*) = nullptr;
@@ -47,6 +48,7 @@ int32_t load_api() {
     RB_SYM(Broadcast, "ncclBroadcast") RB_SYM(AllGather, "ncclAllGather") RB_SYM(ReduceScatter, "ncclReduceScatter")
     RB_SYM(GetErrorString, "ncclGetErrorString") RB_SYM(GetVersion, "ncclGetVersion")
 #undef RB_SYM
+    *reinterpret_cast<void**>(&g_api.CommInitRankConfig) = dlsym(lib, "ncclCommInitRankConfig");  // optional
     g_api.library = lib;
     return RB_OK;
 }
@@ -85,6 +87,9 @@ struct rb_comm {
     uint32_t rank = 0, world = 1;
     cudaStream_t stream = nullptr;
     cudaEvent_t before = nullptr, after = nullptr;
+    static constexpr int TICKETS = 32;
+    cudaEvent_t done[TICKETS] = {};   // completion event of collective number n lives in slot n % TICKETS
+    uint64_t issued = 0;              // collectives issued so far; the ticket of the latest one
     bool poisoned = false;
 };
 
@@ -109,6 +114,8 @@ int32_t leave(rb_comm* c, const char* operation, ncclResult_t r, int32_t deferre
     c->ctx->stats.launches++;
     if (r != ncclSuccess) { c->poisoned = true; return nccl_fail(operation, r); }
     RB_CUDA(c->ctx, "cudaEventRecord", cudaEventRecord(c->after, c->stream));
+    c->issued++;
+    RB_CUDA(c->ctx, "cudaEventRecord", cudaEventRecord(c->done[c->issued % rb_comm::TICKETS], c->stream));
     if (!deferred) RB_CUDA(c->ctx, "cudaStreamWaitEvent", cudaStreamWaitEvent(c->ctx->stream, c->after, 0));
     if (c->ctx->synchronous) {  // the reference synchronises after every collective (hccl.rs:290-305)
         c->ctx->stats.synchronizations++;
@@ -142,11 +149,26 @@ int32_t rb_comm_init(rb_ctx* ctx, const uint8_t* id_128_bytes, uint32_t rank, ui
     ncclUniqueId id; memcpy(&id, id_128_bytes, 128);
     rb_comm* c = new rb_comm();
     c->ctx = ctx; c->rank = rank; c->world = world_size;
-    ncclResult_t r = g_api.CommInitRank(&c->comm, (int)world_size, id, (int)rank);
+    // RUDA_NCCL_MAX_CTAS bounds the SMs a collective may occupy, so that it can run beside a GEMM that leaves
+    // that many SMs free (rb_set_sm_limit).
+    const char* max_ctas = getenv("RUDA_NCCL_MAX_CTAS");
+    ncclResult_t r;
+    if (max_ctas && atoi(max_ctas) > 0 && g_api.CommInitRankConfig) {
+        ncclConfig_t config = NCCL_CONFIG_INITIALIZER;
+        config.maxCTAs = atoi(max_ctas);
+        config.minCTAs = 1;
+        r = g_api.CommInitRankConfig(&c->comm, (int)world_size, id, (int)rank, &config);
+    } else {
+        r = g_api.CommInitRank(&c->comm, (int)world_size, id, (int)rank);
+    }
     if (r != ncclSuccess) { delete c; return nccl_fail("ncclCommInitRank", r); }
-    cudaError_t e = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
+    // Highest priority: when an SM frees up, a waiting collective block is placed before a compute block.
+    int least = 0, greatest = 0;
+    cudaDeviceGetStreamPriorityRange(&least, &greatest);
+    cudaError_t e = cudaStreamCreateWithPriority(&c->stream, cudaStreamNonBlocking, greatest);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->before, cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->after, cudaEventDisableTiming);
+    for (int i = 0; e == cudaSuccess && i < rb_comm::TICKETS; ++i) e = cudaEventCreateWithFlags(&c->done[i], cudaEventDisableTiming);
     if (e != cudaSuccess) { g_api.CommAbort(c->comm); delete c; return fail(RB_STATUS, "communicator stream/event creation failed with CUDA status %d", (int)e); }
     *out = c;
     return RB_OK;
@@ -157,9 +179,18 @@ int32_t rb_comm_destroy(rb_comm* c) {
     // Drain first; if the work cannot be drained the communicator is aborted and its objects are leaked rather than
     // destroyed under running kernels (hccl.rs:119-131).
     bool drained = cudaStreamSynchronize(c->stream) == cudaSuccess && !c->poisoned;
+    // Recorded graphs may hold collectives of this communicator, and NCCL does not finish destroying a communicator
+    // while such a graph exists: drop every graph of the context first.
+    {
+        std::lock_guard<std::mutex> lk(c->ctx->lock);
+        for (auto& kv : c->ctx->graphs) cudaGraphExecDestroy(kv.second);
+        c->ctx->graphs.clear();
+    }
     if (drained) {
         g_api.CommDestroy(c->comm);
-        cudaEventDestroy(c->before); cudaEventDestroy(c->after); cudaStreamDestroy(c->stream);
+        cudaEventDestroy(c->before); cudaEventDestroy(c->after);
+        for (int i = 0; i < rb_comm::TICKETS; ++i) if (c->done[i]) cudaEventDestroy(c->done[i]);
+        cudaStreamDestroy(c->stream);
     } else if (c->comm) {
         g_api.CommAbort(c->comm);
     }
@@ -181,6 +212,22 @@ int32_t rb_comm_fence(rb_comm* c) {
     ncclResult_t async = ncclSuccess;
     ncclResult_t r = g_api.CommGetAsyncError(c->comm, &async);
     if (r != ncclSuccess || async != ncclSuccess) { c->poisoned = true; return nccl_fail("asynchronous NCCL error", r != ncclSuccess ? r : async); }
+    return RB_OK;
+}
+
+int32_t rb_comm_ticket(rb_comm* c, uint64_t* ticket) {
+    if (!c || !ticket) return fail(RB_NULL_HANDLE, "null pointer");
+    *ticket = c->issued;
+    return RB_OK;
+}
+
+int32_t rb_comm_wait_ticket(rb_comm* c, uint64_t ticket) {
+    RB_TRY(check_comm(c));
+    if (ticket == 0) return RB_OK;
+    if (ticket > c->issued) return fail(RB_INVALID_TENSOR, "ticket %llu has not been issued", (unsigned long long)ticket);
+    // Events are recycled after TICKETS further collectives; an older ticket is already covered by a newer one in
+    // the same slot because collectives of one communicator complete in issue order.
+    RB_CUDA(c->ctx, "cudaStreamWaitEvent", cudaStreamWaitEvent(c->ctx->stream, c->done[ticket % rb_comm::TICKETS], 0));
     return RB_OK;
 }
 

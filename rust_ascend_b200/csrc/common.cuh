@@ -41,6 +41,10 @@ struct rb_ctx {
     bool poisoned = false;             // set after a failed launch or synchronisation
     rb_stats stats{};
     int sm_count = 0;
+    int sm_limit = 0;                  // 0: persistent kernels use every SM
+    std::unordered_map<uint64_t, cudaGraphExec_t> graphs;
+    uint64_t next_graph = 1;
+    bool capturing = false;
     size_t smem_optin = 0;
     void* workspace = nullptr;         // lazily grown scratch owned by the context
     uint64_t workspace_bytes = 0;

@@ -257,7 +257,8 @@ int32_t launch(rb_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const 
         configured = true;
     }
     uint32_t tiles = p.tiles_m * p.tiles_n * p.batches;
-    uint32_t grid = tiles < (uint32_t)ctx->sm_count ? tiles : (uint32_t)ctx->sm_count;
+    const uint32_t sms = ctx->sm_limit > 0 ? (uint32_t)ctx->sm_limit : (uint32_t)ctx->sm_count;
+    uint32_t grid = tiles < sms ? tiles : sms;
     gemm_bf16_kernel<BN><<<grid, THREADS, C::SMEM_BYTES, ctx->stream>>>(ma, mb, mb2, p);
     return rb::after_launch(ctx, "gemm");
 }

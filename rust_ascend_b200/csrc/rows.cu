@@ -61,6 +61,8 @@ __device__ __forceinline__ float row_reduce(float v, float* smem /* [rows_per_bl
 struct RowArgs {
     const void* x; const void* w; const void* b; void* y; float* stat0; float* stat1;
     uint64_t rows; uint32_t width; float eps;
+    const void* delta = nullptr;   // fused residual: x <- x + delta (stored to x_out in x's type) before the norm
+    void* x_out = nullptr;
 };
 
 constexpr int MAXV = 4;  // 16-byte vectors per thread on the register-resident path
@@ -87,6 +89,14 @@ row_kernel(RowArgs a) {
             have[i] = live && c < width;
             if (have[i]) load4(xr + c, v[i], true);
             else { v[i][0] = v[i][1] = v[i][2] = v[i][3] = 0.f; }
+            if (OP == OP_RMS && a.delta != nullptr && have[i]) {
+                // residual stream update fused into the norm: the sum is rounded to the storage type first, so the
+                // normalised value is computed from exactly what a separate add kernel would have stored
+                float d[4]; load4(static_cast<const TIn*>(a.delta) + row * width + c, d, true);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) v[i][j] = to_f32(from_f32<TIn>(__fadd_rn(v[i][j], d[j])));
+                store4(static_cast<TIn*>(a.x_out) + row * width + c, v[i]);
+            }
         }
         if (OP == OP_RMS) {
             float acc = 0.f;
@@ -309,6 +319,30 @@ int32_t rb_rms_norm(rb_ctx* ctx, const rb_tensor* x, const rb_tensor* weight, do
     RowArgs a{px, pw, nullptr, py, (float*)ps, nullptr, rows, (uint32_t)width, eps};
     bool aligned = vec_aligned(px, width, dtype_size(x->dtype)) && vec_aligned(py, width, dtype_size(y->dtype)) && vec_aligned(pw, width, dtype_size(weight->dtype));
     return dispatch<OP_RMS>(ctx, a, x->dtype, y->dtype, weight->dtype, aligned, "RMSNorm");
+}
+
+int32_t rb_add_rms_norm(rb_ctx* ctx, const rb_tensor* x, const rb_tensor* delta, const rb_tensor* weight, double epsilon,
+                        const rb_tensor* x_out, const rb_tensor* y) {
+    RB_TRY(check_ctx(ctx));
+    void *px, *pd, *pw, *pxo, *py; float eps;
+    RB_TRY(resolve(ctx, x, "add+RMSNorm input", &px)); RB_TRY(resolve(ctx, delta, "add+RMSNorm delta", &pd));
+    RB_TRY(resolve(ctx, weight, "add+RMSNorm weight", &pw)); RB_TRY(resolve(ctx, x_out, "add+RMSNorm sum output", &pxo));
+    RB_TRY(resolve(ctx, y, "add+RMSNorm output", &py)); RB_TRY(epsilon_f32(epsilon, "RMSNorm", &eps));
+    uint64_t rows, width; rows_width(x, &rows, &width);
+    if (width == 0 || width % 4 != 0 || width > 1024 * MAXV * 4) return fail(RB_INVALID_TENSOR, "add+RMSNorm needs a last dimension that is a multiple of 4 within 16384");
+    if (!same_shape(x, delta) || !same_shape(x, x_out) || !same_shape(x, y) || elements(weight) != width || delta->dtype != x->dtype || x_out->dtype != x->dtype)
+        return fail(RB_INVALID_TENSOR, "add+RMSNorm buffer shape, stride, dtype or byte length mismatch");
+    const uint64_t bytes = rows * width * dtype_size(x->dtype);
+    // x_out may be x itself (the residual stream is updated in place); every other pair must be disjoint
+    if (pxo != px) RB_TRY(no_overlap(pxo, bytes, px, bytes, "add+RMSNorm"));
+    RB_TRY(no_overlap(pxo, bytes, pd, bytes, "add+RMSNorm")); RB_TRY(no_overlap(py, rows * width * dtype_size(y->dtype), px, bytes, "add+RMSNorm"));
+    RB_TRY(no_overlap(py, rows * width * dtype_size(y->dtype), pd, bytes, "add+RMSNorm"));
+    if (rows == 0) return empty_call(ctx);
+    bool aligned = vec_aligned(px, width, dtype_size(x->dtype)) && vec_aligned(py, width, dtype_size(y->dtype)) && vec_aligned(pw, width, dtype_size(weight->dtype));
+    if (!aligned) return fail(RB_INVALID_TENSOR, "add+RMSNorm needs 16-byte aligned rows");
+    RowArgs a{px, pw, nullptr, py, nullptr, nullptr, rows, (uint32_t)width, eps};
+    a.delta = pd; a.x_out = pxo;
+    return dispatch<OP_RMS>(ctx, a, x->dtype, y->dtype, weight->dtype, true, "add+RMSNorm");
 }
 
 int32_t rb_layer_norm(rb_ctx* ctx, const rb_tensor* x, const rb_tensor* weight, const rb_tensor* bias, double epsilon,

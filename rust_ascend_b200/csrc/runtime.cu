@@ -356,6 +356,63 @@ int32_t rb_profile_end(rb_ctx* ctx, float* milliseconds) {
     return raise_sticky(ctx);
 }
 
+int32_t rb_set_sm_limit(rb_ctx* ctx, int32_t sm_limit) {
+    if (!ctx) return fail(RB_NULL_HANDLE, "null runtime context");
+    if (sm_limit < 0 || sm_limit > ctx->sm_count) return fail(RB_INVALID_TENSOR, "SM limit must be within 0..%d", ctx->sm_count);
+    ctx->sm_limit = sm_limit;
+    return RB_OK;
+}
+
+int32_t rb_graph_begin(rb_ctx* ctx) {
+    RB_TRY(check_ctx(ctx));
+    if (ctx->capturing) return fail(RB_INVALID_TENSOR, "a graph is already being recorded");
+    if (ctx->synchronous) return fail(RB_INVALID_TENSOR, "graphs cannot be recorded in synchronous mode");
+    RB_CUDA(ctx, "cudaStreamBeginCapture", cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeRelaxed));
+    ctx->capturing = true;
+    return RB_OK;
+}
+
+int32_t rb_graph_end(rb_ctx* ctx, uint64_t* graph) {
+    if (!ctx || !graph) return fail(RB_NULL_HANDLE, "null pointer");
+    if (!ctx->capturing) return fail(RB_INVALID_TENSOR, "no graph is being recorded");
+    ctx->capturing = false;
+    cudaGraph_t g = nullptr;
+    cudaError_t e = cudaStreamEndCapture(ctx->stream, &g);
+    if (e != cudaSuccess || !g) return fail(RB_STATUS, "cudaStreamEndCapture failed with CUDA status %d (%s)", (int)e, cudaGetErrorString(e));
+    cudaGraphExec_t exec = nullptr;
+    e = cudaGraphInstantiate(&exec, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) return fail(RB_STATUS, "cudaGraphInstantiate failed with CUDA status %d (%s)", (int)e, cudaGetErrorString(e));
+    std::lock_guard<std::mutex> lk(ctx->lock);
+    *graph = ctx->next_graph++;
+    ctx->graphs[*graph] = exec;
+    return RB_OK;
+}
+
+int32_t rb_graph_launch(rb_ctx* ctx, uint64_t graph) {
+    RB_TRY(check_ctx(ctx));
+    cudaGraphExec_t exec;
+    {
+        std::lock_guard<std::mutex> lk(ctx->lock);
+        auto it = ctx->graphs.find(graph);
+        if (it == ctx->graphs.end()) return fail(RB_NULL_HANDLE, "unknown graph %llu", (unsigned long long)graph);
+        exec = it->second;
+    }
+    RB_CUDA(ctx, "cudaGraphLaunch", cudaGraphLaunch(exec, ctx->stream));
+    ctx->stats.launches++;
+    return RB_OK;
+}
+
+int32_t rb_graph_destroy(rb_ctx* ctx, uint64_t graph) {
+    if (!ctx) return fail(RB_NULL_HANDLE, "null runtime context");
+    std::lock_guard<std::mutex> lk(ctx->lock);
+    auto it = ctx->graphs.find(graph);
+    if (it == ctx->graphs.end()) return fail(RB_NULL_HANDLE, "unknown graph %llu", (unsigned long long)graph);
+    cudaGraphExecDestroy(it->second);
+    ctx->graphs.erase(it);
+    return RB_OK;
+}
+
 int32_t rb_stream(rb_ctx* ctx, void** stream) {
     if (!ctx || !stream) return fail(RB_NULL_HANDLE, "null pointer");
     *stream = (void*)ctx->stream;

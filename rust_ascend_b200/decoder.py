@@ -17,6 +17,7 @@ overlaps the GEMM of chunk i+1 (deferred fences on the communicator's own stream
 """
 from __future__ import annotations
 
+import ctypes as C
 from dataclasses import dataclass
 
 import numpy as np
@@ -98,8 +99,15 @@ class WeightSource:
 
 
 class TensorParallelDecoder:
+    """Builds the weights, the activation buffers and a flat launch plan once; `forward` replays the plan (or the CUDA
+    graph recorded from it).
+
+    micro_batches > 1 splits the batch into groups of sequences that walk through the layers in lock step: while one
+    group computes, the all-reduce of the other group's row-parallel projection is in flight on the communicator's
+    stream.  `sm_reserve` SMs are then kept free of the persistent GEMM so that the collective can run beside it."""
+
     def __init__(self, client: ComputeClient, cfg: LlamaConfig, batch: int, seq: int, comm=None, rank: int = 0, world: int = 1,
-                 seed: int = 0, exact_weights: bool = False, chunks: int = 1):
+                 seed: int = 0, exact_weights: bool = False, micro_batches: int = 1, sm_reserve: int = 0, use_graph: bool = False):
         if world > 1 and comm is None:
             raise InvalidTensor("a communicator is required for tensor parallelism")
         if cfg.head_dim != 128:
@@ -108,10 +116,11 @@ class TensorParallelDecoder:
         self.batch, self.seq, self.tokens = batch, seq, batch * seq
         if self.tokens % 16 or seq % 32:
             raise InvalidTensor("batch*seq must be a multiple of 16 and seq a multiple of 32")
-        self.chunks = chunks if world > 1 else 1
-        if self.tokens % (self.chunks * 128):
-            raise InvalidTensor("row chunks must be multiples of 128 tokens")
-        self.plan = p = shard_plan(cfg, rank, world)
+        if batch % micro_batches or (batch // micro_batches * seq) % 16:
+            raise InvalidTensor("micro batches must hold whole sequences")
+        self.micro = micro_batches
+        self.plan = shard_plan(cfg, rank, world)
+        p = self.plan
         src = WeightSource(seed, exact_weights)
         up = lambda a: client.upload(np.ascontiguousarray(a), DType.BF16)
         h, d = cfg.hidden, cfg.head_dim
@@ -134,63 +143,150 @@ class TensorParallelDecoder:
             })
         cos, sin = rope_tables(seq, d, cfg.theta)
         self.cos, self.sin = client.upload(cos), client.upload(sin)
-        # activation buffers, allocated once
+        # activation buffers, allocated once; micro batches are row ranges of them
         t, hq, hkv, f = self.tokens, p["q_heads"], p["kv_heads"], cfg.ffn // world
         self.qkv_width = (hq + 2 * hkv) * d
         T = lambda *shape: client.tensor(shape, DType.BF16)
-        self.x, self.h, self.qkv, self.attn = T(t, h), T(t, h), T(t, self.qkv_width), T(batch, seq, hq, d)
+        self.x, self.h, self.qkv, self.attn = T(t, h), T(t, h), T(t, self.qkv_width), T(t, hq * d)
         self.proj, self.ffn_act = T(t, h), T(t, f)
         self.logits = T(t, cfg.vocab // world)
         self.tokens_dev = client.tensor((batch, seq), DType.I32)
         self.scale = 1.0 / float(np.sqrt(d))
-        self.launches_per_forward = None
+        self._keep = []          # ctypes structures referenced by the plan
+        self._steps = []         # (function, argument tuple)
+        self.launches_per_forward = 0
+        self.collectives_per_forward = 0
+        if sm_reserve:
+            from .runtime import _check
+            _check(client._lib.rb_set_sm_limit(client._ctx, C.c_int32(client.properties()["sm_count"] - sm_reserve)))
+        self._build_plan()
+        self._graph = None
+        if use_graph:
+            self._run_plan()                     # first use of every kernel and every workspace size happens outside the recording
+            client.sync()
+            from .runtime import _check
+            _check(client._lib.rb_graph_begin(client._ctx))
+            try:
+                self._run_plan()
+            finally:
+                g = C.c_uint64()
+                _check(client._lib.rb_graph_end(client._ctx, C.byref(g)))
+            self._graph = g
 
-    # -- views into the packed QKV buffer: [B,S,H,D] storage presented as [B,H,S,D] -------------------------
-    def _head_view(self, first_head: int, heads: int) -> TensorBuffer:
-        d, w, s = self.cfg.head_dim, self.qkv_width, self.seq
-        return TensorBuffer(self.qkv.handle, (self.batch, heads, s, d), DType.BF16, (s * w, d, w, 1), offset=first_head * d * 2)
+    # -- plan construction ------------------------------------------------------------------------------------
+    def _t(self, t: TensorBuffer | None):
+        if t is None:
+            return None
+        c = t._c()
+        self._keep.append(c)
+        return C.byref(c)
 
-    def _rows(self, t: TensorBuffer, chunk: int) -> TensorBuffer:
-        rows = self.tokens // self.chunks
+    def _rows(self, t: TensorBuffer, mb: int) -> TensorBuffer:
+        rows = self.tokens // self.micro
         width = t.elements // self.tokens
-        return TensorBuffer(t.handle, (rows, width), t.dtype, None, offset=t.offset + chunk * rows * width * t.dtype.size)
+        return TensorBuffer(t.handle, (rows, width), t.dtype, None, offset=t.offset + mb * rows * width * t.dtype.size)
 
-    def _row_parallel(self, inp: TensorBuffer, weight: TensorBuffer) -> None:
-        """proj = inp @ weight^T summed over ranks, chunked so the all-reduce overlaps the next chunk's GEMM."""
-        c = self.client
-        inp2 = inp.reshape((self.tokens, inp.elements // self.tokens))
-        for ch in range(self.chunks):
-            out = self._rows(self.proj, ch)
-            RT.gemm_into(c, self._rows(inp2, ch), weight, Transpose.No, Transpose.Yes, out)
+    def _head_view(self, mb: int, first_head: int, heads: int) -> TensorBuffer:
+        """[B,S,H,D] storage of the packed QKV projection presented as [B,H,S,D]."""
+        d, w, s = self.cfg.head_dim, self.qkv_width, self.seq
+        b = self.batch // self.micro
+        return TensorBuffer(self.qkv.handle, (b, heads, s, d), DType.BF16, (s * w, d, w, 1), offset=(mb * b * s * w + first_head * d) * 2)
+
+    def _op(self, name: str, *args, kernel: bool = True):
+        self._steps.append((getattr(self.client._lib, name), args))
+        if kernel:
+            self.launches_per_forward += 1
+
+    def _gemm(self, a, w, out, b_up=None):
+        self._op("rb_gemm", self.client._ctx, self._t(a), self._t(w), C.c_int32(0), C.c_int32(1), None, self._t(b_up),
+                 C.c_int32(2 if b_up is not None else 0), self._t(out))
+
+    def _build_plan(self):
+        cfg, p, c, ctx = self.cfg, self.plan, self.client, self.client._ctx
+        hq, hkv, n = p["q_heads"], p["kv_heads"], self.micro
+        b = self.batch // n
+        eps = C.c_double(cfg.eps)
+        comm = self.comm.native._comm if self.world > 1 else None
+        self._op("rb_embedding", ctx, self._t(self.embedding), self._t(self.tokens_dev), self._t(self.x.reshape((self.batch, self.seq, cfg.hidden))))
+        pending = [False] * n     # a deferred all-reduce of proj[mb] is in flight
+        tickets = [0] * n
+
+        def wait(mb):
+            if pending[mb]:
+                self._op("rb_comm_wait_ticket", comm, C.c_uint64(tickets[mb]), kernel=False)
+                pending[mb] = False
+
+        def reduce(mb, view):
             if self.world > 1:
-                self.comm.native.all_reduce(out, "sum", out=out, deferred=self.chunks > 1)
-        if self.world > 1 and self.chunks > 1:
-            self.comm.native.fence()
+                self._op("rb_all_reduce", comm, self._t(view), C.c_int32(0), self._t(view), C.c_int32(1))
+                self.collectives_per_forward += 1
+                self._issued += 1
+                tickets[mb], pending[mb] = self._issued, True
+
+        self._issued = 0
+        first = True
+        for lw in self.layers + [None]:
+            norm_w = self.final_norm if lw is None else lw["norm1"]
+            for mb in range(n):
+                x, h, proj = self._rows(self.x, mb), self._rows(self.h, mb), self._rows(self.proj, mb)
+                wait(mb)
+                if first:
+                    self._op("rb_rms_norm", ctx, self._t(x), self._t(norm_w), eps, self._t(h), None)
+                else:  # residual of the previous layer's FFN fused into this norm
+                    self._op("rb_add_rms_norm", ctx, self._t(x), self._t(proj), self._t(norm_w), eps, self._t(x), self._t(h))
+                if lw is None:
+                    self._gemm(h, self.lm_head, self._rows(self.logits, mb))
+                    continue
+                self._gemm(h, lw["wqkv"], self._rows(self.qkv, mb))
+                q, k, v = self._head_view(mb, 0, hq), self._head_view(mb, hq, hkv), self._head_view(mb, hq + hkv, hkv)
+                attn = self._rows(self.attn, mb)
+                self._op("rb_attention", ctx, self._t(q), self._t(k), self._t(v), None, C.c_float(self.scale), C.c_int32(1), C.c_uint64(0), C.c_uint64(0),
+                         self._t(self.cos), self._t(self.sin), C.c_int32(int(RotaryLayout.SplitHalf)), C.c_int32(1), self._t(attn.reshape((b, self.seq, hq, cfg.head_dim))))
+                self.launches_per_forward += 2   # the Q and K rotations run as two small kernels inside rb_attention
+                self._gemm(attn, lw["wo"], proj)
+                reduce(mb, proj)
+            if lw is None:
+                break
+            first = False
+            for mb in range(n):
+                x, h, proj, act = self._rows(self.x, mb), self._rows(self.h, mb), self._rows(self.proj, mb), self._rows(self.ffn_act, mb)
+                wait(mb)
+                self._op("rb_add_rms_norm", ctx, self._t(x), self._t(proj), self._t(lw["norm2"]), eps, self._t(x), self._t(h))
+                self._gemm(h, lw["wg"], act, b_up=lw["wu"])
+                self._gemm(act, lw["wd"], proj)
+                reduce(mb, proj)
+
+    def _run_plan(self):
+        from .runtime import _check
+        if self.world > 1:
+            # tickets in the plan count this forward's collectives from one; add the communicator's counter so far
+            cur = C.c_uint64()
+            _check(self.client._lib.rb_comm_ticket(self.comm.native._comm, C.byref(cur)))
+            shift = cur.value
+        for fn, args in self._steps:
+            if self.world > 1 and fn.__name__ == "rb_comm_wait_ticket":
+                rc = fn(args[0], C.c_uint64(args[1].value + shift))
+            else:
+                rc = fn(*args)
+            if rc:
+                _check(rc)
+
+    def close(self) -> None:
+        """Drops the recorded graph.  Call this before destroying the communicator: NCCL does not finish destroying a
+        communicator while a graph that holds its collectives exists."""
+        if self._graph is not None:
+            self.client._lib.rb_graph_destroy(self.client._ctx, self._graph)
+            self._graph = None
 
     def forward(self, tokens: np.ndarray | None = None) -> TensorBuffer:
         """Returns this rank's logits shard [T, vocab/world] (BF16).  `tokens` int32 [B,S]; None reuses the last upload."""
-        c, cfg, p = self.client, self.cfg, self.plan
+        c = self.client
         if tokens is not None:
             c.write(self.tokens_dev.handle, np.ascontiguousarray(tokens, dtype=np.int32))
             c.sync()
-        before = c.stats()["launches"]
-        hq, hkv = p["q_heads"], p["kv_heads"]
-        import ctypes as C
-        from .runtime import _check, _ref
-        _check(c._lib.rb_embedding(c._ctx, _ref(self.embedding), _ref(self.tokens_dev), _ref(self.x.reshape((self.batch, self.seq, cfg.hidden)))))
-        q, k, v = self._head_view(0, hq), self._head_view(hq, hkv), self._head_view(hq + hkv, hkv)
-        for lw in self.layers:
-            _check(c._lib.rb_rms_norm(c._ctx, _ref(self.x), _ref(lw["norm1"]), C.c_double(cfg.eps), _ref(self.h), None))
-            RT.gemm_into(c, self.h, lw["wqkv"], Transpose.No, Transpose.Yes, self.qkv)
-            RT.attention(c, q, k, v, self.scale, causal=True, cos=self.cos, sin=self.sin, rotary_layout=RotaryLayout.SplitHalf,
-                         bmhd_output=True, out=self.attn)
-            self._row_parallel(self.attn, lw["wo"])
-            RT.add(c, self.x, self.proj, out=self.x)
-            _check(c._lib.rb_rms_norm(c._ctx, _ref(self.x), _ref(lw["norm2"]), C.c_double(cfg.eps), _ref(self.h), None))
-            RT.gemm_into(c, self.h, lw["wg"], Transpose.No, Transpose.Yes, self.ffn_act, b_up=lw["wu"])
-            self._row_parallel(self.ffn_act, lw["wd"])
-            RT.add(c, self.x, self.proj, out=self.x)
-        _check(c._lib.rb_rms_norm(c._ctx, _ref(self.x), _ref(self.final_norm), C.c_double(cfg.eps), _ref(self.h), None))
-        RT.gemm_into(c, self.h, self.lm_head, Transpose.No, Transpose.Yes, self.logits)
-        self.launches_per_forward = c.stats()["launches"] - before
+        if self._graph is not None:
+            from .runtime import _check
+            _check(c._lib.rb_graph_launch(c._ctx, self._graph))
+        else:
+            self._run_plan()
         return self.logits
