@@ -345,6 +345,9 @@ def decoder_extra(client, pk, rank, world, dist):
     if world > 1:
         from rust_ascend_b200.distributed import NcclCommunicator, TorchControl
         os.environ.setdefault("RUDA_NCCL_MAX_CTAS", str(NCCL_CTAS))
+        # No NVLink multicast binding: the watchdog may end a rank while collectives are pending, and a rank that
+        # leaves while bound to a multicast object can fault its peers.  Ring/tree all-reduce is used instead.
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         comm = NcclCommunicator.initialize(TorchControl(), client)
     cfg = LlamaConfig()
     micro = 1 if world == 1 else 2

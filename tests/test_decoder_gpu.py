@@ -54,7 +54,7 @@ def _two_gpu_worker(rank, world, port, results):
         if p not in sys.path:
             sys.path.insert(0, p)
     import torch.distributed as dist
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     dist.init_process_group("gloo", rank=rank, world_size=world)
     from rust_ascend_b200 import B200Runtime as RT
     from rust_ascend_b200 import DType, RuntimeOptions
