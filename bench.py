@@ -339,36 +339,55 @@ def attention_extra(client, RT, pk):
 
 
 def decoder_extra(client, pk, rank, world, dist):
-    """Config 5: Llama-style stack, 8 layers, T = 8 x 2048, tensor-parallel over `world` GPUs with NCCL all-reduces."""
+    """Config 5: Llama-style stack, 8 layers, T = 8 x 2048, tensor-parallel over `world` GPUs with NCCL all-reduces.
+    For world > 1 a few schedules are timed on the same resident model and the fastest is the reported value."""
     from rust_ascend_b200.decoder import LlamaConfig, TensorParallelDecoder
-    comm = None
-    if world > 1:
+    cfg = LlamaConfig()
+    tokens = np.random.default_rng(5).integers(0, cfg.vocab, size=(8, 2048)).astype(np.int32)
+    if world == 1:
+        candidates = [{"micro_batches": 1, "sms_left_to_nccl": 0, "nccl_max_ctas": 0}]
+    else:
         from rust_ascend_b200.distributed import NcclCommunicator, TorchControl
-        os.environ.setdefault("RUDA_NCCL_MAX_CTAS", str(NCCL_CTAS))
         # No NVLink multicast binding: the watchdog may end a rank while collectives are pending, and a rank that
         # leaves while bound to a multicast object can fault its peers.  Ring/tree all-reduce is used instead.
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-        comm = NcclCommunicator.initialize(TorchControl(), client)
-    cfg = LlamaConfig()
-    micro = 1 if world == 1 else 2
-    reserve = 0 if world == 1 else NCCL_CTAS
-    model = TensorParallelDecoder(client, cfg, 8, 2048, comm=comm, rank=rank, world=world, micro_batches=micro, sm_reserve=reserve, use_graph=True)
-    tokens = np.random.default_rng(5).integers(0, cfg.vocab, size=(8, 2048)).astype(np.int32)
-    model.forward(tokens)
-    for _ in range(2):
-        model.forward()
-    client.sync()
-    if dist is not None:
-        dist.barrier()
-    steps = 8
-    client.start_profile()
-    for _ in range(steps):
-        model.forward()
-    ms = max_over_ranks(dist, client.end_profile() / steps)
-    tf = cfg.flops(8 * 2048, 2048) / (ms * 1e-3) / 1e12
+        candidates = [{"micro_batches": 2, "sms_left_to_nccl": NCCL_CTAS, "nccl_max_ctas": NCCL_CTAS},   # all-reduce under the other group's GEMMs
+                      {"micro_batches": 1, "sms_left_to_nccl": 0, "nccl_max_ctas": 0},                    # sequential, NCCL at full width
+                      {"micro_batches": 2, "sms_left_to_nccl": 0, "nccl_max_ctas": 0}]
+    comms, model, results = {}, None, []
+    for cand in candidates:
+        comm = None
+        if world > 1:
+            cap = cand["nccl_max_ctas"]
+            if cap not in comms:
+                if cap:
+                    os.environ["RUDA_NCCL_MAX_CTAS"] = str(cap)
+                else:
+                    os.environ.pop("RUDA_NCCL_MAX_CTAS", None)
+                comms[cap] = NcclCommunicator.initialize(TorchControl(), client)
+            comm = comms[cap]
+        if model is None:
+            model = TensorParallelDecoder(client, cfg, 8, 2048, comm=comm, rank=rank, world=world, micro_batches=cand["micro_batches"],
+                                          sm_reserve=cand["sms_left_to_nccl"], use_graph=True)
+        else:
+            model.configure(comm, cand["micro_batches"], cand["sms_left_to_nccl"], True)
+        model.forward(tokens)
+        for _ in range(2):
+            model.forward()
+        client.sync()
+        if dist is not None:
+            dist.barrier()
+        steps = 6
+        client.start_profile()
+        for _ in range(steps):
+            model.forward()
+        ms = max_over_ranks(dist, client.end_profile() / steps)
+        results.append(dict(cand, ms_per_forward=ms, launches_per_forward=model.launches_per_forward, all_reduces_per_forward=model.collectives_per_forward))
     model.close()
-    return {"value": tf, "unit": "TFLOP/s (whole job)", "ms_per_forward": ms, "n_gpus": world, "micro_batches": micro, "sms_left_to_nccl": reserve, "cuda_graph": True,
-            "launches_per_forward": model.launches_per_forward, "all_reduces_per_forward": model.collectives_per_forward,
+    best = min(results, key=lambda r: r["ms_per_forward"])
+    tf = cfg.flops(8 * 2048, 2048) / (best["ms_per_forward"] * 1e-3) / 1e12
+    return {"value": tf, "unit": "TFLOP/s (whole job)", "ms_per_forward": best["ms_per_forward"], "n_gpus": world, "cuda_graph": True,
+            "schedule": best, "schedules_timed": results,
             "config": "8 layers, hidden 4096, 32q/8kv heads, ffn 14336, vocab 32000, batch 8 x seq 2048, BF16",
             "frac_of_sustained_peak_per_gpu": tf / world / pk["bf16_tflops_sustained"]}
 

@@ -194,6 +194,21 @@ RB_API int32_t rb_cast(rb_ctx* ctx, const rb_tensor* x, const rb_tensor* y);
 /* AscendRuntime::embedding, runtime/mod.rs:231-233 -> indexing.rs:33-37: out[i,:] = table[ids[i],:]. */
 RB_API int32_t rb_embedding(rb_ctx* ctx, const rb_tensor* table, const rb_tensor* ids, const rb_tensor* out);
 
+/* ---- first-order backward programs (FP32) -------------------------------------------------------------- */
+/* AscendRuntime::rms_norm_backward, runtime/mod.rs:411-414 -> normalization.rs:168-186, IR row_programs.rs:189-217:
+ * [input gradient, weight gradient] from the saved rstd; the weight gradient sums all leading rows on the device. */
+RB_API int32_t rb_rms_norm_backward(rb_ctx* ctx, const rb_tensor* x, const rb_tensor* weight, const rb_tensor* grad,
+                                    const rb_tensor* rstd, const rb_tensor* dx, const rb_tensor* dweight);
+/* AscendRuntime::softmax_backward / log_softmax_backward, runtime/mod.rs:332-343 -> rows.rs, IR row_programs.rs:152-163. */
+RB_API int32_t rb_softmax_backward(rb_ctx* ctx, const rb_tensor* output, const rb_tensor* grad, int32_t logarithmic, const rb_tensor* dx);
+/* AscendRuntime::silu_mul_backward, runtime/mod.rs:287-290 -> elementwise.rs:21-28, IR programs.rs:29,43. */
+RB_API int32_t rb_silu_mul_backward(rb_ctx* ctx, const rb_tensor* gate, const rb_tensor* up, const rb_tensor* grad,
+                                    const rb_tensor* dgate, const rb_tensor* dup);
+/* AscendRuntime::repeat_kv_heads_backward, runtime/mod.rs:211-213 -> heads.rs:30-51, IR heads_programs.rs:59-86. */
+RB_API int32_t rb_repeat_kv_heads_backward(rb_ctx* ctx, const rb_tensor* grad, uint32_t kv_heads, const rb_tensor* dx);
+/* AscendRuntime::bias_add_backward, runtime/mod.rs:183-185 -> affine.rs:24-26: sum of dY over all leading axes. */
+RB_API int32_t rb_bias_add_backward(rb_ctx* ctx, const rb_tensor* grad, const rb_tensor* dbias);
+
 /* ---- BF16 matrix programs (tcgen05 tensor cores, FP32 accumulation) ------------------------------ */
 /* AscendRuntime::gemm / gemm_into, runtime/mod.rs:346-355 -> matrix.rs:47-59 -> GemmSpec deepgemm/plan.rs:49-80;
  * device program rust-ascend-kernels/src/kernel.rs:11-76.  out = op(A) op(B): contiguous BF16 operands, rank 2

@@ -239,3 +239,48 @@ def attention(q, k, v, scale: float, mask=None, causal: bool = False, query_star
                         _i64(d), _i64(dv), C.c_float(scale), C.c_int(int(causal)), C.c_uint64(query_start),
                         C.c_uint64(key_start), C.c_int(int(out_bf16)), _i64(rows_limit), _p(out))
     return out[:, 0] if squeeze else out
+
+
+def rms_norm_backward(x, w, dy, rstd):
+    """[dx, dw] (row_programs.rs:189-217; normalization.rs:168-186)."""
+    x, w, dy, rstd = _f32(x), _f32(w), _f32(dy), _f32(rstd)
+    rows, width = _rows(x)
+    dx = np.empty_like(x)
+    dw = np.empty(width, dtype=np.float32)
+    lib().orc_rms_norm_backward(_p(x), _p(w), _p(dy), _p(rstd), _i64(rows), _i64(width), _p(dx), _p(dw))
+    return dx, dw
+
+
+def softmax_backward(y, dy, log: bool = False) -> np.ndarray:
+    """Input gradient from the saved forward output (row_programs.rs:152-163)."""
+    y, dy = _f32(y), _f32(dy)
+    rows, width = _rows(y)
+    dx = np.empty_like(y)
+    lib().orc_softmax_backward(_p(y), _p(dy), _i64(rows), _i64(width), C.c_int(int(log)), _p(dx))
+    return dx
+
+
+def silu_mul_backward(gate, up, dy):
+    """[dgate, dup] (programs.rs:29,43)."""
+    gate, up, dy = _f32(gate), _f32(up), _f32(dy)
+    dg, du = np.empty_like(gate), np.empty_like(gate)
+    lib().orc_silu_mul_backward(_p(gate), _p(up), _p(dy), _i64(gate.size), _p(dg), _p(du))
+    return dg, du
+
+
+def repeat_kv_heads_backward(dy, kv_heads: int) -> np.ndarray:
+    """Sum of the replicas' gradients (heads_programs.rs:59-86)."""
+    dy = _f32(dy)
+    b, hq, n, d = dy.shape
+    dx = np.empty((b, kv_heads, n, d), dtype=np.float32)
+    lib().orc_repeat_kv_heads_backward(_p(dy), _i64(b), _i64(kv_heads), _i64(hq), _i64(n), _i64(d), _p(dx))
+    return dx
+
+
+def column_sum(x) -> np.ndarray:
+    """Sum over every leading axis (bias gradient, affine.rs)."""
+    x = _f32(x)
+    rows, width = _rows(x)
+    out = np.empty(width, dtype=np.float32)
+    lib().orc_column_sum(_p(x), _i64(rows), _i64(width), _p(out))
+    return out

@@ -391,3 +391,93 @@ ORC_API void orc_attention(const float* q, const float* k, const float* v, const
     }
     free(kb); free(vb);
 }
+
+/* ---------------------------------------------------------------- first-order backward ------ */
+/* row_programs.rs:200-217 (RmsNormInputBackward): g=dy*w; mean=sum(g*x)/W; corr=mean*(r*r); dx=(g-x*corr)*r.
+ * row_programs.rs:189-199 (RmsNormWeightContributions): (x*r)*dy per element, summed over the rows
+ * (rust-ascend-driver/src/tensor/runtime/normalization.rs:95-114,168-186). */
+ORC_API void orc_rms_norm_backward(const float* x, const float* w, const float* dy, const float* rstd, int64_t rows,
+                                   int64_t width, float* dx, float* dw) {
+    float* contrib = (float*)malloc(sizeof(float) * (size_t)(rows * width + 1));
+#pragma omp parallel
+    {
+        float* scratch = (float*)malloc(sizeof(float) * TILE);
+        float* gx = (float*)malloc(sizeof(float) * (size_t)(width + 1));
+#pragma omp for schedule(static)
+        for (int64_t r = 0; r < rows; ++r) {
+            const float* xr = x + r * width; const float* gr = dy + r * width; float rs = rstd[r];
+            for (int64_t c = 0; c < width; ++c) gx[c] = (gr[c] * w[c]) * xr[c];
+            float mean = row_reduce_map(gx, width, 0, NULL, NULL, scratch) / (float)width;
+            float corr = mean * (rs * rs);
+            for (int64_t c = 0; c < width; ++c) {
+                float g = gr[c] * w[c];
+                dx[r * width + c] = (g - xr[c] * corr) * rs;
+                contrib[r * width + c] = (xr[c] * rs) * gr[c];
+            }
+        }
+        free(scratch); free(gx);
+    }
+#pragma omp parallel for schedule(static)
+    for (int64_t c = 0; c < width; ++c) {
+        double acc = 0.0;   /* the reference sums pairwise in FP32; order is not part of the contract */
+        for (int64_t r = 0; r < rows; ++r) acc += (double)contrib[r * width + c];
+        dw[c] = (float)acc;
+    }
+    free(contrib);
+}
+/* row_programs.rs:152-163: softmax dx = y*(dy - sum(y*dy)); log-softmax dx = dy - exp(y)*sum(dy). */
+ORC_API void orc_softmax_backward(const float* y, const float* dy, int64_t rows, int64_t width, int logarithmic, float* dx) {
+#pragma omp parallel
+    {
+        float* scratch = (float*)malloc(sizeof(float) * TILE);
+        float* prod = (float*)malloc(sizeof(float) * (size_t)(width + 1));
+#pragma omp for schedule(static)
+        for (int64_t r = 0; r < rows; ++r) {
+            const float* yr = y + r * width; const float* gr = dy + r * width;
+            if (logarithmic) {
+                float dot = row_reduce_map(gr, width, 0, NULL, NULL, scratch);
+                for (int64_t c = 0; c < width; ++c) dx[r * width + c] = gr[c] - expf(yr[c]) * dot;
+            } else {
+                for (int64_t c = 0; c < width; ++c) prod[c] = yr[c] * gr[c];
+                float dot = row_reduce_map(prod, width, 0, NULL, NULL, scratch);
+                for (int64_t c = 0; c < width; ++c) dx[r * width + c] = yr[c] * (gr[c] - dot);
+            }
+        }
+        free(scratch); free(prod);
+    }
+}
+/* programs.rs:29,43: s=sigmoid(x); h=x*s; ds=s*(1+x*(1-s)); dgate=(dy*up)*ds; dup=dy*h. */
+ORC_API void orc_silu_mul_backward(const float* gate, const float* up, const float* dy, int64_t n, float* dgate, float* dup) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) {
+        float x = gate[i];
+        float s = 1.0f / (1.0f + expf(-x));
+        float h = x * s;
+        float ds = s * (1.0f + x * (1.0f - s));
+        dgate[i] = (dy[i] * up[i]) * ds;
+        dup[i] = dy[i] * h;
+    }
+}
+/* heads_programs.rs:59-86: the gradient of a KV head is the sum of its query-head replicas. */
+ORC_API void orc_repeat_kv_heads_backward(const float* dy, int64_t batch, int64_t kv_heads, int64_t q_heads, int64_t seq,
+                                          int64_t width, float* dx) {
+    int64_t g = q_heads / kv_heads, plane_n = seq * width;
+#pragma omp parallel for schedule(static)
+    for (int64_t bk = 0; bk < batch * kv_heads; ++bk) {
+        int64_t b = bk / kv_heads, kv = bk % kv_heads;
+        for (int64_t p = 0; p < plane_n; ++p) {
+            double acc = 0.0;
+            for (int64_t r = 0; r < g; ++r) acc += (double)dy[((b * q_heads + kv * g + r) * plane_n) + p];
+            dx[bk * plane_n + p] = (float)acc;
+        }
+    }
+}
+/* affine.rs bias_backward: dbias[c] = sum of dY over every leading axis. */
+ORC_API void orc_column_sum(const float* x, int64_t rows, int64_t width, float* out) {
+#pragma omp parallel for schedule(static)
+    for (int64_t c = 0; c < width; ++c) {
+        double acc = 0.0;
+        for (int64_t r = 0; r < rows; ++r) acc += (double)x[r * width + c];
+        out[c] = (float)acc;
+    }
+}

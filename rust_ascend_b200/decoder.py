@@ -116,9 +116,6 @@ class TensorParallelDecoder:
         self.batch, self.seq, self.tokens = batch, seq, batch * seq
         if self.tokens % 16 or seq % 32:
             raise InvalidTensor("batch*seq must be a multiple of 16 and seq a multiple of 32")
-        if batch % micro_batches or (batch // micro_batches * seq) % 16:
-            raise InvalidTensor("micro batches must hold whole sequences")
-        self.micro = micro_batches
         self.plan = shard_plan(cfg, rank, world)
         p = self.plan
         src = WeightSource(seed, exact_weights)
@@ -152,19 +149,29 @@ class TensorParallelDecoder:
         self.logits = T(t, cfg.vocab // world)
         self.tokens_dev = client.tensor((batch, seq), DType.I32)
         self.scale = 1.0 / float(np.sqrt(d))
+        self._graph = None
+        self.configure(comm, micro_batches, sm_reserve, use_graph)
+
+    def configure(self, comm, micro_batches: int = 1, sm_reserve: int = 0, use_graph: bool = False) -> None:
+        """(Re)builds the launch plan, and the recorded graph if asked for, on the weights and buffers already resident.
+        Lets a caller compare schedules (micro batches, SMs left to NCCL, communicators with different CTA limits)
+        without loading the model again."""
+        from .runtime import _check
+        client = self.client
+        if self.batch % micro_batches or (self.batch // micro_batches * self.seq) % 16:
+            raise InvalidTensor("micro batches must hold whole sequences")
+        self.close()
+        self.comm, self.micro = comm, micro_batches
         self._keep = []          # ctypes structures referenced by the plan
         self._steps = []         # (function, argument tuple)
         self.launches_per_forward = 0
         self.collectives_per_forward = 0
-        if sm_reserve:
-            from .runtime import _check
-            _check(client._lib.rb_set_sm_limit(client._ctx, C.c_int32(client.properties()["sm_count"] - sm_reserve)))
+        sms = client.properties()["sm_count"]
+        _check(client._lib.rb_set_sm_limit(client._ctx, C.c_int32(sms - sm_reserve if sm_reserve else 0)))
         self._build_plan()
-        self._graph = None
         if use_graph:
             self._run_plan()                     # first use of every kernel and every workspace size happens outside the recording
             client.sync()
-            from .runtime import _check
             _check(client._lib.rb_graph_begin(client._ctx))
             try:
                 self._run_plan()

@@ -497,6 +497,88 @@ class B200Runtime:
         return B200Runtime.gemm(client, B200Runtime.cast(client, input, DType.BF16), weight, Transpose.No, Transpose.Yes, DType.F32)
 
 
+    # -- first-order backward --------------------------------------------------------------------
+    @staticmethod
+    def linear_nt_backward(client, input: TensorBuffer, weight: TensorBuffer, grad: TensorBuffer):
+        """[BF16 dX, FP32 dWeight] for Y = X W^T with BF16 X, W and dY (runtime/mod.rs:360-363 -> matrix.rs:60-74)."""
+        if any(t.dtype != DType.BF16 or len(t.shape) != 2 for t in (input, weight, grad)) or grad.shape != (input.shape[0], weight.shape[0]):
+            raise InvalidTensor("linear backward requires rank-2 BF16 dY matching X @ W^T")
+        return [B200Runtime.gemm(client, grad, weight, Transpose.No, Transpose.No, DType.BF16),
+                B200Runtime.gemm(client, grad, input, Transpose.Yes, Transpose.No, DType.F32)]
+
+    @staticmethod
+    def gemm_bf16_fp32_backward(client, a: TensorBuffer, b: TensorBuffer, grad: TensorBuffer, ta: Transpose, tb: Transpose):
+        """[FP32 dA, FP32 dB] in the original physical layouts from the saved BF16 operands and FP32 dY, which is
+        rounded to BF16 first (runtime/mod.rs:428-431 -> matrix.rs:95-121)."""
+        if a.dtype != DType.BF16 or b.dtype != DType.BF16 or grad.dtype != DType.F32 or grad.shape != B200Runtime._gemm_shape(a, b, ta, tb):
+            raise InvalidTensor("BF16-compute matmul backward requires saved BF16 inputs and matching FP32 dY")
+        g = B200Runtime.cast(client, grad, DType.BF16)
+        no, yes = Transpose.No, Transpose.Yes
+        opposite = lambda t: yes if t == no else no
+        da = B200Runtime.gemm(client, g, b, no, opposite(tb), DType.F32) if ta == no else B200Runtime.gemm(client, b, g, tb, yes, DType.F32)
+        db = B200Runtime.gemm(client, a, g, opposite(ta), no, DType.F32) if tb == no else B200Runtime.gemm(client, g, a, yes, ta, DType.F32)
+        return [da, db]
+
+    @staticmethod
+    def linear_bf16_fp32_backward(client, input: TensorBuffer, weight: TensorBuffer, grad: TensorBuffer):
+        """[FP32 dX, FP32 dW] from the saved BF16 X/W of linear_bf16_fp32 (runtime/mod.rs:375-378)."""
+        if len(input.shape) != 2 or len(weight.shape) != 2:
+            raise InvalidTensor("BF16-compute linear backward requires saved rank-2 inputs")
+        return B200Runtime.gemm_bf16_fp32_backward(client, input, weight, grad, Transpose.No, Transpose.Yes)
+
+    @staticmethod
+    def linear_frozen_bf16_fp32_backward(client, input_shape, weight: TensorBuffer, grad: TensorBuffer) -> TensorBuffer:
+        """Input-only FP32 gradient with the fixed BF16 weight (runtime/mod.rs:387-389 -> matrix.rs:160-173)."""
+        if weight.dtype != DType.BF16 or grad.dtype != DType.F32 or tuple(grad.shape) != (input_shape[0], weight.shape[0]) or input_shape[1] != weight.shape[1]:
+            raise InvalidTensor("frozen BF16 linear backward requires matching FP32 dY")
+        return B200Runtime.gemm(client, B200Runtime.cast(client, grad, DType.BF16), weight, Transpose.No, Transpose.No, DType.F32)
+
+    @staticmethod
+    def rms_norm_backward(client, input: TensorBuffer, weight: TensorBuffer, grad: TensorBuffer, rstd: TensorBuffer):
+        """[input gradient, weight gradient] (runtime/mod.rs:411-414)."""
+        dx, dw = client.tensor(input.shape, DType.F32), client.tensor(weight.shape, DType.F32)
+        _check(client._lib.rb_rms_norm_backward(client._ctx, _ref(input), _ref(weight), _ref(grad), _ref(rstd), _ref(dx), _ref(dw)))
+        return [dx, dw]
+
+    @staticmethod
+    def softmax_backward(client, output: TensorBuffer, grad: TensorBuffer) -> TensorBuffer:
+        """runtime/mod.rs:332-336."""
+        dx = client.tensor(output.shape, DType.F32)
+        _check(client._lib.rb_softmax_backward(client._ctx, _ref(output), _ref(grad), C.c_int32(0), _ref(dx)))
+        return dx
+
+    @staticmethod
+    def log_softmax_backward(client, output: TensorBuffer, grad: TensorBuffer) -> TensorBuffer:
+        """runtime/mod.rs:339-343."""
+        dx = client.tensor(output.shape, DType.F32)
+        _check(client._lib.rb_softmax_backward(client._ctx, _ref(output), _ref(grad), C.c_int32(1), _ref(dx)))
+        return dx
+
+    @staticmethod
+    def silu_mul_backward(client, gate: TensorBuffer, up: TensorBuffer, grad: TensorBuffer):
+        """[gate gradient, up gradient] (runtime/mod.rs:287-290)."""
+        dg, du = client.tensor(gate.shape, DType.F32), client.tensor(gate.shape, DType.F32)
+        _check(client._lib.rb_silu_mul_backward(client._ctx, _ref(gate), _ref(up), _ref(grad), _ref(dg), _ref(du)))
+        return [dg, du]
+
+    @staticmethod
+    def repeat_kv_heads_backward(client, input_shape, query_heads: int, grad: TensorBuffer) -> TensorBuffer:
+        """runtime/mod.rs:211-213."""
+        if len(input_shape) != 4 or len(grad.shape) != 4 or grad.shape[1] != query_heads:
+            raise InvalidTensor("KV repetition backward requires [B,Hkv,N,D] and a [B,Hq,N,D] gradient")
+        dx = client.tensor(input_shape, DType.F32)
+        _check(client._lib.rb_repeat_kv_heads_backward(client._ctx, _ref(grad), C.c_uint32(input_shape[1]), _ref(dx)))
+        return dx
+
+    @staticmethod
+    def bias_add_backward(client, grad: TensorBuffer, input_shape) -> TensorBuffer:
+        """runtime/mod.rs:183-185."""
+        if tuple(grad.shape) != tuple(input_shape):
+            raise InvalidTensor("bias backward requires dY of the input's shape")
+        db = client.tensor((input_shape[-1],), DType.F32)
+        _check(client._lib.rb_bias_add_backward(client._ctx, _ref(grad), _ref(db)))
+        return db
+
     # -- attention -------------------------------------------------------------------------------
     @staticmethod
     def attention(client, q: TensorBuffer, k: TensorBuffer, v: TensorBuffer, scale: float, mask: TensorBuffer | None = None,

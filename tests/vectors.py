@@ -255,3 +255,41 @@ def gqa_case(kv_heads, group, n, causal, batch=2, m=32, d=16, dv=16):
     p = e / e.sum(-1, keepdims=True)
     out = np.einsum("bhmn,bhnd->bhmd", bf16_f64(p.astype(np.float32)), vb)
     return q, k, v, mask, prefix, out
+
+
+# ---- backward known-answer cases ------------------------------------------------------------------
+def rms_backward_case(rows, width):
+    """examples/rms_norm_runtime.rs:37-73: dy = (i%11)/5 - 0.7; f64 dX and dWeight."""
+    x, w, _, r = rms_case(rows, width)
+    dy = ((np.arange(rows * width) % 11).astype(np.float32) / np.float32(5.0) - np.float32(0.7)).reshape(rows, width)
+    xd, wd, gd = x.astype(np.float64), w.astype(np.float64), dy.astype(np.float64)
+    mean_gx = (gd * wd * xd).sum(-1, keepdims=True) / max(width, 1)
+    dx = r[:, None] * (gd * wd - xd * (r ** 2)[:, None] * mean_gx)
+    dw = (gd * xd * r[:, None]).sum(0)
+    return x, w, dy, r.astype(np.float32), dx, dw
+
+
+def softmax_backward_case(rows, width, log):
+    """examples/softmax_tensor.rs:25-48 with a single upstream gradient (the example doubles it)."""
+    x, y = softmax_case(rows, width, log)
+    dy = ((np.arange(rows * width) % 11).astype(np.float32) / np.float32(5.0) - np.float32(0.7)).reshape(rows, width)
+    g = dy.astype(np.float64)
+    p = np.exp(y) if log else y
+    dx = (g - p * g.sum(-1, keepdims=True)) if log else p * (g - (p * g).sum(-1, keepdims=True))
+    return y.astype(np.float32), dy, dx
+
+
+def silu_mul_backward_case(n):
+    """examples/silu_mul_tensor.rs:25-46."""
+    x, u, _ = silu_mul_case(n)
+    dy = (np.arange(n) % 7).astype(np.float32) * np.float32(0.25) - np.float32(0.75)
+    a = x.astype(np.float64); s = 1.0 / (1.0 + np.exp(-a)); d = s * (1.0 + a * (1.0 - s))
+    return x, u, dy, dy.astype(np.float64) * u.astype(np.float64) * d, dy.astype(np.float64) * a * s
+
+
+def linear_backward_case(m=32, n=48, k=16):
+    """examples/matrix_runtime.rs:67-77: dX = dY W, dW = dY^T X with exactly representable values."""
+    x = (((np.arange(m * k) % 17).astype(np.float32) - 8.0) * 0.125).reshape(m, k)
+    w = (((np.arange(n * k) % 13).astype(np.float32) - 6.0) * 0.25).reshape(n, k)
+    dy = (((np.arange(m * n) % 11).astype(np.float32) - 5.0) * 0.0625).reshape(m, n)
+    return x, w, dy, dy.astype(np.float64) @ w.astype(np.float64), dy.astype(np.float64).T @ x.astype(np.float64)
