@@ -12,7 +12,7 @@
 
 namespace {
 
-enum RowOp { OP_RMS = 0, OP_LAYER = 1, OP_SOFTMAX = 2, OP_LOGSOFTMAX = 3, OP_SUM = 4, OP_MEAN = 5, OP_MAX = 6 };
+enum RowOp { OP_RMS = 0, OP_LAYER = 1, OP_SOFTMAX = 2, OP_LOGSOFTMAX = 3, OP_SUM = 4, OP_MEAN = 5, OP_MAX = 6, OP_ADD_RMS = 7 };
 
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
@@ -89,16 +89,26 @@ row_kernel(RowArgs a) {
             have[i] = live && c < width;
             if (have[i]) load4(xr + c, v[i], true);
             else { v[i][0] = v[i][1] = v[i][2] = v[i][3] = 0.f; }
-            if (OP == OP_RMS && a.delta != nullptr && have[i]) {
-                // residual stream update fused into the norm: the sum is rounded to the storage type first, so the
-                // normalised value is computed from exactly what a separate add kernel would have stored
-                float d[4]; load4(static_cast<const TIn*>(a.delta) + row * width + c, d, true);
+        }
+        if (OP == OP_ADD_RMS) {
+            // residual stream update fused into the norm (its own instantiation, so the plain norm keeps its four
+            // loads in flight): the sum is rounded to the storage type first, so the normalised value is computed
+            // from exactly what a separate add kernel would have stored
+            float d[MAXV][4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) v[i][j] = to_f32(from_f32<TIn>(__fadd_rn(v[i][j], d[j])));
+            for (int i = 0; i < MAXV; ++i) {
+                uint32_t c = (i * THREADS + threadIdx.x) * 4;
+                if (have[i]) load4(static_cast<const TIn*>(a.delta) + row * width + c, d[i], true);
+            }
+#pragma unroll
+            for (int i = 0; i < MAXV; ++i) if (have[i]) {
+                uint32_t c = (i * THREADS + threadIdx.x) * 4;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) v[i][j] = to_f32(from_f32<TIn>(__fadd_rn(v[i][j], d[i][j])));
                 store4(static_cast<TIn*>(a.x_out) + row * width + c, v[i]);
             }
         }
-        if (OP == OP_RMS) {
+        if (OP == OP_RMS || OP == OP_ADD_RMS) {
             float acc = 0.f;
 #pragma unroll
             for (int i = 0; i < MAXV; ++i)
@@ -342,7 +352,7 @@ int32_t rb_add_rms_norm(rb_ctx* ctx, const rb_tensor* x, const rb_tensor* delta,
     if (!aligned) return fail(RB_INVALID_TENSOR, "add+RMSNorm needs 16-byte aligned rows");
     RowArgs a{px, pw, nullptr, py, nullptr, nullptr, rows, (uint32_t)width, eps};
     a.delta = pd; a.x_out = pxo;
-    return dispatch<OP_RMS>(ctx, a, x->dtype, y->dtype, weight->dtype, true, "add+RMSNorm");
+    return dispatch<OP_ADD_RMS>(ctx, a, x->dtype, y->dtype, weight->dtype, true, "add+RMSNorm");
 }
 
 int32_t rb_layer_norm(rb_ctx* ctx, const rb_tensor* x, const rb_tensor* weight, const rb_tensor* bias, double epsilon,
