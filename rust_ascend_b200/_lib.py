@@ -38,8 +38,6 @@ def load() -> C.CDLL:
                           "(the B200 backend has no CPU fallback)")
         _lib = C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL)
         _lib.rb_last_error.restype = C.c_char_p
-        for name in dir(_lib):
-            pass
     return _lib
 
 

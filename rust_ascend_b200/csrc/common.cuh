@@ -18,7 +18,6 @@
 
 namespace rb {
 
-void set_error(const char* fmt, ...);
 int32_t fail(rb_status code, const char* fmt, ...);
 
 struct Storage {

@@ -6,9 +6,6 @@ namespace rb {
 
 static thread_local char g_error[1024] = "";
 
-void set_error(const char* fmt, ...) {
-    va_list ap; va_start(ap, fmt); vsnprintf(g_error, sizeof(g_error), fmt, ap); va_end(ap);
-}
 int32_t fail(rb_status code, const char* fmt, ...) {
     va_list ap; va_start(ap, fmt); vsnprintf(g_error, sizeof(g_error), fmt, ap); va_end(ap);
     return (int32_t)code;
