@@ -119,12 +119,11 @@ def cpu_linear_rate(orc, rows: int, seconds_target: float | None = None):
 
 def run_reference(args):
     """Reference arm: the CPU oracle port of the same step on the host cores, bounded sample per step."""
-    rank, world, local, dist = dist_setup(args.gpus)
-    if rank != 0:
-        return
+    if int(os.environ.get("RANK", 0)) != 0:
+        return   # rank 0 alone runs the CPU arm; the other ranks leave without work
     import oracle as orc
     orc.build()
-    cores = orc.threads()
+    cores = orc.use_all_cores()
     rate, dt = cpu_linear_rate(orc, 16)
     budget = 90.0  # seconds for warmup + steps
     rows = int(max(1, min(M, (rate * 1e12 * budget / (args.steps + args.warmup)) / (2.0 * N * K))))
@@ -236,6 +235,7 @@ def run_ours(args):
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         import oracle as orc
         orc.build()
+        orc.use_all_cores()
         rate, _ = cpu_linear_rate(orc, 64)
         rows = int(max(16, min(M, rate * 1e12 * 12.0 / (2.0 * N * K))))
         reps, spent, rates = 0, 0.0, []

@@ -41,6 +41,13 @@ def threads() -> int:
     return int(lib().orc_threads())
 
 
+def use_all_cores() -> int:
+    """Use every core this process may run on, whatever OMP_NUM_THREADS says (launchers such as torchrun set it to 1)."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().orc_set_threads(C.c_int(n))
+    return threads()
+
+
 def _f32(a) -> np.ndarray:
     return np.ascontiguousarray(a, dtype=np.float32)
 

@@ -53,6 +53,13 @@ ORC_API void orc_bf16_bits_to_f32(const uint16_t* in, float* out, int64_t n) {
 #pragma omp parallel for schedule(static)
     for (int64_t i = 0; i < n; ++i) out[i] = u2f((uint32_t)in[i] << 16);
 }
+ORC_API void orc_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
 ORC_API int orc_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();
