@@ -16,6 +16,7 @@
 // The running maximum is only refreshed when it grows by more than 2^8 (the accumulator and the sum are then
 // rescaled), so most key blocks need no pass over O.
 #include "common.cuh"
+#include "schedule.h"
 #include "sm100.cuh"
 
 namespace {
@@ -48,15 +49,8 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 // Number of key blocks tile rows [row0, row_end) must visit.
 __device__ __forceinline__ uint32_t blocks_for(const AttnParams& p, uint32_t row0, uint32_t row_end) {
-    if (row0 >= p.M) return 0;
-    uint32_t all = (p.N + TK - 1) / TK;
-    if (!p.causal) return all;
-    int64_t last_q = (int64_t)(row_end < p.M ? row_end : p.M) - 1 + p.delta;  // largest visible key index
-    if (last_q < 0) return 0;
-    int64_t need = last_q / TK + 1;
-    return need < (int64_t)all ? (uint32_t)need : all;
+    return rb_attention_blocks(p.M, p.N, p.causal, p.delta, row0, row_end, TK);
 }
-
 
 // Packed FP32 pairs (fma.rn.f32x2 / add.rn.f32x2) and the three-input max halve the issue slots of the softmax.
 __device__ __forceinline__ uint64_t pack2(uint32_t lo, uint32_t hi) { uint64_t r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi)); return r; }

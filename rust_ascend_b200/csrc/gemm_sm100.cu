@@ -14,6 +14,7 @@
 // Operands that are not K-major (A transposed, B not transposed) are first rewritten K-major by a tiled
 // transpose kernel; the hot Linear layout (X [M,K], W [N,K]) needs no rewrite.
 #include "common.cuh"
+#include "schedule.h"
 #include "sm100.cuh"
 
 namespace {
@@ -49,13 +50,7 @@ template <int BN> struct Config {
 };
 
 __device__ __forceinline__ void tile_coords(uint32_t t, const GemmParams& p, uint32_t& batch, uint32_t& tm, uint32_t& tn) {
-    uint32_t per_batch = p.tiles_m * p.tiles_n;
-    batch = t / per_batch; t -= batch * per_batch;
-    uint32_t group_size = GROUP_M * p.tiles_n;
-    uint32_t group = t / group_size, first_m = group * GROUP_M;
-    uint32_t rows = p.tiles_m - first_m < GROUP_M ? p.tiles_m - first_m : GROUP_M;
-    uint32_t r = t - group * group_size;
-    tm = first_m + r % rows; tn = r / rows;
+    rb_tile_coords(t, p.tiles_m, p.tiles_n, GROUP_M, batch, tm, tn);
 }
 
 __device__ __forceinline__ float bias_at(const GemmParams& p, uint32_t col) {

@@ -1,0 +1,10 @@
+// Host build of the kernels' shared index arithmetic (rust_ascend_b200/csrc/schedule.h) for CPU tests.
+#include "schedule.h"
+extern "C" {
+void host_tile_coords(uint32_t t, uint32_t tiles_m, uint32_t tiles_n, uint32_t group_m, uint32_t* out3) {
+    rb_tile_coords(t, tiles_m, tiles_n, group_m, out3[0], out3[1], out3[2]);
+}
+uint32_t host_attention_blocks(uint32_t M, uint32_t N, int causal, int64_t delta, uint32_t row0, uint32_t row_end, uint32_t block) {
+    return rb_attention_blocks(M, N, causal, delta, row0, row_end, block);
+}
+}
