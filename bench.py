@@ -125,8 +125,8 @@ def run_reference(args):
     orc.build()
     cores = orc.use_all_cores()
     rate, dt = cpu_linear_rate(orc, 16)
-    budget = 90.0  # seconds for warmup + steps
-    rows = int(max(1, min(M, (rate * 1e12 * budget / (args.steps + args.warmup)) / (2.0 * N * K))))
+    total_seconds = 90.0  # target for warmup + steps together
+    rows = int(max(1, min(M, (rate * 1e12 * total_seconds / (args.steps + args.warmup)) / (2.0 * N * K))))
     rng = np.random.default_rng(1)
     w = (rng.standard_normal((N, K), dtype=np.float32) * 0.02)
     bias = (rng.standard_normal(N) * 0.02).astype(np.float32)
