@@ -291,3 +291,42 @@ def column_sum(x) -> np.ndarray:
     out = np.empty(width, dtype=np.float32)
     lib().orc_column_sum(_p(x), _i64(rows), _i64(width), _p(out))
     return out
+
+
+def layer_norm_backward(x, w, dy, mean, rstd):
+    """[dx, dw, db] (row_programs.rs LayerNormInputBackward / LayerNormWeightContributions)."""
+    x, w, dy, mean, rstd = _f32(x), _f32(w), _f32(dy), _f32(mean), _f32(rstd)
+    rows, width = _rows(x)
+    dx = np.empty_like(x)
+    dw, db = np.empty(width, dtype=np.float32), np.empty(width, dtype=np.float32)
+    lib().orc_layer_norm_backward(_p(x), _p(w), _p(dy), _p(mean), _p(rstd), _i64(rows), _i64(width), _p(dx), _p(dw), _p(db))
+    return dx, dw, db
+
+
+def attention_backward(q, k, v, dy, scale: float, mask=None, causal: bool = False, query_start: int = 0, key_start: int = 0,
+                       want_mask_grad: bool = False):
+    """[dq, dk, dv(, dmask)] of the composed attention with the reference's rounding points
+    (examples/grouped_attention_tensor.rs:14-44).  Rank-4 tensors as in `attention`."""
+    q, k, v, dy = _f32(q), _f32(k), _f32(v), _f32(dy)
+    mask = None if mask is None else _f32(mask)
+    b, hq, m, d = q.shape
+    _, hkv, n, dv_ = v.shape
+    if d > 512:
+        raise ValueError("head dim above 512")
+    dq, dk, dv = np.empty_like(q), np.empty_like(k), np.empty_like(v)
+    dmask = np.empty((b, hq, m, n), dtype=np.float32) if want_mask_grad else None
+    lib().orc_attention_backward(_p(q), _p(k), _p(v), _p(dy), _p(mask), _i64(b), _i64(hq), _i64(hkv), _i64(m), _i64(n), _i64(d), _i64(dv_),
+                                 C.c_float(scale), C.c_int(int(causal)), C.c_uint64(query_start), C.c_uint64(key_start), _p(dq), _p(dk), _p(dv), _p(dmask))
+    return (dq, dk, dv, dmask) if want_mask_grad else (dq, dk, dv)
+
+
+def causal_cross_entropy(logits, labels, ignore_index: int = -100, shift: bool = True, upstream: float = 1.0):
+    """(loss_sum, valid_tokens, dlogits of the mean loss) (src/nn/causal_lm.rs:118-196)."""
+    logits = _f32(logits)
+    labels = np.ascontiguousarray(labels, dtype=np.int64)
+    b, t, vocab = logits.shape
+    loss, valid = C.c_float(), C.c_float()
+    d = np.empty_like(logits)
+    lib().orc_causal_cross_entropy(_p(logits), _p(labels), _i64(b), _i64(t), _i64(vocab), _i64(ignore_index), C.c_int(int(shift)),
+                                   C.c_float(upstream), C.byref(loss), C.byref(valid), _p(d))
+    return loss.value, valid.value, d

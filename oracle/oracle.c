@@ -15,8 +15,10 @@
  *   - GEMM, RoPE, SiLU*up, KV repeat, causal mask, bias/residual, attention composition: pinned
  *     against the deterministic index-formula vectors of the reference's in-crate tests and device
  *     examples (cited in tests/).
- *   - decoder-stack composition (orc_decoder_layer): PARITY UNPINNED — no reference test fixes a
- *     Llama forward value; it is the standard pre-norm block assembled from the pinned ops.
+ *   - backward programs, attention backward, LayerNorm backward, causal cross entropy: pinned against the f64
+ *     expectations of the reference's device examples (tests/test_backward.py, tests/test_oracle_next.py).
+ *   - decoder-stack composition (tests/decoder_reference.py, built from these functions): PARITY UNPINNED — no
+ *     reference test fixes a Llama forward value; it is the standard pre-norm block assembled from the pinned ops.
  *
  * Build: see oracle/Makefile (gcc -O3 -fopenmp -ffp-contract=off; contraction is disabled because
  * the reference IR rounds every multiply and add separately).
@@ -487,4 +489,132 @@ ORC_API void orc_column_sum(const float* x, int64_t rows, int64_t width, float* 
         for (int64_t r = 0; r < rows; ++r) acc += (double)x[r * width + c];
         out[c] = (float)acc;
     }
+}
+
+/* row_programs.rs (LayerNormInputBackward): n=(x-mean)*r; g=dy*w; dx=((g-mean(g)) - n*mean(g*n))*r;
+ * LayerNormWeightContributions: n*dy summed over rows; the bias gradient is the column sum of dy. */
+ORC_API void orc_layer_norm_backward(const float* x, const float* w, const float* dy, const float* mean, const float* rstd,
+                                     int64_t rows, int64_t width, float* dx, float* dw, float* db) {
+    float* contrib = (float*)malloc(sizeof(float) * (size_t)(rows * width + 1));
+#pragma omp parallel
+    {
+        float* scratch = (float*)malloc(sizeof(float) * TILE);
+        float* g = (float*)malloc(sizeof(float) * (size_t)(width + 1));
+        float* gy = (float*)malloc(sizeof(float) * (size_t)(width + 1));
+#pragma omp for schedule(static)
+        for (int64_t r = 0; r < rows; ++r) {
+            const float* xr = x + r * width; const float* gr = dy + r * width; float mu = mean[r], rs = rstd[r];
+            for (int64_t c = 0; c < width; ++c) { float n = (xr[c] - mu) * rs; g[c] = gr[c] * w[c]; gy[c] = g[c] * n; }
+            float mean_g = row_reduce_map(g, width, 0, NULL, NULL, scratch) / (float)width;
+            float mean_gy = row_reduce_map(gy, width, 0, NULL, NULL, scratch) / (float)width;
+            for (int64_t c = 0; c < width; ++c) {
+                float n = (xr[c] - mu) * rs;
+                dx[r * width + c] = ((g[c] - mean_g) - n * mean_gy) * rs;
+                contrib[r * width + c] = n * gr[c];
+            }
+        }
+        free(scratch); free(g); free(gy);
+    }
+    orc_column_sum(contrib, rows, width, dw);
+    orc_column_sum(dy, rows, width, db);
+    free(contrib);
+}
+
+/* Backward of the composed attention as the reference's autodiff builds it from its BF16 matmuls
+ * (examples/grouped_attention_tensor.rs:14-44 states the rounding points): dP = bf16(dY) bf16(V)^T in FP32,
+ * dS = P * (dP - sum(P*dP)) in FP32 (this is also the additive-mask gradient), then bf16(scale*dS) feeds
+ * dQ = dS_b bf16(K) and dK = dS_b^T bf16(Q), and dV = bf16(P)^T bf16(dY).  K/V gradients of a KV head sum over the
+ * query heads of its group (heads_programs.rs:59-86).  Shapes as orc_attention; dmask may be NULL. */
+ORC_API void orc_attention_backward(const float* q, const float* k, const float* v, const float* dy, const float* mask,
+                                    int64_t B, int64_t Hq, int64_t Hkv, int64_t M, int64_t N, int64_t D, int64_t Dv, float scale,
+                                    int causal, uint64_t query_start, uint64_t key_start, float* dq, float* dk, float* dv, float* dmask) {
+    int64_t g = Hq / Hkv;
+    double* dk_acc = (double*)calloc((size_t)(B * Hkv * N * D + 1), sizeof(double));
+    double* dv_acc = (double*)calloc((size_t)(B * Hkv * N * Dv + 1), sizeof(double));
+    /* one (batch, kv head) per task so that the K/V accumulators are private to a thread */
+#pragma omp parallel
+    {
+        float* s = (float*)malloc(sizeof(float) * (size_t)N);
+        float* p = (float*)malloc(sizeof(float) * (size_t)N);
+        float* dp = (float*)malloc(sizeof(float) * (size_t)N);
+        float* scratch = (float*)malloc(sizeof(float) * TILE);
+#pragma omp for schedule(dynamic, 1)
+        for (int64_t bk = 0; bk < B * Hkv; ++bk) {
+            int64_t b = bk / Hkv, kv = bk % Hkv;
+            const float* kr = k + bk * N * D; const float* vr = v + bk * N * Dv;
+            for (int64_t hh = 0; hh < g; ++hh) {
+                int64_t bh = b * Hq + kv * g + hh;
+                for (int64_t i = 0; i < M; ++i) {
+                    const float* qr = q + (bh * M + i) * D; const float* gr = dy + (bh * M + i) * Dv;
+                    for (int64_t j = 0; j < N; ++j) {
+                        double acc = 0.0, accp = 0.0;
+                        for (int64_t c = 0; c < D; ++c) acc += (double)bf16r(qr[c]) * (double)bf16r(kr[j * D + c]);
+                        for (int64_t c = 0; c < Dv; ++c) accp += (double)bf16r(gr[c]) * (double)bf16r(vr[j * Dv + c]);
+                        float sc = (float)acc * scale;
+                        if (mask) sc = sc + mask[(bh * M + i) * N + j];
+                        if (causal && key_start + (uint64_t)j > query_start + (uint64_t)i) sc = sc + -INFINITY;
+                        s[j] = sc; dp[j] = (float)accp;
+                    }
+                    float mx = row_reduce_map(s, N, 1, NULL, NULL, scratch);
+                    float dn = row_reduce_map(s, N, 0, f_shift_exp, &mx, scratch);
+                    for (int64_t j = 0; j < N; ++j) p[j] = expf(s[j] - mx) / dn;
+                    for (int64_t j = 0; j < N; ++j) s[j] = p[j] * dp[j];
+                    float dot = row_reduce_map(s, N, 0, NULL, NULL, scratch);
+                    float* dqr = dq + (bh * M + i) * D;
+                    for (int64_t c = 0; c < D; ++c) dqr[c] = 0.0f;
+                    double dq_acc[512];
+                    for (int64_t c = 0; c < D; ++c) dq_acc[c] = 0.0;
+                    for (int64_t j = 0; j < N; ++j) {
+                        float ds = p[j] * (dp[j] - dot);
+                        if (dmask) dmask[(bh * M + i) * N + j] = ds;
+                        double pb = (double)bf16r(p[j]), dsb = (double)bf16r(ds * scale);
+                        for (int64_t c = 0; c < Dv; ++c) dv_acc[(bk * N + j) * Dv + c] += pb * (double)bf16r(gr[c]);
+                        for (int64_t c = 0; c < D; ++c) {
+                            dq_acc[c] += dsb * (double)bf16r(kr[j * D + c]);
+                            dk_acc[(bk * N + j) * D + c] += dsb * (double)bf16r(qr[c]);
+                        }
+                    }
+                    for (int64_t c = 0; c < D; ++c) dqr[c] = (float)dq_acc[c];
+                }
+            }
+        }
+        free(s); free(p); free(dp); free(scratch);
+    }
+    for (int64_t i = 0; i < B * Hkv * N * D; ++i) dk[i] = (float)dk_acc[i];
+    for (int64_t i = 0; i < B * Hkv * N * Dv; ++i) dv[i] = (float)dv_acc[i];
+    free(dk_acc); free(dv_acc);
+}
+
+/* Causal cross entropy over logits [B,T,V] (src/nn/causal_lm.rs:118-196; examples/causal_lm_tensor.rs:24-118):
+ * with shift, position t is scored against label t+1 and the last position is dropped; labels equal to ignore_index
+ * are skipped.  loss_sum = sum(ln sum exp(x-max) + max - x[label]) on the FP32 row schedule, valid = counted tokens,
+ * dlogits (may be NULL) = (softmax - onehot) * upstream / max(valid,1) for a mean loss with upstream gradient `upstream`. */
+ORC_API void orc_causal_cross_entropy(const float* logits, const int64_t* labels, int64_t batch, int64_t time, int64_t vocab,
+                                      int64_t ignore_index, int shift, float upstream, float* loss_sum, float* valid, float* dlogits) {
+    int64_t steps = shift ? time - 1 : time, count = 0;
+    double total = 0.0;
+    float* scratch = (float*)malloc(sizeof(float) * TILE);
+    if (dlogits) memset(dlogits, 0, sizeof(float) * (size_t)(batch * time * vocab));
+    for (int64_t b = 0; b < batch; ++b)
+        for (int64_t t = 0; t < steps; ++t) {
+            int64_t label = labels[b * time + t + (shift ? 1 : 0)];
+            if (label == ignore_index) continue;
+            ++count;
+        }
+    for (int64_t b = 0; b < batch; ++b)
+        for (int64_t t = 0; t < steps; ++t) {
+            int64_t label = labels[b * time + t + (shift ? 1 : 0)];
+            if (label == ignore_index) continue;
+            const float* x = logits + (b * time + t) * vocab;
+            float mx = row_reduce_map(x, vocab, 1, NULL, NULL, scratch);
+            float dn = row_reduce_map(x, vocab, 0, f_shift_exp, &mx, scratch);
+            total += (double)(-((x[label] - mx) - logf(dn)));   /* NLL of the log-softmax row */
+            if (dlogits) {
+                float* d = dlogits + (b * time + t) * vocab;
+                float k = upstream / (float)(count > 0 ? count : 1);
+                for (int64_t c = 0; c < vocab; ++c) d[c] = (expf(x[c] - mx) / dn - (c == label ? 1.0f : 0.0f)) * k;
+            }
+        }
+    free(scratch);
+    *loss_sum = (float)total; *valid = (float)count;
 }
