@@ -209,6 +209,22 @@ RB_API int32_t rb_repeat_kv_heads_backward(rb_ctx* ctx, const rb_tensor* grad, u
 /* AscendRuntime::bias_add_backward, runtime/mod.rs:183-185 -> affine.rs:24-26: sum of dY over all leading axes. */
 RB_API int32_t rb_bias_add_backward(rb_ctx* ctx, const rb_tensor* grad, const rb_tensor* dbias);
 
+/* Runtime::layer_norm_backward, runtime/mod.rs:449-455 -> normalization.rs:134-152, IR row_programs.rs (LayerNormInputBackward,
+ * LayerNormWeightContributions): [input gradient, weight gradient, bias gradient] from the saved mean and rstd. */
+RB_API int32_t rb_layer_norm_backward(rb_ctx* ctx, const rb_tensor* x, const rb_tensor* weight, const rb_tensor* grad,
+                                      const rb_tensor* mean, const rb_tensor* rstd, const rb_tensor* dx,
+                                      const rb_tensor* dweight, const rb_tensor* dbias);
+/* nn::CausalCrossEntropyConfig::forward_hidden, src/nn/causal_lm.rs:118-196, which chunks tokens through log_softmax
+ * (runtime/mod.rs:327-329) and nll_loss (runtime/mod.rs:222-230, ignore index, sum reduction).  logits FP32 [B,T,V],
+ * labels I32/I64 [B,T]; with shift != 0 position t is scored against label t+1 and the last position of every sequence is
+ * dropped.  loss_sum and valid_tokens are FP32 [1].  dlogits (NULL or FP32 [B,T,V]) receives the gradient of the mean
+ * loss times `upstream`: (softmax - onehot) * upstream / max(valid, 1), zero for rows that are not scored.  A label
+ * outside [0, V) other than ignore_index is never used as an index: its row is left unscored, and a synchronous context
+ * returns RB_INVALID_TENSOR for the call. */
+RB_API int32_t rb_causal_cross_entropy(rb_ctx* ctx, const rb_tensor* logits, const rb_tensor* labels, int64_t ignore_index,
+                                       int32_t shift, float upstream, const rb_tensor* loss_sum,
+                                       const rb_tensor* valid_tokens, const rb_tensor* dlogits);
+
 /* ---- BF16 matrix programs (tcgen05 tensor cores, FP32 accumulation) ------------------------------ */
 /* AscendRuntime::gemm / gemm_into, runtime/mod.rs:346-355 -> matrix.rs:47-59 -> GemmSpec deepgemm/plan.rs:49-80;
  * device program rust-ascend-kernels/src/kernel.rs:11-76.  out = op(A) op(B): contiguous BF16 operands, rank 2

@@ -579,6 +579,24 @@ class B200Runtime:
         _check(client._lib.rb_bias_add_backward(client._ctx, _ref(grad), _ref(db)))
         return db
 
+    @staticmethod
+    def layer_norm_backward(client, input: TensorBuffer, weight: TensorBuffer, grad: TensorBuffer, mean: TensorBuffer, rstd: TensorBuffer):
+        """[input gradient, weight gradient, bias gradient] (runtime/mod.rs:449-455)."""
+        dx, dw, db = client.tensor(input.shape, DType.F32), client.tensor(weight.shape, DType.F32), client.tensor(weight.shape, DType.F32)
+        _check(client._lib.rb_layer_norm_backward(client._ctx, _ref(input), _ref(weight), _ref(grad), _ref(mean), _ref(rstd), _ref(dx), _ref(dw), _ref(db)))
+        return [dx, dw, db]
+
+    @staticmethod
+    def causal_cross_entropy(client, logits: TensorBuffer, labels: TensorBuffer, ignore_index: int = -100, shift: bool = True,
+                             upstream: float = 1.0, with_gradient: bool = True):
+        """[loss_sum [1], valid_tokens [1], dlogits or None]: the CausalLoss of src/nn/causal_lm.rs:118-196 in one pass over
+        the logits, plus the gradient of the mean loss."""
+        loss, valid = client.tensor((1,), DType.F32), client.tensor((1,), DType.F32)
+        d = client.tensor(logits.shape, DType.F32) if with_gradient else None
+        _check(client._lib.rb_causal_cross_entropy(client._ctx, _ref(logits), _ref(labels), C.c_int64(ignore_index), C.c_int32(int(shift)),
+                                                   C.c_float(upstream), _ref(loss), _ref(valid), _ref(d)))
+        return [loss, valid, d]
+
     # -- attention -------------------------------------------------------------------------------
     @staticmethod
     def attention(client, q: TensorBuffer, k: TensorBuffer, v: TensorBuffer, scale: float, mask: TensorBuffer | None = None,
