@@ -193,6 +193,19 @@ RB_API int32_t rb_causal_mask(rb_ctx* ctx, uint64_t query_start, uint64_t key_st
 RB_API int32_t rb_cast(rb_ctx* ctx, const rb_tensor* x, const rb_tensor* y);
 /* AscendRuntime::embedding, runtime/mod.rs:231-233 -> indexing.rs:33-37: out[i,:] = table[ids[i],:]. */
 RB_API int32_t rb_embedding(rb_ctx* ctx, const rb_tensor* table, const rb_tensor* ids, const rb_tensor* out);
+/* AscendRuntime::embedding_backward, runtime/mod.rs:253-256 -> indexing.rs:60-64 -> tensor/embedding.rs:60-78: dense weight
+ * gradient out[num_weights, W] (the row count is out's) from grad ids.shape + [W]; repeated ids accumulate in FP32,
+ * padding_idx (UINT64_MAX = none, else < num_weights) suppresses that row's derivative, scale_grad_by_freq divides each
+ * touched row by its number of occurrences. */
+RB_API int32_t rb_embedding_backward(rb_ctx* ctx, const rb_tensor* grad, const rb_tensor* ids, uint64_t padding_idx,
+                                     int32_t scale_grad_by_freq, const rb_tensor* out);
+/* AscendRuntime::copy_contiguous, runtime/mod.rs:223-225 -> indexing.rs:46-59: a private device copy of a contiguous tensor of
+ * any storage dtype (the saved indices of embedding_with_saved_indices, runtime/mod.rs:249-251). */
+RB_API int32_t rb_copy(rb_ctx* ctx, const rb_tensor* x, const rb_tensor* y);
+/* resize_prefix of runtime/padded_matrix.rs:6-16,24-37 (the worker's zero pad / crop that gemm_padded_bf16_fp32,
+ * runtime/mod.rs:188-204, is built from): y holds x's values wherever the index lies inside x and +0 elsewhere; equal rank
+ * 1..8, positive axes, FP32 or BF16, values moved as bits. */
+RB_API int32_t rb_resize_prefix(rb_ctx* ctx, const rb_tensor* x, const rb_tensor* y);
 
 /* ---- first-order backward programs (FP32) -------------------------------------------------------------- */
 /* AscendRuntime::rms_norm_backward, runtime/mod.rs:411-414 -> normalization.rs:168-186, IR row_programs.rs:189-217:

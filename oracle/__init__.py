@@ -189,6 +189,18 @@ def causal_mask(batch: int, queries: int, keys: int, query_start: int, key_start
     return out
 
 
+def embedding_backward(grad, ids, num_weights: int, padding_idx=None, scale_grad_by_freq: bool = False) -> np.ndarray:
+    """Dense weight gradient [num_weights, W] (rust-ascend-driver/src/tensor/embedding.rs:60-78)."""
+    grad = _f32(grad)
+    ids = np.ascontiguousarray(ids, dtype=np.int64)
+    width = grad.shape[-1]
+    out = np.zeros((num_weights, width), dtype=np.float32)
+    if out.size:
+        lib().orc_embedding_backward(_p(grad), _p(ids), _i64(ids.size), _i64(width), _i64(num_weights),
+                                     _i64(-1 if padding_idx is None else padding_idx), C.c_int(int(scale_grad_by_freq)), _p(out))
+    return out
+
+
 def embedding(table, ids) -> np.ndarray:
     """Row gather (rust-ascend-driver/src/tensor/runtime/indexing.rs:33-37)."""
     table = _f32(table)

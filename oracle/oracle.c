@@ -278,6 +278,25 @@ ORC_API void orc_embedding(const float* table, const int32_t* ids, int64_t count
         memcpy(out + i * width, table + (int64_t)ids[i] * width, sizeof(float) * width);
 }
 
+/* Dense embedding weight gradient (rust-ascend-driver/src/tensor/embedding.rs:60-78; expectation written out in
+ * examples/embedding_tensor.rs:44-53): rows accumulate in position order, the padding row (negative = none) receives
+ * nothing, and with scale each touched row is divided by its number of occurrences afterwards. */
+ORC_API void orc_embedding_backward(const float* grad, const int64_t* ids, int64_t count, int64_t width, int64_t rows,
+                                    int64_t padding, int scale, float* out) {
+    int64_t* freq = (int64_t*)calloc((size_t)(rows + 1), sizeof(int64_t));
+    memset(out, 0, sizeof(float) * (size_t)(rows * width));
+    for (int64_t p = 0; p < count; ++p) {
+        int64_t id = ids[p];
+        if (id == padding) continue;
+        ++freq[id];
+        for (int64_t c = 0; c < width; ++c) out[id * width + c] += grad[p * width + c];
+    }
+    if (scale)
+        for (int64_t r = 0; r < rows; ++r)
+            if (freq[r] != 0) for (int64_t c = 0; c < width; ++c) out[r * width + c] /= (float)freq[r];
+    free(freq);
+}
+
 /* ---------------------------------------------------------------- BF16 GEMM ----------------- */
 /* rust-ascend-kernels/src/tests.rs:93-103: inputs BF16-representable, f64 accumulation over k in
  * increasing order, result cast to f32 and, for BF16 output, rounded by bf16().  Transposes index

@@ -150,6 +150,20 @@ __global__ void __launch_bounds__(256) embedding_kernel(const uint4* table, cons
     }
 }
 
+// The same lookup for rows that are not a multiple of 16 bytes (width 65 FP32 in examples/embedding_tensor.rs:22): rows move
+// as 4- or 2-byte words.
+template <typename I, typename W>
+__global__ void __launch_bounds__(256) embedding_words_kernel(const W* table, const I* ids, W* out, uint64_t count, uint32_t row_words,
+                                                             uint64_t vocab, int* bad) {
+    uint64_t total = count * row_words, stride = (uint64_t)gridDim.x * 256;
+    for (uint64_t i = (uint64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += stride) {
+        uint64_t r = i / row_words; uint32_t c = (uint32_t)(i % row_words);
+        int64_t id = (int64_t)ids[r];
+        if (id < 0 || (uint64_t)id >= vocab) { if (c == 0) atomicExch(bad, 1); out[i] = W(0); continue; }
+        out[i] = table[(uint64_t)id * row_words + c];
+    }
+}
+
 unsigned grid_for(rb_ctx* ctx, uint64_t work_items) {
     uint64_t blocks = (work_items + 255) / 256, cap = (uint64_t)ctx->sm_count * 16;
     return (unsigned)(blocks < cap ? (blocks ? blocks : 1) : cap);
@@ -336,11 +350,27 @@ int32_t rb_embedding(rb_ctx* ctx, const rb_tensor* table, const rb_tensor* ids, 
     if (out->rank != ids->rank + 1 || out->shape[out->rank - 1] != width || elements(out) != count * width)
         return fail(RB_INVALID_TENSOR, "embedding output must be ids.shape + [width]");
     uint64_t row_bytes = width * dtype_size(table->dtype);
-    if (row_bytes == 0 || row_bytes % 16 != 0) return fail(RB_INVALID_TENSOR, "embedding rows must be a positive multiple of 16 bytes");
+    if (row_bytes == 0 || (table->shape[0] == 0 && count != 0)) return fail(RB_INVALID_TENSOR, "embedding needs a positive width and, for any id, at least one table row");
     if (count == 0) return empty_call(ctx);
     RB_TRY(ensure_workspace(ctx, 256));
     int* bad = (int*)ctx->workspace;
     RB_CUDA(ctx, "cudaMemsetAsync", cudaMemsetAsync(bad, 0, sizeof(int), ctx->stream));
+    if (row_bytes % 16 != 0) {
+        const bool w4 = row_bytes % 4 == 0;
+        const uint32_t words = (uint32_t)(row_bytes / (w4 ? 4 : 2));
+        unsigned gw = grid_for(ctx, count * words);
+        const bool i32 = ids->dtype == RB_I32;
+        if (w4 && i32) embedding_words_kernel<int32_t, uint32_t><<<gw, 256, 0, ctx->stream>>>((const uint32_t*)pt, (const int32_t*)pi, (uint32_t*)po, count, words, table->shape[0], bad);
+        else if (w4) embedding_words_kernel<int64_t, uint32_t><<<gw, 256, 0, ctx->stream>>>((const uint32_t*)pt, (const int64_t*)pi, (uint32_t*)po, count, words, table->shape[0], bad);
+        else if (i32) embedding_words_kernel<int32_t, uint16_t><<<gw, 256, 0, ctx->stream>>>((const uint16_t*)pt, (const int32_t*)pi, (uint16_t*)po, count, words, table->shape[0], bad);
+        else embedding_words_kernel<int64_t, uint16_t><<<gw, 256, 0, ctx->stream>>>((const uint16_t*)pt, (const int64_t*)pi, (uint16_t*)po, count, words, table->shape[0], bad);
+        RB_TRY(after_launch(ctx, "embedding"));
+        if (ctx->synchronous) {
+            int h = 0; cudaMemcpy(&h, bad, sizeof(int), cudaMemcpyDeviceToHost);
+            if (h) return fail(RB_INVALID_TENSOR, "embedding id outside [0, vocabulary rows)");
+        }
+        return RB_OK;
+    }
     unsigned g = grid_for(ctx, count * (row_bytes / 16));
     if (ids->dtype == RB_I32) embedding_kernel<int32_t><<<g, 256, 0, ctx->stream>>>((const uint4*)pt, (const int32_t*)pi, (uint4*)po, count, (uint32_t)(row_bytes / 16), table->shape[0], bad);
     else embedding_kernel<int64_t><<<g, 256, 0, ctx->stream>>>((const uint4*)pt, (const int64_t*)pi, (uint4*)po, count, (uint32_t)(row_bytes / 16), table->shape[0], bad);

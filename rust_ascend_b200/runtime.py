@@ -439,6 +439,49 @@ class B200Runtime:
         _check(client._lib.rb_embedding(client._ctx, _ref(weight), _ref(indices), _ref(out)))
         return out
 
+    @staticmethod
+    def embedding_with_saved_indices(client, weight: TensorBuffer, indices: TensorBuffer):
+        """[output, private copy of the indices] (runtime/mod.rs:249-251 -> indexing.rs:38-45)."""
+        if indices.dtype not in (DType.I32, DType.I64):
+            raise InvalidTensor("embedding indices must be INT32 or INT64")
+        saved = B200Runtime.copy_contiguous(client, indices)
+        return [B200Runtime.embedding(client, weight, saved), saved]
+
+    @staticmethod
+    def copy_contiguous(client, input: TensorBuffer) -> TensorBuffer:
+        """Private device copy (runtime/mod.rs:223-225)."""
+        out = client.tensor(input.shape, input.dtype)
+        _check(client._lib.rb_copy(client._ctx, _ref(input), _ref(out)))
+        return out
+
+    @staticmethod
+    def embedding_backward(client, grad: TensorBuffer, indices: TensorBuffer, num_weights: int, padding_idx: int | None = None,
+                           scale_grad_by_freq: bool = False) -> TensorBuffer:
+        """Dense weight gradient [num_weights, W] accumulating repeated ids (runtime/mod.rs:253-256 -> indexing.rs:60-64)."""
+        if padding_idx is not None and not 0 <= padding_idx < num_weights:
+            raise InvalidTensor("embedding padding index must be within the weight rows")
+        if not grad.shape:
+            raise InvalidTensor("embedding gradient must have the index shape followed by the embedding width and floating dtype")
+        out = client.tensor((num_weights, grad.shape[-1]), grad.dtype)
+        _check(client._lib.rb_embedding_backward(client._ctx, _ref(grad), _ref(indices), C.c_uint64(2**64 - 1 if padding_idx is None else padding_idx),
+                                                 C.c_int32(int(scale_grad_by_freq)), _ref(out)))
+        return out
+
+    @staticmethod
+    def resize_prefix(client, input: TensorBuffer, shape) -> TensorBuffer:
+        """Zero pad / crop to `shape` keeping the common prefix of every axis (runtime/padded_matrix.rs:24-37); returns the
+        input itself when nothing changes, as the reference does."""
+        shape = tuple(int(d) for d in shape)
+        if shape == tuple(input.shape):
+            if len(shape) not in range(1, 9) or input.dtype not in (DType.F32, DType.BF16) or any(d <= 0 for d in shape):
+                raise InvalidTensor("prefix resize requires positive matching-rank FP32/BF16 layouts of the same dtype")
+            return input
+        if len(shape) != len(input.shape):
+            raise InvalidTensor("prefix resize requires positive matching-rank FP32/BF16 layouts of the same dtype")
+        out = client.tensor(shape, input.dtype)
+        _check(client._lib.rb_resize_prefix(client._ctx, _ref(input), _ref(out)))
+        return out
+
 
     # -- BF16 matrix programs --------------------------------------------------------------------
     @staticmethod
@@ -495,6 +538,87 @@ class B200Runtime:
         if input.dtype != DType.F32 or weight.dtype != DType.BF16:
             raise InvalidTensor("frozen linear requires FP32 input and BF16 weight storage")
         return B200Runtime.gemm(client, B200Runtime.cast(client, input, DType.BF16), weight, Transpose.No, Transpose.Yes, DType.F32)
+
+
+    # -- matrices whose axes are not multiples of 16 (runtime/padded_matrix.rs, deepgemm/padded.rs) --------------
+    @staticmethod
+    def _padded_spec(a_shape, b_shape, a_dtype, b_dtype, ta: Transpose, tb: Transpose):
+        """PaddedGemmSpec::new (deepgemm/padded.rs:15-41): logical output shape and the physical 16-aligned A, B shapes."""
+        rank = len(a_shape)
+        if rank not in (2, 3) or len(b_shape) != rank or a_dtype not in (DType.F32, DType.BF16) or b_dtype not in (DType.F32, DType.BF16):
+            raise InvalidTensor("padded GEMM requires matching rank-2/3 FP32/BF16 inputs")
+        if rank == 3 and a_shape[0] != b_shape[0]:
+            raise InvalidTensor("padded GEMM does not broadcast batches")
+        m, k = (a_shape[-2], a_shape[-1]) if not ta else (a_shape[-1], a_shape[-2])
+        kb, n = (b_shape[-2], b_shape[-1]) if not tb else (b_shape[-1], b_shape[-2])
+        if k != kb:
+            raise InvalidTensor("padded GEMM logical contraction mismatch")
+
+        def pad(shape):
+            if any(d <= 0 for d in shape[-2:]):
+                raise InvalidTensor("padded GEMM matrix axes must be positive")
+            tail = tuple((d + 15) // 16 * 16 for d in shape[-2:])
+            if any(d > 2**31 - 1 for d in tail):
+                raise InvalidTensor("padded GEMM aligned axis exceeds INT32_MAX")
+            return tuple(shape[:-2]) + tail
+        pa, pb = pad(tuple(a_shape)), pad(tuple(b_shape))
+        if rank == 3 and not 1 <= a_shape[0] <= 4096:
+            raise InvalidTensor("GEMM batch count must be within 1..4096")
+        out = (tuple(a_shape[:-2]) + (m, n))
+        return out, pa, pb
+
+    @staticmethod
+    def _rounded(client, t: TensorBuffer, shape) -> TensorBuffer:
+        return B200Runtime.resize_prefix(client, t if t.dtype == DType.BF16 else B200Runtime.cast(client, t, DType.BF16), shape)
+
+    @staticmethod
+    def gemm_padded_bf16_fp32(client, a: TensorBuffer, b: TensorBuffer, ta: Transpose, tb: Transpose):
+        """[FP32 output cropped to the logical M x N, padded BF16 A, padded BF16 B] for positive M/N/K of any size
+        (runtime/mod.rs:188-191 -> padded_matrix.rs:42-50)."""
+        if a.dtype != DType.F32 or b.dtype != DType.F32:
+            raise InvalidTensor("padded trainable matmul requires FP32 inputs")
+        out_shape, pa, pb = B200Runtime._padded_spec(a.shape, b.shape, a.dtype, b.dtype, ta, tb)
+        a16, b16 = B200Runtime._rounded(client, a, pa), B200Runtime._rounded(client, b, pb)
+        y = B200Runtime.gemm(client, a16, b16, ta, tb, DType.F32)
+        return [B200Runtime.resize_prefix(client, y, out_shape), a16, b16]
+
+    @staticmethod
+    def gemm_padded_bf16_fp32_backward(client, a: TensorBuffer, b: TensorBuffer, grad: TensorBuffer, a_shape, b_shape, ta: Transpose, tb: Transpose):
+        """[FP32 dA, FP32 dB] cropped to the original physical input shapes, from the saved padded BF16 operands and the
+        logical FP32 dY (runtime/mod.rs:192-197 -> padded_matrix.rs:51-66)."""
+        out_shape, pa, pb = B200Runtime._padded_spec(tuple(a_shape), tuple(b_shape), DType.F32, DType.F32, ta, tb)
+        if (tuple(a.shape), a.dtype) != (pa, DType.BF16) or (tuple(b.shape), b.dtype) != (pb, DType.BF16) or (tuple(grad.shape), grad.dtype) != (out_shape, DType.F32):
+            raise InvalidTensor("padded matmul backward saved input or logical dY layout mismatch")
+        g = B200Runtime._rounded(client, grad, B200Runtime._gemm_shape(a, b, ta, tb))
+        no, yes = Transpose.No, Transpose.Yes
+        opposite = lambda t: yes if t == no else no
+        da = B200Runtime.gemm(client, g, b, no, opposite(tb), DType.F32) if ta == no else B200Runtime.gemm(client, b, g, tb, yes, DType.F32)
+        db = B200Runtime.gemm(client, a, g, opposite(ta), no, DType.F32) if tb == no else B200Runtime.gemm(client, g, a, yes, ta, DType.F32)
+        return [B200Runtime.resize_prefix(client, da, a_shape), B200Runtime.resize_prefix(client, db, b_shape)]
+
+    @staticmethod
+    def linear_frozen_padded_bf16_fp32(client, input: TensorBuffer, weight: TensorBuffer):
+        """[FP32 Y [M,N], BF16 weight as used (the caller's handle when already aligned)] for FP32 X [M,K] and a fixed BF16
+        W [N,K] of any positive size (runtime/mod.rs:198-200 -> padded_matrix.rs:67-79)."""
+        if len(input.shape) != 2 or len(weight.shape) != 2 or input.dtype != DType.F32 or weight.dtype != DType.BF16:
+            raise InvalidTensor("frozen padded linear requires rank-2 FP32 input and fixed BF16 weight")
+        out_shape, pa, pb = B200Runtime._padded_spec(input.shape, weight.shape, input.dtype, weight.dtype, Transpose.No, Transpose.Yes)
+        x16 = B200Runtime._rounded(client, input, pa)
+        w16 = B200Runtime.resize_prefix(client, weight, pb)
+        y = B200Runtime.gemm(client, x16, w16, Transpose.No, Transpose.Yes, DType.F32)
+        return [B200Runtime.resize_prefix(client, y, out_shape), w16]
+
+    @staticmethod
+    def linear_frozen_padded_bf16_fp32_backward(client, weight: TensorBuffer, grad: TensorBuffer, input_shape, weight_shape) -> TensorBuffer:
+        """FP32 dX [M,K] from the padded fixed weight and the logical FP32 dY (runtime/mod.rs:201-204 -> padded_matrix.rs:80-90)."""
+        if len(input_shape) != 2 or len(weight_shape) != 2:
+            raise InvalidTensor("frozen padded linear backward requires rank-2 shapes")
+        out_shape, pa, pb = B200Runtime._padded_spec(tuple(input_shape), tuple(weight_shape), DType.F32, DType.BF16, Transpose.No, Transpose.Yes)
+        if (tuple(weight.shape), weight.dtype) != (pb, DType.BF16) or (tuple(grad.shape), grad.dtype) != (out_shape, DType.F32):
+            raise InvalidTensor("frozen padded linear saved weight or dY layout mismatch")
+        g = B200Runtime._rounded(client, grad, (pa[0], pb[0]))
+        dx = B200Runtime.gemm(client, g, weight, Transpose.No, Transpose.No, DType.F32)
+        return B200Runtime.resize_prefix(client, dx, input_shape)
 
 
     # -- first-order backward --------------------------------------------------------------------
