@@ -361,8 +361,8 @@ def decoder_extra(client, pk, rank, world, dist):
         candidates = [{"micro_batches": 1, "sms_left_to_nccl": 0, "nccl_max_ctas": 0}]
     else:
         from rust_ascend_b200.distributed import NcclCommunicator, TorchControl
-        # No NVLink multicast binding: the watchdog may end a rank while collectives are pending, and a rank that
-        # leaves while bound to a multicast object can fault its peers.  Ring/tree all-reduce is used instead.
+        # NVLS (in-switch reduction) stays off: the watchdog may end a rank while collectives are pending, and a rank that
+        # leaves while its memory is bound to an NVLS group can fault its peers.  Ring/tree all-reduce is used instead.
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         candidates = [{"micro_batches": 2, "sms_left_to_nccl": NCCL_CTAS, "nccl_max_ctas": NCCL_CTAS},   # all-reduce under the other group's GEMMs
                       {"micro_batches": 1, "sms_left_to_nccl": 0, "nccl_max_ctas": 0},                    # sequential, NCCL at full width
