@@ -125,7 +125,7 @@ def run_reference(args):
     orc.build()
     cores = orc.use_all_cores()
     rate, dt = cpu_linear_rate(orc, 16)
-    total_seconds = 90.0  # target for warmup + steps together
+    total_seconds = args.reference_seconds  # target for warmup + steps together
     rows = int(max(1, min(M, (rate * 1e12 * total_seconds / (args.steps + args.warmup)) / (2.0 * N * K))))
     rng = np.random.default_rng(1)
     w = (rng.standard_normal((N, K), dtype=np.float32) * 0.02)
@@ -259,27 +259,34 @@ def run_ours(args):
             print(json.dumps(line), flush=True)
 
     def give_up():
-        emit(f"extras did not finish within {args.extras_timeout} s and were abandoned")
-        os._exit(0)
+        note = f"extras did not finish within {args.extras_timeout} s; what had finished by then is reported"
+        try:
+            emit(note)
+        except Exception:                      # the main thread was writing into the dictionary being printed
+            emitted.clear()
+            line["extras"] = {}
+            emit(note)
+        finally:
+            os._exit(0)
 
     if not args.no_extras:
         dog = threading.Timer(args.extras_timeout, give_up)
         dog.daemon = True
         dog.start()
         try:
-            line["extras"] = extras(client, RT, pk, args, rank, world, dist)
+            extras(client, RT, pk, args, rank, world, dist, line["extras"])
         except Exception as error:  # an extra must never cost the headline
-            line["extras"] = {"error": f"{type(error).__name__}: {error}"}
+            line["extras"]["error"] = f"{type(error).__name__}: {error}"
         dog.cancel()
     emit()
 
 
-def extras(client, RT, pk, args, rank, world, dist):
-    """Secondary kernels of the same hot path, each against its own roofline (reported, not the headline)."""
+def extras(client, RT, pk, args, rank, world, dist, out):
+    """Secondary kernels of the same hot path, each against its own roofline (reported, not the headline).  Results are
+    written into `out` as they arrive, so that a run cut short by the watchdog still reports what finished."""
     from rust_ascend_b200 import DType
-    out = {}
     if world > 1:
-        out["tp_decoder"] = decoder_extra(client, pk, rank, world, dist)
+        decoder_extra(client, pk, rank, world, dist, out)
         return out
     rows, width = 4096, 4096
     rng = np.random.default_rng(0)
@@ -317,7 +324,7 @@ def extras(client, RT, pk, args, rank, world, dist):
         for t in s:
             client.free(t.handle)
     out.update(attention_extra(client, RT, pk))
-    out["tp_decoder"] = decoder_extra(client, pk, rank, world, dist)
+    decoder_extra(client, pk, rank, world, dist, out)
     return out
 
 
@@ -351,40 +358,82 @@ def attention_extra(client, RT, pk):
     return out
 
 
-def decoder_extra(client, pk, rank, world, dist):
-    """Config 5: Llama-style stack, 8 layers, T = 8 x 2048, tensor-parallel over `world` GPUs with NCCL all-reduces.
-    For world > 1 a few schedules are timed on the same resident model and the fastest is the reported value."""
+def decoder_candidates(world: int, sequences: int = 8):
+    """What the decoder extra times at `world` GPUs: pure tensor parallelism first (three schedules), then tensor-parallel
+    groups of world/2, world/4, ... GPUs that each take their own share of the sequences, and last plain replicas (every GPU
+    runs whole sequences, no exchange).  Every entry names its tensor-parallel degree `tp`; the others split the batch."""
+    overlap = {"micro_batches": 2, "sms_left_to_nccl": NCCL_CTAS, "nccl_max_ctas": NCCL_CTAS}   # all-reduce under the other group's GEMMs
+    plain = {"micro_batches": 1, "sms_left_to_nccl": 0, "nccl_max_ctas": 0}                      # sequential, NCCL at full width
+    if world == 1:
+        return [dict(plain, tp=1)]
+    out = [dict(overlap, tp=world), dict(plain, tp=world), dict(plain, tp=world, micro_batches=2)]
+    tp = world // 2
+    while tp >= 1:
+        per_group = sequences * tp // world
+        if per_group >= 1 and sequences * tp % world == 0:
+            if tp > 1 and per_group >= 2:
+                out.append(dict(overlap, tp=tp))
+            out.append(dict(plain, tp=tp))
+        tp //= 2
+    return out
+
+
+def decoder_extra(client, pk, rank, world, dist, sink):
+    """Config 5: Llama-style stack, 8 layers, T = 8 x 2048.  The reported value is tensor parallelism over all `world` GPUs
+    with NCCL all-reduces (fastest of three schedules); the same forward with smaller tensor-parallel groups that split the
+    sequences between them is timed too and reported beside it, labelled with its parallelism."""
     from rust_ascend_b200.decoder import LlamaConfig, TensorParallelDecoder
     cfg = LlamaConfig()
-    tokens = np.random.default_rng(5).integers(0, cfg.vocab, size=(8, 2048)).astype(np.int32)
-    if world == 1:
-        candidates = [{"micro_batches": 1, "sms_left_to_nccl": 0, "nccl_max_ctas": 0}]
-    else:
-        from rust_ascend_b200.distributed import NcclCommunicator, TorchControl
+    sequences, seq = 8, 2048
+    tokens = np.random.default_rng(5).integers(0, cfg.vocab, size=(sequences, seq)).astype(np.int32)
+    if world > 1:
+        from rust_ascend_b200.distributed import GroupControl, NcclCommunicator, TorchControl, tensor_parallel_groups
         # NVLS (in-switch reduction) stays off: the watchdog may end a rank while collectives are pending, and a rank that
         # leaves while its memory is bound to an NVLS group can fault its peers.  Ring/tree all-reduce is used instead.
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-        candidates = [{"micro_batches": 2, "sms_left_to_nccl": NCCL_CTAS, "nccl_max_ctas": NCCL_CTAS},   # all-reduce under the other group's GEMMs
-                      {"micro_batches": 1, "sms_left_to_nccl": 0, "nccl_max_ctas": 0},                    # sequential, NCCL at full width
-                      {"micro_batches": 2, "sms_left_to_nccl": 0, "nccl_max_ctas": 0}]
-    comms, model, results = {}, None, []
-    for cand in candidates:
+    comms, models, results = {}, {}, []
+    total_flops = cfg.flops(sequences * seq, seq)
+
+    def summary():
+        pure = [r for r in results if r["tp"] == world]
+        best = min(pure, key=lambda r: r["ms_per_forward"])
+        tf = total_flops / (best["ms_per_forward"] * 1e-3) / 1e12
+        out = {"value": tf, "unit": "TFLOP/s (whole job)", "ms_per_forward": best["ms_per_forward"], "n_gpus": world, "cuda_graph": True,
+               "parallelism": f"tp{world}", "schedule": best, "schedules_timed": list(results),
+               "config": "8 layers, hidden 4096, 32q/8kv heads, ffn 14336, vocab 32000, batch 8 x seq 2048, BF16",
+               "frac_of_sustained_peak_per_gpu": tf / world / pk["bf16_tflops_sustained"]}
+        mixed = [r for r in results if r["tp"] != world]
+        if mixed:
+            b = min(mixed, key=lambda r: r["ms_per_forward"])
+            out["smaller_groups_best"] = {"parallelism": b["parallelism"], "ms_per_forward": b["ms_per_forward"],
+                                          "value": total_flops / (b["ms_per_forward"] * 1e-3) / 1e12, "unit": "TFLOP/s (whole job)"}
+        return out
+
+    for cand in decoder_candidates(world, sequences):
+        tp = cand["tp"]
+        groups = world // tp
+        group, tp_rank = rank // tp, rank % tp
         comm = None
-        if world > 1:
+        if tp > 1:
             cap = cand["nccl_max_ctas"]
-            if cap not in comms:
+            if (tp, cap) not in comms:
                 if cap:
                     os.environ["RUDA_NCCL_MAX_CTAS"] = str(cap)
                 else:
                     os.environ.pop("RUDA_NCCL_MAX_CTAS", None)
-                comms[cap] = NcclCommunicator.initialize(TorchControl(), client)
-            comm = comms[cap]
-        if model is None:
-            model = TensorParallelDecoder(client, cfg, 8, 2048, comm=comm, rank=rank, world=world, micro_batches=cand["micro_batches"],
-                                          sm_reserve=cand["sms_left_to_nccl"], use_graph=True)
+                control = TorchControl() if tp == world else GroupControl(TorchControl(), tensor_parallel_groups(world, tp)[group])
+                comms[(tp, cap)] = NcclCommunicator.initialize(control, client)
+            comm = comms[(tp, cap)]
+        per_group = sequences // groups
+        if tp not in models:
+            for other in models.values():
+                other.close()
+            models[tp] = TensorParallelDecoder(client, cfg, per_group, seq, comm=comm, rank=tp_rank, world=tp, micro_batches=cand["micro_batches"],
+                                               sm_reserve=cand["sms_left_to_nccl"], use_graph=True)
         else:
-            model.configure(comm, cand["micro_batches"], cand["sms_left_to_nccl"], True)
-        model.forward(tokens)
+            models[tp].configure(comm, cand["micro_batches"], cand["sms_left_to_nccl"], True)
+        model = models[tp]
+        model.forward(tokens[group * per_group:(group + 1) * per_group])
         for _ in range(2):
             model.forward()
         client.sync()
@@ -395,14 +444,13 @@ def decoder_extra(client, pk, rank, world, dist):
         for _ in range(steps):
             model.forward()
         ms = max_over_ranks(dist, client.end_profile() / steps)
-        results.append(dict(cand, ms_per_forward=ms, launches_per_forward=model.launches_per_forward, all_reduces_per_forward=model.collectives_per_forward))
-    model.close()
-    best = min(results, key=lambda r: r["ms_per_forward"])
-    tf = cfg.flops(8 * 2048, 2048) / (best["ms_per_forward"] * 1e-3) / 1e12
-    return {"value": tf, "unit": "TFLOP/s (whole job)", "ms_per_forward": best["ms_per_forward"], "n_gpus": world, "cuda_graph": True,
-            "schedule": best, "schedules_timed": results,
-            "config": "8 layers, hidden 4096, 32q/8kv heads, ffn 14336, vocab 32000, batch 8 x seq 2048, BF16",
-            "frac_of_sustained_peak_per_gpu": tf / world / pk["bf16_tflops_sustained"]}
+        label = f"tp{tp}" if groups == 1 else (f"tp{tp} x {groups} groups of {per_group} sequences" if tp > 1 else f"{groups} replicas of {per_group} sequences, no exchange")
+        results.append(dict(cand, parallelism=label, ms_per_forward=ms, launches_per_forward=model.launches_per_forward,
+                            all_reduces_per_forward=model.collectives_per_forward))
+        sink["tp_decoder"] = summary()
+    for model in models.values():
+        model.close()
+    return sink["tp_decoder"]
 
 
 def run_single_kernel(args):
@@ -451,6 +499,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--extras-timeout", type=float, default=150.0, help="seconds before the secondary measurements are abandoned")
+    ap.add_argument("--reference-seconds", type=float, default=90.0, help="CPU time the reference arm aims to spend over warm-up and steps together")
     ap.add_argument("--kernel", default=None, choices=["gemm", "attention", "rms_norm"], help="time one kernel alone (profiling helper)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

@@ -47,6 +47,32 @@ class SingleControl:
         return [bytes(payload)]
 
 
+class GroupControl:
+    """A subset of a parent control plane's ranks seen as a world of its own (group-local `rank`, `world_size`), for one
+    communicator per tensor-parallel group when the job also splits its batch across groups.  Every rank of the parent
+    must enter the same number of `all_gather_bytes` rounds, which holds when all groups run the same initialisation at
+    the same time; each group reads only its members' replies."""
+
+    def __init__(self, parent, members):
+        self._parent, self._members = parent, [int(m) for m in members]
+        if len(set(self._members)) != len(self._members) or any(not 0 <= m < parent.world_size for m in self._members):
+            raise ContractError("group members must be distinct ranks of the parent world")
+        if parent.rank not in self._members:
+            raise ContractError(f"rank {parent.rank} is not a member of the group {self._members}")
+        self.rank, self.world_size = self._members.index(parent.rank), len(self._members)
+
+    def all_gather_bytes(self, payload: bytes) -> list[bytes]:
+        replies = self._parent.all_gather_bytes(payload)
+        return [replies[m] for m in self._members]
+
+
+def tensor_parallel_groups(world_size: int, tensor_parallel: int) -> list[list[int]]:
+    """Ranks [g*tp, (g+1)*tp) form tensor-parallel group g; the world_size/tp groups each take their own sequences."""
+    if tensor_parallel < 1 or world_size % tensor_parallel:
+        raise ContractError("the tensor-parallel degree must divide the world size")
+    return [list(range(g * tensor_parallel, (g + 1) * tensor_parallel)) for g in range(world_size // tensor_parallel)]
+
+
 def failure_bytes(error) -> bytes:
     return b"\x01" + str(error).encode()
 

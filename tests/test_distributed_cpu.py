@@ -134,3 +134,54 @@ def test_tensor_parallel_sharding_equals_unsharded_model_on_cpu_ranks():
         mp.spawn(_tp_worker, args=(world, port, results), nprocs=world, join=True)
         err, scale = results["err"], results["scale"]
     assert err <= 0.03 * scale + 1e-3, (err, scale)   # BF16 partial sums round differently from the unsharded sum
+
+
+class GroupFake:
+    """Records which root id each rank was initialised with; the id names the global rank that made it."""
+
+    def __init__(self, client):
+        self.global_rank = client
+        self.rank, self.world_size, self.root = 0, 1, None
+
+    def root_info(self):
+        return bytes([self.global_rank]) * 128
+
+    def initialize(self, root, rank, world_size):
+        self.rank, self.world_size, self.root = rank, world_size, root[0]
+        return self
+
+
+def _group_worker(rank, world, port, tp, results):
+    dist = _init(rank, world, port)
+    from rust_ascend_b200.distributed import GroupControl, NcclCommunicator, TorchControl, tensor_parallel_groups
+    groups = tensor_parallel_groups(world, tp)
+    mine = next(g for g in groups if rank in g)
+    control = GroupControl(TorchControl(), mine)
+    comm = NcclCommunicator.initialize(control, rank, native_factory=GroupFake)
+    gathered = control.all_gather_bytes(bytes([rank]))
+    results[rank] = (comm.rank, comm.world_size, comm.native.root, [b[0] for b in gathered])
+    dist.destroy_process_group()
+
+
+def test_one_communicator_per_tensor_parallel_group():
+    # Four ranks, two tensor-parallel groups of two: each group's communicator is rooted at its own first rank and the
+    # group-local control plane sees only its members.
+    world, tp, port = 4, 2, _free_port()
+    with mp.Manager() as manager:
+        results = manager.dict()
+        mp.spawn(_group_worker, args=(world, port, tp, results), nprocs=world, join=True)
+        results = dict(results)
+    assert results == {0: (0, 2, 0, [0, 1]), 1: (1, 2, 0, [0, 1]), 2: (0, 2, 2, [2, 3]), 3: (1, 2, 2, [2, 3])}
+
+
+def test_group_rules():
+    from rust_ascend_b200.distributed import ContractError, GroupControl, SingleControl, tensor_parallel_groups
+    assert tensor_parallel_groups(8, 2) == [[0, 1], [2, 3], [4, 5], [6, 7]]
+    assert tensor_parallel_groups(8, 8) == [list(range(8))] and tensor_parallel_groups(4, 1) == [[0], [1], [2], [3]]
+    with pytest.raises(ContractError):
+        tensor_parallel_groups(8, 3)
+    with pytest.raises(ContractError):
+        GroupControl(SingleControl(), [1])
+    with pytest.raises(ContractError):
+        GroupControl(SingleControl(), [0, 0])
+    assert GroupControl(SingleControl(), [0]).all_gather_bytes(b"x") == [b"x"]
