@@ -281,6 +281,49 @@ RB_API int32_t rb_attention(rb_ctx* ctx, const rb_tensor* q, const rb_tensor* k,
                             const rb_tensor* cos, const rb_tensor* sin, int32_t rotary_layout, int32_t out_layout,
                             const rb_tensor* out);
 
+/* ---- peer memory and the fused tensor-parallel exchange (no counterpart in the reference: its row-parallel projection is a
+ * GEMM followed by a vendor all-reduce, runtime/hccl.rs:386-548; src/distributed.rs:139-156) ------------------------- */
+#define RB_MAX_PEERS 8
+/* This entry has no counterpart in the reference.  Exports a storage of this process as a 64-byte token (CUDA IPC) that another process of
+ * the node passes to rb_peer_open; tokens travel over the control plane that carries the communicator's root id
+ * (src/distributed.rs:74-110). */
+RB_API int32_t rb_peer_export(rb_ctx* ctx, uint64_t handle, uint8_t token[64]);
+/* This entry has no counterpart in the reference.  Opens a peer's token as a storage handle of `bytes` bytes whose device address is the
+ * peer's memory; the handle is used like any other in rb_tensor descriptors.  Close it with rb_peer_close, not rb_free. */
+RB_API int32_t rb_peer_open(rb_ctx* ctx, const uint8_t token[64], uint64_t bytes, uint64_t* handle);
+/* This entry has no counterpart in the reference.  Drains the stream, forgets the handle and unmaps the peer's memory. */
+RB_API int32_t rb_peer_close(rb_ctx* ctx, uint64_t handle);
+/* Row-parallel Linear with the reduce-scatter half of its all-reduce fused into the epilogue; stands where the reference runs
+ * gemm (runtime/mod.rs:346-349) and then HcclCommunicator::reduce_scatter (src/distributed.rs:139-156).  a BF16 [T, K],
+ * b BF16 [H, K] (this rank's K shard); T a multiple of 128 * world, H of 64.  Rows [o*T/world, (o+1)*T/world) of the partial
+ * product are stored into staging[o] (BF16 [world, T/world, H], rank o's memory) at slot [rank], and every 32-row slice is
+ * announced by adding 1 to word [rank] of flags[o] (INT32 [world + 1], rank o's memory).  rb_gemm_scatter_signals gives the
+ * number of announcements one call makes per owner. */
+RB_API int32_t rb_gemm_scatter(rb_ctx* ctx, const rb_tensor* a, const rb_tensor* b, uint32_t rank, uint32_t world,
+                               const rb_tensor* const* staging, const rb_tensor* const* flags);
+/* This entry has no counterpart in the reference.  Announcements per owner of one rb_gemm_scatter call with T tokens and H columns (0 when
+ * the shape is not accepted). */
+RB_API uint32_t rb_gemm_scatter_signals(uint64_t tokens, uint64_t hidden, uint32_t world);
+/* This entry has no counterpart in the reference.  Waits on this GPU, with a 2 s limit, until words [0, world) of `flags` (INT32
+ * [world + 1], local memory that peers add to) have each grown by `count` beyond the running target kept in word [world],
+ * then advances the target.  On expiry the next rb_sync reports RB_SERVER_UNHEALTHY; nothing faults. */
+RB_API int32_t rb_peer_wait(rb_ctx* ctx, const rb_tensor* flags, uint32_t world, uint32_t count);
+/* This entry has no counterpart in the reference.  Adds 1 to word [rank] of every flags[d] (INT32 [world + 1], rank d's memory) once
+ * everything enqueued before it on this context has finished; with rb_peer_wait(count = 1) on every rank this is a barrier
+ * between the GPUs that never leaves the stream. */
+RB_API int32_t rb_peer_signal(rb_ctx* ctx, uint32_t rank, uint32_t world, const rb_tensor* const* flags);
+/* The rest of the fused all-reduce, on the rows this rank owns; stands where the reference runs the all-reduce's second half
+ * (all_gather, src/distributed.rs:121-138) and then rms_norm (runtime/mod.rs:405-408) on the full tensor.  Sums the `world`
+ * staged partials (staging BF16 [world, rows, width], may be NULL) in rank order in FP32, rounds once to BF16, adds the residual
+ * x_in (BF16 [rows, width], may be NULL) with the rounding of rb_add_rms_norm, stores the new residual to x_out (may be NULL),
+ * applies RMSNorm with `weight` (NULL: no normalisation, which makes scatter + this call a plain all-reduce), and stores the rows into every destinations[d] (BF16 [world * rows, width], rank
+ * d's memory) at row offset rank * rows; then adds 1 to word [rank] of flags[d].  `done` is one zeroed INT32 word of local
+ * scratch. */
+RB_API int32_t rb_reduce_norm_push(rb_ctx* ctx, const rb_tensor* staging, const rb_tensor* x_in, const rb_tensor* weight,
+                                   double epsilon, const rb_tensor* x_out, uint32_t rank, uint32_t world,
+                                   const rb_tensor* const* destinations, const rb_tensor* const* flags,
+                                   const rb_tensor* done);
+
 /* ---- collectives: NCCL over NVLink 5 / NVSwitch in place of HCCL ----------------------------------------------- */
 typedef struct rb_comm rb_comm;
 /* HcclGetRootInfo, runtime/hccl.rs:340-357: rank 0 creates the 128-byte id (ncclUniqueId) that the control plane

@@ -34,3 +34,27 @@ RB_HD uint32_t rb_attention_blocks(uint32_t M, uint32_t N, int causal, int64_t d
     const int64_t need = last_q / block + 1;
     return need < (int64_t)all ? (uint32_t)need : all;
 }
+
+// Scatter GEMM (row-parallel projection whose output rows belong to `world` owners of rows_per_owner rows each).
+// Tile t of a rank is the raster tile shifted by `tile_shift` tile rows, so that rank r starts in the rows of owner r + 1 and
+// the ranks write to different owners at any moment instead of all to the same one.
+RB_HD void rb_scatter_tile(uint32_t t, uint32_t tiles_m, uint32_t tiles_n, uint32_t group_m, uint32_t tile_shift, uint32_t& tm, uint32_t& tn) {
+    uint32_t batch;
+    rb_tile_coords(t, tiles_m, tiles_n, group_m, batch, tm, tn);
+    tm += tile_shift;
+    if (tm >= tiles_m) tm -= tiles_m;
+}
+RB_HD uint32_t rb_scatter_shift(uint32_t rank, uint32_t world, uint32_t rows_per_owner, uint32_t tile_rows) {
+    return ((rank + 1) % world) * (rows_per_owner / tile_rows);
+}
+// Owner of output row `row` and the row's index inside the owner's block.
+RB_HD void rb_scatter_owner(uint32_t row, uint32_t rows_per_owner, uint32_t& owner, uint32_t& local_row) {
+    owner = row / rows_per_owner;
+    local_row = row - owner * rows_per_owner;
+}
+// A warp's copy-out of a 32-row x 64-column BF16 slice (256 words of 16 bytes): in step `it` lane `lane` moves word `j` of
+// row `r`, so that eight neighbouring lanes cover one 128-byte row segment.
+RB_HD void rb_scatter_word(uint32_t it, uint32_t lane, uint32_t& r, uint32_t& j) {
+    const uint32_t idx = it * 32 + lane;
+    r = idx >> 3; j = idx & 7;
+}

@@ -73,6 +73,33 @@ def rope_tables(positions: int, head_dim: int, theta: float):
     return np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
 
 
+def fused_schedule(layers: int, micro_batches: int):
+    """Order of one forward's steps in fused mode (exchange folded into the kernels, residual stream sharded by rows).
+    Pure function: the launch plan is emitted from it and the CPU protocol model replays it.  Steps:
+    ("embed", mb) | ("wait_scatter", mb) | ("push", mb, layer, which) | ("wait_gather", mb) | ("attention_block", mb, layer) |
+    ("ffn_block", mb, layer) | ("scatter", mb, layer, "wo" or "wd") | ("lm_head", mb) | ("barrier",).
+    A push reduces the staged partials of the scatter before it (none for the very first), so its wait comes first; the
+    closing barrier keeps a fast rank's next forward from storing into buffers that a slow rank is still reading."""
+    steps = [("embed", mb) for mb in range(micro_batches)]
+    pending = [False] * micro_batches
+    for layer in range(layers + 1):
+        for mb in range(micro_batches):
+            if pending[mb]:
+                steps.append(("wait_scatter", mb))
+            steps += [("push", mb, layer, 0), ("wait_gather", mb)]
+            if layer == layers:
+                steps.append(("lm_head", mb))
+                continue
+            steps += [("attention_block", mb, layer), ("scatter", mb, layer, "wo")]
+            pending[mb] = True
+        if layer == layers:
+            break
+        for mb in range(micro_batches):
+            steps += [("wait_scatter", mb), ("push", mb, layer, 1), ("wait_gather", mb), ("ffn_block", mb, layer), ("scatter", mb, layer, "wd")]
+    steps.append(("barrier",))
+    return steps
+
+
 class WeightSource:
     """Seeded N(0, 0.02) BF16 weights.  `exact=True` draws every full matrix from its own seed so that any shard of
     it is identical on every rank and for every world size (parity tests); `exact=False` tiles one random block,
@@ -107,7 +134,8 @@ class TensorParallelDecoder:
     stream.  `sm_reserve` SMs are then kept free of the persistent GEMM so that the collective can run beside it."""
 
     def __init__(self, client: ComputeClient, cfg: LlamaConfig, batch: int, seq: int, comm=None, rank: int = 0, world: int = 1,
-                 seed: int = 0, exact_weights: bool = False, micro_batches: int = 1, sm_reserve: int = 0, use_graph: bool = False):
+                 seed: int = 0, exact_weights: bool = False, micro_batches: int = 1, sm_reserve: int = 0, use_graph: bool = False,
+                 fused: bool = False):
         if world > 1 and comm is None:
             raise InvalidTensor("a communicator is required for tensor parallelism")
         if cfg.head_dim != 128:
@@ -150,9 +178,10 @@ class TensorParallelDecoder:
         self.tokens_dev = client.tensor((batch, seq), DType.I32)
         self.scale = 1.0 / float(np.sqrt(d))
         self._graph = None
-        self.configure(comm, micro_batches, sm_reserve, use_graph)
+        self._exchanges, self._peer_h, self._x_own = [], None, None
+        self.configure(comm, micro_batches, sm_reserve, use_graph, fused)
 
-    def configure(self, comm, micro_batches: int = 1, sm_reserve: int = 0, use_graph: bool = False) -> None:
+    def configure(self, comm, micro_batches: int = 1, sm_reserve: int = 0, use_graph: bool = False, fused: bool = False) -> None:
         """(Re)builds the launch plan, and the recorded graph if asked for, on the weights and buffers already resident.
         Lets a caller compare schedules (micro batches, SMs left to NCCL, communicators with different CTA limits)
         without loading the model again."""
@@ -160,15 +189,21 @@ class TensorParallelDecoder:
         client = self.client
         if self.batch % micro_batches or (self.batch // micro_batches * self.seq) % 16:
             raise InvalidTensor("micro batches must hold whole sequences")
+        if fused and (self.world < 2 or (self.tokens // micro_batches) % (128 * self.world) or self.cfg.hidden % 64):
+            raise InvalidTensor("fused exchange needs at least two ranks and micro batches of a multiple of 128 * world tokens")
         self.close()
-        self.comm, self.micro = comm, micro_batches
+        self.comm, self.micro, self.fused = comm, micro_batches, fused
         self._keep = []          # ctypes structures referenced by the plan
         self._steps = []         # (function, argument tuple)
         self.launches_per_forward = 0
         self.collectives_per_forward = 0
+        self.fused_exchanges_per_forward = 0     # scatter-GEMM + owner-side reduce pairs that stand where all-reduces stood
         sms = client.properties()["sm_count"]
         _check(client._lib.rb_set_sm_limit(client._ctx, C.c_int32(sms - sm_reserve if sm_reserve else 0)))
-        self._build_plan()
+        if fused:
+            self._build_fused_plan()
+        else:
+            self._build_plan()
         if use_graph:
             self._run_plan()                     # first use of every kernel and every workspace size happens outside the recording
             client.sync()
@@ -263,15 +298,88 @@ class TensorParallelDecoder:
                 self._gemm(act, lw["wd"], proj)
                 reduce(mb, proj)
 
+    # -- fused mode: the exchange lives inside the kernels, the residual stream is sharded by rows ------------------
+    def _release_fused(self) -> None:
+        """Collective: every rank of the group drops its exchange buffers in the same order."""
+        for ex in self._exchanges:
+            ex.close()
+        if self._peer_h is not None:
+            self._peer_h.close()
+        if self._x_own is not None:
+            self.client.free(self._x_own.handle)
+        self._exchanges, self._peer_h, self._x_own = [], None, None
+
+    def _build_fused_plan(self):
+        from .fused import BARRIER, GATHER, SCATTER, FusedExchange, PeerBuffer
+        cfg, p, c, ctx = self.cfg, self.plan, self.client, self.client._ctx
+        hq, hkv, n = p["q_heads"], p["kv_heads"], self.micro
+        b, hidden = self.batch // n, cfg.hidden
+        tm = self.tokens // n                      # tokens of one micro batch
+        rows = tm // self.world                    # rows of it this rank owns
+        control = self.comm.control
+        self._peer_h = PeerBuffer(c, control, self.tokens * hidden * 2)
+        self._exchanges = [FusedExchange(c, control, tm, hidden, activations=self._peer_h, activation_offset=mb * tm * hidden * 2) for mb in range(n)]
+        self._x_own = c.tensor((n, rows, hidden), DType.BF16)
+        eps = cfg.eps
+        keep = self._keep
+
+        def x_own(mb):
+            return TensorBuffer(self._x_own.handle, (rows, hidden), DType.BF16, None, offset=mb * rows * hidden * 2)
+
+        for step in fused_schedule(cfg.layers, n):
+            kind = step[0]
+            if kind == "barrier":
+                ex = self._exchanges[0]
+                self._op("rb_peer_signal", *ex.signal_args(keep))
+                self._op("rb_peer_wait", *ex.wait_args(BARRIER, 1, keep))
+                continue
+            mb = step[1]
+            ex = self._exchanges[mb]
+            h = ex.gathered()
+            if kind == "embed":
+                first = mb * tm + self.rank * rows          # this rank's rows of the micro batch, as flat token positions
+                ids = TensorBuffer(self.tokens_dev.handle, (rows,), DType.I32, None, offset=first * 4)
+                self._op("rb_embedding", ctx, self._t(self.embedding), self._t(ids), self._t(x_own(mb)))
+            elif kind == "wait_scatter":
+                self._op("rb_peer_wait", *ex.wait_args(SCATTER, ex.signals, keep))
+            elif kind == "wait_gather":
+                self._op("rb_peer_wait", *ex.wait_args(GATHER, 1, keep))
+            elif kind == "push":
+                _, _, layer, which = step
+                lw = self.layers[layer] if layer < cfg.layers else None
+                weight = self.final_norm if lw is None else (lw["norm1"] if which == 0 else lw["norm2"])
+                very_first = layer == 0 and which == 0     # nothing staged yet: normalise the embedding rows
+                self._op("rb_reduce_norm_push", *ex.push_args(not very_first, x_own(mb), weight, eps, None if very_first else x_own(mb), keep))
+                self.fused_exchanges_per_forward += 0 if very_first else 1
+            elif kind == "attention_block":
+                lw = self.layers[step[2]]
+                self._gemm(h, lw["wqkv"], self._rows(self.qkv, mb))
+                q, k, v = self._head_view(mb, 0, hq), self._head_view(mb, hq, hkv), self._head_view(mb, hq + hkv, hkv)
+                attn = self._rows(self.attn, mb)
+                self._op("rb_attention", ctx, self._t(q), self._t(k), self._t(v), None, C.c_float(self.scale), C.c_int32(1), C.c_uint64(0), C.c_uint64(0),
+                         self._t(self.cos), self._t(self.sin), C.c_int32(int(RotaryLayout.SplitHalf)), C.c_int32(1), self._t(attn.reshape((b, self.seq, hq, cfg.head_dim))))
+                self.launches_per_forward += 2   # the Q and K rotations run as two small kernels inside rb_attention
+            elif kind == "ffn_block":
+                lw = self.layers[step[2]]
+                self._gemm(h, lw["wg"], self._rows(self.ffn_act, mb), b_up=lw["wu"])
+            elif kind == "scatter":
+                lw = self.layers[step[2]]
+                a = self._rows(self.attn, mb) if step[3] == "wo" else self._rows(self.ffn_act, mb)
+                self._op("rb_gemm_scatter", *ex.scatter_args(a, lw[step[3]], keep))
+            elif kind == "lm_head":
+                self._gemm(h, self.lm_head, self._rows(self.logits, mb))
+            else:
+                raise AssertionError(kind)
+
     def _run_plan(self):
         from .runtime import _check
-        if self.world > 1:
+        if self.world > 1 and not self.fused:
             # tickets in the plan count this forward's collectives from one; add the communicator's counter so far
             cur = C.c_uint64()
             _check(self.client._lib.rb_comm_ticket(self.comm.native._comm, C.byref(cur)))
             shift = cur.value
         for fn, args in self._steps:
-            if self.world > 1 and fn.__name__ == "rb_comm_wait_ticket":
+            if self.world > 1 and not self.fused and fn.__name__ == "rb_comm_wait_ticket":
                 rc = fn(args[0], C.c_uint64(args[1].value + shift))
             else:
                 rc = fn(*args)
@@ -279,11 +387,13 @@ class TensorParallelDecoder:
                 _check(rc)
 
     def close(self) -> None:
-        """Drops the recorded graph.  Call this before destroying the communicator: NCCL does not finish destroying a
-        communicator while a graph that holds its collectives exists."""
+        """Drops the recorded graph and, in fused mode, the peer buffers (a collective step: every rank of the group calls it
+        at the same point).  Call this before destroying the communicator: NCCL does not finish destroying a communicator
+        while a graph that holds its collectives exists."""
         if self._graph is not None:
             self.client._lib.rb_graph_destroy(self.client._ctx, self._graph)
             self._graph = None
+        self._release_fused()
 
     def forward(self, tokens: np.ndarray | None = None) -> TensorBuffer:
         """Returns this rank's logits shard [T, vocab/world] (BF16).  `tokens` int32 [B,S]; None reuses the last upload."""

@@ -1,0 +1,147 @@
+"""Two GPUs: peer buffers, the fused row-parallel projection (scatter GEMM + owner-side reduce + push) against a host
+reference and against the NCCL path, and the decoder in fused mode against the same host reference the NCCL decoder meets.
+
+These kernels store into another GPU's memory and wait on flags that another GPU sets, so the test is opt-in
+(RUDA_FUSED_TESTS=1) until it has been run on two GPUs of the target pool; every wait in the kernels is bounded (2 s) and
+the workers are joined with a deadline, so a protocol error ends as a failed test, not as a hang."""
+import os
+import socket
+import sys
+import time
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _cfg():
+    from rust_ascend_b200.decoder import LlamaConfig
+    return LlamaConfig(layers=2, hidden=256, heads=4, kv_heads=2, head_dim=128, ffn=512, vocab=1024)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _inputs(world, tokens=512, hidden=320, k=192):
+    rng = np.random.default_rng(17)
+    x = rng.standard_normal((tokens, k * world)).astype(np.float32)
+    w = (rng.standard_normal((hidden, k * world)) * 0.05).astype(np.float32)
+    return x, w
+
+
+def _worker(rank, world, port, results):
+    for p in (ROOT, os.path.join(ROOT, "tests")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from rust_ascend_b200 import B200Runtime as RT
+    from rust_ascend_b200 import DType, RuntimeOptions
+    from rust_ascend_b200.decoder import TensorParallelDecoder
+    from rust_ascend_b200.distributed import NcclCommunicator, TorchControl
+    from rust_ascend_b200.fused import FusedExchange, PeerBuffer, row_parallel_linear_allreduce
+    from rust_ascend_b200.runtime import TensorBuffer, bf16_bits_to_f32, f32_to_bf16_bits
+    client = RT.client(RT.initialize_exclusive(RuntimeOptions(device=rank)))
+    control = TorchControl()
+    out = {}
+    # 1. peer buffer: every rank writes its own buffer, then reads everybody's through the mapping
+    buf = PeerBuffer(client, control, 4096)
+    mine = np.full(1024, 1000 + rank, np.int32)
+    client.write(buf.handles[rank], mine); client.sync()
+    control.all_gather_bytes(b"written")
+    out["peer"] = [int(client.read(buf.view(r, (1024,), DType.I32))[5]) for r in range(world)]
+    control.all_gather_bytes(b"read")
+    buf.close()
+    # 2. fused row-parallel Linear + all-reduce, twice on the same exchange (buffer reuse), against NumPy
+    x, w = _inputs(world)
+    k = x.shape[1] // world
+    xs = client.upload(f32_to_bf16_bits(x[:, rank * k:(rank + 1) * k]))
+    ws = client.upload(f32_to_bf16_bits(w[:, rank * k:(rank + 1) * k]))
+    ex = FusedExchange(client, control, x.shape[0], w.shape[0])
+    y1 = bf16_bits_to_f32(client.read(row_parallel_linear_allreduce(ex, xs, ws)))
+    y2 = bf16_bits_to_f32(client.read(row_parallel_linear_allreduce(ex, xs, ws)))
+    out["fused_linear"], out["fused_linear_again_equal"] = y1, bool(np.array_equal(y1, y2))
+    # residual + RMSNorm folded into the owner-side step
+    rows = x.shape[0] // world
+    resid = np.random.default_rng(5).standard_normal((x.shape[0], w.shape[0])).astype(np.float32)
+    weight = np.random.default_rng(6).uniform(0.5, 1.5, w.shape[0]).astype(np.float32)
+    x_own = client.upload(f32_to_bf16_bits(resid[rank * rows:(rank + 1) * rows]))
+    ex.gemm_scatter(xs, ws); ex.wait_scatter()
+    ex.reduce_norm_push(x_in=x_own, weight=client.upload(f32_to_bf16_bits(weight)), eps=1e-5, x_out=x_own)
+    ex.wait_gather(); ex.barrier()
+    out["normed"] = bf16_bits_to_f32(client.read(ex.gathered()))
+    out["residual_rows"] = bf16_bits_to_f32(client.read(x_own))
+    client.sync()
+    ex.close()
+    # 3. the decoder: fused mode against the NCCL mode on the same weights and tokens
+    comm = NcclCommunicator.initialize(control, client)
+    cfg = _cfg()
+    tokens = np.random.default_rng(0).integers(0, cfg.vocab, size=(2, 128)).astype(np.int32)
+    for name, kwargs in (("nccl", {}), ("fused", {"fused": True}), ("fused_graph", {"fused": True, "use_graph": True})):
+        model = TensorParallelDecoder(client, cfg, 2, 128, comm=comm, rank=rank, world=world, seed=3, exact_weights=True, **kwargs)
+        model.forward(tokens)
+        out[name] = bf16_bits_to_f32(client.read(model.forward()))
+        model.close()
+    results[rank] = out
+    comm.native.destroy()
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_two_gpu_fused_exchange(oracle):
+    import torch
+    if os.environ.get("RUDA_FUSED_TESTS") != "1":
+        pytest.skip("peer-memory kernels not yet run on the target pool: opt in with RUDA_FUSED_TESTS=1")
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    from decoder_reference import forward, full_weights
+    from test_index_padded import bf16
+    world, port = 2, _free_port()
+    with mp.Manager() as manager:
+        results = manager.dict()
+        ctx = mp.spawn(_worker, args=(world, port, results), nprocs=world, join=False)
+        deadline = time.time() + 240
+        while not ctx.join(timeout=5):
+            if time.time() > deadline:   # a rank is stuck: end exactly the processes this test started
+                for proc in ctx.processes:
+                    if proc.is_alive():
+                        proc.terminate()
+                pytest.fail("two-GPU workers did not finish within 240 s")
+        r = {k: dict(v) for k, v in results.items()}
+    x, w = _inputs(world)
+    k = x.shape[1] // world
+    partial = [bf16(bf16(x[:, i * k:(i + 1) * k]) @ bf16(w[:, i * k:(i + 1) * k]).T) for i in range(world)]   # each rank's BF16 partial tile
+    total = bf16(sum(partial))
+    for rank in range(world):
+        assert r[rank]["peer"] == [1000, 1001]
+        assert r[rank]["fused_linear_again_equal"]
+        got = r[rank]["fused_linear"]
+        assert got.shape == total.shape
+        err = np.abs(got - total)
+        assert err.max() <= 2.0 ** -7 * np.abs(total).max() and err.mean() <= 1e-3 * np.abs(total).mean() + 1e-6, (err.max(), err.mean())
+        np.testing.assert_array_equal(got, r[0]["fused_linear"])          # every rank holds the same bits
+    rows = x.shape[0] // world
+    resid = np.random.default_rng(5).standard_normal(total.shape).astype(np.float32)
+    weight = bf16(np.random.default_rng(6).uniform(0.5, 1.5, total.shape[1]).astype(np.float32))
+    xn = bf16(bf16(resid) + r[0]["fused_linear"])                          # residual update with the sums the GPUs produced
+    want = bf16(xn / np.sqrt((xn ** 2).mean(-1, keepdims=True) + 1e-5) * weight)
+    for rank in range(world):
+        got_x = r[rank]["residual_rows"]; want_x = xn[rank * rows:(rank + 1) * rows]
+        assert np.abs(got_x - want_x).max() <= 2.0 ** -8 * np.abs(want_x).max()   # FP32 add then BF16 rounding against f64: at most one ulp
+        err = np.abs(r[rank]["normed"] - want)
+        assert err.max() <= 2.0 ** -7 * np.abs(want).max(), err.max()
+    cfg = _cfg()
+    tokens = np.random.default_rng(0).integers(0, cfg.vocab, size=(2, 128)).astype(np.int32)
+    want = forward(oracle, cfg, full_weights(cfg, 3), tokens)
+    for name in ("nccl", "fused", "fused_graph"):
+        got = np.concatenate([r[0][name], r[1][name]], axis=1)
+        err = np.abs(got - want)
+        assert err.max() <= 0.04 * np.abs(want).max() and err.mean() <= 0.015 * np.abs(want).mean() + 1e-4, (name, err.max(), err.mean())
+    np.testing.assert_array_equal(r[0]["fused"], r[0]["fused_graph"])
