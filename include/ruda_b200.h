@@ -297,14 +297,14 @@ RB_API int32_t rb_peer_close(rb_ctx* ctx, uint64_t handle);
  * gemm (runtime/mod.rs:346-349) and then HcclCommunicator::reduce_scatter (src/distributed.rs:139-156).  a BF16 [T, K],
  * b BF16 [H, K] (this rank's K shard); T a multiple of 128 * world, H of 64.  Rows [o*T/world, (o+1)*T/world) of the partial
  * product are stored into staging[o] (BF16 [world, T/world, H], rank o's memory) at slot [rank], and every 32-row slice is
- * announced by adding 1 to word [rank] of flags[o] (INT32 [world + 1], rank o's memory).  rb_gemm_scatter_signals gives the
+ * announced (in batches, once the storing CTA is done) by adding to word [rank] of flags[o] (INT32 [world + 1], rank o's memory).  rb_gemm_scatter_signals gives the
  * number of announcements one call makes per owner. */
 RB_API int32_t rb_gemm_scatter(rb_ctx* ctx, const rb_tensor* a, const rb_tensor* b, uint32_t rank, uint32_t world,
                                const rb_tensor* const* staging, const rb_tensor* const* flags);
 /* This entry has no counterpart in the reference.  Announcements per owner of one rb_gemm_scatter call with T tokens and H columns (0 when
  * the shape is not accepted). */
 RB_API uint32_t rb_gemm_scatter_signals(uint64_t tokens, uint64_t hidden, uint32_t world);
-/* This entry has no counterpart in the reference.  Waits on this GPU, with a 2 s limit, until words [0, world) of `flags` (INT32
+/* This entry has no counterpart in the reference.  Waits on this GPU, with a limit of RUDA_PEER_WAIT_MS milliseconds (default 5000), until words [0, world) of `flags` (INT32
  * [world + 1], local memory that peers add to) have each grown by `count` beyond the running target kept in word [world],
  * then advances the target.  On expiry the next rb_sync reports RB_SERVER_UNHEALTHY; nothing faults. */
 RB_API int32_t rb_peer_wait(rb_ctx* ctx, const rb_tensor* flags, uint32_t world, uint32_t count);

@@ -7,8 +7,8 @@
 //   1. gemm_scatter_kernel: Y_partial = A[T, K/N] * B[H, K/N]^T on the tensor cores (same pipeline as the plain GEMM: TMA
 //      producer warp, tcgen05.mma issuer warp, four epilogue warps, two TMEM accumulators).  The epilogue does not write a
 //      local [T, H]: rows [o*R, (o+1)*R) belong to rank o (R = T / world), and every finished 32-row slice is stored
-//      straight into rank o's staging area slot [this rank] and announced with one release-add to rank o's flag word
-//      [this rank].  The transfer of tile i overlaps the main loop of tile i+1.  (reduce-scatter, fused tile by tile)
+//      straight into rank o's staging area slot [this rank]; when a CTA has stored all its tiles, each epilogue warp
+//      fences once and adds the number of slices it stored for rank o to rank o's flag word [this rank].  The transfer of tile i overlaps the main loop of tile i+1.  (reduce-scatter, fused tile by tile)
 //   2. reduce_norm_push_kernel, on the R rows a rank owns: sums the `world` staged partials in rank order in FP32 (one
 //      rounding to BF16, as an all-reduce result would have), adds the residual stream, applies RMSNorm, and stores the
 //      normalised rows into every rank's activation buffer at the owner's row offset, then announces them with one
@@ -25,6 +25,7 @@
 #include "common.cuh"
 
 #include <cmath>
+#include <cstdlib>
 
 #include "schedule.h"
 #include "sm100.cuh"
@@ -38,7 +39,6 @@ constexpr int BM = 128, BK = 64, UMMA_K = 16, GROUP_M = 8, THREADS = 192;
 constexpr int MAX_PEERS = RB_MAX_PEERS;
 constexpr int CHUNK = 64;                       // output columns moved through shared memory at a time
 constexpr int PITCH = CHUNK * 2 + 16;           // bytes per staged row: 128 payload + 16 pad (conflict-free 16-byte accesses)
-constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;
 
 struct ScatterParams {
     uint32_t m, n, k;               // m = world * rows_per_owner
@@ -66,8 +66,8 @@ __device__ __forceinline__ void scatter_coords(uint32_t t, const ScatterParams& 
     rb_scatter_tile(t, p.tiles_m, p.tiles_n, GROUP_M, p.tile_shift, tm, tn);
 }
 
-__device__ __forceinline__ void signal_release_sys(uint32_t* flag) {
-    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(flag), "r"(1u) : "memory");
+__device__ __forceinline__ void signal_release_sys(uint32_t* flag, uint32_t count = 1u) {
+    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(flag), "r"(count) : "memory");
 }
 __device__ __forceinline__ uint32_t load_acquire_sys(const uint32_t* p) {
     uint32_t v;
@@ -166,6 +166,7 @@ gemm_scatter_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const uint32_t quarter = warp & 3;
         uint8_t* my_smem = out_smem + quarter * 32 * PITCH;
         uint32_t iter = 0;
+        uint32_t slices = 0;                 // lane o counts the slices this warp stored for owner o
         bool ok = true;
         for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++iter) {
             const uint32_t acc = iter & 1, acc_phase = (iter >> 1) & 1;
@@ -222,11 +223,14 @@ gemm_scatter_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 }
                 __syncwarp();
             }
-            // Everything this warp wrote for the tile is ordered before the announcement at system scope.
-            __threadfence_system();
-            __syncwarp();
-            if (lane == 0) signal_release_sys(p.flag[owner]);
+            slices += lane == owner;
         }
+        // One fence for everything this warp stored, then its announcements: waiting for the link's acknowledgements once
+        // per CTA instead of once per tile keeps the epilogue shorter than the next tile's main loop.  Slices of a tile
+        // that was abandoned after an expired wait are not announced, so the owner's wait runs out instead of passing.
+        __threadfence_system();
+        __syncwarp();
+        if (lane < p.world && slices) signal_release_sys(p.flag[lane], slices);
     }
 
     tc_fence_before();
@@ -238,14 +242,14 @@ gemm_scatter_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // flags[0..world) count up as peers announce their stores; flags[world] is the running target.  Lane i waits until
 // flags[i] has reached target + count (wrap-safe), with a time limit after which the status word is raised and the wait
 // ends, so the context stays usable.  Then the target moves on.
-__global__ void __launch_bounds__(32) peer_wait_kernel(uint32_t* flags, uint32_t world, uint32_t count, uint32_t* status) {
+__global__ void __launch_bounds__(32) peer_wait_kernel(uint32_t* flags, uint32_t world, uint32_t count, uint32_t* status, uint64_t limit_ns) {
     const uint32_t lane = threadIdx.x;
     const uint32_t target = flags[world] + count;
     bool expired = false;
     if (lane < world) {
         const uint64_t start = global_timer_ns();
         while ((int32_t)(load_acquire_sys(flags + lane) - target) < 0) {
-            if (global_timer_ns() - start > WAIT_LIMIT_NS) { expired = true; break; }
+            if (global_timer_ns() - start > limit_ns) { expired = true; break; }
             __nanosleep(64);
         }
     }
@@ -482,7 +486,10 @@ int32_t rb_peer_wait(rb_ctx* ctx, const rb_tensor* flags, uint32_t world, uint32
     uint32_t* pf = nullptr; uint32_t* status = nullptr;
     RB_TRY(resolve_flags(ctx, flags, world, "peer wait flags", &pf));
     RB_TRY(kernel_status_word(ctx, &status));
-    peer_wait_kernel<<<1, 32, 0, ctx->stream>>>(pf, world, count, status);
+    // Long enough for a peer whose host thread is late with its launch, short enough that a lost rank ends as an error.
+    uint64_t limit_ms = 5000;
+    if (const char* env = std::getenv("RUDA_PEER_WAIT_MS")) { const long v = std::atol(env); if (v > 0 && v <= 60000) limit_ms = (uint64_t)v; }
+    peer_wait_kernel<<<1, 32, 0, ctx->stream>>>(pf, world, count, status, limit_ms * 1000000ull);
     return after_launch(ctx, "peer_wait");
 }
 

@@ -172,3 +172,115 @@ def causal_grouped_query_attention_bf16_fp32(query: Tensor, key: Tensor, value: 
     if len(query.dims()) != 4:
         raise InvalidTensor("causal_grouped_query_attention takes rank-4 tensors")
     return _attention(query, key, value, scale, None, True, query_start, key_start)
+
+
+# -- matrices whose axes are not multiples of 16 (src/nn/padded.rs) ----------------------------------------------------
+def matmul_padded_bf16_fp32(a: Tensor, b: Tensor, ta: Transpose = Transpose.No, tb: Transpose = Transpose.No) -> Tensor:
+    """Positive M/N/K of any size, rank 2 or matching-batch rank 3, all four transposes; X/W rounded to BF16 on the device,
+    FP32 result cropped to the logical shape (src/nn/padded.rs:21-27)."""
+    c = _same_client(a, b)
+    return _wrap(c, RT.gemm_padded_bf16_fp32(c, a.buffer, b.buffer, ta, tb)[0])
+
+
+def linear_padded_bf16_fp32(input: Tensor, weight: Tensor) -> Tensor:
+    """X[M,K] W[N,K]^T with explicit padding (src/nn/padded.rs:28-31)."""
+    if len(input.dims()) != 2 or len(weight.dims()) != 2:
+        raise InvalidTensor("padded GEMM requires matching rank-2/3 FP32/BF16 inputs")
+    return matmul_padded_bf16_fp32(input, weight, Transpose.No, Transpose.Yes)
+
+
+def linear_frozen_padded_bf16_fp32(input: Tensor, weight: Tensor) -> Tensor:
+    """FP32 X times a fixed BF16 W^T of any positive size, FP32 result; the weight is neither copied (when aligned) nor
+    written (src/nn/padded.rs:9-11, runtime/padded_matrix.rs:67-79)."""
+    c = _same_client(input, weight)
+    return _wrap(c, RT.linear_frozen_padded_bf16_fp32(c, input.buffer, weight.buffer)[0])
+
+
+# -- embedding and the causal-LM loss edge (src/nn/embedding.rs, src/nn/frozen.rs, src/nn/causal_lm.rs) -----------------------
+@dataclass
+class EmbeddingOptions:
+    """runtime::EmbeddingOptions (rust-ascend-driver/src/tensor/embedding.rs:5-8): both fields act on the derivative only."""
+    padding_idx: int | None = None
+    scale_grad_by_freq: bool = False
+
+
+def embedding(weight: Tensor, indices: Tensor, options: EmbeddingOptions | None = None) -> Tensor:
+    """FP32 weight [V,H] and INT32/INT64 ids of rank 1..7 give output ids.shape + [H] (src/nn/embedding.rs:14-33,35-45)."""
+    options = options or EmbeddingOptions()
+    c = _same_client(weight, indices)
+    if not 1 <= len(indices.dims()) <= 7:
+        raise InvalidTensor("embedding output rank must append one axis to rank 1..7 IDs")
+    if weight.dtype() != DType.F32 or len(weight.dims()) != 2:
+        raise InvalidTensor("RUDA embedding autodiff requires a rank-2 FP32 table")
+    if options.padding_idx is not None and options.padding_idx >= weight.dims()[0]:
+        raise InvalidTensor("embedding padding row is outside its table")
+    return _wrap(c, RT.embedding(c, weight.buffer, indices.buffer))
+
+
+def embedding_backward(grad: Tensor, indices: Tensor, num_weights: int, options: EmbeddingOptions | None = None) -> Tensor:
+    """Dense weight gradient [V,H] that the reference's EmbeddingBackward registers (src/nn/embedding.rs:55-70)."""
+    options = options or EmbeddingOptions()
+    c = _same_client(grad, indices)
+    return _wrap(c, RT.embedding_backward(c, grad.buffer, indices.buffer, num_weights, options.padding_idx, options.scale_grad_by_freq))
+
+
+def embedding_frozen_bf16_fp32(weight: Tensor, indices: Tensor) -> Tensor:
+    """Fixed BF16 table [V,H], ids of rank 1..7, FP32 activations; no table gradient (src/nn/frozen.rs:15-26)."""
+    c = _same_client(weight, indices)
+    if not 1 <= len(indices.dims()) <= 7:
+        raise InvalidTensor("frozen embedding output rank must append one axis to rank 1..7 IDs")
+    if weight.dtype() != DType.BF16 or len(weight.dims()) != 2:
+        raise InvalidTensor("frozen BF16 embedding requires unquantized BF16 table")
+    return _wrap(c, RT.cast(c, RT.embedding(c, weight.buffer, indices.buffer), DType.F32))
+
+
+def layer_norm(input: Tensor, weight: Tensor, bias: Tensor | None, epsilon: float) -> Tensor:
+    """Last-axis LayerNorm, missing bias = zeros (runtime/mod.rs:442-448)."""
+    c = _same_client(input, weight, bias)
+    return _wrap(c, RT.layer_norm(c, input.buffer, weight.buffer, None if bias is None else bias.buffer, epsilon)[0])
+
+
+@dataclass
+class CausalLoss:
+    """Full-vocabulary FP32 loss sum and FP32 count of scored tokens (src/nn/causal_lm.rs:55-66)."""
+    loss_sum: Tensor
+    valid_tokens: Tensor
+
+    def mean(self) -> Tensor:
+        """loss_sum / max(valid_tokens, 1); ignored or empty windows have zero mean.  The two scalars are read back to form
+        the quotient (the reference divides on the device)."""
+        s = np.float32(self.loss_sum.into_data()[0]); n = np.float32(self.valid_tokens.into_data()[0])
+        return Tensor.from_data(self.loss_sum.client, np.array([s / max(n, np.float32(1))], np.float32))
+
+
+@dataclass
+class CausalCrossEntropyConfig:
+    """src/nn/causal_lm.rs:38-53.  `token_chunk_size` bounds the reference's per-launch logits; here the whole [B,T,V] block
+    goes through one fused kernel, so the field is validated and otherwise unused."""
+    token_chunk_size: int = 32
+    ignore_index: int = -100
+    shift: bool = True
+
+    def forward_hidden(self, hidden: Tensor, labels: Tensor, project) -> CausalLoss:
+        """hidden FP32 [B,T,H], labels INT32/INT64 [B,T]; `project` maps FP32 [rows,H] to FP32 logits [rows,V]
+        (src/nn/causal_lm.rs:118-196).  With shift, position t is scored against label t+1 of the same sequence."""
+        c = _same_client(hidden, labels)
+        if len(hidden.dims()) != 3 or len(labels.dims()) != 2:
+            raise InvalidTensor("causal loss requires matching [B,T,H]/[B,T], positive H and token chunk size")
+        batch, time, width = hidden.dims()
+        if self.token_chunk_size <= 0 or labels.dims() != [batch, time] or width == 0:
+            raise InvalidTensor("causal loss requires matching [B,T,H]/[B,T], positive H and token chunk size")
+        steps = max(time - 1, 0) if self.shift else time
+        if batch * steps > 1 << 24:
+            raise InvalidTensor("causal loss FP32 token count requires at most 2^24 logical tokens per call")
+        if hidden.dtype() != DType.F32 or labels.dtype() not in (DType.I32, DType.I64):
+            raise InvalidTensor("causal loss requires same-device FP32 hidden and I32/I64 labels")
+        if batch * time == 0:
+            zero = lambda: Tensor.from_data(c, np.zeros(1, np.float32))
+            return CausalLoss(zero(), zero())
+        logits = project(hidden.reshape((batch * time, width)))
+        if len(logits.dims()) != 2 or logits.dims()[0] != batch * time or logits.dims()[1] == 0 or logits.dtype() != DType.F32:
+            raise InvalidTensor("causal projection must return FP32 [tokens,V] with positive V")
+        loss, valid, _ = RT.causal_cross_entropy(c, logits.buffer.reshape((batch, time, logits.dims()[1])), labels.buffer, self.ignore_index,
+                                                 self.shift, 1.0, with_gradient=False)
+        return CausalLoss(_wrap(c, loss), _wrap(c, valid))

@@ -2,7 +2,7 @@
 reference and against the NCCL path, and the decoder in fused mode against the same host reference the NCCL decoder meets.
 
 These kernels store into another GPU's memory and wait on flags that another GPU sets, so the test is opt-in
-(RUDA_FUSED_TESTS=1) until it has been run on two GPUs of the target pool; every wait in the kernels is bounded (2 s) and
+(RUDA_FUSED_TESTS=1) until it has been run on two GPUs of the target pool; every wait in the kernels is bounded (a few seconds) and
 the workers are joined with a deadline, so a protocol error ends as a failed test, not as a hang."""
 import os
 import socket
