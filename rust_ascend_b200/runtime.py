@@ -721,6 +721,55 @@ class B200Runtime:
                                                    C.c_float(upstream), _ref(loss), _ref(valid), _ref(d)))
         return [loss, valid, d]
 
+    @staticmethod
+    def attention_backward(client, q: TensorBuffer, k: TensorBuffer, v: TensorBuffer, grad: TensorBuffer, scale: float,
+                           mask: TensorBuffer | None = None, causal: bool = False, query_start: int = 0, key_start: int = 0,
+                           want_mask_grad: bool = False):
+        """[dQ, dK, dV(, dMask)] of the composed attention for FP32 q [B,Hq,M,D], k [B,Hkv,N,D], v [B,Hkv,N,Dv] and upstream
+        grad [B,Hq,M,Dv], with the rounding points of the reference's autodiff graph (src/nn/attention.rs:10-29,49-67 and
+        examples/grouped_attention_tensor.rs:14-44): the probabilities are rebuilt as softmax(scale * bf16(Q) bf16(K)^T + mask),
+        dP = bf16(dY) bf16(V)^T, dS = P (dP - sum(P dP)) in FP32, bf16(scale dS) feeds dQ and dK, bf16(P) feeds dV, and the
+        K/V gradients of a KV head sum over its query heads (heads_programs.rs:59-86).  Scores are materialised, as in the
+        reference; the fused forward kernel keeps nothing to reuse here."""
+        RT = B200Runtime
+        if any(len(t.shape) != 4 or t.dtype != DType.F32 for t in (q, k, v, grad)):
+            raise InvalidTensor("attention backward requires FP32 rank-4 Q/K/V and upstream gradient")
+        b, hq, m, d = q.shape
+        _, hkv, n, dv = v.shape
+        if hkv == 0 or hq % hkv or k.shape != (b, hkv, n, d) or v.shape[0] != b or grad.shape != (b, hq, m, dv):
+            raise InvalidTensor("GQA requires matching batches, positive divisible Q/KV heads and matching K/V lengths and Q/K widths")
+        if not np.isfinite(scale) or scale == 0.0:
+            raise InvalidTensor("attention backward needs a finite non-zero scale")
+        flat = b * hq
+        if mask is not None and (mask.dtype != DType.F32 or mask.elements != flat * m * n):
+            raise InvalidTensor("attention additive mask must be FP32 [B,Hq,M,N]")
+        bf = lambda t, shape: RT.cast(client, t, DType.BF16).reshape(shape)
+        no, yes = Transpose.No, Transpose.Yes
+        qb, gb = bf(q, (flat, m, d)), bf(grad, (flat, m, dv))
+        kb = bf(RT.repeat_kv_heads(client, k, hq), (flat, n, d))
+        vb = bf(RT.repeat_kv_heads(client, v, hq), (flat, n, dv))
+
+        def times_scale(t):   # t * scale as a division by 1/scale (exact for the power-of-two scales of the reference examples)
+            _check(client._lib.rb_div_scalar(client._ctx, _ref(t), C.c_float(1.0 / scale), _ref(t)))
+            return t
+        scores = times_scale(RT.gemm(client, qb, kb, no, yes, DType.F32))
+        additive = mask.reshape((flat, m, n)) if mask is not None else None
+        if causal:
+            tri = RT.causal_mask(client, flat, m, n, query_start, key_start)
+            additive = tri if additive is None else RT.add(client, additive, tri)
+        if additive is not None:
+            RT.add(client, scores, additive, out=scores)
+        p = RT.softmax(client, scores)
+        dp = RT.gemm(client, gb, vb, no, yes, DType.F32)
+        ds = RT.softmax_backward(client, p, dp)
+        dmask = RT.copy_contiguous(client, ds).reshape((b, hq, m, n)) if want_mask_grad else None
+        dsb = RT.cast(client, times_scale(ds), DType.BF16)
+        pb = RT.cast(client, p, DType.BF16)
+        dq = RT.gemm(client, dsb, kb, no, no, DType.F32).reshape((b, hq, m, d))
+        dk = RT.repeat_kv_heads_backward(client, k.shape, hq, RT.gemm(client, dsb, qb, yes, no, DType.F32).reshape((b, hq, n, d)))
+        dv_ = RT.repeat_kv_heads_backward(client, v.shape, hq, RT.gemm(client, pb, gb, yes, no, DType.F32).reshape((b, hq, n, dv)))
+        return [dq, dk, dv_] + ([dmask] if want_mask_grad else [])
+
     # -- attention -------------------------------------------------------------------------------
     @staticmethod
     def attention(client, q: TensorBuffer, k: TensorBuffer, v: TensorBuffer, scale: float, mask: TensorBuffer | None = None,

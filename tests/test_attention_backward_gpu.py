@@ -1,0 +1,53 @@
+"""Attention backward composed from the C ABI's matrix, softmax and head-reduction entry points, against the oracle that
+tests/test_oracle_next.py pins to examples/grouped_attention_tensor.rs:14-44,74-99 (tolerance 2e-3 + 3e-3 relative, as
+there), plus a larger seeded case with a scale that is not a power of two."""
+import numpy as np
+import pytest
+
+import vectors as V
+from test_backward import close
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("kv_heads,group,n,causal", V.GQA_CASES)
+def test_attention_backward_reference_example(client, oracle, kv_heads, group, n, causal):
+    from rust_ascend_b200 import B200Runtime as RT
+    q, k, v, mask, prefix, _ = V.gqa_case(kv_heads, group, n, causal)
+    batch, heads, m, d = q.shape
+    dv_ = v.shape[3]
+    dy = ((np.arange(batch * heads * m * dv_) % 7).astype(np.float32) / np.float32(8.0) - np.float32(0.25)).reshape(batch, heads, m, dv_)
+    up = client.upload
+    if causal:
+        want = oracle.attention_backward(q, k, v, dy, 0.25, causal=True, query_start=(1 << 40) + prefix, key_start=1 << 40)
+        got = RT.attention_backward(client, up(q), up(k), up(v), up(dy), 0.25, causal=True, query_start=(1 << 40) + prefix, key_start=1 << 40)
+    else:
+        want = oracle.attention_backward(q, k, v, dy, 0.25, mask=mask, want_mask_grad=True)
+        got = RT.attention_backward(client, up(q), up(k), up(v), up(dy), 0.25, mask=up(mask), want_mask_grad=True)
+        assert got[3].shape == mask.shape
+        close(client.read(got[3]), want[3], 2e-3, 3e-3)
+    assert got[0].shape == q.shape and got[1].shape == k.shape and got[2].shape == v.shape
+    for g, w in zip(got[:3], want[:3]):
+        close(client.read(g), w, 2e-3, 3e-3)
+
+
+def test_attention_backward_seeded_case_and_rejections(client, oracle):
+    from rust_ascend_b200 import B200Runtime as RT, InvalidTensor
+    rng = np.random.default_rng(33)
+    b, hq, hkv, m, n, d, dv_ = 2, 4, 2, 48, 64, 32, 16
+    q = rng.standard_normal((b, hq, m, d)).astype(np.float32); k = rng.standard_normal((b, hkv, n, d)).astype(np.float32)
+    v = rng.standard_normal((b, hkv, n, dv_)).astype(np.float32); dy = rng.standard_normal((b, hq, m, dv_)).astype(np.float32)
+    scale = float(1.0 / np.sqrt(d))
+    up = client.upload
+    want = oracle.attention_backward(q, k, v, dy, scale, causal=True, query_start=n - m, key_start=0)
+    got = RT.attention_backward(client, up(q), up(k), up(v), up(dy), scale, causal=True, query_start=n - m, key_start=0)
+    for g, w in zip(got, want):
+        g = client.read(g)
+        err = np.abs(g - w)
+        assert np.all(np.isfinite(g)) and err.max() <= 2e-2 * max(1.0, np.abs(w).max()) and err.mean() <= 1e-2 * np.abs(w).mean() + 1e-5
+    with pytest.raises(InvalidTensor):
+        RT.attention_backward(client, up(q), up(k[:, :1].repeat(3, axis=1)), up(v), up(dy), scale)          # Hq % Hkv != 0 / KV mismatch
+    with pytest.raises(InvalidTensor):
+        RT.attention_backward(client, up(q), up(k), up(v), up(dy[:, :, :32]), scale)                           # upstream shape
+    with pytest.raises(InvalidTensor):
+        RT.attention_backward(client, up(q), up(k), up(v), up(dy), 0.0)
