@@ -1,6 +1,7 @@
 """Attention backward composed from the C ABI's matrix, softmax and head-reduction entry points, against the oracle that
 tests/test_oracle_next.py pins to examples/grouped_attention_tensor.rs:14-44,74-99 (tolerance 2e-3 + 3e-3 relative, as
-there), plus a larger seeded case with a scale that is not a power of two."""
+there), plus a larger seeded case with a scale that is not a power of two.  The file name sorts it near the end of the suite: it
+exercises compositions of entry points that the earlier files test one by one."""
 import numpy as np
 import pytest
 
