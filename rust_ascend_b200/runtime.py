@@ -540,6 +540,52 @@ class B200Runtime:
         return B200Runtime.gemm(client, B200Runtime.cast(client, input, DType.BF16), weight, Transpose.No, Transpose.Yes, DType.F32)
 
 
+    @staticmethod
+    def group_ends(ends) -> list[int]:
+        """GroupEnds::new (deepgemm/plan.rs:15-29): 1..4096 nondecreasing physical row prefix sums, each a multiple of 256,
+        not all empty."""
+        ends = [int(e) for e in ends]
+        if not 1 <= len(ends) <= 4096:
+            raise InvalidTensor("group count must be 1..=4096")
+        previous = 0
+        for end in ends:
+            if end < previous or end % 256:
+                raise InvalidTensor("group ends must be nondecreasing multiples of 256")
+            previous = end
+        if previous == 0:
+            raise InvalidTensor("all-empty grouped GEMM is not implemented")
+        return ends
+
+    @staticmethod
+    def gemm_grouped_nt(client, a: TensorBuffer, weights: TensorBuffer, ends, dtype: DType) -> TensorBuffer:
+        """M-grouped GEMM of GemmSpec::grouped_nt (deepgemm/plan.rs:61-67, tile walk scheduler.rs:21-33): A [M,K], weights
+        [G,N,K], rows [ends[g-1], ends[g]) of A meet expert g's weight; output [M,N].  One launch of the dense kernel per
+        non-empty group on row slices of A and of the output (groups start on 256-row boundaries, so every slice is a
+        whole number of 128-row tiles)."""
+        ends = B200Runtime.group_ends(ends)
+        if len(a.shape) != 2 or len(weights.shape) != 3:
+            raise InvalidTensor("grouped NT requires [M,K] and [G,N,K]")
+        m, k = a.shape
+        g, n, kw = weights.shape
+        if m != ends[-1] or g != len(ends) or k != kw:
+            raise InvalidTensor("grouped NT dimensions do not match the physical prefix sums")
+        if a.dtype != DType.BF16 or weights.dtype != DType.BF16 or dtype not in (DType.BF16, DType.F32):
+            raise InvalidTensor("native DeepGEMM accepts BF16 inputs and BF16/F32 output only")
+        if any(x <= 0 or x % 16 or x > 2**31 - 1 for x in (m, n, k)):
+            raise InvalidTensor("M/N/K must be positive multiples of 16 <= INT32_MAX; batches/groups 1..=4096")
+        out = client.tensor((m, n), dtype)
+        size = DType(dtype).size
+        start = 0
+        for group, end in enumerate(ends):
+            rows = end - start
+            if rows:
+                a_g = TensorBuffer(a.handle, (rows, k), DType.BF16, None, offset=a.offset + start * k * 2)
+                w_g = TensorBuffer(weights.handle, (n, k), DType.BF16, None, offset=weights.offset + group * n * k * 2)
+                o_g = TensorBuffer(out.handle, (rows, n), dtype, None, offset=start * n * size)
+                B200Runtime.gemm_into(client, a_g, w_g, Transpose.No, Transpose.Yes, o_g)
+            start = end
+        return out
+
     # -- matrices whose axes are not multiples of 16 (runtime/padded_matrix.rs, deepgemm/padded.rs) --------------
     @staticmethod
     def _padded_spec(a_shape, b_shape, a_dtype, b_dtype, ta: Transpose, tb: Transpose):

@@ -80,6 +80,14 @@ def test_padded_spec_shapes_follow_reference_cases():
             RT._padded_spec(a, b, dt, DType.F32, no, no)
 
 
+def test_group_ends_follow_the_reference_rules():
+    from rust_ascend_b200 import B200Runtime as RT, InvalidTensor
+    assert RT.group_ends([0, 256, 256, 768]) == [0, 256, 256, 768]           # deepgemm/plan.rs:101: empty experts are fine
+    for bad in ([1, 17], [256, 0], [0, 0], [], [256] * 4097):               # plan.rs:102 and the 4096-group limit
+        with pytest.raises(InvalidTensor):
+            RT.group_ends(bad)
+
+
 @gpu
 def test_gpu_embedding_lookup_unaligned_rows(client):
     from rust_ascend_b200 import B200Runtime as RT

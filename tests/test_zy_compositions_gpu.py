@@ -1,6 +1,9 @@
-"""Attention backward composed from the C ABI's matrix, softmax and head-reduction entry points, against the oracle that
+"""Operators that are compositions of other entry points.
+
+Attention backward composed from the C ABI's matrix, softmax and head-reduction entry points, against the oracle that
 tests/test_oracle_next.py pins to examples/grouped_attention_tensor.rs:14-44,74-99 (tolerance 2e-3 + 3e-3 relative, as
-there), plus a larger seeded case with a scale that is not a power of two.  The file name sorts it near the end of the suite: it
+there), plus a larger seeded case with a scale that is not a power of two.  The M-grouped GEMM of deepgemm/plan.rs:61-67 as one
+dense launch per expert, against the oracle's GEMM on each group's rows, with the empty-expert case of plan.rs:101.  The file name sorts it near the end of the suite: it
 exercises compositions of entry points that the earlier files test one by one."""
 import numpy as np
 import pytest
@@ -52,3 +55,28 @@ def test_attention_backward_seeded_case_and_rejections(client, oracle):
         RT.attention_backward(client, up(q), up(k), up(v), up(dy[:, :, :32]), scale)                           # upstream shape
     with pytest.raises(InvalidTensor):
         RT.attention_backward(client, up(q), up(k), up(v), up(dy), 0.0)
+
+
+def test_grouped_gemm_matches_per_group_products(client, oracle):
+    from rust_ascend_b200 import B200Runtime as RT, DType, InvalidTensor
+    from rust_ascend_b200.runtime import bf16_bits_to_f32, f32_to_bf16_bits
+    rng = np.random.default_rng(12)
+    ends, n, k = [0, 256, 256, 768], 128, 64                      # plan.rs:101: aligned prefix sums with empty experts
+    a = rng.standard_normal((ends[-1], k)).astype(np.float32); w = (rng.standard_normal((len(ends), n, k)) * 0.1).astype(np.float32)
+    a16, w16 = f32_to_bf16_bits(a), f32_to_bf16_bits(w)
+    want = np.zeros((ends[-1], n), np.float64)
+    start = 0
+    for g, end in enumerate(ends):
+        if end > start:
+            want[start:end] = oracle.gemm_bf16(bf16_bits_to_f32(a16[start:end]), bf16_bits_to_f32(w16[g]), False, True, False)
+        start = end
+    out = RT.gemm_grouped_nt(client, client.upload(a16), client.upload(w16), ends, DType.F32)
+    assert out.shape == (768, 128)
+    assert np.abs(client.read(out) - want).max() <= 1e-4 * max(1.0, np.abs(want).max())
+    out16 = RT.gemm_grouped_nt(client, client.upload(a16), client.upload(w16), ends, DType.BF16)
+    assert np.abs(bf16_bits_to_f32(client.read(out16)) - want).max() <= 2.0 ** -8 * np.abs(want).max() + 1e-6
+    for bad in ([1, 17], [256, 0], [0, 0], []):                   # plan.rs:102
+        with pytest.raises(InvalidTensor):
+            RT.group_ends(bad)
+    with pytest.raises(InvalidTensor):
+        RT.gemm_grouped_nt(client, client.upload(a16), client.upload(w16), [256, 512], DType.F32)
