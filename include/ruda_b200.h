@@ -284,13 +284,14 @@ RB_API int32_t rb_attention(rb_ctx* ctx, const rb_tensor* q, const rb_tensor* k,
 /* ---- peer memory and the fused tensor-parallel exchange (no counterpart in the reference: its row-parallel projection is a
  * GEMM followed by a vendor all-reduce, runtime/hccl.rs:386-548; src/distributed.rs:139-156) ------------------------- */
 #define RB_MAX_PEERS 8
-/* This entry has no counterpart in the reference.  Exports a storage of this process as a 64-byte token (CUDA IPC) that another process of
+#define RB_PEER_TOKEN_BYTES 72 /* 64-byte CUDA IPC handle of the allocation + 8-byte offset of the storage inside it */
+/* This entry has no counterpart in the reference.  Exports a storage of this process as a token (CUDA IPC) that another process of
  * the node passes to rb_peer_open; tokens travel over the control plane that carries the communicator's root id
  * (src/distributed.rs:74-110). */
-RB_API int32_t rb_peer_export(rb_ctx* ctx, uint64_t handle, uint8_t token[64]);
+RB_API int32_t rb_peer_export(rb_ctx* ctx, uint64_t handle, uint8_t token[RB_PEER_TOKEN_BYTES]);
 /* This entry has no counterpart in the reference.  Opens a peer's token as a storage handle of `bytes` bytes whose device address is the
  * peer's memory; the handle is used like any other in rb_tensor descriptors.  Close it with rb_peer_close, not rb_free. */
-RB_API int32_t rb_peer_open(rb_ctx* ctx, const uint8_t token[64], uint64_t bytes, uint64_t* handle);
+RB_API int32_t rb_peer_open(rb_ctx* ctx, const uint8_t token[RB_PEER_TOKEN_BYTES], uint64_t bytes, uint64_t* handle);
 /* This entry has no counterpart in the reference.  Drains the stream, forgets the handle and unmaps the peer's memory. */
 RB_API int32_t rb_peer_close(rb_ctx* ctx, uint64_t handle);
 /* Row-parallel Linear with the reduce-scatter half of its all-reduce fused into the epilogue; stands where the reference runs

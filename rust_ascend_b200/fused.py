@@ -24,6 +24,7 @@ from .distributed import check_replies, failure_bytes
 from .runtime import ComputeClient, DType, InvalidTensor, TensorBuffer, _check, _ref
 
 MAX_PEERS = 8
+TOKEN_BYTES = 72                     # RB_PEER_TOKEN_BYTES
 FLAG_WORDS = 16                      # words per flag group: world counters, the running target, padding
 SCATTER, GATHER, BARRIER = 0, 1, 2   # flag groups inside one flags buffer; word 48 is the local block counter
 
@@ -54,7 +55,7 @@ class PeerBuffer:
             local = client.empty(self.nbytes)
             client.memset(TensorBuffer(local, (self.nbytes,), DType.U8), 0)
             client.sync()
-            token = (C.c_uint8 * 64)()
+            token = (C.c_uint8 * TOKEN_BYTES)()
             _check(lib.rb_peer_export(client._ctx, C.c_uint64(local), token))
             payload = b"\x00" + bytes(token)
         except Exception as error:          # every rank must still answer the round
@@ -68,7 +69,7 @@ class PeerBuffer:
                     self.handles.append(local)
                     continue
                 h = C.c_uint64()
-                _check(lib.rb_peer_open(client._ctx, (C.c_uint8 * 64)(*reply[1:65]), C.c_uint64(self.nbytes), C.byref(h)))
+                _check(lib.rb_peer_open(client._ctx, (C.c_uint8 * TOKEN_BYTES)(*reply[1:1 + TOKEN_BYTES]), C.c_uint64(self.nbytes), C.byref(h)))
                 self.handles.append(h.value)
             payload = b"\x00"
         except Exception as error:
@@ -191,11 +192,11 @@ class FusedExchange:
 def row_parallel_linear_allreduce(exchange: FusedExchange, x: TensorBuffer, w_shard: TensorBuffer) -> TensorBuffer:
     """Y = sum over ranks of x_r [T, K/world] . w_r [H, K/world]^T, complete on every rank: what the reference computes with a
     row-parallel Linear followed by all_reduce(sum) (src/distributed.rs:139-156), here as scatter-GEMM, owner-side sum in rank
-    order and a push of the summed rows to every rank.  Returns this rank's gathered [T, H] (valid until the exchange is used
-    again).  The closing barrier lets the next call reuse the buffers at once."""
+    order and a push of the summed rows to every rank.  Returns this rank's gathered [T, H], valid until the next push on this
+    exchange; work enqueued on this context before the next call still reads it safely, because a peer can only push again
+    after it has seen this rank's next scatter, which is enqueued behind that work."""
     exchange.gemm_scatter(x, w_shard)
     exchange.wait_scatter()
     exchange.reduce_norm_push(weight=None)
     exchange.wait_gather()
-    exchange.barrier()
     return exchange.gathered()
