@@ -281,6 +281,16 @@ RB_API int32_t rb_attention(rb_ctx* ctx, const rb_tensor* q, const rb_tensor* k,
                             const rb_tensor* cos, const rb_tensor* sin, int32_t rotary_layout, int32_t out_layout,
                             const rb_tensor* out);
 
+/* ---- a side stream beside the compute stream (no counterpart in the reference, where every operation is a launch followed
+ * by a stream synchronisation, runtime/worker.rs:404-415) ------------------------------------------------------------ */
+/* This entry has no counterpart in the reference.  Forks: until rb_aux_end, everything enqueued on the context goes to a
+ * higher-priority side stream, ordered after what the compute stream held at this call. */
+RB_API int32_t rb_aux_begin(rb_ctx* ctx);
+/* This entry has no counterpart in the reference.  Ends the fork and records the side stream's position in `slot` (0..31). */
+RB_API int32_t rb_aux_end(rb_ctx* ctx, uint32_t slot);
+/* This entry has no counterpart in the reference.  Joins: later work on the compute stream waits for what `slot` recorded. */
+RB_API int32_t rb_aux_wait(rb_ctx* ctx, uint32_t slot);
+
 /* ---- peer memory and the fused tensor-parallel exchange (no counterpart in the reference: its row-parallel projection is a
  * GEMM followed by a vendor all-reduce, runtime/hccl.rs:386-548; src/distributed.rs:139-156) ------------------------- */
 #define RB_MAX_PEERS 8

@@ -75,6 +75,8 @@ int32_t check_ctx(rb_ctx* ctx);
 int32_t empty_call(rb_ctx* ctx);
 int32_t poll_kernel_status(rb_ctx* ctx);
 int32_t kernel_status_word(rb_ctx* ctx, uint32_t** out);
+// True between rb_aux_begin and rb_aux_end: launches are going to the side stream, beside the compute stream's kernels.
+bool aux_active(rb_ctx* ctx);
 int32_t gemm_kmajor(rb_ctx* ctx, const void* a, const void* b, const void* b_up, uint32_t batches, uint32_t m, uint32_t n, uint32_t k,
                     int epilogue, const void* bias, bool bias_bf16, void* out, bool out_f32);
 

@@ -548,7 +548,9 @@ int32_t rb_reduce_norm_push(rb_ctx* ctx, const rb_tensor* staging, const rb_tens
         p.dst[d] = static_cast<bf*>(pdst);
         p.flag[d] = pf + rank;
     }
-    const uint64_t cap = (uint64_t)(ctx->sm_limit > 0 ? ctx->sm_limit : ctx->sm_count) * 8;
+    // Beside the compute stream's persistent GEMMs this kernel gets the SMs they leave free; alone it gets them all.
+    const int sms = ctx->sm_limit > 0 ? (aux_active(ctx) ? ctx->sm_count - ctx->sm_limit : ctx->sm_limit) : ctx->sm_count;
+    const uint64_t cap = (uint64_t)(sms > 0 ? sms : 1) * 8;
     reduce_norm_push_kernel<<<(unsigned)(rows < cap ? rows : cap), PUSH_THREADS, 0, ctx->stream>>>(p);
     return after_launch(ctx, "reduce_norm_push");
 }

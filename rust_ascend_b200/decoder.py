@@ -73,29 +73,49 @@ def rope_tables(positions: int, head_dim: int, theta: float):
     return np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
 
 
-def fused_schedule(layers: int, micro_batches: int):
+def fused_schedule(layers: int, micro_batches: int, overlap: bool = False):
     """Order of one forward's steps in fused mode (exchange folded into the kernels, residual stream sharded by rows).
     Pure function: the launch plan is emitted from it and the CPU protocol model replays it.  Steps:
     ("embed", mb) | ("wait_scatter", mb) | ("push", mb, layer, which) | ("wait_gather", mb) | ("attention_block", mb, layer) |
-    ("ffn_block", mb, layer) | ("scatter", mb, layer, "wo" or "wd") | ("lm_head", mb) | ("barrier",).
+    ("ffn_block", mb, layer) | ("scatter", mb, layer, "wo" or "wd") | ("lm_head", mb) | ("barrier",) and, with `overlap`,
+    ("aux_begin", mb) | ("aux_end", mb) | ("aux_wait", mb).
     A push reduces the staged partials of the scatter before it (none for the very first), so its wait comes first; the
-    closing barrier keeps a fast rank's next forward from storing into buffers that a slow rank is still reading."""
+    closing barrier keeps a fast rank's next forward from storing into buffers that a slow rank is still reading.
+    With `overlap` the exchange that follows a scatter (wait, push, wait) is forked to the side stream right behind the
+    scatter and joined just before the micro batch's next block, so that it runs under the other micro batches' GEMMs."""
     steps = [("embed", mb) for mb in range(micro_batches)]
-    pending = [False] * micro_batches
+    if not overlap:
+        pending = [False] * micro_batches
+        for layer in range(layers + 1):
+            for mb in range(micro_batches):
+                if pending[mb]:
+                    steps.append(("wait_scatter", mb))
+                steps += [("push", mb, layer, 0), ("wait_gather", mb)]
+                if layer == layers:
+                    steps.append(("lm_head", mb))
+                    continue
+                steps += [("attention_block", mb, layer), ("scatter", mb, layer, "wo")]
+                pending[mb] = True
+            if layer == layers:
+                break
+            for mb in range(micro_batches):
+                steps += [("wait_scatter", mb), ("push", mb, layer, 1), ("wait_gather", mb), ("ffn_block", mb, layer), ("scatter", mb, layer, "wd")]
+        steps.append(("barrier",))
+        return steps
+
+    def exchange(mb, layer, which):
+        return [("aux_begin", mb), ("wait_scatter", mb), ("push", mb, layer, which), ("wait_gather", mb), ("aux_end", mb)]
     for layer in range(layers + 1):
         for mb in range(micro_batches):
-            if pending[mb]:
-                steps.append(("wait_scatter", mb))
-            steps += [("push", mb, layer, 0), ("wait_gather", mb)]
+            steps += [("push", mb, 0, 0), ("wait_gather", mb)] if layer == 0 else [("aux_wait", mb)]
             if layer == layers:
                 steps.append(("lm_head", mb))
                 continue
-            steps += [("attention_block", mb, layer), ("scatter", mb, layer, "wo")]
-            pending[mb] = True
+            steps += [("attention_block", mb, layer), ("scatter", mb, layer, "wo")] + exchange(mb, layer, 1)
         if layer == layers:
             break
         for mb in range(micro_batches):
-            steps += [("wait_scatter", mb), ("push", mb, layer, 1), ("wait_gather", mb), ("ffn_block", mb, layer), ("scatter", mb, layer, "wd")]
+            steps += [("aux_wait", mb), ("ffn_block", mb, layer), ("scatter", mb, layer, "wd")] + exchange(mb, layer + 1, 0)
     steps.append(("barrier",))
     return steps
 
@@ -135,7 +155,7 @@ class TensorParallelDecoder:
 
     def __init__(self, client: ComputeClient, cfg: LlamaConfig, batch: int, seq: int, comm=None, rank: int = 0, world: int = 1,
                  seed: int = 0, exact_weights: bool = False, micro_batches: int = 1, sm_reserve: int = 0, use_graph: bool = False,
-                 fused: bool = False):
+                 fused: bool = False, overlap_exchange: bool = False):
         if world > 1 and comm is None:
             raise InvalidTensor("a communicator is required for tensor parallelism")
         if cfg.head_dim != 128:
@@ -179,9 +199,10 @@ class TensorParallelDecoder:
         self.scale = 1.0 / float(np.sqrt(d))
         self._graph = None
         self._exchanges, self._peer_h, self._x_own = [], None, None
-        self.configure(comm, micro_batches, sm_reserve, use_graph, fused)
+        self.configure(comm, micro_batches, sm_reserve, use_graph, fused, overlap_exchange)
 
-    def configure(self, comm, micro_batches: int = 1, sm_reserve: int = 0, use_graph: bool = False, fused: bool = False) -> None:
+    def configure(self, comm, micro_batches: int = 1, sm_reserve: int = 0, use_graph: bool = False, fused: bool = False,
+                  overlap_exchange: bool = False) -> None:
         """(Re)builds the launch plan, and the recorded graph if asked for, on the weights and buffers already resident.
         Lets a caller compare schedules (micro batches, SMs left to NCCL, communicators with different CTA limits)
         without loading the model again."""
@@ -192,7 +213,7 @@ class TensorParallelDecoder:
         if fused and (self.world < 2 or (self.tokens // micro_batches) % (128 * self.world) or self.cfg.hidden % 64):
             raise InvalidTensor("fused exchange needs at least two ranks and micro batches of a multiple of 128 * world tokens")
         self.close()
-        self.comm, self.micro, self.fused = comm, micro_batches, fused
+        self.comm, self.micro, self.fused, self.overlap_exchange = comm, micro_batches, fused, bool(fused and overlap_exchange)
         self._keep = []          # ctypes structures referenced by the plan
         self._steps = []         # (function, argument tuple)
         self.launches_per_forward = 0
@@ -326,8 +347,11 @@ class TensorParallelDecoder:
         def x_own(mb):
             return TensorBuffer(self._x_own.handle, (rows, hidden), DType.BF16, None, offset=mb * rows * hidden * 2)
 
-        for step in fused_schedule(cfg.layers, n):
+        for step in fused_schedule(cfg.layers, n, self.overlap_exchange):
             kind = step[0]
+            if kind in ("aux_begin", "aux_end", "aux_wait"):   # fork to / join from the side stream; the slot is the micro batch
+                self._op("rb_" + kind, ctx, *(() if kind == "aux_begin" else (C.c_uint32(step[1]),)), kernel=False)
+                continue
             if kind == "barrier":
                 ex = self._exchanges[0]
                 self._op("rb_peer_signal", *ex.signal_args(keep))

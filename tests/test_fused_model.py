@@ -123,50 +123,81 @@ class Flags:
         self.count, self.target = [0] * world, 0
 
 
-def simulate(world, layers, micro, forwards, seed, barrier=True):
+def simulate(world, layers, micro, forwards, seed, barrier=True, overlap=False, joins=True):
+    """Every rank runs the schedule `forwards` times.  Steps between aux_begin and aux_end belong to the rank's side
+    stream: they run in order among themselves, not before the compute stream has passed their aux_begin, and an aux_wait
+    on the compute stream passes only when the latest segment recorded in its slot has finished."""
     from rust_ascend_b200.decoder import fused_schedule
-    schedule = []
-    for s in fused_schedule(layers, micro):
-        if s[0] != "barrier":
-            schedule.append(s)
-        elif barrier:                                             # rb_peer_signal, then rb_peer_wait on the barrier flags
-            schedule += [("barrier_signal",), ("barrier_wait",)]
+    main, side = [], []                 # per forward: compute-stream steps and side-stream steps, in program order
+    open_segment = None
+    for s in fused_schedule(layers, micro, overlap):
+        if s[0] == "barrier":
+            if barrier:                                           # rb_peer_signal, then rb_peer_wait on the barrier flags
+                main += [("barrier_signal",), ("barrier_wait",)]
+        elif s[0] == "aux_begin":
+            open_segment = len(main)
+            main.append(None)                                     # becomes ("fork", end of the segment) at aux_end
+        elif s[0] == "aux_end":
+            main[open_segment] = ("fork", len(side))              # side steps before this position may start
+            main.append(("record", s[1], len(side)))              # slot <- side position after this segment
+            open_segment = None
+        elif s[0] == "aux_wait" and not joins:
+            continue
+        elif open_segment is not None:
+            side.append(s)
+        else:
+            main.append(s)
     rng = random.Random(seed)
     signals = 5                                                    # announcements per scatter and owner (any positive count)
     staging = [[[Cell() for _src in range(world)] for _owner in range(world)] for _mb in range(micro)]
     gathered = [[[Cell() for _owner in range(world)] for _dest in range(world)] for _mb in range(micro)]
     flags = {kind: [[Flags(world) for _r in range(world)] for _mb in range(micro)] for kind in ("scatter", "gather", "barrier")}
-    pc = [0] * world                                               # position in forwards * schedule
+    pc = {"m": [0] * world, "a": [0] * world}                      # positions over forwards * len(list)
+    forked = [0] * world                                           # side position the compute stream has released
+    slots = [dict() for _ in range(world)]                         # slot -> side position that must be reached
     scatter_no = [[0] * micro for _ in range(world)]               # per rank and micro batch: scatters / pushes issued so far
     push_no = [[0] * micro for _ in range(world)]
-    total = forwards * len(schedule)
     waits = {"wait_scatter": ("scatter", signals), "wait_gather": ("gather", 1), "barrier_wait": ("barrier", 1)}
+    total = {"m": forwards * len(main), "a": forwards * len(side)}
+    program = {"m": main, "a": side}
 
     def ready(rank, kind, mb, count):
         f = flags[kind][mb][rank]
         return all(c - (f.target + count) >= 0 for c in f.count)
 
+    def runnable(r, stream):
+        if pc[stream][r] >= total[stream]:
+            return False
+        step = program[stream][pc[stream][r] % len(program[stream])]
+        if stream == "a" and pc["a"][r] >= forked[r]:
+            return False                                           # the compute stream has not reached this segment's fork
+        if step[0] in waits:
+            kind, count = waits[step[0]]
+            return ready(r, kind, step[1] if len(step) > 1 else 0, count)
+        if step[0] == "aux_wait":
+            return pc["a"][r] >= slots[r].get(step[1], 0)
+        return True
+
     steps = 0
-    while any(p < total for p in pc):
+    while any(pc[st][r] < total[st] for st in ("m", "a") for r in range(world)):
         steps += 1
-        runnable = []
-        for r in range(world):
-            if pc[r] >= total:
-                continue
-            step = schedule[pc[r] % len(schedule)]
-            if step[0] in waits:
-                kind, count = waits[step[0]]
-                if not ready(r, kind, step[1] if len(step) > 1 else 0, count):
-                    continue
-            runnable.append(r)
-        if not runnable:
-            raise Hazard("deadlock: every unfinished rank waits")
-        r = rng.choice(runnable)
-        step = schedule[pc[r] % len(schedule)]
+        choices = [(r, st) for r in range(world) for st in ("m", "a") if runnable(r, st)]
+        if not choices:
+            raise Hazard("deadlock: every unfinished stream waits")
+        r, st = rng.choice(choices)
+        position = pc[st][r]
+        step = program[st][position % len(program[st])]
+        base = position // len(program[st]) * len(side)            # side positions of earlier forwards
         kind = step[0]
         if kind in waits:
             group, count = waits[kind]
             flags[group][step[1] if len(step) > 1 else 0][r].target += count
+        elif kind == "fork":
+            forked[r] = base + step[1]
+        elif kind == "record":
+            slots[r][step[1]] = base + step[2]
+        elif kind == "aux_wait":
+            pass
         elif kind == "scatter":
             mb = step[1]
             scatter_no[r][mb] += 1
@@ -192,14 +223,22 @@ def simulate(world, layers, micro, forwards, seed, barrier=True):
                 flags["barrier"][0][dest].count[r] += 1
         else:
             assert kind == "embed", kind
-        pc[r] += 1
+        pc[st][r] += 1
     return steps
 
 
 @pytest.mark.parametrize("world,layers,micro", [(2, 1, 1), (2, 2, 2), (4, 2, 1), (8, 3, 2), (3, 2, 2)])
+@pytest.mark.parametrize("overlap", [False, True])
 @pytest.mark.parametrize("seed", range(6))
-def test_fused_schedule_has_no_buffer_hazard_under_any_interleaving(world, layers, micro, seed):
-    simulate(world, layers, micro, forwards=3, seed=seed)
+def test_fused_schedule_has_no_buffer_hazard_under_any_interleaving(world, layers, micro, overlap, seed):
+    simulate(world, layers, micro, forwards=3, seed=seed, overlap=overlap)
+
+
+def test_model_detects_a_missing_join_of_the_side_stream():
+    # Without aux_wait the compute stream's next block reads activations that the side stream has not gathered yet.
+    with pytest.raises(Hazard):
+        for seed in range(20):
+            simulate(2, 2, 2, forwards=2, seed=seed, overlap=True, joins=False)
 
 
 def test_model_detects_the_hazard_the_closing_barrier_prevents():
@@ -291,8 +330,8 @@ class FakeComm:
         self.control = FakeControl(rank, world)
 
 
-@pytest.mark.parametrize("world,micro", [(2, 1), (4, 2), (8, 1)])
-def test_fused_plan_follows_the_schedule_and_stays_inside_its_buffers(monkeypatch, world, micro):
+@pytest.mark.parametrize("world,micro,overlap", [(2, 1, False), (4, 2, False), (8, 1, False), (2, 2, True), (8, 2, True)])
+def test_fused_plan_follows_the_schedule_and_stays_inside_its_buffers(monkeypatch, world, micro, overlap):
     import rust_ascend_b200.fused as fused
     from rust_ascend_b200._lib import rb_tensor
     from rust_ascend_b200.decoder import LlamaConfig, TensorParallelDecoder, fused_schedule
@@ -302,13 +341,15 @@ def test_fused_plan_follows_the_schedule_and_stays_inside_its_buffers(monkeypatc
     batch, seq = 2 * micro, 64 * world
     rank = world - 1
     client = FakeClient()
-    model = TensorParallelDecoder(client, cfg, batch, seq, comm=FakeComm(rank, world), rank=rank, world=world, micro_batches=micro, fused=True)
+    model = TensorParallelDecoder(client, cfg, batch, seq, comm=FakeComm(rank, world), rank=rank, world=world, micro_batches=micro, fused=True,
+                                  overlap_exchange=overlap, sm_reserve=16 if overlap else 0)
     names = [fn.__name__ for fn, _ in model._steps]
     expected = []
-    for step in fused_schedule(cfg.layers, micro):
+    for step in fused_schedule(cfg.layers, micro, overlap):
         expected += {"embed": ["rb_embedding"], "wait_scatter": ["rb_peer_wait"], "wait_gather": ["rb_peer_wait"], "push": ["rb_reduce_norm_push"],
                      "attention_block": ["rb_gemm", "rb_attention"], "ffn_block": ["rb_gemm"], "scatter": ["rb_gemm_scatter"],
-                     "lm_head": ["rb_gemm"], "barrier": ["rb_peer_signal", "rb_peer_wait"]}[step[0]]
+                     "lm_head": ["rb_gemm"], "barrier": ["rb_peer_signal", "rb_peer_wait"],
+                     "aux_begin": ["rb_aux_begin"], "aux_end": ["rb_aux_end"], "aux_wait": ["rb_aux_wait"]}[step[0]]
     assert names == expected
     assert model.fused_exchanges_per_forward == micro * (2 * cfg.layers) and model.collectives_per_forward == 0
     # every descriptor the plan keeps alive lies inside the storage it names
