@@ -358,7 +358,7 @@ def attention_extra(client, RT, pk):
     return out
 
 
-def decoder_candidates(world: int, sequences: int = 8):
+def decoder_candidates(world: int, sequences: int = 8, fused: bool = False):
     """What the decoder extra times at `world` GPUs: pure tensor parallelism first (three schedules), then tensor-parallel
     groups of world/2, world/4, ... GPUs that each take their own share of the sequences, and last plain replicas (every GPU
     runs whole sequences, no exchange).  Every entry names its tensor-parallel degree `tp`; the others split the batch."""
@@ -367,6 +367,8 @@ def decoder_candidates(world: int, sequences: int = 8):
     if world == 1:
         return [dict(plain, tp=1)]
     out = [dict(overlap, tp=world), dict(plain, tp=world), dict(plain, tp=world, micro_batches=2)]
+    if fused:   # exchange fused into the kernels over peer memory: on one stream, and with the owner-side step on the side stream
+        out += [dict(plain, tp=world, fused=True), dict(overlap, tp=world, fused=True, overlap_exchange=True, nccl_max_ctas=0)]
     tp = world // 2
     while tp >= 1:
         per_group = sequences * tp // world
@@ -409,7 +411,8 @@ def decoder_extra(client, pk, rank, world, dist, sink):
                                           "value": total_flops / (b["ms_per_forward"] * 1e-3) / 1e12, "unit": "TFLOP/s (whole job)"}
         return out
 
-    for cand in decoder_candidates(world, sequences):
+    # The fused exchange is timed only on request until it has been validated on this pool's GPUs.
+    for cand in decoder_candidates(world, sequences, fused=os.environ.get("RUDA_BENCH_FUSED") == "1"):
         tp = cand["tp"]
         groups = world // tp
         group, tp_rank = rank // tp, rank % tp
@@ -429,9 +432,10 @@ def decoder_extra(client, pk, rank, world, dist, sink):
             for other in models.values():
                 other.close()
             models[tp] = TensorParallelDecoder(client, cfg, per_group, seq, comm=comm, rank=tp_rank, world=tp, micro_batches=cand["micro_batches"],
-                                               sm_reserve=cand["sms_left_to_nccl"], use_graph=True)
+                                               sm_reserve=cand["sms_left_to_nccl"], use_graph=True, fused=cand.get("fused", False),
+                                               overlap_exchange=cand.get("overlap_exchange", False))
         else:
-            models[tp].configure(comm, cand["micro_batches"], cand["sms_left_to_nccl"], True)
+            models[tp].configure(comm, cand["micro_batches"], cand["sms_left_to_nccl"], True, cand.get("fused", False), cand.get("overlap_exchange", False))
         model = models[tp]
         model.forward(tokens[group * per_group:(group + 1) * per_group])
         for _ in range(2):
@@ -445,8 +449,10 @@ def decoder_extra(client, pk, rank, world, dist, sink):
             model.forward()
         ms = max_over_ranks(dist, client.end_profile() / steps)
         label = f"tp{tp}" if groups == 1 else (f"tp{tp} x {groups} groups of {per_group} sequences" if tp > 1 else f"{groups} replicas of {per_group} sequences, no exchange")
+        if cand.get("fused"):
+            label += ", exchange fused into the kernels" + (" and overlapped on the side stream" if cand.get("overlap_exchange") else "")
         results.append(dict(cand, parallelism=label, ms_per_forward=ms, launches_per_forward=model.launches_per_forward,
-                            all_reduces_per_forward=model.collectives_per_forward))
+                            all_reduces_per_forward=model.collectives_per_forward, fused_exchanges_per_forward=model.fused_exchanges_per_forward))
         sink["tp_decoder"] = summary()
     for model in models.values():
         model.close()

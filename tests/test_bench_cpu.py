@@ -22,7 +22,16 @@ def test_decoder_candidates_cover_pure_and_grouped_tensor_parallelism():
             groups = world // c["tp"]
             assert 8 % groups == 0 and (8 // groups) % c["micro_batches"] == 0   # every group gets whole sequences
             assert (c["nccl_max_ctas"] == 0) == (c["sms_left_to_nccl"] == 0)
+            assert "fused" not in c                                     # the fused exchange is timed only on request
             assert c["tp"] > 1 or c["micro_batches"] == 1               # replicas have nothing to overlap
+
+
+def test_fused_candidates_are_added_on_request():
+    import bench
+    extra = [c for c in bench.decoder_candidates(8, fused=True) if c.get("fused")]
+    assert [(c["tp"], c["micro_batches"], c.get("overlap_exchange", False)) for c in extra] == [(8, 1, False), (8, 2, True)]
+    assert all(c["nccl_max_ctas"] == 0 for c in extra)                  # NCCL is not on this path
+    assert bench.decoder_candidates(1, fused=True) == bench.decoder_candidates(1)
 
 
 def test_reference_arm_prints_one_json_line():
