@@ -185,3 +185,78 @@ def test_group_rules():
     with pytest.raises(ContractError):
         GroupControl(SingleControl(), [0, 0])
     assert GroupControl(SingleControl(), [0]).all_gather_bytes(b"x") == [b"x"]
+
+
+class _FakePeerLib:
+    """rb_peer_* without a device: a token names the exporting rank, opening it yields handle 100 + that rank."""
+
+    def __init__(self, rank, fail_export):
+        self.rank, self.fail_export, self.closed = rank, fail_export, []
+
+    def rb_peer_export(self, ctx, handle, token):
+        if self.fail_export:
+            return 5
+        token[0] = self.rank
+        return 0
+
+    def rb_peer_open(self, ctx, token, nbytes, out):
+        out._obj.value = 100 + token[0]
+        return 0
+
+    def rb_peer_close(self, ctx, handle):
+        self.closed.append(handle.value)
+        return 0
+
+    def rb_last_error(self):
+        return b"cudaIpcGetMemHandle failed with CUDA status 1"
+
+
+class _FakePeerClient:
+    def __init__(self, rank, fail_export):
+        self._lib, self._ctx, self.freed = _FakePeerLib(rank, fail_export), None, []
+
+    def empty(self, size):
+        return 7
+
+    def memset(self, t, value=0):
+        pass
+
+    def sync(self):
+        pass
+
+    def free(self, handle):
+        self.freed.append(handle)
+
+
+def _peer_worker(rank, world, port, fail_rank, results):
+    dist = _init(rank, world, port)
+    import rust_ascend_b200.fused as fused
+    from rust_ascend_b200.distributed import CollectiveError, TorchControl
+    from rust_ascend_b200.runtime import B200Error
+    fused._check = lambda code: (_ for _ in ()).throw(B200Error("cudaIpcGetMemHandle failed with CUDA status 1")) if code else None
+    client = _FakePeerClient(rank, fail_rank == rank)
+    try:
+        buf = fused.PeerBuffer(client, TorchControl(), 4096)
+        handles = list(buf.handles)
+        buf.close()
+        results[rank] = ("ok", handles, client._lib.closed, client.freed)
+    except CollectiveError as e:
+        results[rank] = ("error", str(e))
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("fail_rank", [None, 1])
+def test_peer_buffer_exchange_orders_handles_by_rank_and_fails_on_every_rank(fail_rank):
+    world, port = 3, _free_port()
+    with mp.Manager() as manager:
+        results = manager.dict()
+        mp.spawn(_peer_worker, args=(world, port, fail_rank, results), nprocs=world, join=True)
+        results = dict(results)
+    for rank in range(world):
+        if fail_rank is None:
+            status, handles, closed, freed = results[rank]
+            assert status == "ok"
+            assert handles == [7 if r == rank else 100 + r for r in range(world)]       # own allocation, peers' mappings by rank
+            assert sorted(closed) == [100 + r for r in range(world) if r != rank] and freed == [7]
+        else:
+            assert results[rank][0] == "error" and f"NCCL rank {fail_rank}:" in results[rank][1]
