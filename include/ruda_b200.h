@@ -363,6 +363,12 @@ RB_API int32_t rb_broadcast(rb_comm* comm, const rb_tensor* in, uint32_t root, c
 RB_API int32_t rb_all_gather(rb_comm* comm, const rb_tensor* in, const rb_tensor* out);
 /* HcclCommunicator::reduce_scatter, runtime/hccl.rs:467-473: this rank's equal leading-axis shard of the reduction. */
 RB_API int32_t rb_reduce_scatter(rb_comm* comm, const rb_tensor* in, int32_t op, const rb_tensor* out);
+/* Row-parallel Linear and its all-reduce in one call: what a tensor-parallel caller writes as gemm (runtime/mod.rs:346-349) on its
+ * K shard followed by HcclCommunicator::all_reduce(sum) (runtime/hccl.rs:452-460).  x BF16 [T, K/world], w_shard BF16
+ * [H, K/world], out BF16 or FP32 [T, H], complete on every rank.  overlap_mode 0: one GEMM then one all-reduce; 1: up to four
+ * row chunks whose all-reduces run on the communicator's stream under the next chunk's GEMM. */
+RB_API int32_t rb_row_parallel_linear_allreduce(rb_comm* comm, const rb_tensor* x, const rb_tensor* w_shard,
+                                                const rb_tensor* out, int32_t overlap_mode);
 
 #ifdef __cplusplus
 }

@@ -290,4 +290,33 @@ int32_t rb_reduce_scatter(rb_comm* c, const rb_tensor* in, int32_t op, const rb_
     return leave(c, "ncclReduceScatter", g_api.ReduceScatter(pi, po, n, dt, ro, c->comm, c->stream), 0);
 }
 
+// Row-parallel Linear followed by all-reduce(sum) in one call: out [T, H] = sum over ranks of x_r [T, K/world] w_r [H, K/world]^T.
+// overlap_mode 0: one GEMM, one all-reduce.  overlap_mode 1: the rows are cut into up to four chunks of whole 128-row tiles;
+// the all-reduce of chunk i runs on the communicator's stream while the GEMM of chunk i+1 runs on the compute stream
+// (deferred fences), and later compute is ordered after the last chunk.
+int32_t rb_row_parallel_linear_allreduce(rb_comm* c, const rb_tensor* x, const rb_tensor* w_shard, const rb_tensor* out, int32_t overlap_mode) {
+    RB_TRY(check_comm(c));
+    if (!x || !w_shard || !out) return fail(RB_NULL_HANDLE, "null tensor");
+    if (overlap_mode != 0 && overlap_mode != 1) return fail(RB_INVALID_TENSOR, "overlap mode is 0 (sequential) or 1 (row chunks)");
+    if (x->rank != 2 || w_shard->rank != 2 || out->rank != 2 || out->shape[0] != x->shape[0] || out->shape[1] != w_shard->shape[0] || x->shape[1] != w_shard->shape[1])
+        return fail(RB_INVALID_TENSOR, "row-parallel linear takes x [T, K/world], w [H, K/world] and out [T, H]");
+    const uint64_t rows = x->shape[0], k = x->shape[1], n = out->shape[1];
+    uint64_t chunks = 1;
+    if (overlap_mode == 1 && c->world > 1) {
+        const uint64_t tiles = rows / 128;
+        chunks = tiles >= 4 && rows % 128 == 0 ? 4 : (tiles >= 2 && rows % 128 == 0 ? 2 : 1);
+        while (chunks > 1 && tiles % chunks) chunks /= 2;
+    }
+    const uint64_t chunk_rows = rows / chunks;
+    for (uint64_t i = 0; i < chunks; ++i) {
+        rb_tensor xi = *x, oi = *out;
+        xi.shape[0] = chunk_rows; xi.offset = x->offset + i * chunk_rows * k * dtype_size(x->dtype);
+        oi.shape[0] = chunk_rows; oi.offset = out->offset + i * chunk_rows * n * dtype_size(out->dtype);
+        RB_TRY(rb_gemm(c->ctx, &xi, w_shard, RB_NO_TRANSPOSE, RB_TRANSPOSE, nullptr, nullptr, RB_EPILOGUE_NONE, &oi));
+        RB_TRY(rb_all_reduce(c, &oi, RB_SUM, &oi, chunks > 1 ? 1 : 0));
+    }
+    if (chunks > 1) RB_TRY(rb_comm_fence(c));
+    return RB_OK;
+}
+
 }  // extern "C"

@@ -132,6 +132,15 @@ class NativeNccl:
         _check(self._lib.rb_all_gather(self._comm, _ref(value), _ref(out)))
         return out
 
+    def row_parallel_linear_allreduce(self, x: TensorBuffer, w_shard: TensorBuffer, dtype: DType = DType.BF16, overlap: bool = False) -> TensorBuffer:
+        """out [T, H] = sum over ranks of x_r [T, K/world] w_r [H, K/world]^T on every rank: GEMM and all-reduce(sum) in one call,
+        optionally in row chunks so that a chunk's all-reduce runs under the next chunk's GEMM."""
+        if len(x.shape) != 2 or len(w_shard.shape) != 2:
+            raise InvalidTensor("row-parallel linear takes x [T, K/world], w [H, K/world] and out [T, H]")
+        out = self.client.tensor((x.shape[0], w_shard.shape[0]), dtype)
+        _check(self._lib.rb_row_parallel_linear_allreduce(self._comm, _ref(x), _ref(w_shard), _ref(out), C.c_int32(int(overlap))))
+        return out
+
     def reduce_scatter(self, value: TensorBuffer, op: str = "sum") -> TensorBuffer:
         if value.shape[0] % self.world_size:
             raise InvalidTensor("reduce_scatter needs a leading axis divisible by the world size")

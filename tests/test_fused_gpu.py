@@ -81,6 +81,9 @@ def _worker(rank, world, port, results):
     ex.close()
     # 3. the decoder: fused mode against the NCCL mode on the same weights and tokens
     comm = NcclCommunicator.initialize(control, client)
+    for overlap in (False, True):   # the NCCL form of the same projection, sequential and in row chunks
+        y = comm.native.row_parallel_linear_allreduce(xs, ws, DType.BF16, overlap)
+        out[f"nccl_linear_{int(overlap)}"] = bf16_bits_to_f32(client.read(y))
     cfg = _cfg()
     tokens = np.random.default_rng(0).integers(0, cfg.vocab, size=(2, 128)).astype(np.int32)
     for name, kwargs in (("nccl", {}), ("fused", {"fused": True}), ("fused_graph", {"fused": True, "use_graph": True})):
@@ -134,6 +137,8 @@ def test_two_gpu_fused_exchange(oracle):
         err = np.abs(got - total)
         assert err.max() <= 2.0 ** -7 * np.abs(total).max() and err.mean() <= 1e-3 * np.abs(total).mean() + 1e-6, (err.max(), err.mean())
         np.testing.assert_array_equal(got, r[0]["fused_linear"])          # every rank holds the same bits
+        for key in ("nccl_linear_0", "nccl_linear_1"):
+            assert np.abs(r[rank][key] - total).max() <= 2.0 ** -7 * np.abs(total).max()
     rows = x.shape[0] // world
     resid = np.random.default_rng(5).standard_normal(total.shape).astype(np.float32)
     weight = bf16(np.random.default_rng(6).uniform(0.5, 1.5, total.shape[1]).astype(np.float32))
