@@ -286,6 +286,13 @@ def extras(client, RT, pk, args, rank, world, dist, out):
     written into `out` as they arrive, so that a run cut short by the watchdog still reports what finished."""
     from rust_ascend_b200 import DType
     if world > 1:
+        # NVLS (in-switch reduction) stays off for every communicator of this process: the watchdog may end a rank while
+        # collectives are pending, and a rank that leaves while its memory is bound to an NVLS group can fault its peers.
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        try:
+            out["row_parallel_linear"] = row_parallel_extra(client, pk, rank, world, dist)
+        except Exception as error:      # the decoder measurement below does not depend on this one
+            out["row_parallel_linear"] = {"error": f"{type(error).__name__}: {error}"}
         decoder_extra(client, pk, rank, world, dist, out)
         return out
     rows, width = 4096, 4096
@@ -356,6 +363,42 @@ def attention_extra(client, RT, pk):
             for t in st:
                 client.free(t.handle)
     return out
+
+
+def row_parallel_extra(client, pk, rank, world, dist):
+    """Config 2a as a row-parallel Linear: every rank holds K/world columns of X [4096, 4096] and W [4096, 4096] and the
+    partial products are summed by one all-reduce of the BF16 [4096, 4096] result; timed sequentially and with the rows cut
+    into chunks whose all-reduces run under the next chunk's GEMM.  Whole-job flops are those of the full product."""
+    from rust_ascend_b200 import DType
+    from rust_ascend_b200.distributed import NcclCommunicator, TorchControl
+    from rust_ascend_b200.runtime import f32_to_bf16_bits
+    os.environ.pop("RUDA_NCCL_MAX_CTAS", None)
+    comm = NcclCommunicator.initialize(TorchControl(), client)
+    rng = np.random.default_rng(100 + rank)
+    k = K // world
+    x = client.upload(f32_to_bf16_bits(rng.standard_normal((M, k), dtype=np.float32)))
+    w = client.upload(f32_to_bf16_bits(rng.standard_normal((N, k), dtype=np.float32) * np.float32(0.02)))
+    result = {"config": f"X [{M}, {K}/{world}] . W [{N}, {K}/{world}]^T summed over {world} ranks, BF16 result on every rank", "unit": "TFLOP/s (whole job)"}
+    import ctypes as C
+    from rust_ascend_b200.runtime import _check
+    y = client.tensor((M, N), DType.BF16)
+    keep = [x._c(), w._c(), y._c()]
+
+    def call(overlap):
+        _check(client._lib.rb_row_parallel_linear_allreduce(comm.native._comm, C.byref(keep[0]), C.byref(keep[1]), C.byref(keep[2]), C.c_int32(int(overlap))))
+    for name, overlap in (("sequential", False), ("row_chunks_overlapped", True)):
+        for _ in range(5):
+            call(overlap)
+        client.sync()
+        if dist is not None:
+            dist.barrier()
+        steps = 20
+        client.start_profile()
+        for _ in range(steps):
+            call(overlap)
+        ms = max_over_ranks(dist, client.end_profile() / steps)
+        result[name] = {"us": ms * 1e3, "value": 2.0 * M * N * K / (ms * 1e-3) / 1e12}
+    return result
 
 
 def decoder_candidates(world: int, sequences: int = 8, fused: bool = False):
