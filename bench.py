@@ -332,6 +332,34 @@ def extras(client, RT, pk, args, rank, world, dist, out):
             client.free(t.handle)
     out.update(attention_extra(client, RT, pk))
     decoder_extra(client, pk, rank, world, dist, out)
+    if not args.no_cpu_baseline:
+        try:
+            import oracle as orc
+            orc.build()
+            orc.use_all_cores()
+            out["cpu_baselines"] = cpu_side_baselines(orc)
+        except Exception as error:
+            out["cpu_baselines"] = {"error": f"{type(error).__name__}: {error}"}
+    return out
+
+
+def cpu_side_baselines(orc):
+    """The oracle port of the secondary kernels on the host cores, beside their GPU numbers: RMSNorm at config 1's full size
+    and causal attention on one (batch, head) pair of config 3 (the flops of that pair; the full config is 128 such pairs)."""
+    out = {"cores": orc.threads(), "kind": "port"}
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((4096, 4096), dtype=np.float32); w = rng.uniform(0.5, 1.5, 4096).astype(np.float32)
+    orc.rms_norm(x[:64], w, 1e-6)
+    times = []
+    for _ in range(3):
+        t0 = time.perf_counter(); orc.rms_norm(x, w, 1e-6); times.append(time.perf_counter() - t0)
+    dt = float(np.median(times))
+    out["rms_norm_fp32_4096x4096"] = {"value": (2 * x.nbytes + w.nbytes + 4096 * 4) / dt / 1e9, "unit": "GB/s", "ms": dt * 1e3, "sample": "full size, median of 3"}
+    s, d = 2048, 128
+    q, k, v = (rng.standard_normal((1, 1, s, d), dtype=np.float32) for _ in range(3))
+    t0 = time.perf_counter(); orc.attention(q, k, v, d ** -0.5, causal=True); dt = time.perf_counter() - t0
+    out["attention_causal_s2048_d128"] = {"value": 2 * s * s * d / dt / 1e12, "unit": "TFLOP/s", "ms": dt * 1e3,
+                                          "sample": "1 of the 128 (batch, head) pairs of config 3, once"}
     return out
 
 
