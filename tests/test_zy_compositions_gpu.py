@@ -103,3 +103,58 @@ def test_row_parallel_linear_allreduce_on_a_world_of_one(client, oracle):
     finally:
         client.sync()
         comm.native.destroy()
+
+
+# ---- the reference's device validation programs, through the C ABI -------------------------------------------------------
+@pytest.mark.parametrize("batch", [1, 3])
+@pytest.mark.parametrize("ta", [False, True])
+@pytest.mark.parametrize("tb", [False, True])
+def test_driver_gemm_validation_cases(client, batch, ta, tb):
+    from rust_ascend_b200 import B200Runtime as RT, DType, Transpose
+    from rust_ascend_b200.runtime import bf16_bits_to_f32, f32_to_bf16_bits
+    a, b, d = V.driver_gemm_case(batch, ta, tb)                    # deepgemm_validate.rs:32-45: gemm, then gemm_into the same output
+    da, db = client.upload(f32_to_bf16_bits(a)), client.upload(f32_to_bf16_bits(b))
+    T = lambda flag: Transpose.Yes if flag else Transpose.No
+    for dtype in (DType.BF16, DType.F32):
+        out = RT.gemm(client, da, db, T(ta), T(tb), dtype)
+        read = lambda: bf16_bits_to_f32(client.read(out)) if dtype == DType.BF16 else client.read(out)
+        close(read(), d, 0.05, 0.01)
+        client.memset(out, 0xFF)
+        RT.gemm_into(client, da, db, T(ta), T(tb), out)
+        close(read(), d, 0.05, 0.01)
+
+
+def test_driver_grouped_and_linear_backward_cases(client):
+    from rust_ascend_b200 import B200Runtime as RT, DType
+    from rust_ascend_b200.runtime import bf16_bits_to_f32, f32_to_bf16_bits
+    a, w, ends, d = V.driver_grouped_case()                        # deepgemm_validate.rs:47-53
+    for dtype in (DType.BF16, DType.F32):
+        out = client.read(RT.gemm_grouped_nt(client, client.upload(f32_to_bf16_bits(a)), client.upload(f32_to_bf16_bits(w)), ends, dtype))
+        close(bf16_bits_to_f32(out) if dtype == DType.BF16 else out, d, 0.05, 0.01)
+    x, w, dy, dx, dw = V.driver_linear_backward_case()             # deepgemm_validate.rs:55-59
+    up = lambda v: client.upload(f32_to_bf16_bits(v))
+    gdx, gdw = RT.linear_nt_backward(client, up(x), up(w), up(dy))
+    close(bf16_bits_to_f32(client.read(gdx)), dx, 0.05, 0.01); close(client.read(gdw), dw, 0.05, 0.01)
+
+
+@pytest.mark.parametrize("n", V.COMMON_IR_SIZES)
+def test_common_ir_silu_programs(client, n):
+    from rust_ascend_b200 import B200Runtime as RT
+    x, up, dy, y, dgate, dup = V.common_ir_case(n)                 # common_ir_validate.rs:17-31
+    dx, dup_, ddy = client.upload(x), client.upload(up), client.upload(dy)
+    close(client.read(RT.silu_mul(client, dx, dup_)), y, 5e-4, 5e-4)
+    g, u = RT.silu_mul_backward(client, dx, dup_, ddy)
+    close(client.read(g), dgate, 5e-4, 5e-4); close(client.read(u), dup, 5e-4, 5e-4)
+
+
+@pytest.mark.parametrize("table_shape", V.PREFIX_TABLE_SHAPES)
+@pytest.mark.parametrize("layout", ["interleaved", "split_half"])
+def test_rotary_prefix_tensor_example(client, table_shape, layout):
+    from rust_ascend_b200 import B200Runtime as RT, RotaryLayout
+    x, cos, sin, dy, y, dx = V.rotary_prefix_tensor_case(table_shape, layout)   # rotary_prefix_tensor.rs:16-45
+    lay = RotaryLayout.Interleaved if layout == "interleaved" else RotaryLayout.SplitHalf
+    dcos, dsin = client.upload(cos), client.upload(sin)
+    got = client.read(RT.rotary_prefix(client, client.upload(x), dcos, dsin, 6, lay))
+    close(got, y, 3e-5, 3e-5)
+    np.testing.assert_array_equal(got[..., 6:].view(np.uint32), x[..., 6:].view(np.uint32))
+    close(client.read(RT.rotary_prefix_backward(client, client.upload(dy), dcos, dsin, 6, lay)), dx, 3e-5, 3e-5)

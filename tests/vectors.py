@@ -293,3 +293,77 @@ def linear_backward_case(m=32, n=48, k=16):
     w = (((np.arange(n * k) % 13).astype(np.float32) - 6.0) * 0.25).reshape(n, k)
     dy = (((np.arange(m * n) % 11).astype(np.float32) - 5.0) * 0.0625).reshape(m, n)
     return x, w, dy, dy.astype(np.float64) @ w.astype(np.float64), dy.astype(np.float64).T @ x.astype(np.float64)
+
+
+# ---- device validation programs of the driver crate -----------------------------------------------
+def driver_host(n, seed):
+    """rust-ascend-driver/examples/deepgemm_validate.rs:6: ((i*7+seed)%17)/8 - 1, exactly representable in BF16."""
+    return ((np.arange(n) * 7 + seed) % 17).astype(np.float32) / np.float32(8.0) - np.float32(1.0)
+
+
+def driver_gemm_case(batch, ta, tb):
+    """deepgemm_validate.rs:32-41: 32 x 64 x 48, batch 1 or 3; returns A, B in their stored shapes and the f64 product."""
+    m, n, k = 32, 64, 48
+    a = driver_host(batch * m * k, 1).reshape((batch, k, m) if ta else (batch, m, k))
+    b = driver_host(batch * k * n, 4).reshape((batch, n, k) if tb else (batch, k, n))
+    opa = a.transpose(0, 2, 1) if ta else a
+    opb = b.transpose(0, 2, 1) if tb else b
+    d = opa.astype(np.float64) @ opb.astype(np.float64)
+    if batch == 1:
+        return a[0], b[0], d[0]
+    return a, b, d
+
+
+def driver_grouped_case():
+    """deepgemm_validate.rs:47-53: 512 x 64 x 48, ends [256, 256, 512] (an empty expert in the middle)."""
+    m, n, k = 512, 64, 48
+    a = driver_host(m * k, 2).reshape(m, k); w = driver_host(3 * n * k, 5).reshape(3, n, k)
+    d = np.concatenate([a[:256].astype(np.float64) @ w[0].astype(np.float64).T, a[256:].astype(np.float64) @ w[2].astype(np.float64).T])
+    return a, w, [256, 256, 512], d
+
+
+def driver_linear_backward_case():
+    """deepgemm_validate.rs:55-59: dX = dY W, dW = dY^T X for 32 x 64 x 48."""
+    m, n, k = 32, 64, 48
+    x = driver_host(m * k, 3).reshape(m, k); w = driver_host(n * k, 2).reshape(n, k); dy = driver_host(m * n, 7).reshape(m, n)
+    return x, w, dy, dy.astype(np.float64) @ w.astype(np.float64), dy.astype(np.float64).T @ x.astype(np.float64)
+
+
+COMMON_IR_SIZES = [1, 7, 256, 257, 1025]
+
+
+def common_ir_case(n):
+    """rust-ascend-driver/examples/common_ir_validate.rs:17-25: SiLU*up and its backward with f64 expectations."""
+    i = np.arange(n)
+    x = (i % 61).astype(np.float32) / np.float32(7.0) - np.float32(4.0)
+    up = (i % 19).astype(np.float32) / np.float32(9.0) - np.float32(1.0)
+    dy = (i % 11).astype(np.float32) / np.float32(8.0) - np.float32(0.5)
+    a, b, g = x.astype(np.float64), up.astype(np.float64), dy.astype(np.float64)
+    s = 1.0 / (1.0 + np.exp(-a)); h = a * s; d = s * (1.0 + a * (1.0 - s))
+    return x, up, dy, h * b, g * b * d, g * h
+
+
+PREFIX_TABLE_SHAPES = [(1, 1, 5, 3), (2, 1, 5, 3), (1, 3, 1, 3), (2, 3, 5, 3)]
+
+
+def rotary_prefix_tensor_case(table_shape, layout):
+    """examples/rotary_prefix_tensor.rs:16-45: x [2,3,5,11], prefix 6, tables with singleton axes; output and the input
+    gradient for upstream dy (the example's factor 2 comes from its y*dy + y*dy and is left out here)."""
+    batch, heads, seq, width, prefix = 2, 3, 5, 11, 6
+    half = prefix // 2
+    t = int(np.prod(table_shape)); n = batch * heads * seq * width
+    cos = (np.float32(0.75) + (np.arange(t) % 3).astype(np.float32) / np.float32(16.0)).reshape(table_shape)
+    sin = (np.float32(0.25) - (np.arange(t) % 5).astype(np.float32) / np.float32(32.0)).reshape(table_shape)
+    x = ((np.arange(n) % 19).astype(np.float32) / np.float32(8.0) - np.float32(1.0)).reshape(batch, heads, seq, width)
+    dy = ((np.arange(n) % 13).astype(np.float32) / np.float32(8.0) - np.float32(0.5)).reshape(batch, heads, seq, width)
+    c = np.broadcast_to(cos, (batch, heads, seq, half)).astype(np.float64); s = np.broadcast_to(sin, (batch, heads, seq, half)).astype(np.float64)
+    y = x.astype(np.float64).copy(); dx = dy.astype(np.float64).copy()
+    if layout == "interleaved":
+        ia, ib = slice(0, prefix, 2), slice(1, prefix, 2)
+    else:
+        ia, ib = slice(0, half), slice(half, prefix)
+    xa, xb = x[..., ia].astype(np.float64), x[..., ib].astype(np.float64)
+    ga, gb = dy[..., ia].astype(np.float64), dy[..., ib].astype(np.float64)
+    y[..., ia] = xa * c - xb * s; y[..., ib] = xb * c + xa * s
+    dx[..., ia] = ga * c + gb * s; dx[..., ib] = gb * c - ga * s
+    return x, cos, sin, dy, y, dx
