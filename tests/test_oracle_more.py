@@ -41,3 +41,19 @@ def test_rotary_prefix_tensor_example(oracle, table_shape, layout):
     close(got, y, 3e-5, 3e-5)
     np.testing.assert_array_equal(got[..., 6:].view(np.uint32), x[..., 6:].view(np.uint32))   # the tail keeps its bits
     close(oracle.rotary_prefix(dy, cos, sin, 6, layout, backward=True), dx, 3e-5, 3e-5)
+
+
+@pytest.mark.parametrize("shape", V.BIAS_SHAPES)
+def test_bias_tensor_example_is_exact(oracle, shape):
+    x, r, b, dy, plain, with_res, doubled, db = V.bias_tensor_case(shape)       # examples/bias_tensor.rs:11-41: exact equality
+    np.testing.assert_array_equal(oracle.bias_add(x, b), plain)
+    np.testing.assert_array_equal(oracle.bias_add(x, b, r), with_res)
+    np.testing.assert_array_equal(oracle.bias_add(x, b, x), doubled)
+    np.testing.assert_array_equal(oracle.column_sum(dy), db)
+
+
+@pytest.mark.parametrize("m,n,k", [(16, 32, 32), (32, 48, 16)])
+def test_frozen_linear_example(oracle, m, n, k):
+    x, w, dy, y, dx = V.frozen_linear_case(m, n, k)                # examples/frozen_bf16_tensor.rs:33-52, 5e-4 + 5e-4 |b|
+    close(oracle.gemm_bf16(x, w, False, True, False), y, 5e-4, 5e-4)
+    close(oracle.gemm_bf16(dy, w, False, False, False), dx, 5e-4, 5e-4)

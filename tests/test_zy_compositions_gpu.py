@@ -158,3 +158,26 @@ def test_rotary_prefix_tensor_example(client, table_shape, layout):
     close(got, y, 3e-5, 3e-5)
     np.testing.assert_array_equal(got[..., 6:].view(np.uint32), x[..., 6:].view(np.uint32))
     close(client.read(RT.rotary_prefix_backward(client, client.upload(dy), dcos, dsin, 6, lay)), dx, 3e-5, 3e-5)
+
+
+@pytest.mark.parametrize("shape", V.BIAS_SHAPES)
+def test_bias_tensor_example_is_exact(client, shape):
+    from rust_ascend_b200 import B200Runtime as RT
+    x, r, b, dy, plain, with_res, doubled, db = V.bias_tensor_case(shape)       # examples/bias_tensor.rs:11-41: exact equality
+    dx, db_ = client.upload(x), client.upload(b)
+    np.testing.assert_array_equal(client.read(RT.bias_add(client, dx, db_)), plain)
+    np.testing.assert_array_equal(client.read(RT.bias_add(client, dx, db_, client.upload(r))), with_res)
+    np.testing.assert_array_equal(client.read(RT.bias_add(client, dx, db_, client.upload(x))), doubled)
+    np.testing.assert_array_equal(client.read(RT.bias_add_backward(client, client.upload(dy), x.shape)), db)
+
+
+@pytest.mark.parametrize("m,n,k", [(16, 32, 32), (32, 48, 16)])
+def test_frozen_linear_example(client, m, n, k):
+    from rust_ascend_b200 import B200Runtime as RT
+    from rust_ascend_b200.runtime import f32_to_bf16_bits
+    x, w, dy, y, dx = V.frozen_linear_case(m, n, k)                # examples/frozen_bf16_tensor.rs:33-52
+    stored = f32_to_bf16_bits(w)
+    weight = client.upload(stored)
+    close(client.read(RT.linear_frozen_bf16_fp32(client, client.upload(x), weight)), y, 5e-4, 5e-4)
+    close(client.read(RT.linear_frozen_bf16_fp32_backward(client, x.shape, weight, client.upload(dy))), dx, 5e-4, 5e-4)
+    np.testing.assert_array_equal(client.read(weight), stored)     # the fixed weight is never written

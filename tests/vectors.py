@@ -367,3 +367,28 @@ def rotary_prefix_tensor_case(table_shape, layout):
     y[..., ia] = xa * c - xb * s; y[..., ib] = xb * c + xa * s
     dx[..., ia] = ga * c + gb * s; dx[..., ib] = gb * c - ga * s
     return x, cos, sin, dy, y, dx
+
+
+# ---- examples/bias_tensor.rs:11-41 and examples/frozen_bf16_tensor.rs:33-52 -----------------------------------------
+BIAS_SHAPES = [(1,), (7,), (3, 31), (2, 3, 33), (5, 4097)]
+
+
+def bias_tensor_case(shape):
+    """Dyadic values, so every expectation is exact in FP32: outputs of the three modes and the bias gradient of dy."""
+    count, width = int(np.prod(shape)), shape[-1]
+    i = np.arange(count)
+    x = ((i % 13).astype(np.float32) / np.float32(8.0) - np.float32(0.5)).reshape(shape)
+    r = ((i % 5).astype(np.float32) / np.float32(4.0) - np.float32(0.25)).reshape(shape)
+    b = (np.arange(width) % 7).astype(np.float32) / np.float32(16.0) - np.float32(0.125)
+    dy = ((i % 11).astype(np.float32) / np.float32(8.0) - np.float32(0.375)).reshape(shape)
+    db = dy.reshape(-1, width).astype(np.float64).sum(0).astype(np.float32)
+    return x, r, b, dy, x + b, (x + r) + b, (x + x) + b, db
+
+
+def frozen_linear_case(m, n, k):
+    """X FP32 [m,k], fixed W [n,k] stored as BF16, upstream dY; Y = bf16(X) W^T and dX = bf16(dY) W in f64."""
+    x = ((np.arange(m * k) % 17).astype(np.float32) * np.float32(0.037) - np.float32(0.25)).reshape(m, k)
+    w = ((np.arange(n * k) % 13).astype(np.float32) * np.float32(0.019) - np.float32(0.125)).reshape(n, k)
+    dy = ((np.arange(m * n) % 11).astype(np.float32) * np.float32(0.017) - np.float32(0.0625)).reshape(m, n)
+    wb = bf16_f64(w)
+    return x, w, dy, bf16_f64(x) @ wb.T, bf16_f64(dy) @ wb
