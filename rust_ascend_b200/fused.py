@@ -52,8 +52,11 @@ class PeerBuffer:
         lib = client._lib
         local, payload = None, None
         try:
-            local = client.empty(self.nbytes)
-            client.memset(TensorBuffer(local, (self.nbytes,), DType.U8), 0)
+            # At least 2 MiB per buffer: an allocation of that size is a mapping of its own in the driver, so the exported
+            # handle names exactly this buffer and not a block it shares with unrelated small allocations.
+            self.allocated = max(self.nbytes, 2 << 20)
+            local = client.empty(self.allocated)
+            client.memset(TensorBuffer(local, (self.allocated,), DType.U8), 0)
             client.sync()
             token = (C.c_uint8 * TOKEN_BYTES)()
             _check(lib.rb_peer_export(client._ctx, C.c_uint64(local), token))
@@ -69,7 +72,7 @@ class PeerBuffer:
                     self.handles.append(local)
                     continue
                 h = C.c_uint64()
-                _check(lib.rb_peer_open(client._ctx, (C.c_uint8 * TOKEN_BYTES)(*reply[1:1 + TOKEN_BYTES]), C.c_uint64(self.nbytes), C.byref(h)))
+                _check(lib.rb_peer_open(client._ctx, (C.c_uint8 * TOKEN_BYTES)(*reply[1:1 + TOKEN_BYTES]), C.c_uint64(self.allocated), C.byref(h)))
                 self.handles.append(h.value)
             payload = b"\x00"
         except Exception as error:
