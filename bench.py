@@ -289,11 +289,17 @@ def extras(client, RT, pk, args, rank, world, dist, out):
         # NVLS (in-switch reduction) stays off for every communicator of this process: the watchdog may end a rank while
         # collectives are pending, and a rank that leaves while its memory is bound to an NVLS group can fault its peers.
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        # Order: tensor parallelism over all GPUs (the north-star figure) first, then the row-parallel Linear, then the
+        # smaller tensor-parallel groups; whatever the watchdog cuts off is the least important part.
+        fused = os.environ.get("RUDA_BENCH_FUSED") == "1"   # timed only on request until validated on this pool's GPUs
+        candidates = decoder_candidates(world, fused=fused)
+        results = []
+        decoder_extra(client, pk, rank, world, dist, out, [c for c in candidates if c["tp"] == world], results)
         try:
             out["row_parallel_linear"] = row_parallel_extra(client, pk, rank, world, dist)
-        except Exception as error:      # the decoder measurement below does not depend on this one
+        except Exception as error:      # the decoder measurements do not depend on this one
             out["row_parallel_linear"] = {"error": f"{type(error).__name__}: {error}"}
-        decoder_extra(client, pk, rank, world, dist, out)
+        decoder_extra(client, pk, rank, world, dist, out, [c for c in candidates if c["tp"] != world], results)
         return out
     rows, width = 4096, 4096
     rng = np.random.default_rng(0)
@@ -331,7 +337,7 @@ def extras(client, RT, pk, args, rank, world, dist, out):
         for t in s:
             client.free(t.handle)
     out.update(attention_extra(client, RT, pk))
-    decoder_extra(client, pk, rank, world, dist, out)
+    decoder_extra(client, pk, rank, world, dist, out, decoder_candidates(world), [])
     if not args.no_cpu_baseline:
         try:
             import oracle as orc
@@ -451,7 +457,7 @@ def decoder_candidates(world: int, sequences: int = 8, fused: bool = False):
     return out
 
 
-def decoder_extra(client, pk, rank, world, dist, sink):
+def decoder_extra(client, pk, rank, world, dist, sink, candidates, results):
     """Config 5: Llama-style stack, 8 layers, T = 8 x 2048.  The reported value is tensor parallelism over all `world` GPUs
     with NCCL all-reduces (fastest of three schedules); the same forward with smaller tensor-parallel groups that split the
     sequences between them is timed too and reported beside it, labelled with its parallelism."""
@@ -464,7 +470,7 @@ def decoder_extra(client, pk, rank, world, dist, sink):
         # NVLS (in-switch reduction) stays off: the watchdog may end a rank while collectives are pending, and a rank that
         # leaves while its memory is bound to an NVLS group can fault its peers.  Ring/tree all-reduce is used instead.
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-    comms, models, results = {}, {}, []
+    comms, models = {}, {}
     total_flops = cfg.flops(sequences * seq, seq)
 
     def summary():
@@ -482,8 +488,7 @@ def decoder_extra(client, pk, rank, world, dist, sink):
                                           "value": total_flops / (b["ms_per_forward"] * 1e-3) / 1e12, "unit": "TFLOP/s (whole job)"}
         return out
 
-    # The fused exchange is timed only on request until it has been validated on this pool's GPUs.
-    for cand in decoder_candidates(world, sequences, fused=os.environ.get("RUDA_BENCH_FUSED") == "1"):
+    for cand in candidates:
         tp = cand["tp"]
         groups = world // tp
         group, tp_rank = rank // tp, rank % tp
@@ -527,7 +532,7 @@ def decoder_extra(client, pk, rank, world, dist, sink):
         sink["tp_decoder"] = summary()
     for model in models.values():
         model.close()
-    return sink["tp_decoder"]
+    return sink.get("tp_decoder")
 
 
 def run_single_kernel(args):
