@@ -284,3 +284,38 @@ class CausalCrossEntropyConfig:
         loss, valid, _ = RT.causal_cross_entropy(c, logits.buffer.reshape((batch, time, logits.dims()[1])), labels.buffer, self.ignore_index,
                                                  self.shift, 1.0, with_gradient=False)
         return CausalLoss(_wrap(c, loss), _wrap(c, valid))
+
+
+# -- bias / residual (src/nn/affine.rs) and fixed BF16 weights (src/nn/frozen.rs) ---------------------------------------
+def bias_add(input: Tensor, bias: Tensor) -> Tensor:
+    """X[...,H] + bias[H], contiguous FP32 of rank 1..8 (src/nn/affine.rs:14-19)."""
+    c = _same_client(input, bias)
+    return _wrap(c, RT.bias_add(c, input.buffer, bias.buffer))
+
+
+def residual_bias_add(input: Tensor, residual: Tensor, bias: Tensor) -> Tensor:
+    """(X + residual) + bias in that FP32 order; the residual must match X exactly (src/nn/affine.rs:20-25)."""
+    c = _same_client(input, residual, bias)
+    return _wrap(c, RT.bias_add(c, input.buffer, bias.buffer, residual.buffer))
+
+
+def linear_frozen_bf16_fp32(input: Tensor, weight: Tensor) -> Tensor:
+    """FP32 X [M,K] times a fixed BF16-stored W [N,K]^T, FP32 result; the weight is used in place (src/nn/frozen.rs:44-59)."""
+    c = _same_client(input, weight)
+    return _wrap(c, RT.linear_frozen_bf16_fp32(c, input.buffer, weight.buffer))
+
+
+def swiglu_frozen_bf16_fp32(input: Tensor, gate: Tensor, up: Tensor, down: Tensor) -> Tensor:
+    """SwiGLU with fixed BF16-stored gate/up [H,K] and down [N,H] and FP32 activations (src/nn/frozen.rs:95-107).  Gate and up
+    run as one tensor-core GEMM whose epilogue applies SiLU*up on the FP32 accumulators; the hidden activation is FP32."""
+    c = _same_client(input, gate, up, down)
+    m, k = input.dims()
+    hidden, gk = gate.dims()
+    n, dh = down.dims()
+    if gk != k or up.dims() != [hidden, k] or dh != hidden or any(s == 0 or s % 16 for s in (m, n, k, hidden)):
+        raise InvalidTensor("frozen BF16 SwiGLU requires aligned X[M,K], gate/up[H,K], down[N,H]")
+    if input.dtype() != DType.F32 or any(w.dtype() != DType.BF16 for w in (gate, up, down)):
+        raise InvalidTensor("frozen BF16 SwiGLU requires FP32 input and fixed BF16 weights on the same device")
+    x16 = RT.cast(c, input.buffer, DType.BF16)
+    h = RT.gemm(c, x16, gate.buffer, Transpose.No, Transpose.Yes, DType.F32, b_up=up.buffer)
+    return _wrap(c, RT.linear_frozen_bf16_fp32(c, h, down.buffer))

@@ -181,3 +181,26 @@ def test_frozen_linear_example(client, m, n, k):
     close(client.read(RT.linear_frozen_bf16_fp32(client, client.upload(x), weight)), y, 5e-4, 5e-4)
     close(client.read(RT.linear_frozen_bf16_fp32_backward(client, x.shape, weight, client.upload(dy))), dx, 5e-4, 5e-4)
     np.testing.assert_array_equal(client.read(weight), stored)     # the fixed weight is never written
+
+
+def test_nn_affine_and_frozen_wrappers(client, oracle):
+    import rust_ascend_b200.nn as nn
+    from rust_ascend_b200 import DType, InvalidTensor
+    from rust_ascend_b200.runtime import bf16_bits_to_f32, f32_to_bf16_bits
+    x, r, b, _, plain, with_res, _, _ = V.bias_tensor_case((3, 31))
+    t = lambda a: nn.Tensor.from_data(client, a)
+    np.testing.assert_array_equal(nn.bias_add(t(x), t(b)).into_data(), plain)
+    np.testing.assert_array_equal(nn.residual_bias_add(t(x), t(r), t(b)).into_data(), with_res)
+    xf, w, _, y, _ = V.frozen_linear_case(16, 32, 32)
+    close(nn.linear_frozen_bf16_fp32(t(xf), t(f32_to_bf16_bits(w))).into_data(), y, 5e-4, 5e-4)
+    rng = np.random.default_rng(2)                                  # SwiGLU with fixed weights against the oracle's fused Linear
+    m, k, hidden, n = 32, 48, 64, 16
+    xs = rng.standard_normal((m, k)).astype(np.float32)
+    g16, u16, d16 = (f32_to_bf16_bits((rng.standard_normal(s) * 0.2).astype(np.float32)) for s in ((hidden, k), (hidden, k), (n, hidden)))
+    out = nn.swiglu_frozen_bf16_fp32(t(xs), t(g16), t(u16), t(d16))
+    assert out.dims() == [m, n] and out.dtype() == DType.F32
+    hid = oracle.linear(xs, bf16_bits_to_f32(g16), w_up=bf16_bits_to_f32(u16))
+    want = oracle.gemm_bf16(hid, bf16_bits_to_f32(d16), False, True, False)
+    close(out.into_data(), want, 2e-3, 5e-3)
+    with pytest.raises(InvalidTensor):
+        nn.swiglu_frozen_bf16_fp32(t(xs), t(bf16_bits_to_f32(g16)), t(u16), t(d16))
