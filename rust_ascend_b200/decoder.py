@@ -12,8 +12,13 @@ assembled from the operators this package provides, sharded Megatron-style:
 
 Activations are BF16 [T, width] row-major; the QKV projection output is consumed by the attention kernel in
 place through strides ([B,S,H,D] storage viewed as [B,H,S,D]) and attention writes [B,S,H,D] so the output
-projection needs no transpose either.  `chunks > 1` splits T into row chunks so that the all-reduce of chunk i
-overlaps the GEMM of chunk i+1 (deferred fences on the communicator's own stream).
+projection needs no transpose either.  `micro_batches > 1` splits the batch into groups of sequences so that the
+all-reduce of one group overlaps the GEMMs of the other (deferred fences on the communicator's own stream).
+
+`fused=True` replaces the two all-reduces of a layer by the fused exchange of fused.py: the row-parallel GEMMs scatter
+their partial rows into the staging area of the rank that owns those rows, the owner sums them, updates its rows of the
+residual stream (which is then sharded by rows), normalises and pushes the result into every rank's activation buffer;
+`overlap_exchange=True` moves the owner-side step to a side stream under the other micro batch's GEMMs.
 """
 from __future__ import annotations
 
