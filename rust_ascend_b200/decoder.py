@@ -215,8 +215,8 @@ class TensorParallelDecoder:
         client = self.client
         if self.batch % micro_batches or (self.batch // micro_batches * self.seq) % 16:
             raise InvalidTensor("micro batches must hold whole sequences")
-        if fused and (self.world < 2 or (self.tokens // micro_batches) % (128 * self.world) or self.cfg.hidden % 64):
-            raise InvalidTensor("fused exchange needs at least two ranks and micro batches of a multiple of 128 * world tokens")
+        if fused and (comm is None or not hasattr(comm, "control") or (self.tokens // micro_batches) % (128 * self.world) or self.cfg.hidden % 64):
+            raise InvalidTensor("fused exchange needs a communicator with a control plane and micro batches of a multiple of 128 * world tokens")
         self.close()
         self.comm, self.micro, self.fused, self.overlap_exchange = comm, micro_batches, fused, bool(fused and overlap_exchange)
         self._keep = []          # ctypes structures referenced by the plan

@@ -192,6 +192,15 @@ class FusedExchange:
             buf.close()
 
 
+class LocalGroup:
+    """A world of one with a control plane: lets the fused exchange (and the decoder's fused mode) run on a single GPU, where
+    every store, announcement and wait stays inside that GPU's memory."""
+
+    def __init__(self):
+        from .distributed import SingleControl
+        self.control = SingleControl()
+
+
 def row_parallel_linear_allreduce(exchange: FusedExchange, x: TensorBuffer, w_shard: TensorBuffer) -> TensorBuffer:
     """Y = sum over ranks of x_r [T, K/world] . w_r [H, K/world]^T, complete on every rank: what the reference computes with a
     row-parallel Linear followed by all_reduce(sum) (src/distributed.rs:139-156), here as scatter-GEMM, owner-side sum in rank

@@ -13,6 +13,8 @@ import numpy as np
 import pytest
 
 pytestmark = pytest.mark.gpu
+OPT_IN = pytest.mark.skipif(os.environ.get("RUDA_FUSED_TESTS") != "1",
+                            reason="peer-memory kernels not yet run on the target pool: opt in with RUDA_FUSED_TESTS=1")
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
@@ -103,11 +105,10 @@ def _worker(rank, world, port, results):
     dist.destroy_process_group()
 
 
+@OPT_IN
 @pytest.mark.timeout(300)
 def test_two_gpu_fused_exchange(oracle):
     import torch
-    if os.environ.get("RUDA_FUSED_TESTS") != "1":
-        pytest.skip("peer-memory kernels not yet run on the target pool: opt in with RUDA_FUSED_TESTS=1")
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
@@ -159,3 +160,46 @@ def test_two_gpu_fused_exchange(oracle):
     np.testing.assert_array_equal(r[0]["fused"], r[0]["fused_graph"])
     for rank in range(world):      # the schedule changes, the arithmetic does not
         assert np.abs(r[rank]["fused4"] - r[rank]["fused4_overlap"]).max() <= 2.0 ** -7 * np.abs(r[rank]["fused4"]).max()
+
+
+@OPT_IN
+def test_single_gpu_fused_exchange(client, oracle):
+    """The same kernels on one GPU (a world of one): every store, announcement and wait stays in local memory, which makes
+    this the cheapest first check of the scatter GEMM, the owner-side step, the waits and the side stream."""
+    from decoder_reference import forward, full_weights
+    from rust_ascend_b200.decoder import TensorParallelDecoder
+    from rust_ascend_b200.distributed import SingleControl
+    from rust_ascend_b200.fused import FusedExchange, LocalGroup, row_parallel_linear_allreduce
+    from rust_ascend_b200.runtime import bf16_bits_to_f32, f32_to_bf16_bits
+    from test_index_padded import bf16
+    try:
+        x, w = _inputs(1)
+        xs, ws = client.upload(f32_to_bf16_bits(x)), client.upload(f32_to_bf16_bits(w))
+        ex = FusedExchange(client, SingleControl(), x.shape[0], w.shape[0])
+        want = bf16(bf16(bf16(x) @ bf16(w).T))
+        for _ in range(2):                                           # twice: flags only count up, buffers are reused
+            got = bf16_bits_to_f32(client.read(row_parallel_linear_allreduce(ex, xs, ws)))
+            assert np.abs(got - want).max() <= 2.0 ** -7 * np.abs(want).max()
+        resid = np.random.default_rng(5).standard_normal(want.shape).astype(np.float32)
+        weight = np.random.default_rng(6).uniform(0.5, 1.5, want.shape[1]).astype(np.float32)
+        x_own = client.upload(f32_to_bf16_bits(resid))
+        ex.gemm_scatter(xs, ws); ex.wait_scatter()
+        ex.reduce_norm_push(x_in=x_own, weight=client.upload(f32_to_bf16_bits(weight)), eps=1e-5, x_out=x_own)
+        ex.wait_gather(); ex.barrier()
+        xn = bf16(bf16(resid) + got)
+        normed = bf16(xn / np.sqrt((xn ** 2).mean(-1, keepdims=True) + 1e-5) * bf16(weight))
+        assert np.abs(bf16_bits_to_f32(client.read(x_own)) - xn).max() <= 2.0 ** -8 * np.abs(xn).max()
+        assert np.abs(bf16_bits_to_f32(client.read(ex.gathered())) - normed).max() <= 2.0 ** -7 * np.abs(normed).max()
+        ex.close()
+        cfg = _cfg()
+        tokens = np.random.default_rng(0).integers(0, cfg.vocab, size=(4, 128)).astype(np.int32)
+        want_logits = forward(oracle, cfg, full_weights(cfg, 3), tokens)
+        for kwargs in ({}, {"use_graph": True}, {"micro_batches": 2, "overlap_exchange": True, "sm_reserve": 16, "use_graph": True}):
+            model = TensorParallelDecoder(client, cfg, 4, 128, comm=LocalGroup(), seed=3, exact_weights=True, fused=True, **kwargs)
+            model.forward(tokens)
+            got = bf16_bits_to_f32(client.read(model.forward()))
+            model.close()
+            err = np.abs(got - want_logits)
+            assert err.max() <= 0.04 * np.abs(want_logits).max() and err.mean() <= 0.015 * np.abs(want_logits).mean() + 1e-4, (kwargs, err.max(), err.mean())
+    finally:
+        client.take_errors()          # an expired wait is a sticky error; it must not follow the context into other tests

@@ -383,5 +383,5 @@ def test_fused_mode_rejects_shapes_the_kernels_cannot_take():
     cfg = LlamaConfig(layers=1, hidden=256, heads=8, kv_heads=8, head_dim=128, ffn=1024, vocab=512)
     with pytest.raises(InvalidTensor):      # 2 * 96 tokens is not a multiple of 128 * world
         TensorParallelDecoder(FakeClient(), cfg, 2, 96, comm=FakeComm(0, 2), rank=0, world=2, fused=True)
-    with pytest.raises(InvalidTensor):      # a single rank has nothing to exchange
+    with pytest.raises(InvalidTensor):      # no communicator, no control plane to exchange peer tokens over
         TensorParallelDecoder(FakeClient(), cfg, 2, 128, fused=True)
