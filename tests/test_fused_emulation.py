@@ -221,7 +221,7 @@ class EmuComm:
         self.control = EmuControl(rank, world)
 
 
-@pytest.mark.parametrize("world,micro,overlap", [(1, 1, False), (1, 2, True), (2, 1, False), (2, 2, True), (4, 1, False)])
+@pytest.mark.parametrize("world,micro,overlap", [(1, 1, False), (1, 2, True), (2, 1, False), (2, 2, False), (2, 2, True), (4, 1, False)])
 def test_fused_plan_computes_the_decoder(monkeypatch, oracle, world, micro, overlap):
     import rust_ascend_b200.fused as fused
     from decoder_reference import forward, full_weights
