@@ -300,6 +300,10 @@ def extras(client, RT, pk, args, rank, world, dist, out):
         except Exception as error:      # the decoder measurements do not depend on this one
             out["row_parallel_linear"] = {"error": f"{type(error).__name__}: {error}"}
         decoder_extra(client, pk, rank, world, dist, out, [c for c in candidates if c["tp"] != world], results)
+        try:
+            out["sharded_kernels"] = sharded_extras(client, RT, pk, rank, world, dist)
+        except Exception as error:
+            out["sharded_kernels"] = {"error": f"{type(error).__name__}: {error}"}
         return out
     rows, width = 4096, 4096
     rng = np.random.default_rng(0)
@@ -346,6 +350,62 @@ def extras(client, RT, pk, args, rank, world, dist, out):
             out["cpu_baselines"] = cpu_side_baselines(orc)
         except Exception as error:
             out["cpu_baselines"] = {"error": f"{type(error).__name__}: {error}"}
+    return out
+
+
+def sharded_extras(client, RT, pk, rank, world, dist):
+    """Configs 1, 3 and 4 split over the GPUs without any exchange (strong scaling: the whole-job work is that of one
+    config): RMSNorm by rows, attention by heads (query heads and their KV heads stay together).  Time is the slowest
+    rank's; value is whole-job work over that time."""
+    import ctypes as C
+    from rust_ascend_b200 import DType
+    from rust_ascend_b200.runtime import _check, f32_to_bf16_bits
+    out = {"scaling": "strong", "n_gpus": world}
+    rng = np.random.default_rng(50 + rank)
+    rows, width = 4096 // world, 4096
+    sets = []
+    for _ in range(6):
+        x = client.upload(rng.standard_normal((rows, width), dtype=np.float32))
+        w = client.upload(rng.uniform(0.5, 1.5, width).astype(np.float32))
+        sets.append((x, w, client.tensor((rows, width), DType.F32), client.tensor((rows,), DType.F32)))
+    keep = [[t._c() for t in st] for st in sets]
+    calls = [(client._ctx, C.byref(k[0]), C.byref(k[1]), C.c_double(1e-6), C.byref(k[2]), C.byref(k[3])) for k in keep]
+    for i in range(10):
+        _check(client._lib.rb_rms_norm(*calls[i % 6]))
+    client.sync()
+    if dist is not None:
+        dist.barrier()
+    client.start_profile()
+    for i in range(200):
+        _check(client._lib.rb_rms_norm(*calls[i % 6]))
+    ms = max_over_ranks(dist, client.end_profile() / 200)
+    nbytes = 2 * 4096 * width * 4 + width * 4 + 4096 * 4
+    out["rms_norm_fp32_4096x4096_by_rows"] = {"value": nbytes / (ms * 1e-3) / 1e9, "unit": "GB/s (whole job)", "us": ms * 1e3, "rows_per_gpu": rows}
+    for st in sets:
+        for t in st:
+            client.free(t.handle)
+    for name, (b, hq, hkv, s) in {"attention_causal_b4_h32_s2048_d128_by_heads": (4, 32, 32, 2048),
+                                   "attention_causal_gqa_b2_h32_kv8_s4096_d128_by_heads": (2, 32, 8, 4096)}.items():
+        if hkv % world:
+            out[name] = {"skipped": f"{hkv} KV heads do not divide over {world} GPUs"}
+            continue
+        lq, lkv = hq // world, hkv // world
+        mk = lambda h: client.upload(f32_to_bf16_bits(rng.standard_normal((b, h, s, 128), dtype=np.float32)))
+        sets = [(mk(lq), mk(lkv), mk(lkv), client.tensor((b, s, lq, 128), DType.BF16)) for _ in range(3)]
+        run = lambda i: RT.attention(client, sets[i % 3][0], sets[i % 3][1], sets[i % 3][2], 128 ** -0.5, causal=True, bmhd_output=True, out=sets[i % 3][3])
+        for i in range(5):
+            run(i)
+        client.sync()
+        if dist is not None:
+            dist.barrier()
+        client.start_profile()
+        for i in range(30):
+            run(i)
+        ms = max_over_ranks(dist, client.end_profile() / 30)
+        out[name] = {"value": 2 * b * hq * s * s * 128 / (ms * 1e-3) / 1e12, "unit": "TFLOP/s (whole job)", "us": ms * 1e3, "query_heads_per_gpu": lq, "kv_heads_per_gpu": lkv}
+        for st in sets:
+            for t in st:
+                client.free(t.handle)
     return out
 
 
