@@ -640,7 +640,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true")
-    ap.add_argument("--extras-timeout", type=float, default=150.0, help="seconds before the secondary measurements are abandoned")
+    ap.add_argument("--extras-timeout", type=float, default=200.0, help="seconds before the secondary measurements are abandoned")
     ap.add_argument("--reference-seconds", type=float, default=90.0, help="CPU time the reference arm aims to spend over warm-up and steps together")
     ap.add_argument("--kernel", default=None, choices=["gemm", "attention", "rms_norm"], help="time one kernel alone (profiling helper)")
     args = ap.parse_args()
