@@ -540,6 +540,102 @@ class B200Runtime:
         return B200Runtime.gemm(client, B200Runtime.cast(client, input, DType.BF16), weight, Transpose.No, Transpose.Yes, DType.F32)
 
 
+    # -- dtype-preserving broadcast matmul (runtime/generic_matrix.rs; the vendor aclnnMatmul(KEEP_DTYPE) in the reference) ----
+    @staticmethod
+    def matmul_shape(a_shape, b_shape) -> tuple:
+        """Output shape of A[..., M, K] @ B[..., K, N] with singleton batch axes broadcasting (tensor/layout.rs:123-142)."""
+        a_shape, b_shape = tuple(a_shape), tuple(b_shape)
+        if a_shape[-1] != b_shape[-2]:
+            raise InvalidTensor("matmul contraction dimensions differ")
+        ba, bb = a_shape[:-2], b_shape[:-2]
+        rank = max(len(ba), len(bb))
+        ba, bb = (1,) * (rank - len(ba)) + ba, (1,) * (rank - len(bb)) + bb
+        batch = []
+        for x, y in zip(ba, bb):
+            if x != y and x != 1 and y != 1:
+                raise InvalidTensor("matmul batch axes cannot be broadcast")
+            batch.append(y if x == 1 else x)
+        return tuple(batch) + (a_shape[-2], b_shape[-1])
+
+    @staticmethod
+    def _bf16_parts(client, t: TensorBuffer):
+        """t as a sum of BF16 tensors, exactly for finite values: one part for BF16 storage, two for FP16 (11 significant bits),
+        three for FP32 (24 bits).  Built from the cast, scalar-division and add entry points."""
+        RT = B200Runtime
+        if t.dtype == DType.BF16:
+            return [t]
+        rest = t if t.dtype == DType.F32 else RT.cast(client, t, DType.F32)
+        parts = []
+        for index in range(2 if t.dtype == DType.F16 else 3):
+            part = RT.cast(client, rest, DType.BF16)
+            parts.append(part)
+            if index + 1 < (2 if t.dtype == DType.F16 else 3):
+                negative = RT.cast(client, part, DType.F32)
+                _check(client._lib.rb_div_scalar(client._ctx, _ref(negative), C.c_float(-1.0), _ref(negative)))
+                rest = RT.add(client, rest, negative)              # exact: the part holds the leading bits of `rest`
+        return parts
+
+    @staticmethod
+    def tensor_matmul(client, a: TensorBuffer, b: TensorBuffer) -> TensorBuffer:
+        """A[..., M, K] @ B[..., K, N] in the operands' own dtype (FP32, FP16 or BF16), ranks 2..6, singleton batch axes
+        broadcasting, any non-negative sizes (runtime/mod.rs:156-158 -> generic_matrix.rs:17-54).  The products run on the BF16
+        tensor-core GEMM with FP32 accumulation: BF16 operands directly; FP16 and FP32 operands as exact sums of two or three
+        BF16 parts, whose cross products are accumulated in FP32 smallest first (FP32: the three terms below 2^-26 of the
+        result are dropped), so the result carries the precision of the storage type rather than BF16's.  Finite inputs."""
+        RT = B200Runtime
+        floats = (DType.F32, DType.F16, DType.BF16)
+        if a.dtype not in floats or b.dtype != a.dtype or not 2 <= len(a.shape) <= 6 or not 2 <= len(b.shape) <= 6:
+            raise InvalidTensor("generic Ascend matmul requires matching floating dtypes and rank 2..6")
+        out_shape = RT.matmul_shape(a.shape, b.shape)
+        m, k, n = a.shape[-2], a.shape[-1], b.shape[-1]
+        if 0 in out_shape or k == 0:                     # an empty result, or an empty contraction: zeros
+            out = client.tensor(out_shape, a.dtype)
+            if out.elements:
+                client.memset(out, 0)
+            return out
+        batch = out_shape[:-2]
+        count = lambda dims: int(np.prod(dims)) if len(dims) else 1
+        na, nb, no = count(a.shape[:-2]), count(b.shape[:-2]), count(batch)
+        up = lambda d: (d + 15) // 16 * 16
+        mp, kp, np_ = up(m), up(k), up(n)
+        pa = [RT.resize_prefix(client, t.reshape((na, m, k)), (na, mp, kp)) for t in RT._bf16_parts(client, a)]
+        pb = [RT.resize_prefix(client, t.reshape((nb, k, n)), (nb, kp, np_)) for t in RT._bf16_parts(client, b)]
+        limit = max(len(pa), len(pb)) - 1
+        pairs = sorted(((i, j) for i in range(len(pa)) for j in range(len(pb)) if i + j <= limit), key=lambda ij: -(ij[0] + ij[1]))
+        acc = client.tensor((no, mp, np_), DType.F32)
+        same_batches = tuple(a.shape[:-2]) == tuple(b.shape[:-2]) and no <= 4096
+
+        def slab(t, index, rows, cols):
+            return TensorBuffer(t.handle, (rows, cols), t.dtype, None, offset=t.offset + index * rows * cols * t.dtype.size)
+
+        def products(out_t, first):
+            """out_t (+)= sum over the part pairs, for one batched launch set or one batch entry."""
+            for number, (i, j) in enumerate(pairs):
+                x, y = first(pa[i], True), first(pb[j], False)
+                if number == 0:
+                    RT.gemm_into(client, x, y, Transpose.No, Transpose.No, out_t)
+                else:
+                    term = RT.gemm(client, x, y, Transpose.No, Transpose.No, DType.F32)
+                    RT.add(client, out_t, term, out=out_t)
+        if same_batches:
+            products(acc, lambda t, is_a: t)
+        else:
+            ba = (1,) * (len(batch) - len(a.shape[:-2])) + tuple(a.shape[:-2])
+            bb = (1,) * (len(batch) - len(b.shape[:-2])) + tuple(b.shape[:-2])
+            for flat, index in enumerate(np.ndindex(*batch)):
+                ia = int(np.ravel_multi_index([0 if d == 1 else i for i, d in zip(index, ba)], ba)) if ba else 0
+                ib = int(np.ravel_multi_index([0 if d == 1 else i for i, d in zip(index, bb)], bb)) if bb else 0
+                products(slab(acc, flat, mp, np_), lambda t, is_a: slab(t, ia, mp, kp) if is_a else slab(t, ib, kp, np_))
+        cropped = RT.resize_prefix(client, acc, (no, m, n)).reshape(out_shape)
+        return cropped if a.dtype == DType.F32 else RT.cast(client, cropped, a.dtype)
+
+    @staticmethod
+    def matmul_fp32(client, a: TensorBuffer, b: TensorBuffer) -> TensorBuffer:
+        """FP32 ND matrix product without a BF16 or TF32 cast of the result's precision (runtime/mod.rs:148-155)."""
+        if a.dtype != DType.F32 or b.dtype != DType.F32:
+            raise InvalidTensor("matmul_fp32 requires FP32 inputs")
+        return B200Runtime.tensor_matmul(client, a, b)
+
     @staticmethod
     def group_ends(ends) -> list[int]:
         """GroupEnds::new (deepgemm/plan.rs:15-29): 1..4096 nondecreasing physical row prefix sums, each a multiple of 256,

@@ -80,6 +80,16 @@ def test_padded_spec_shapes_follow_reference_cases():
             RT._padded_spec(a, b, dt, DType.F32, no, no)
 
 
+def test_matmul_shape_follows_the_reference_rules():
+    from rust_ascend_b200 import B200Runtime as RT, InvalidTensor
+    assert RT.matmul_shape((2, 1, 3, 5), (1, 4, 5, 7)) == (2, 4, 3, 7)        # runtime/generic_matrix.rs:60-66
+    assert RT.matmul_shape((0, 5), (5, 7)) == (0, 7) and RT.matmul_shape((3, 0), (0, 7)) == (3, 7)
+    assert RT.matmul_shape((6, 3, 5), (5, 7)) == (6, 3, 7)
+    for a, b in (((3, 5), (4, 7)), ((2, 3, 5), (3, 5, 7))):
+        with pytest.raises(InvalidTensor):
+            RT.matmul_shape(a, b)
+
+
 def test_group_ends_follow_the_reference_rules():
     from rust_ascend_b200 import B200Runtime as RT, InvalidTensor
     assert RT.group_ends([0, 256, 256, 768]) == [0, 256, 256, 768]           # deepgemm/plan.rs:101: empty experts are fine

@@ -204,3 +204,46 @@ def test_nn_affine_and_frozen_wrappers(client, oracle):
     close(out.into_data(), want, 2e-3, 5e-3)
     with pytest.raises(InvalidTensor):
         nn.swiglu_frozen_bf16_fp32(t(xs), t(bf16_bits_to_f32(g16)), t(u16), t(d16))
+
+
+def _as_dtype(x, dtype):
+    from rust_ascend_b200 import DType
+    from rust_ascend_b200.runtime import f32_to_bf16_bits
+    return x.astype(np.float32) if dtype == DType.F32 else (x.astype(np.float16) if dtype == DType.F16 else f32_to_bf16_bits(x))
+
+
+def _to_f64(raw, dtype):
+    from rust_ascend_b200 import DType
+    from rust_ascend_b200.runtime import bf16_bits_to_f32
+    return (bf16_bits_to_f32(raw) if dtype == DType.BF16 else raw).astype(np.float64)
+
+
+@pytest.mark.parametrize("dtype_name,tolerance", [("F32", 2e-6), ("F16", 2.0 ** -10), ("BF16", 2.0 ** -7)])
+@pytest.mark.parametrize("a_shape,b_shape", [((2, 1, 3, 5), (1, 4, 5, 7)), ((32, 48), (48, 16)), ((3, 17, 33), (3, 33, 20)), ((2, 2, 16, 64), (64, 32))])
+def test_tensor_matmul_keeps_the_dtype_and_broadcasts(client, dtype_name, tolerance, a_shape, b_shape):
+    # Shape rules of generic_matrix.rs:60-73 (first case is the reference's own); values against an f64 product of the stored operands.
+    from rust_ascend_b200 import B200Runtime as RT, DType
+    dtype = DType[dtype_name]
+    rng = np.random.default_rng(sum(a_shape) + len(b_shape))
+    a = _as_dtype(rng.standard_normal(a_shape).astype(np.float32), dtype); b = _as_dtype(rng.standard_normal(b_shape).astype(np.float32), dtype)
+    out = RT.tensor_matmul(client, client.upload(a), client.upload(b))
+    want = np.matmul(_to_f64(a, dtype), _to_f64(b, dtype))
+    assert out.dtype == dtype and out.shape == want.shape
+    got = _to_f64(client.read(out), dtype)
+    assert np.abs(got - want).max() <= tolerance * max(1.0, np.abs(want).max())
+
+
+def test_tensor_matmul_empty_axes_and_rejections(client):
+    from rust_ascend_b200 import B200Runtime as RT, DType, InvalidTensor
+    z = lambda *shape: client.upload(np.zeros(shape, np.float32))
+    assert RT.tensor_matmul(client, z(0, 5), z(5, 7)).shape == (0, 7)              # generic_matrix.rs:67-72
+    out = RT.tensor_matmul(client, z(3, 0), z(0, 7))                                # generic_matrix.rs:73-78: empty contraction
+    assert out.shape == (3, 7) and not client.read(out).any()
+    with pytest.raises(InvalidTensor):
+        RT.tensor_matmul(client, z(3, 5), z(4, 7))
+    with pytest.raises(InvalidTensor):
+        RT.tensor_matmul(client, z(3, 5), client.upload(np.zeros((5, 7), np.uint16)))
+    with pytest.raises(InvalidTensor):
+        RT.tensor_matmul(client, z(2, 3, 5), z(3, 5, 7))
+    with pytest.raises(InvalidTensor):
+        RT.matmul_fp32(client, client.upload(np.zeros((3, 5), np.float16)), client.upload(np.zeros((5, 7), np.float16)))
