@@ -334,6 +334,20 @@ class B200Runtime:
         return out
 
     @staticmethod
+    def tensor_softmax(client: ComputeClient, input: TensorBuffer, dim: int, log: bool = False) -> TensorBuffer:
+        """Softmax / log-softmax that keeps a half storage dtype (runtime/typed.rs:769-776, the vendor softmax in the
+        reference): FP32 goes straight to the row kernel; FP16 and BF16 are widened to FP32, normalised there and rounded
+        back once.  Only the last axis is supported (the one the dense-transformer path uses)."""
+        if dim != len(input.shape) - 1:
+            raise InvalidTensor("softmax is implemented over the last axis only")
+        if input.dtype not in (DType.F32, DType.F16, DType.BF16):
+            raise InvalidTensor("softmax requires FP32, FP16 or BF16 storage")
+        fn = B200Runtime.log_softmax if log else B200Runtime.softmax
+        if input.dtype == DType.F32:
+            return fn(client, input)
+        return B200Runtime.cast(client, fn(client, B200Runtime.cast(client, input, DType.F32)), input.dtype)
+
+    @staticmethod
     def _reduce(client, input, op):
         out = client.tensor(input.shape[:-1] + (1,), DType.F32)
         _check(client._lib.rb_reduce_last(client._ctx, _ref(input), C.c_int32(op), _ref(out)))

@@ -247,3 +247,18 @@ def test_tensor_matmul_empty_axes_and_rejections(client):
         RT.tensor_matmul(client, z(2, 3, 5), z(3, 5, 7))
     with pytest.raises(InvalidTensor):
         RT.matmul_fp32(client, client.upload(np.zeros((3, 5), np.float16)), client.upload(np.zeros((5, 7), np.float16)))
+
+
+@pytest.mark.parametrize("dtype_name,tolerance", [("F32", 2e-6), ("F16", 2.0 ** -10), ("BF16", 2.0 ** -7)])
+@pytest.mark.parametrize("log", [False, True])
+def test_tensor_softmax_keeps_half_storage(client, dtype_name, tolerance, log):
+    from rust_ascend_b200 import B200Runtime as RT, DType, InvalidTensor
+    dtype = DType[dtype_name]
+    x = _as_dtype((np.random.default_rng(9).standard_normal((5, 7, 96)) * 3).astype(np.float32), dtype)
+    out = RT.tensor_softmax(client, client.upload(x), 2, log)
+    assert out.dtype == dtype and out.shape == x.shape
+    xf = _to_f64(x, dtype); e = np.exp(xf - xf.max(-1, keepdims=True)); p = e / e.sum(-1, keepdims=True)
+    want = np.log(p) if log else p
+    assert np.abs(_to_f64(client.read(out), dtype) - want).max() <= tolerance * max(1.0, np.abs(want).max())
+    with pytest.raises(InvalidTensor):
+        RT.tensor_softmax(client, client.upload(x), 0, log)
