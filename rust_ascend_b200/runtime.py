@@ -61,6 +61,11 @@ class CompletionError(B200Error): status = 7
 class ServerUnhealthy(B200Error): status = 8
 
 
+class CompilationError(B200Error):
+    """LaunchError::CompilationError of the reference's server (runtime/mod.rs:723-751)."""
+    status = 5
+
+
 _ERRORS = {c.status: c for c in (LibraryError, SymbolError, StatusError, InvalidDevice, InvalidTensor, NullHandle,
                                  CompletionError, ServerUnhealthy)}
 
@@ -248,6 +253,20 @@ class ComputeClient:
         return {k: getattr(s, k) for k, _ in rb_stats._fields_}
 
     memory_usage = stats
+
+    def memory_cleanup(self) -> None:
+        """AscendServer::memory_cleanup (runtime/mod.rs:854-856).  Storage here is returned to the driver by `free`, so there is
+        no pool to trim; the call drains the stream so that everything freed so far is really released."""
+        self.sync()
+
+    def allocation_mode(self, mode) -> None:
+        """AscendServer::allocation_mode (runtime/mod.rs:874-876): accepted for interface parity; there is one allocation mode."""
+
+    def launch(self, kernel, count=None, arguments=None, mode=None) -> None:
+        """AscendServer::launch (runtime/mod.rs:832-845) compiles RUDA IR for the device.  This backend ships named operators
+        only: any IR kernel is refused the way the reference refuses unsupported IR (a compilation error, never a fallback,
+        runtime/mod.rs:723-751)."""
+        raise CompilationError(f"LaunchError::CompilationError: no IR compiler in the B200 backend (kernel {kernel!r}); use the named operators")
 
     def start_profile(self) -> None:
         _check(self._lib.rb_profile_begin(self._ctx))

@@ -61,3 +61,10 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "libruda_b200.so"))
     with pytest.raises(OSError, match="no CPU fallback"):
         _lib.load()
+
+
+def test_ir_launch_is_a_compilation_error_not_a_fallback():
+    from rust_ascend_b200.runtime import CompilationError, ComputeClient
+    client = ComputeClient(None, None)            # no device needed: the refusal happens on the host
+    with pytest.raises(CompilationError, match="CompilationError"):
+        client.launch("elementwise_add_f32")
