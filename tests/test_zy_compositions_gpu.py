@@ -17,6 +17,16 @@ from test_backward import close
 pytestmark = [pytest.mark.gpu, pytest.mark.xfail(reason="first run on a GPU pending", strict=False)]
 
 
+@pytest.fixture(autouse=True)
+def _leave_no_sticky_error_behind(client):
+    """A failure here must not follow the shared context into the files collected after this one."""
+    yield
+    try:
+        client.take_errors()
+    except Exception:
+        pass
+
+
 @pytest.mark.parametrize("kv_heads,group,n,causal", V.GQA_CASES)
 def test_attention_backward_reference_example(client, oracle, kv_heads, group, n, causal):
     from rust_ascend_b200 import B200Runtime as RT
