@@ -319,3 +319,81 @@ def swiglu_frozen_bf16_fp32(input: Tensor, gate: Tensor, up: Tensor, down: Tenso
     x16 = RT.cast(c, input.buffer, DType.BF16)
     h = RT.gemm(c, x16, gate.buffer, Transpose.No, Transpose.Yes, DType.F32, b_up=up.buffer)
     return _wrap(c, RT.linear_frozen_bf16_fp32(c, h, down.buffer))
+
+
+# -- attention on logical shapes of any size (src/nn/padded_attention.rs) ------------------------------------------------
+def _padded_dimensions(query, key, value, scale):
+    batch, m, d = query
+    kb, n, kd = key
+    vb, vn, _ = value
+    if kb != batch or vb != batch or kd != d or vn != n or not np.isfinite(scale) or batch * m * n > 0xFFFFFFFF:
+        raise InvalidTensor("padded attention requires matching batches/contractions, finite scale and logical scores within u32")
+    if min(batch, m, n, d, value[2]) <= 0:
+        raise InvalidTensor("padded GEMM matrix axes must be positive")
+
+
+def scaled_dot_product_attention_padded_bf16_fp32(query: Tensor, key: Tensor, value: Tensor, scale: float,
+                                                  additive_mask: Tensor | None = None) -> Tensor:
+    """Materialised attention on FP32 Q[B,M,D], K[B,N,D], V[B,N,Dv] with positive axes of any size: each BF16 GEMM pads and
+    crops explicitly, softmax and mask see only the logical keys (src/nn/padded_attention.rs:26-45).  The optional additive
+    mask is exactly FP32 [B,M,N]."""
+    c = _same_client(query, key, value, additive_mask)
+    if any(len(t.dims()) != 3 for t in (query, key, value)):
+        raise InvalidTensor("padded attention requires matching batches/contractions, finite scale and logical scores within u32")
+    _padded_dimensions(query.dims(), key.dims(), value.dims(), scale)
+    if any(t.dtype() != DType.F32 for t in (query, key, value)):
+        raise InvalidTensor("padded attention requires FP32 Q/K/V on the same device")
+    batch, m, _ = query.dims()
+    n = key.dims()[1]
+    if additive_mask is not None and (additive_mask.dims() != [batch, m, n] or additive_mask.dtype() != DType.F32):
+        raise InvalidTensor("padded attention mask must be same-device FP32[B,M,N] without broadcasting")
+    if scale == 0.0:
+        raise InvalidTensor("padded attention needs a non-zero scale")
+    scores = RT.gemm_padded_bf16_fp32(c, query.buffer, key.buffer, Transpose.No, Transpose.Yes)[0]
+    RT.scale_in_place(c, scores, scale)
+    if additive_mask is not None:
+        RT.add(c, scores, additive_mask.buffer, out=scores)
+    return _wrap(c, RT.gemm_padded_bf16_fp32(c, RT.softmax(c, scores), value.buffer, Transpose.No, Transpose.No)[0])
+
+
+def causal_attention_padded_bf16_fp32(query: Tensor, key: Tensor, value: Tensor, scale: float, query_start: int, key_start: int) -> Tensor:
+    """The same with the fixed exact-position causal mask; the starts are explicit (src/nn/padded_attention.rs:46-54)."""
+    c = _same_client(query, key, value)
+    if any(len(t.dims()) != 3 for t in (query, key, value)):
+        raise InvalidTensor("padded attention requires matching batches/contractions, finite scale and logical scores within u32")
+    _padded_dimensions(query.dims(), key.dims(), value.dims(), scale)
+    batch, m, _ = query.dims()
+    mask = causal_mask(c, (batch, m, key.dims()[1]), query_start, key_start)
+    return scaled_dot_product_attention_padded_bf16_fp32(query, key, value, scale, mask)
+
+
+def grouped_query_attention_padded_bf16_fp32(query: Tensor, key: Tensor, value: Tensor, scale: float, additive_mask: Tensor | None = None) -> Tensor:
+    """Q[B,Hq,M,D], K[B,Hkv,N,D], V[B,Hkv,N,Dv] of any positive sizes: KV heads repeated on the device, then the padded
+    materialised path; the optional mask is exactly FP32 [B,Hq,M,N] (src/nn/padded_attention.rs:55-92)."""
+    c = _same_client(query, key, value, additive_mask)
+    if any(len(t.dims()) != 4 for t in (query, key, value)):
+        raise InvalidTensor("padded GQA requires matching batches/KV shapes and positive divisible Q/KV heads")
+    batch, heads, m, d = query.dims()
+    kb, kv_heads, n, kd = key.dims()
+    vb, vh, vn, dv = value.dims()
+    if heads == 0 or kv_heads == 0 or heads % kv_heads or kb != batch or vb != batch or vh != kv_heads or vn != n or kd != d:
+        raise InvalidTensor("padded GQA requires matching batches/KV shapes and positive divisible Q/KV heads")
+    flat = batch * heads
+    if additive_mask is not None and (additive_mask.dims() != [batch, heads, m, n] or additive_mask.dtype() != DType.F32):
+        raise InvalidTensor("padded GQA additive mask must be FP32 [B,Hq,M,N] on the same device")
+    k = repeat_kv_heads(key, heads).reshape((flat, n, d))
+    v = repeat_kv_heads(value, heads).reshape((flat, n, dv))
+    out = scaled_dot_product_attention_padded_bf16_fp32(query.reshape((flat, m, d)), k, v, scale,
+                                                        None if additive_mask is None else additive_mask.reshape((flat, m, n)))
+    return out.reshape((batch, heads, m, dv))
+
+
+def causal_grouped_query_attention_padded_bf16_fp32(query: Tensor, key: Tensor, value: Tensor, scale: float, query_start: int, key_start: int) -> Tensor:
+    """Padded GQA with the exact-position causal mask (src/nn/padded_attention.rs:93-104)."""
+    c = _same_client(query, key, value)
+    if len(query.dims()) != 4 or len(key.dims()) != 4:
+        raise InvalidTensor("padded GQA requires matching batches/KV shapes and positive divisible Q/KV heads")
+    batch, heads, m, _ = query.dims()
+    n = key.dims()[2]
+    mask = causal_mask(c, (batch * heads, m, n), query_start, key_start).reshape((batch, heads, m, n))
+    return grouped_query_attention_padded_bf16_fp32(query, key, value, scale, mask)

@@ -353,6 +353,12 @@ class B200Runtime:
         return out
 
     @staticmethod
+    def scale_in_place(client, t: TensorBuffer, scale: float) -> TensorBuffer:
+        """t *= scale, issued as a division by 1/scale (exact for powers of two, within one ulp otherwise)."""
+        _check(client._lib.rb_div_scalar(client._ctx, _ref(t), C.c_float(1.0 / scale), _ref(t)))
+        return t
+
+    @staticmethod
     def tensor_softmax(client: ComputeClient, input: TensorBuffer, dim: int, log: bool = False) -> TensorBuffer:
         """Softmax / log-softmax that keeps a half storage dtype (runtime/typed.rs:769-776, the vendor softmax in the
         reference): FP32 goes straight to the row kernel; FP16 and BF16 are widened to FP32, normalised there and rounded

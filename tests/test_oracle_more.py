@@ -57,3 +57,16 @@ def test_frozen_linear_example(oracle, m, n, k):
     x, w, dy, y, dx = V.frozen_linear_case(m, n, k)                # examples/frozen_bf16_tensor.rs:33-52, 5e-4 + 5e-4 |b|
     close(oracle.gemm_bf16(x, w, False, True, False), y, 5e-4, 5e-4)
     close(oracle.gemm_bf16(dy, w, False, False, False), dx, 5e-4, 5e-4)
+
+
+@pytest.mark.parametrize("shape", V.PADDED_GQA_SHAPES[:4] + [(2, 1, 1, 3, 7, 5, 9), (1, 1, 1, 17, 33, 7, 3)])
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_padded_attention_example_shapes(oracle, shape, mode):
+    q, k, v, mask = V.padded_attention_case(shape, mode)          # examples/padded_attention_tensor.rs:14-36,47-62
+    want = V.padded_attention_expected(q, k, v, mask)
+    n, m = shape[4], shape[3]
+    if mode == 2:
+        got = oracle.attention(q, k, v, 0.25, causal=True, query_start=(1 << 40) + (n - m), key_start=1 << 40)
+    else:
+        got = oracle.attention(q, k, v, 0.25, mask=mask if mode == 1 else None)
+    close(got, want, 2e-3, 3e-3)

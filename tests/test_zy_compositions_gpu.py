@@ -272,3 +272,44 @@ def test_tensor_softmax_keeps_half_storage(client, dtype_name, tolerance, log):
     assert np.abs(_to_f64(client.read(out), dtype) - want).max() <= tolerance * max(1.0, np.abs(want).max())
     with pytest.raises(InvalidTensor):
         RT.tensor_softmax(client, client.upload(x), 0, log)
+
+
+@pytest.mark.parametrize("shape", V.PADDED_SDPA_SHAPES)
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_padded_attention_reference_example(client, shape, mode):
+    import rust_ascend_b200.nn as nn
+    b, m, n, d, dv = shape                                          # examples/padded_attention_tensor.rs:66-77, 2e-3 + 3e-3 |b|
+    q, k, v, mask = V.padded_attention_case((b, 1, 1, m, n, d, dv), mode)
+    want = V.padded_attention_expected(q, k, v, mask)[:, 0]
+    t = lambda a: nn.Tensor.from_data(client, np.ascontiguousarray(a))
+    if mode == 2:
+        out = nn.causal_attention_padded_bf16_fp32(t(q[:, 0]), t(k[:, 0]), t(v[:, 0]), 0.25, (1 << 40) + (n - m), 1 << 40)
+    else:
+        out = nn.scaled_dot_product_attention_padded_bf16_fp32(t(q[:, 0]), t(k[:, 0]), t(v[:, 0]), 0.25, t(mask[:, 0]) if mode == 1 else None)
+    assert out.dims() == [b, m, dv]
+    close(out.into_data(), want, 2e-3, 3e-3)
+
+
+@pytest.mark.parametrize("shape", V.PADDED_GQA_SHAPES)
+@pytest.mark.parametrize("mode", [1, 2])
+def test_padded_grouped_attention_reference_example(client, shape, mode):
+    import rust_ascend_b200.nn as nn
+    b, h, kv, m, n, d, dv = shape                                   # examples/padded_attention_tensor.rs:86-98
+    q, k, v, mask = V.padded_attention_case(shape, mode)
+    want = V.padded_attention_expected(q, k, v, mask)
+    t = lambda a: nn.Tensor.from_data(client, a)
+    if mode == 2:
+        out = nn.causal_grouped_query_attention_padded_bf16_fp32(t(q), t(k), t(v), 0.25, (1 << 40) + (n - m), 1 << 40)
+    else:
+        out = nn.grouped_query_attention_padded_bf16_fp32(t(q), t(k), t(v), 0.25, t(mask))
+    assert out.dims() == [b, h, m, dv]
+    close(out.into_data(), want, 2e-3, 3e-3)
+
+
+def test_padded_attention_logical_keys_only(client):
+    import rust_ascend_b200.nn as nn                                # examples/padded_attention_tensor.rs:99-105
+    t = lambda a: nn.Tensor.from_data(client, np.asarray(a, np.float32))
+    q, k, v = t(np.ones((1, 1, 1))), t(np.ones((1, 3, 1))), t(np.full((1, 3, 1), 2.0))
+    close(nn.scaled_dot_product_attention_padded_bf16_fp32(q, k, v, 0.25).into_data(), [[[2.0]]], 2e-3, 3e-3)   # three equal BF16 probabilities
+    masked = nn.scaled_dot_product_attention_padded_bf16_fp32(q, k, v, 0.25, t(np.full((1, 1, 3), -np.inf)))
+    assert np.isnan(masked.into_data()).all()                       # every key excluded: no value, as in the reference

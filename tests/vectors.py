@@ -392,3 +392,35 @@ def frozen_linear_case(m, n, k):
     dy = ((np.arange(m * n) % 11).astype(np.float32) * np.float32(0.017) - np.float32(0.0625)).reshape(m, n)
     wb = bf16_f64(w)
     return x, w, dy, bf16_f64(x) @ wb.T, bf16_f64(dy) @ wb
+
+
+# ---- examples/padded_attention_tensor.rs:47-62 ------------------------------------------------------------------------
+PADDED_SDPA_SHAPES = [(1, 1, 1, 1, 1), (2, 3, 7, 5, 9), (1, 17, 33, 7, 3)]
+PADDED_GQA_SHAPES = [(1, 4, 4, 1, 1, 1, 1), (2, 3, 1, 3, 7, 5, 9), (1, 6, 2, 17, 33, 7, 3), (2, 10, 2, 3, 31, 5, 7), (1, 9, 3, 3, 4097, 7, 9)]
+
+
+def padded_attention_case(shape, mode):
+    """shape = (b, h, kv, m, n, d, dv); mode 0 no mask, 1 additive mask, 2 causal with prefix n - m.  Returns q, k, v, mask."""
+    b, h, kv, m, n, d, dv = shape
+    q = ((np.arange(b * h * m * d) % 13).astype(np.float32) / np.float32(16.0) - np.float32(0.375)).reshape(b, h, m, d)
+    k = ((np.arange(b * kv * n * d) % 17).astype(np.float32) / np.float32(16.0) - np.float32(0.5)).reshape(b, kv, n, d)
+    v = ((np.arange(b * kv * n * dv) % 11).astype(np.float32) / np.float32(8.0) - np.float32(0.5)).reshape(b, kv, n, dv)
+    i = np.arange(b * h * m * n)
+    if mode == 0:
+        mask = np.zeros(i.size, np.float32)
+    elif mode == 1:
+        mask = (i % 5).astype(np.float32) / np.float32(32.0) - np.float32(0.0625)
+    else:
+        mask = np.where(i % n > n - m + (i // n) % m, np.float32(-np.inf), np.float32(0.0)).astype(np.float32)
+    return q, k, v, mask.reshape(b, h, m, n)
+
+
+def padded_attention_expected(q, k, v, mask, scale=0.25):
+    """The f64 reference of padded_attention_tensor.rs:14-36 (forward part): BF16-rounded Q, K, V and probabilities."""
+    b, h, m, d = q.shape
+    kv = k.shape[1]
+    group = h // kv
+    qb, kb, vb = bf16_f64(q), np.repeat(bf16_f64(k), group, axis=1), np.repeat(bf16_f64(v), group, axis=1)
+    s = scale * np.einsum("bhmd,bhnd->bhmn", qb, kb) + mask.astype(np.float64)
+    e = np.exp(s - s.max(-1, keepdims=True)); p = e / e.sum(-1, keepdims=True)
+    return np.einsum("bhmn,bhnc->bhmc", bf16_f64(p.astype(np.float32)), vb)
