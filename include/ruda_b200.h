@@ -260,7 +260,8 @@ RB_API int32_t rb_gemm(rb_ctx* ctx, const rb_tensor* a, const rb_tensor* b, int3
  * RB_INVALID_TENSOR.  The context's device must be current on the calling thread.  The first call on a device
  * resolves the array's address (cudaGetSymbolAddress); make that first call before any stream capture begins.
  * Every call shares the one array: calls that overlap on the GPU (other streams, other threads) race on it.  The
- * call drains the context's stream before it returns, so that an expired kernel wait is reported by this call. */
+ * call drains the context's stream before it returns, so that an expired kernel wait is reported by this call; for
+ * that reason it returns RB_INVALID_TENSOR between rb_graph_begin and rb_graph_end. */
 RB_API int32_t rb_gemm_no_alloc(rb_ctx* ctx, const rb_tensor* a, const rb_tensor* b, int32_t transpose_a, int32_t transpose_b,
                                 const rb_tensor* out);
 

@@ -97,6 +97,12 @@ gemm_scatter_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t num_kb = (p.k + BK - 1) / BK;
     const uint32_t num_tiles = p.tiles_m * p.tiles_n;
+    // An earlier kernel of this stream gave up on a bounded wait: the step is lost, store and announce nothing.  One thread
+    // reads the word so that the whole CTA takes the same branch.
+    __shared__ uint32_t step_lost;
+    if (threadIdx.x == 0) step_lost = *reinterpret_cast<volatile uint32_t*>(p.status);
+    __syncthreads();
+    if (step_lost) return;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -246,7 +252,10 @@ __global__ void __launch_bounds__(32) peer_wait_kernel(uint32_t* flags, uint32_t
     const uint32_t lane = threadIdx.x;
     const uint32_t target = flags[world] + count;
     bool expired = false;
-    if (lane < world) {
+    // A wait that already ran out (here or in an earlier kernel of this stream) ends the step: the waits queued behind it
+    // return at once instead of each spending its own limit, so a lost rank costs about one limit in total.
+    const bool give_up = *reinterpret_cast<volatile uint32_t*>(status) != 0;
+    if (lane < world && !give_up) {
         const uint64_t start = global_timer_ns();
         while ((int32_t)(load_acquire_sys(flags + lane) - target) < 0) {
             if (global_timer_ns() - start > limit_ns) { expired = true; break; }
@@ -279,6 +288,7 @@ struct PushParams {
     bf* dst[MAX_PEERS];             // destination activation buffers [world * rows (or more), width]
     uint32_t* flag[MAX_PEERS];      // destination d's flag word for this rank
     uint32_t* done;                 // local block counter, zero between launches
+    const uint32_t* status;         // device status word: non-zero once a bounded wait has run out
 };
 
 constexpr int PUSH_THREADS = 256;
@@ -288,6 +298,10 @@ __global__ void __launch_bounds__(PUSH_THREADS) reduce_norm_push_kernel(const Pu
     __shared__ float red[PUSH_THREADS / 32];
     __shared__ bool last;
     const uint32_t vecs = p.width / 8;  // 16-byte vectors per row
+    __shared__ uint32_t step_lost;      // read by one thread so that the whole block takes the same branch
+    if (threadIdx.x == 0) step_lost = *reinterpret_cast<const volatile uint32_t*>(p.status);
+    __syncthreads();
+    if (step_lost) return;              // a bounded wait already ran out: push and announce nothing
     for (uint32_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
         float v[PUSH_MAXV][8];
         bool have[PUSH_MAXV];
@@ -538,6 +552,7 @@ int32_t rb_reduce_norm_push(rb_ctx* ctx, const rb_tensor* staging, const rb_tens
     p.x_in = static_cast<const bf*>(pxi); p.x_out = static_cast<bf*>(pxo); p.weight = static_cast<const bf*>(pw);
     p.eps = (float)epsilon; p.rows = (uint32_t)rows; p.width = (uint32_t)width; p.world = world; p.dst_row0 = (uint64_t)rank * rows;
     p.done = static_cast<uint32_t*>(pd);
+    { uint32_t* st = nullptr; RB_TRY(kernel_status_word(ctx, &st)); p.status = st; }
     for (uint32_t d = 0; d < world; ++d) {
         void* pdst = nullptr; uint32_t* pf = nullptr;
         RB_TRY(resolve(ctx, destinations[d], "reduce+norm+push destination", &pdst));

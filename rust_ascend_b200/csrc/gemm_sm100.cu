@@ -293,7 +293,9 @@ int32_t poll_kernel_status(rb_ctx* ctx) {
     if (h) {
         cudaMemset(st->status, 0, sizeof(h));
         std::lock_guard<std::mutex> g(ctx->lock);
-        ctx->sticky.emplace_back("a tensor-core kernel gave up on a bounded barrier wait (status word = 1); its output is invalid");
+        ctx->sticky.emplace_back(h == 2 ? std::string("a bounded wait ran out (status word = 2: a peer's announcement never arrived, or a barrier inside the "
+                                                      "attention kernel was never completed); the outputs of this step are invalid")
+                                        : std::string("a tensor-core kernel gave up on a bounded barrier wait (status word = 1); its output is invalid"));
     }
     return RB_OK;
 }
@@ -409,6 +411,9 @@ static uint8_t* g_no_alloc_scratch_address[64] = {};
 extern "C" int32_t rb_gemm_no_alloc(rb_ctx* ctx, const rb_tensor* a, const rb_tensor* b, int32_t transpose_a, int32_t transpose_b,
                                     const rb_tensor* out) {
     RB_TRY(check_ctx(ctx));
+    // This call drains the stream and reads the status word back; while rb_graph_begin is recording that would break the
+    // recording and leave the context unusable, so it is refused up front.
+    if (ctx->capturing) return fail(RB_INVALID_TENSOR, "rb_gemm_no_alloc synchronises the stream and cannot run while rb_graph_begin is recording");
     int current = -1;
     RB_CUDA(ctx, "cudaGetDevice", cudaGetDevice(&current));
     if (current != ctx->device || current < 0 || current >= 64)

@@ -167,3 +167,36 @@ def test_general_kernel_matches_tensor_core_kernel(client):
     mask = client.upload(np.zeros((1, 2, 128, 256), np.float32))
     slow = bf16_bits_to_f32(client.read(RT.attention(client, up16(client, q), up16(client, k), up16(client, v), SCALE, mask=mask, causal=True, query_start=128)))
     check_bf16(fast, slow)
+
+
+def test_config4_as_stated_rows_sample(client, oracle):
+    """BASELINE configuration 4 as stated: RMSNorm over hidden [2,4096,4096] (w ~ U(0.5,1.5), eps 1e-6) in front, then causal
+    grouped-query attention B2, 32 query / 8 KV heads, S 4096, D 128 with RoPE (SplitHalf, theta 1e4) applied to Q and K inside
+    the attention call.  The norm is checked on a row sample to 1e-5; the attention output on sampled heads: the first rows,
+    rows around a 256-row block boundary and the last rows, against the oracle with the same BF16 rounding of the rotated Q, K."""
+    b, hq, hkv, s = 2, 32, 8, 4096
+    rng = np.random.default_rng(4)
+    hidden = rng.standard_normal((b * s, 4096), dtype=np.float32)
+    w = np.random.default_rng(4001).uniform(0.5, 1.5, 4096).astype(np.float32)
+    y, _ = RT.rms_norm(client, client.upload(hidden), client.upload(w), 1e-6)
+    rows = np.random.default_rng(7).integers(0, b * s, 64)
+    want_y, _ = oracle.rms_norm(hidden[rows], w, 1e-6)
+    np.testing.assert_allclose(client.read(y)[rows], want_y, rtol=1e-5, atol=1e-7)
+    client.free(y.handle)
+    q, k, v = rand_qkv(4002, b, hq, hkv, s, s)
+    pos = np.arange(s, dtype=np.float64)[:, None]
+    inv = 10000.0 ** (-np.arange(64, dtype=np.float64) * 2 / 128)
+    cos, sin = np.cos(pos * inv).astype(np.float32), np.sin(pos * inv).astype(np.float32)
+    out = RT.attention(client, up16(client, q), up16(client, k), up16(client, v), SCALE, causal=True, cos=client.upload(cos), sin=client.upload(sin),
+                       rotary_layout=RotaryLayout.SplitHalf)
+    got = bf16_bits_to_f32(client.read(out))
+    assert np.all(np.isfinite(got))
+    for bi, h in ((0, 0), (1, 13), (1, 31)):
+        kvh = h // (hq // hkv)
+        tk = np.broadcast_to(cos, (1, 1, s, 64)), np.broadcast_to(sin, (1, 1, s, 64))
+        kr = oracle.bf16(oracle.rotary(k[bi:bi + 1, kvh:kvh + 1], tk[0], tk[1], "split_half"))
+        for r0, r1 in ((0, 32), (240, 272), (s - 32, s)):
+            tq = np.broadcast_to(cos[r0:r1], (1, 1, r1 - r0, 64)), np.broadcast_to(sin[r0:r1], (1, 1, r1 - r0, 64))
+            qr = oracle.bf16(oracle.rotary(q[bi:bi + 1, h:h + 1, r0:r1], tq[0], tq[1], "split_half"))
+            want = oracle.attention(qr, kr, v[bi:bi + 1, kvh:kvh + 1], SCALE, causal=True, query_start=r0)
+            check_bf16(got[bi:bi + 1, h:h + 1, r0:r1], want)

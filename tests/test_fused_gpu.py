@@ -1,9 +1,9 @@
 """Two GPUs: peer buffers, the fused row-parallel projection (scatter GEMM + owner-side reduce + push) against a host
 reference and against the NCCL path, and the decoder in fused mode against the same host reference the NCCL decoder meets.
 
-These kernels store into another GPU's memory and wait on flags that another GPU sets, so the test is opt-in
-(RUDA_FUSED_TESTS=1) until it has been run on two GPUs of the target pool; every wait in the kernels is bounded (a few seconds) and
-the workers are joined with a deadline, so a protocol error ends as a failed test, not as a hang."""
+These kernels store into another GPU's memory and wait on flags that another GPU sets; every wait in the kernels is bounded
+(a few seconds) and the workers are joined with a deadline, so a protocol error ends as a failed test, not as a hang.  The
+single-GPU test runs the same kernels as a world of one, where every store, flag and wait stays in local memory."""
 import os
 import socket
 import sys
@@ -13,8 +13,6 @@ import numpy as np
 import pytest
 
 pytestmark = pytest.mark.gpu
-OPT_IN = pytest.mark.skipif(os.environ.get("RUDA_FUSED_TESTS") != "1",
-                            reason="peer-memory kernels not yet run on the target pool: opt in with RUDA_FUSED_TESTS=1")
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
@@ -105,7 +103,6 @@ def _worker(rank, world, port, results):
     dist.destroy_process_group()
 
 
-@OPT_IN
 @pytest.mark.timeout(300)
 def test_two_gpu_fused_exchange(oracle):
     import torch
@@ -162,7 +159,6 @@ def test_two_gpu_fused_exchange(oracle):
         assert np.abs(r[rank]["fused4"] - r[rank]["fused4_overlap"]).max() <= 2.0 ** -7 * np.abs(r[rank]["fused4"]).max()
 
 
-@OPT_IN
 def test_single_gpu_fused_exchange(client, oracle):
     """The same kernels on one GPU (a world of one): every store, announcement and wait stays in local memory, which makes
     this the cheapest first check of the scatter GEMM, the owner-side step, the waits and the side stream."""
@@ -203,3 +199,40 @@ def test_single_gpu_fused_exchange(client, oracle):
             assert err.max() <= 0.04 * np.abs(want_logits).max() and err.mean() <= 0.015 * np.abs(want_logits).mean() + 1e-4, (kwargs, err.max(), err.mean())
     finally:
         client.take_errors()          # an expired wait is a sticky error; it must not follow the context into other tests
+
+
+def test_bounded_peer_wait_runs_out_and_the_context_survives(client, oracle):
+    """Failure detection on the device without a fault: a peer wait on a flag that nobody signals gives up after its time
+    limit (50 ms here), raises the device status word, the next sync reports ServerUnhealthy, the waits queued behind it return
+    at once, and after take_errors the same context still multiplies matrices correctly."""
+    import ctypes as C
+    from rust_ascend_b200 import B200Runtime as RT
+    from rust_ascend_b200 import DType, ServerUnhealthy
+    from rust_ascend_b200.runtime import _check, f32_to_bf16_bits
+    flags = client.tensor((16,), DType.I32)
+    client.memset(flags, 0)
+    client.sync()
+    before = os.environ.get("RUDA_PEER_WAIT_MS")
+    os.environ["RUDA_PEER_WAIT_MS"] = "50"
+    try:
+        desc = flags._c()
+        started = time.time()
+        for _ in range(20):                                    # 20 queued waits: only the first may spend its limit
+            _check(client._lib.rb_peer_wait(client._ctx, C.byref(desc), C.c_uint32(1), C.c_uint32(1)))
+        with pytest.raises(ServerUnhealthy):
+            client.sync()
+        assert time.time() - started < 0.8                     # far below 20 x 50 ms plus launch overheads
+    finally:
+        if before is None:
+            del os.environ["RUDA_PEER_WAIT_MS"]
+        else:
+            os.environ["RUDA_PEER_WAIT_MS"] = before
+        errors = client.take_errors()
+    assert any("bounded wait" in e for e in errors), errors
+    rng = np.random.default_rng(2)
+    a = rng.standard_normal((128, 64)).astype(np.float32); b = rng.standard_normal((96, 64)).astype(np.float32)
+    from rust_ascend_b200 import Transpose
+    got = client.read(RT.gemm(client, client.upload(f32_to_bf16_bits(a)), client.upload(f32_to_bf16_bits(b)), Transpose.No, Transpose.Yes, DType.F32))
+    client.sync()                                              # raises if the context were still unhealthy
+    want = oracle.gemm_bf16(a, b, False, True, False)
+    np.testing.assert_allclose(got, want, rtol=0, atol=1e-4 * np.abs(want).max())

@@ -168,3 +168,38 @@ def test_domain_errors(client):
         RT.gemm_into(client, a, b, Transpose.No, Transpose.Yes, alias)
     with pytest.raises(InvalidTensor, match="FP32 inputs"):
         RT.gemm_bf16_fp32(client, a, b, Transpose.No, Transpose.Yes)
+
+
+def _normal_bf16(seed, shape, std=1.0):
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal(shape, dtype=np.float32)
+    if std != 1.0:
+        x *= np.float32(std)
+    return bf16_bits_to_f32(f32_to_bf16_bits(x))
+
+
+def test_config2a_full_size_against_oracle_rows(client, oracle):
+    """BASELINE configuration 2a as stated: X [4096,4096] ~ N(0,1), W [4096,4096] ~ N(0,0.02) stored [N,K], FP32 bias
+    ~ N(0,0.02), BF16 output.  The whole output is computed on the GPU; the oracle recomputes 48 sampled rows."""
+    m = n = k = 4096
+    x, w = _normal_bf16(2, (m, k)), _normal_bf16(2001, (n, k), 0.02)
+    bias = (np.random.default_rng(2002).standard_normal(n) * 0.02).astype(np.float32)
+    out = RT.gemm(client, up16(client, x), up16(client, w), Transpose.No, Transpose.Yes, DType.BF16, bias=client.upload(bias))
+    got = read(client, out)
+    rows = np.unique(np.concatenate([[0, 127, 128, m - 1], np.random.default_rng(5).integers(0, m, 44)]))
+    bf16_tolerance(got[rows], oracle.linear(x[rows], w, bias=bias))
+    assert np.all(np.isfinite(got))
+
+
+def test_config2b_full_size_swiglu_against_oracle_rows(client, oracle):
+    """BASELINE configuration 2b: X [8192,4096], gate and up weights [11008,4096], output bf16(silu(g) * u) [8192,11008]
+    from one launch.  The oracle recomputes 24 sampled rows (first/last rows of the first and last row tiles included)."""
+    m, n, k = 8192, 11008, 4096
+    x = _normal_bf16(2, (m, k))
+    wg, wu = _normal_bf16(2003, (n, k), 0.02), _normal_bf16(2004, (n, k), 0.02)
+    out = RT.gemm(client, up16(client, x), up16(client, wg), Transpose.No, Transpose.Yes, DType.BF16, b_up=up16(client, wu))
+    got = read(client, out)
+    rows = np.unique(np.concatenate([[0, 127, m - 128, m - 1], np.random.default_rng(6).integers(0, m, 20)]))
+    bf16_tolerance(got[rows], oracle.linear(x[rows], wg, w_up=wu))
+    assert np.all(np.isfinite(got))
+    client.free(out.handle)

@@ -11,10 +11,7 @@ import pytest
 import vectors as V
 from test_backward import close
 
-# These compositions have so far been run only against a NumPy stand-in for the
-# library (the entry points they are built from are covered one by one by the earlier files).  Until their first run on
-# a GPU a failure here is reported without ending a fail-fast run; a pass is reported as such.
-pytestmark = [pytest.mark.gpu, pytest.mark.xfail(reason="first run on a GPU pending", strict=False)]
+pytestmark = pytest.mark.gpu
 
 
 @pytest.fixture(autouse=True)
