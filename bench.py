@@ -31,6 +31,12 @@ SETS = 4                                 # rotating operand sets: 4 x 96 MiB > 1
 NCCL_CTAS = 16                           # SMs left to NCCL while tensor-parallel GEMMs run (decoder extra)
 
 
+def workload_config(world: int) -> dict:
+    """The `config` object both arms print (identical keys and values, so the two lines describe one workload)."""
+    return {"workload": "linear_bf16_4096x4096x4096_bias", "m": M, "n": N, "k": K, "rows_per_gpu": M,
+            "l2": f"rotating {SETS} operand sets (384 MiB) > 126 MB L2", "parallelism": f"row shards x{world}, no collective"}
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -138,13 +144,15 @@ def run_reference(args):
         orc.linear(x, w, bias=bias, out_bf16=True)
     dt = (time.perf_counter() - t0) / args.steps
     value = 2.0 * rows * N * K / dt / 1e12
-    sample = f"{rows} of {M} rows of the 4096x4096x4096 Linear per step (oracle port, f64 accumulate, OpenMP)"
+    sample = (f"each step multiplies {rows} of the {M} rows of the 4096x4096x4096 Linear (oracle port: unblocked, unvectorised triple loop, "
+              f"f64 accumulate, OpenMP over rows); ms_per_step is the time of that sample, value the rate it implies")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": dt * 1e3 * (M / rows), "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "linear_bf16_4096x4096x4096_bias", "m": M, "n": N, "k": K, "host": "cpu"},
-        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "config": workload_config(int(os.environ.get("WORLD_SIZE", args.gpus))),
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample, "rows_per_step": rows,
+                         "full_step_ms_at_this_rate": dt * 1e3 * (M / rows)},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -196,24 +204,33 @@ def run_ours(args):
     ms_per_step = total_ms / args.steps
     value = world * FLOPS_PER_STEP / (ms_per_step * 1e-3) / 1e12
 
-    # ---- end to end through the C ABI with host buffers: H2D of X, GEMM, D2H of Y, every step ----
+    # ---- end to end through the C ABI with host buffers: every step uploads X from pinned host memory, multiplies and
+    # reads Y back into pinned host memory.  rb_linear_host is the public call for that: it cuts the rows into chunks so that
+    # the upload of one chunk, the GEMM of the previous one and the read-back of the one before run at the same time. ----
     e2e_steps = max(3, min(args.steps, 40))
+    chunks = 8
     hx = client.pinned((M, K), np.uint16)
     hy = client.pinned((M, N), np.uint16)
     hx[...] = f32_to_bf16_bits(rng.standard_normal((M, K), dtype=np.float32))
     x, w, b, y = sets[0]
     for _ in range(3):
-        client.write(x.handle, hx); RT.gemm_into(client, x, w, Transpose.No, Transpose.Yes, y, bias=b); client.read_into(y.handle, hy)
+        RT.linear_host(client, hx, x, w, y, hy, bias=b, row_chunks=chunks)
     if dist is not None:
         dist.barrier()
     t0 = time.perf_counter()
     for i in range(e2e_steps):
         x, w, b, y = sets[i % SETS]
-        client.write(x.handle, hx)
-        RT.gemm_into(client, x, w, Transpose.No, Transpose.Yes, y, bias=b)
-        client.read_into(y.handle, hy)  # synchronises
+        RT.linear_host(client, hx, x, w, y, hy, bias=b, row_chunks=chunks)   # returns when Y is in host memory
     e2e_s = max_over_ranks(dist, (time.perf_counter() - t0) / e2e_steps)
     e2e_value = world * FLOPS_PER_STEP / e2e_s / 1e12
+    # the same three steps one after the other (rb_write, rb_gemm, rb_read), for comparison
+    t0 = time.perf_counter()
+    for i in range(min(e2e_steps, 10)):
+        x, w, b, y = sets[i % SETS]
+        client.write(x.handle, hx)
+        RT.gemm_into(client, x, w, Transpose.No, Transpose.Yes, y, bias=b)
+        client.read_into(y.handle, hy)
+    serial_s = max_over_ranks(dist, (time.perf_counter() - t0) / min(e2e_steps, 10))
 
     kernel_tflops = FLOPS_PER_STEP / (ms_per_step * 1e-3) / 1e12
     sustained = total_ms > 1000.0
@@ -222,13 +239,14 @@ def run_ours(args):
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": "linear_bf16_4096x4096x4096_bias", "m": M, "n": N, "k": K, "rows_per_gpu": M,
-                   "l2": f"rotating {SETS} operand sets (384 MiB) > 126 MB L2", "parallelism": f"row shards x{world}, no collective"},
+        "config": workload_config(world),
         "clocks": clocks, "gpu_launches": int(gpu_launches),
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": int(hx.nbytes), "d2h_bytes_per_step": int(hy.nbytes),
-                "steps": e2e_steps, "note": "X uploaded and Y read back every step through rb_write/rb_gemm/rb_read; W and bias stay resident as module parameters"},
+                "steps": e2e_steps, "ms_per_step": e2e_s * 1e3, "serial_write_gemm_read_ms": serial_s * 1e3,
+                "note": f"rb_linear_host: every byte of X uploaded and of Y read back inside every timed step, in {chunks} row chunks whose H2D copy, GEMM "
+                        "and D2H copy overlap on three streams; W and bias stay resident as module parameters"},
         "roofline": {"bound": "tensor", "achieved": kernel_tflops, "peak": peak, "unit": "TFLOP/s", "frac": kernel_tflops / peak,
-                     "traffic": 80.9e6, "traffic_source": "ncu dram__bytes_read+write per launch, profiles/gemm_bf16_linear4096.txt", "kernel": "gemm_bf16_kernel<256>", "peak_kind": ("sustained" if sustained else "burst") + " of " + pk["source"],
+                     "traffic": 80.9e6, "traffic_source": "ncu dram__bytes_read+write per launch of this shape (profiles/gemm_bf16_linear4096.txt); algorithmic bytes are 100.7e6, the output tail stays in L2", "kernel": "gemm_bf16_kernel<256>", "peak_kind": ("sustained" if sustained else "burst") + " of " + pk["source"],
                      "frac_of_burst": kernel_tflops / pk["bf16_tflops"], "frac_of_sustained": kernel_tflops / pk["bf16_tflops_sustained"],
                      "frac_of_nominal_2250": kernel_tflops / 2250.0},
     }
@@ -246,6 +264,7 @@ def run_ours(args):
                                 "sample": f"{rows} of {M} rows of the same Linear, {reps} repetitions, {spent:.1f} s, oracle port (f64 accumulate, OpenMP)"}
     # The extras (tensor-parallel decoder over NCCL among them) run under a watchdog: if they do not finish, the
     # headline line is still printed and every rank leaves, so one stuck collective cannot take the whole run down.
+    line["tp"] = None            # filled from the decoder-stack measurement below; printed before the longer extras
     line["extras"] = {}
     emitted = threading.Event()
 
@@ -255,11 +274,18 @@ def run_ours(args):
         emitted.set()
         if note:
             line["extras"]["note"] = note
+        line["tp"] = tp_summary(line["extras"], world, rank)
         if rank == 0:
             print(json.dumps(line), flush=True)
 
     def give_up():
         note = f"extras did not finish within {args.extras_timeout} s; what had finished by then is reported"
+        try:
+            # Every device-side wait is bounded (seconds), so the stream drains by itself; leaving before it has would free
+            # buffers that the other ranks' kernels may still be storing into.
+            client._lib.rb_sync(client._ctx)
+        except Exception:
+            pass
         try:
             emit(note)
         except Exception:                      # the main thread was writing into the dictionary being printed
@@ -281,6 +307,42 @@ def run_ours(args):
     emit()
 
 
+TP_N1_FILE = os.path.join(ROOT, "gpurun_out", "bench_tp_decoder_n1.json")
+TP_N1_RECORDED_MS = 56.5     # one-GPU forward of the decoder stack measured on this pool earlier; used only when no N=1 run left its file
+
+
+def tp_summary(extras_out: dict, world: int, rank: int):
+    """The tensor-parallel decoder-stack figure as a short top-level object: time per forward, whole-job TFLOP/s, and the
+    efficiency T1 / (N * TN) against the one-GPU forward (taken from the file an N=1 run of this script leaves behind, else
+    from the recorded constant, and labelled accordingly).  The list of all timed schedules goes to a file, not the line."""
+    tpd = extras_out.get("tp_decoder")
+    if not tpd:
+        return None
+    schedules = tpd.pop("schedules_timed", None)
+    if rank == 0:
+        try:
+            os.makedirs(os.path.dirname(TP_N1_FILE), exist_ok=True)
+            if schedules is not None:
+                json.dump(schedules, open(os.path.join(os.path.dirname(TP_N1_FILE), f"bench_tp_schedules_n{world}.json"), "w"), indent=1)
+            if world == 1:
+                json.dump({"ms_per_forward": tpd["ms_per_forward"]}, open(TP_N1_FILE, "w"))
+        except OSError:
+            pass
+    t1, source = TP_N1_RECORDED_MS, "recorded constant"
+    if world == 1:
+        t1, source = tpd["ms_per_forward"], "this run"
+    elif os.path.exists(TP_N1_FILE):
+        try:
+            t1, source = float(json.load(open(TP_N1_FILE))["ms_per_forward"]), "N=1 run on this box"
+        except (OSError, ValueError, KeyError):
+            pass
+    sched = tpd.get("schedule", {})
+    return {"workload": "llama_decoder_8L_h4096_b8_s2048_bf16", "parallelism": tpd.get("parallelism"), "ms_per_forward": tpd["ms_per_forward"],
+            "value": tpd["value"], "unit": "TFLOP/s (whole job)", "efficiency_vs_n1": t1 / (world * tpd["ms_per_forward"]), "t1_ms": t1, "t1_source": source,
+            "schedule": sched.get("parallelism"), "exchanges_per_forward": sched.get("all_reduces_per_forward", 0) + sched.get("fused_exchanges_per_forward", 0),
+            "exchange_bytes": 16384 * 4096 * 2}
+
+
 def extras(client, RT, pk, args, rank, world, dist, out):
     """Secondary kernels of the same hot path, each against its own roofline (reported, not the headline).  Results are
     written into `out` as they arrive, so that a run cut short by the watchdog still reports what finished."""
@@ -291,7 +353,7 @@ def extras(client, RT, pk, args, rank, world, dist, out):
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         # Order: tensor parallelism over all GPUs (the north-star figure) first, then the row-parallel Linear, then the
         # smaller tensor-parallel groups; whatever the watchdog cuts off is the least important part.
-        fused = os.environ.get("RUDA_BENCH_FUSED") == "1"   # timed only on request until validated on this pool's GPUs
+        fused = os.environ.get("RUDA_BENCH_FUSED", "1") != "0"   # the exchange fused into the kernels over peer memory is timed beside NCCL
         candidates = decoder_candidates(world, fused=fused)
         results = []
         decoder_extra(client, pk, rank, world, dist, out, [c for c in candidates if c["tp"] == world], results)
@@ -341,6 +403,10 @@ def extras(client, RT, pk, args, rank, world, dist, out):
         for t in s:
             client.free(t.handle)
     out.update(attention_extra(client, RT, pk))
+    try:
+        out.update(gemm_extras(client, RT, pk))
+    except Exception as error:
+        out["gemm_extras_error"] = f"{type(error).__name__}: {error}"
     decoder_extra(client, pk, rank, world, dist, out, decoder_candidates(world), [])
     if not args.no_cpu_baseline:
         try:
@@ -426,6 +492,65 @@ def cpu_side_baselines(orc):
     t0 = time.perf_counter(); orc.attention(q, k, v, d ** -0.5, causal=True); dt = time.perf_counter() - t0
     out["attention_causal_s2048_d128"] = {"value": 2 * s * s * d / dt / 1e12, "unit": "TFLOP/s", "ms": dt * 1e3,
                                           "sample": "1 of the 128 (batch, head) pairs of config 3, once"}
+    return out
+
+
+def gemm_extras(client, RT, pk):
+    """Configuration 2b (X [8192,4096] against gate and up weights [11008,4096], SiLU(g)*u fused into the store: one launch) and the
+    headline GEMM held for more than a second, where the 1 kW power cap sets the clock (compared with the sustained peak)."""
+    import ctypes as C
+    from rust_ascend_b200 import DType
+    from rust_ascend_b200.runtime import _check, f32_to_bf16_bits
+    out = {}
+    rng = np.random.default_rng(22)
+    m, n, k = 8192, 11008, 4096
+    block = f32_to_bf16_bits(rng.standard_normal((2048, k), dtype=np.float32))
+    x = client.upload(np.tile(block, (m // 2048, 1)))
+    wblock = f32_to_bf16_bits(rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02))
+    wg, wu = client.upload(wblock), client.upload(np.roll(wblock, 7, axis=0))
+    y = client.tensor((m, n), DType.BF16)
+    keep = [t._c() for t in (x, wg, wu, y)]
+    call = (client._ctx, C.byref(keep[0]), C.byref(keep[1]), C.c_int32(0), C.c_int32(1), None, C.byref(keep[2]), C.c_int32(2), C.byref(keep[3]))
+    for _ in range(3):
+        _check(client._lib.rb_gemm(*call))
+    client.sync()
+    client.start_profile()
+    for _ in range(20):
+        _check(client._lib.rb_gemm(*call))
+    ms = client.end_profile() / 20
+    tf = 2 * 2 * m * n * k / (ms * 1e-3) / 1e12
+    out["swiglu_gemm_8192x11008x4096"] = {"value": tf, "unit": "TFLOP/s", "us": ms * 1e3, "l2": "operands 408 MiB > 126 MB L2",
+                                          "roofline": {"bound": "tensor", "achieved": tf, "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": tf / pk["bf16_tflops"],
+                                                       "peak_kind": "burst of " + pk["source"], "frac_of_sustained": tf / pk["bf16_tflops_sustained"]}}
+    for t in (x, wg, wu, y):
+        client.free(t.handle)
+    sets = []
+    for _ in range(SETS):
+        sets.append((client.upload(f32_to_bf16_bits(rng.standard_normal((M, K), dtype=np.float32))),
+                     client.upload(f32_to_bf16_bits(rng.standard_normal((N, K), dtype=np.float32) * np.float32(0.02))),
+                     client.upload((rng.standard_normal(N) * 0.02).astype(np.float32)), client.tensor((M, N), DType.BF16)))
+    keep = [[t._c() for t in st] for st in sets]
+    calls = [(client._ctx, C.byref(q[0]), C.byref(q[1]), C.c_int32(0), C.c_int32(1), C.byref(q[2]), None, C.c_int32(1), C.byref(q[3])) for q in keep]
+    for i in range(50):
+        _check(client._lib.rb_gemm(*calls[i % SETS]))
+    client.sync()
+    sampler = ClockSampler(0)
+    sampler.start()
+    launches = 12000                       # more than a second of back-to-back launches
+    client.start_profile()
+    for i in range(launches):
+        _check(client._lib.rb_gemm(*calls[i % SETS]))
+    total_ms = client.end_profile()
+    clocks = sampler.stop()
+    us = total_ms / launches * 1e3
+    tf = FLOPS_PER_STEP / (us * 1e-6) / 1e12
+    out["linear_gemm_4096_sustained"] = {"value": tf, "unit": "TFLOP/s", "us": us, "seconds": total_ms * 1e-3, "clocks": clocks,
+                                         "us_times_sm_ghz": (us * clocks["sm_mhz"] * 1e-3) if clocks.get("sm_mhz") else None,
+                                         "roofline": {"bound": "tensor", "achieved": tf, "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                                                      "frac": tf / pk["bf16_tflops_sustained"], "peak_kind": "sustained of " + pk["source"]}}
+    for st in sets:
+        for t in st:
+            client.free(t.handle)
     return out
 
 

@@ -249,6 +249,16 @@ RB_API int32_t rb_causal_cross_entropy(rb_ctx* ctx, const rb_tensor* logits, con
 RB_API int32_t rb_gemm(rb_ctx* ctx, const rb_tensor* a, const rb_tensor* b, int32_t transpose_a, int32_t transpose_b,
                        const rb_tensor* bias, const rb_tensor* b_up, int32_t epilogue, const rb_tensor* out);
 
+/* Linear on host buffers: Y_host = X_host W^T (+ bias), the reference's write -> launch -> read sequence for one call
+ * (AscendServer::write / read, runtime/mod.rs:767-845; launch + stream sync, worker.rs:404-415) as ONE call whose three
+ * steps overlap: X is cut into `row_chunks` groups of rows, and while one group multiplies on the tensor cores the next
+ * one uploads and the previous one downloads on two copy streams.  host_x [M,K] BF16 and host_y [M,N] (dtype of y)
+ * should be pinned (rb_host_alloc); x and y are device staging tensors of those shapes, w [N,K] BF16 and bias [N]
+ * (nullable) stay resident.  Returns when host_y is complete (it synchronises, like rb_read).  The result is
+ * bit-identical to rb_write + rb_gemm + rb_read on the same operands. */
+RB_API int32_t rb_linear_host(rb_ctx* ctx, const void* host_x, const rb_tensor* x, const rb_tensor* w, const rb_tensor* bias,
+                              const rb_tensor* y, void* host_y, uint32_t row_chunks);
+
 /* rb_gemm without any device allocation.  It has no counterpart in the reference (whose GEMM provider allocates
  * through ComputeStorage); it exists for hosts that must not call cudaMalloc once they are running: servers with a
  * memory budget fixed at start-up, real-time loops that cannot take the device-wide synchronisation cudaMalloc and

@@ -5,16 +5,23 @@
 // grouped-query mapping kv_head = q_head / (Hq/Hkv) (heads_programs.rs:48-52).  Nothing is materialised: no
 // score matrix, no mask tensor, no repeated KV heads.
 //
-// One CTA owns 256 query rows of one (batch, head) as two 128-row tiles that ping-pong on the tensor core:
-//   warps 0-3 / 4-7  softmax of tile 0 / tile 1: one query row per thread, running max and sum in FP32,
-//                    exp2 with the scale folded in, P written back to TMEM as BF16 over the scores
-//   warp 8           TMA producer: Q once, then K and V tiles of 128 keys through two 2-stage rings
-//   warp 9           issues tcgen05.mma:  S_t = Q_t K^T (operands in shared memory),  O_t += P_t V (P from TMEM,
-//                    V consumed as stored, Dv-contiguous)
+// Persistent kernel, one CTA per SM.  A work item is 256 query rows of one (batch, head), handled as two 128-row tiles
+// that ping-pong on the tensor core; items are numbered heaviest first (under a causal mask the last query blocks see the
+// most keys) and CTA c takes items c, c + grid, c + 2 grid, ...  Roles (384 threads):
+//   warps 0-3 / 4-7  softmax of tile 0 / tile 1: one query row per thread, running max and sum in FP32, exp2 with the
+//                    scale folded in, P written back to TMEM as BF16 over the scores, handed to the MMA warp in two halves;
+//                    at the end of an item the same warps normalise O and store it, while the TMA and MMA warps already
+//                    load and multiply the first key block of the next item
+//   warp 8           TMA producer: Q of the next item as soon as the last score GEMM of this one has read it, K and V
+//                    tiles of 128 keys through two 2-stage rings
+//   warp 9           issues tcgen05.mma:  S_t = Q_t K^T (operands in shared memory),  O_t += P_t V (P from TMEM, V consumed
+//                    as stored, Dv-contiguous)
 //   warps 10-11      idle; they only donate their registers to the softmax warps (setmaxnreg)
 // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_t aliases the first 64 columns of S_t.
-// The running maximum is only refreshed when it grows by more than 2^8 (the accumulator and the sum are then
-// rescaled), so most key blocks need no pass over O.
+// The running maximum is only refreshed when it grows by more than 2^8 (the accumulator and the sum are then rescaled),
+// so most key blocks need no pass over O.  A key block that the causal rule or the end of the keys cuts is processed in
+// 32-key chunks whose class (all visible / partly / none) is the same for the whole warp, so that only the partly visible
+// chunk runs predicated code and hidden chunks cost no exponentials.
 #include "common.cuh"
 #include "schedule.h"
 #include "sm100.cuh"
@@ -28,13 +35,15 @@ constexpr int D = 128;            // head dim (Q/K) and value dim
 constexpr int TQ = 128;           // query rows per tile
 constexpr int TK = 128;           // keys per block
 constexpr int KV_STAGES = 2;
-constexpr int THREADS = 384;   // warps 0-7 softmax, 8 TMA, 9 MMA, 10-11 only donate registers
+constexpr int THREADS = 384;   // warps 0-7 softmax + epilogue, 8 TMA, 9 MMA, 10-11 only donate registers
 constexpr int TILE_BYTES = 128 * D * 2;       // 32 KiB: one [128 x 128] BF16 tile = two 64-wide swizzle slabs
 constexpr int SLAB_BYTES = 128 * 64 * 2;      // 16 KiB
 constexpr int SMEM_BYTES = 2 * TILE_BYTES + 2 * KV_STAGES * TILE_BYTES + 1024 + 256;
 
 struct AttnParams {
     uint32_t B, Hq, Hkv, M, N;
+    uint32_t items, heads_total;  // work items = query block pairs x B x Hq; heads_total = B * Hq
+    uint32_t q_blocks;            // 256-row query blocks per head
     float scale_log2;             // scale * log2(e)
     int32_t causal;
     int64_t delta;                // query_start - key_start (saturated): key k is masked iff k > q + delta
@@ -51,6 +60,10 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 __device__ __forceinline__ uint32_t blocks_for(const AttnParams& p, uint32_t row0, uint32_t row_end) {
     return rb_attention_blocks(p.M, p.N, p.causal, p.delta, row0, row_end, TK);
 }
+// Work item -> (query block, head, batch): heaviest query blocks first, heads of one KV group next to each other.
+__device__ __forceinline__ void item_coords(const AttnParams& p, uint32_t item, uint32_t& qb, uint32_t& h, uint32_t& b) {
+    rb_attention_item(item, p.q_blocks, p.heads_total, p.Hq, qb, h, b);
+}
 
 // Packed FP32 pairs (fma.rn.f32x2 / add.rn.f32x2) and the three-input max halve the issue slots of the softmax.
 __device__ __forceinline__ uint64_t pack2(uint32_t lo, uint32_t hi) { uint64_t r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi)); return r; }
@@ -60,34 +73,120 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) { u
 __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) { uint64_t d; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
 __device__ __forceinline__ float max3(float a, float b, float c) { float d; asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c)); return d; }
 
-// One key block of the online softmax for one query row (= one thread, one TMEM lane).  The 128 scores are read
-// from TMEM once (four loads in flight, one wait) and stay in registers; P = exp2(s*scale*log2e - m) goes back to
-// TMEM as BF16 pairs over the scores already consumed.  MASKED is false for blocks entirely below the causal
-// diagonal and inside the key range, so their inner loops carry no predicates.
+// Waits on the three hand-offs of the per-tile chain (scores ready, P half ready, P ready): polling by default, since the
+// hardware's wake-up of a suspended waiter costs a few hundred cycles per hand-off.  -DRB_ATTN_SUSPEND selects the
+// suspending wait instead.
+__device__ __forceinline__ bool wait_handoff(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_word) {
+#ifdef RB_ATTN_SUSPEND
+    return mbar_wait(bar, parity, abort_word);
+#else
+    return mbar_wait_spin(bar, parity, abort_word);
+#endif
+}
+
+// Part of the exponentials can run on the FMA pipe instead of the 16-per-clock exp2 unit: 2^x = 2^n * p(f) with n = round(x),
+// f = x - n in [-0.5, 0.5] and a cubic p (relative error 7.5e-5, far below the BF16 rounding P gets next).  RB_ATTN_POLY
+// is the number of element pairs per 32-key chunk (0..16) computed this way.
+#ifndef RB_ATTN_POLY
+#define RB_ATTN_POLY 0
+#endif
+__device__ __forceinline__ void ex2_poly_pair(float x0, float x1, float& p0, float& p1) {
+    x0 = fmaxf(x0, -120.f); x1 = fmaxf(x1, -120.f);
+    const uint64_t x2 = pack2f(x0, x1);
+    const uint64_t t2 = add2(x2, pack2f(12582912.f, 12582912.f));                 // 1.5 * 2^23: the integer part lands in the low mantissa bits
+    const uint64_t n2 = add2(t2, pack2f(-12582912.f, -12582912.f));
+    const uint64_t f2 = fma2(n2, pack2f(-1.f, -1.f), x2);
+    uint64_t q2 = fma2(f2, pack2f(0.055171650f, 0.055171650f), pack2f(0.24261113f, 0.24261113f));
+    q2 = fma2(q2, f2, pack2f(0.69326097f, 0.69326097f));
+    q2 = fma2(q2, f2, pack2f(0.99992806f, 0.99992806f));
+    float q0, q1, t0, t1; unpack2f(q2, q0, q1); unpack2f(t2, t0, t1);
+    p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
+    p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
+}
+
+// Optional cycle trace of one CTA (developer builds only, -DRB_ATTN_TRACE): slot = ((role * 64 + block) * 8 + event).
+#ifdef RB_ATTN_TRACE
+__device__ unsigned long long g_attn_trace[5 * 64 * 8];
+#define RB_TR(on, role, j, e) do { if ((on) && (j) < 64u) g_attn_trace[(((role) * 64u + (j)) * 8u) + (e)] = clock64(); } while (0)
+#else
+#define RB_TR(on, role, j, e) do { } while (0)
+#endif
+
+// Row maximum of one 32-score chunk.  CLS: 2 = every key visible, 1 = keys [0, vis) of the chunk visible (per lane),
+// 0 = none (nothing to do).
+template <int CLS>
+__device__ __forceinline__ void chunk_max(const uint32_t (&r)[32], int32_t vis, float& m) {
+    if (CLS == 2) {
+        float a = __uint_as_float(r[0]), b = __uint_as_float(r[1]);
+#pragma unroll
+        for (int i = 2; i < 32; i += 4) {
+            a = max3(a, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+            if (i + 3 < 32) b = max3(b, __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+        }
+        m = max3(m, a, b);
+    } else if (CLS == 1) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) if (i < vis) m = fmaxf(m, __uint_as_float(r[i]));
+    }
+}
+// P = exp2(s * sc - m) of one chunk as BF16 pairs into `packed`; the FP32 values are added to the row sum.
+template <int CLS>
+__device__ __forceinline__ void chunk_exp(const uint32_t (&r)[32], int32_t vis, float sc, float neg_m, uint32_t (&packed)[16], uint64_t& acc_a, uint64_t& acc_b) {
+    if (CLS == 2) {
+        const uint64_t sc2 = pack2f(sc, sc), nm2 = pack2f(neg_m, neg_m);
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+            float x0, x1; unpack2f(fma2(pack2(r[i], r[i + 1]), sc2, nm2), x0, x1);
+            float p0, p1;
+            // the pairs handed to the polynomial are spread evenly over the chunk
+            if (RB_ATTN_POLY > 0 && ((i >> 1) * RB_ATTN_POLY) % 16 < RB_ATTN_POLY) ex2_poly_pair(x0, x1, p0, p1);
+            else { p0 = ex2(x0); p1 = ex2(x1); }
+            if (i & 2) acc_b = add2(acc_b, pack2f(p0, p1)); else acc_a = add2(acc_a, pack2f(p0, p1));
+            packed[i >> 1] = pack_bf16(p0, p1);
+        }
+    } else if (CLS == 1) {
+        float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+            float p0 = ex2(__fmaf_rn(__uint_as_float(r[i]), sc, neg_m)), p1 = ex2(__fmaf_rn(__uint_as_float(r[i + 1]), sc, neg_m));
+            if (i >= vis) p0 = 0.f;
+            if (i + 1 >= vis) p1 = 0.f;
+            s0 += p0; s1 += p1;
+            packed[i >> 1] = pack_bf16(p0, p1);
+        }
+        acc_a = add2(acc_a, pack2f(s0, s1));
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) packed[i] = 0u;
+    }
+}
+
+// Class of the 32-key chunk c of a block for the whole warp: lane l sees keys [0, min(v0 + l, nk)) of the block.
+__device__ __forceinline__ int chunk_class(int32_t v0, int32_t nk, int c) {
+    const int32_t least = v0 < nk ? v0 : nk, most = v0 + 31 < nk ? v0 + 31 : nk;   // visible keys of lane 0 / lane 31
+    if (least >= 32 * c + 32) return 2;
+    if (most <= 32 * c) return 0;
+    return 1;
+}
+
+// One key block of the online softmax for one query row (= one thread, one TMEM lane).  The 128 scores are read from
+// TMEM once (four loads in flight, one wait) and stay in registers; P goes back to TMEM as BF16 pairs over the scores
+// already consumed, and the MMA warp is told after the first 64 keys and again after all 128 so that P V can start
+// early.  MASKED is false for blocks entirely below the causal diagonal and inside the key range.
 template <bool MASKED>
-__device__ __forceinline__ void softmax_block(uint32_t tmem_s, uint32_t tmem_o, float sc, int32_t visible, bool first, float& m_used, float& l) {
+__device__ __forceinline__ void softmax_block(uint32_t tmem_s, uint32_t tmem_o, float sc, int32_t visible, int32_t v0, int32_t nk, bool first,
+                                              float& m_used, float& l, uint64_t* p_half, uint64_t* p_full, bool tr, uint32_t tr_role, uint32_t tr_j) {
     uint32_t r0[32], r1[32], r2[32], r3[32];
     tmem_ld_32x32(tmem_s, r0); tmem_ld_32x32(tmem_s + 32, r1); tmem_ld_32x32(tmem_s + 64, r2); tmem_ld_32x32(tmem_s + 96, r3);
     tmem_wait_ld();
-    float mx;
-    if (MASKED) {
-        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#define RB_ROWMAX(R, BASE) _Pragma("unroll") for (int i = 0; i < 32; ++i) { if (BASE + i < visible) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(R[i])); }
-        RB_ROWMAX(r0, 0) RB_ROWMAX(r1, 32) RB_ROWMAX(r2, 64) RB_ROWMAX(r3, 96)
-#undef RB_ROWMAX
-        mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-    } else {
-        // four independent chains of three-input maxima: 64 instructions, dependent depth 16
-        float m4[4] = {__uint_as_float(r0[0]), __uint_as_float(r1[0]), __uint_as_float(r2[0]), __uint_as_float(r3[0])};
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-            m4[0] = max3(m4[0], __uint_as_float(r0[i]), __uint_as_float(r0[i + 1]));
-            m4[1] = max3(m4[1], __uint_as_float(r1[i]), __uint_as_float(r1[i + 1]));
-            m4[2] = max3(m4[2], __uint_as_float(r2[i]), __uint_as_float(r2[i + 1]));
-            m4[3] = max3(m4[3], __uint_as_float(r3[i]), __uint_as_float(r3[i + 1]));
-        }
-        mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-    }
+    RB_TR(tr, tr_role, tr_j, 1);
+    int c0 = 2, c1 = 2, c2 = 2, c3 = 2;
+    if (MASKED) { c0 = chunk_class(v0, nk, 0); c1 = chunk_class(v0, nk, 1); c2 = chunk_class(v0, nk, 2); c3 = chunk_class(v0, nk, 3); }
+    float mx = -INFINITY;
+#define RB_MAX(R, CLS, BASE) { if (!MASKED || CLS == 2) chunk_max<2>(R, 32, mx); else if (CLS == 1) chunk_max<1>(R, visible - BASE, mx); }
+    RB_MAX(r0, c0, 0) RB_MAX(r1, c1, 32) RB_MAX(r2, c2, 64) RB_MAX(r3, c3, 96)
+#undef RB_MAX
+    RB_TR(tr, tr_role, tr_j, 2);
     float m_blk = mx * sc;                      // -inf when every key of the block is masked for this row
     if (!(m_blk > -INFINITY)) m_blk = -INFINITY;
     // Refresh the reference maximum only when it grew by more than 8 (a factor 256 in P).
@@ -111,30 +210,26 @@ __device__ __forceinline__ void softmax_block(uint32_t tmem_s, uint32_t tmem_o, 
         m_used = m_new;
     }
     const float neg_m = -m_used;
-    if (MASKED) {
-        float sum0 = 0.f, sum1 = 0.f;
-#define RB_EXP(R, BASE) { uint32_t packed[16]; _Pragma("unroll") for (int i = 0; i < 32; i += 2) { \
-            float p0 = ex2(__fmaf_rn(__uint_as_float(R[i]), sc, neg_m)), p1 = ex2(__fmaf_rn(__uint_as_float(R[i + 1]), sc, neg_m)); \
-            if (BASE + i >= visible) p0 = 0.f; if (BASE + i + 1 >= visible) p1 = 0.f; \
-            sum0 += p0; sum1 += p1; packed[i >> 1] = pack_bf16(p0, p1); } \
-            tmem_st_32x16(tmem_s + BASE / 2, packed); }
-        RB_EXP(r0, 0) RB_EXP(r1, 32) RB_EXP(r2, 64) RB_EXP(r3, 96)
+    RB_TR(tr, tr_role, tr_j, 3);
+    uint64_t acc_a = pack2f(0.f, 0.f), acc_b = acc_a;
+#define RB_EXP(R, CLS, BASE) { uint32_t packed[16]; \
+        if (!MASKED || CLS == 2) chunk_exp<2>(R, 32, sc, neg_m, packed, acc_a, acc_b); \
+        else if (CLS == 1) chunk_exp<1>(R, visible - BASE, sc, neg_m, packed, acc_a, acc_b); \
+        else chunk_exp<0>(R, 0, sc, neg_m, packed, acc_a, acc_b); \
+        tmem_st_32x16(tmem_s + BASE / 2, packed); }
+    RB_EXP(r0, c0, 0) RB_EXP(r1, c1, 32)
+    tmem_wait_st();
+    tc_fence_before();
+    mbar_arrive(p_half);
+    RB_TR(tr, tr_role, tr_j, 4);
+    RB_EXP(r2, c2, 64) RB_EXP(r3, c3, 96)
 #undef RB_EXP
-        l += sum0 + sum1;
-    } else {
-        const uint64_t sc2 = pack2f(sc, sc), nm2 = pack2f(neg_m, neg_m);
-        uint64_t acc_a = pack2f(0.f, 0.f), acc_b = acc_a;
-#define RB_EXP2(R, BASE) { uint32_t packed[16]; _Pragma("unroll") for (int i = 0; i < 32; i += 2) { \
-            float x0, x1; unpack2f(fma2(pack2(R[i], R[i + 1]), sc2, nm2), x0, x1); \
-            const float p0 = ex2(x0), p1 = ex2(x1); \
-            if (i & 2) acc_b = add2(acc_b, pack2f(p0, p1)); else acc_a = add2(acc_a, pack2f(p0, p1)); \
-            packed[i >> 1] = pack_bf16(p0, p1); } \
-            tmem_st_32x16(tmem_s + BASE / 2, packed); }
-        RB_EXP2(r0, 0) RB_EXP2(r1, 32) RB_EXP2(r2, 64) RB_EXP2(r3, 96)
-#undef RB_EXP2
-        float s0, s1; unpack2f(add2(acc_a, acc_b), s0, s1);
-        l += s0 + s1;
-    }
+    tmem_wait_st();
+    tc_fence_before();
+    mbar_arrive(p_full);
+    RB_TR(tr, tr_role, tr_j, 5);
+    float s0, s1; unpack2f(add2(acc_a, acc_b), s0, s1);
+    l += s0 + s1;
 }
 
 __global__ void __launch_bounds__(THREADS, 1)
@@ -146,29 +241,29 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     uint8_t* sk = smem + 2 * TILE_BYTES;                  // [stages][2 slabs][128 keys][64 d]
     uint8_t* sv = sk + KV_STAGES * TILE_BYTES;            // [stages][2 slabs][128 keys][64 dv]
     uint64_t* bars = reinterpret_cast<uint64_t*>(sv + KV_STAGES * TILE_BYTES);
-    uint64_t* q_full = bars;                    // [1]
-    uint64_t* k_full = bars + 1;                // [stages]
+    uint64_t* q_full = bars;                    // [1]  TMA -> MMA: Q of the item has landed
+    uint64_t* q_empty = bars + 1;               // [1]  MMA -> TMA: the item's last score GEMM has read Q
+    uint64_t* k_full = bars + 2;                // [stages]
     uint64_t* k_empty = k_full + KV_STAGES;
     uint64_t* v_full = k_empty + KV_STAGES;
     uint64_t* v_empty = v_full + KV_STAGES;
-    uint64_t* s_full = v_empty + KV_STAGES;     // [2 tiles]
-    uint64_t* p_full = s_full + 2;              // [2 tiles]
-    uint64_t* o_full = p_full + 2;              // [2 tiles]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
+    uint64_t* s_full = v_empty + KV_STAGES;     // [2 tiles]  MMA -> softmax: scores of a block are in TMEM
+    uint64_t* p_half = s_full + 2;              // [2 tiles]  softmax -> MMA: P of the first 64 keys is in TMEM
+    uint64_t* p_full = p_half + 2;              // [2 tiles]  softmax -> MMA: all of P
+    uint64_t* o_full = p_full + 2;              // [2 tiles]  MMA -> softmax warps: the item's last P V has completed
+    uint64_t* o_free = o_full + 2;              // [2 tiles]  softmax warps -> MMA: O has been read out of TMEM
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_free + 2);
     volatile uint32_t* abort_word = tmem_slot + 1;
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // Heaviest query blocks first: under a causal mask the last rows see the most keys.
-    const uint32_t qb = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-    const uint32_t kvh = h / (p.Hq / p.Hkv);
-    const uint32_t row0 = qb * 2 * TQ;
-    const uint32_t n_blocks[2] = {blocks_for(p, row0, row0 + TQ), blocks_for(p, row0 + TQ, row0 + 2 * TQ)};
-    const uint32_t n_max = n_blocks[0] > n_blocks[1] ? n_blocks[0] : n_blocks[1];
 
     if (threadIdx.x == 0) {
-        mbar_init(q_full, 1);
+        mbar_init(q_full, 1); mbar_init(q_empty, 1);
         for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
-        for (int t = 0; t < 2; ++t) { mbar_init(&s_full[t], 1); mbar_init(&p_full[t], 128); mbar_init(&o_full[t], 1); }
+        for (int t = 0; t < 2; ++t) {
+            mbar_init(&s_full[t], 1); mbar_init(&p_half[t], 128); mbar_init(&p_full[t], 128); mbar_init(&o_full[t], 1);
+            mbar_init(&o_free[t], 128);
+        }
         *abort_word = 0;
         fence_barrier_init();
         prefetch_tmap(&map_q); prefetch_tmap(&map_k); prefetch_tmap(&map_v);
@@ -178,156 +273,214 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+#ifdef RB_ATTN_TRACE
+    const bool trace_cta = blockIdx.x == 0;
+#else
+    const bool trace_cta = false;
+#endif
 
-    // Register budget: the two softmax warpgroups keep a whole score row in registers, the third warpgroup
-    // (TMA, MMA and two idle warps) needs almost none.  256*224 + 128*56 = 64512 registers.
-    if (warp == 8) {
+    // Register budget: the two softmax warpgroups keep a whole score row in registers, the third warpgroup (TMA, MMA and
+    // two idle warps) needs few.  256 * 224 + 128 * 56 = 64512 registers.
+    if (warp >= 8) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
-        // ---------------- TMA producer ----------------
-        if (elect_one()) {
+        if (warp == 8 && elect_one()) {
+            // ---------------- TMA producer ----------------
             bool ok = true;
-            mbar_expect_tx(q_full, 2 * TILE_BYTES);
-            for (int t = 0; t < 2; ++t)
-                for (int s = 0; s < 2; ++s)
-                    tma_load_4d(sq + t * TILE_BYTES + s * SLAB_BYTES, &map_q, q_full, s * 64, (int32_t)(row0 + t * TQ), (int32_t)h, (int32_t)b);
-            uint32_t issued_k = 0, issued_v = 0;
-            for (uint32_t j = 0; ok && j < n_max; ++j) {
-                const uint32_t st = j % KV_STAGES, ph = (j / KV_STAGES) & 1;
-                if (!(ok = mbar_wait(&k_empty[st], ph ^ 1, abort_word))) break;
-                mbar_expect_tx(&k_full[st], TILE_BYTES); issued_k = j + 1;
-                for (int s = 0; s < 2; ++s)
-                    tma_load_4d(sk + st * TILE_BYTES + s * SLAB_BYTES, &map_k, &k_full[st], s * 64, (int32_t)(j * TK), (int32_t)kvh, (int32_t)b);
-                if (!(ok = mbar_wait(&v_empty[st], ph ^ 1, abort_word))) break;
-                mbar_expect_tx(&v_full[st], TILE_BYTES); issued_v = j + 1;
-                for (int s = 0; s < 2; ++s)
-                    tma_load_4d(sv + st * TILE_BYTES + s * SLAB_BYTES, &map_v, &v_full[st], s * 64, (int32_t)(j * TK), (int32_t)kvh, (int32_t)b);
+            uint32_t kv_it = 0, q_it = 0;
+            uint32_t armed = 0, armed_parity = 0;      // bit 0: Q, bits 1-2: K stages, bits 3-4: V stages
+            auto arm = [&](uint32_t bit, uint32_t parity) { armed |= 1u << bit; armed_parity = (armed_parity & ~(1u << bit)) | (parity << bit); };
+            for (uint32_t item = blockIdx.x; ok && item < p.items; item += gridDim.x) {
+                uint32_t qb, h, b; item_coords(p, item, qb, h, b);
+                const uint32_t kvh = h / (p.Hq / p.Hkv), row0 = qb * 2 * TQ;
+                const uint32_t nb0 = blocks_for(p, row0, row0 + TQ), nb1 = blocks_for(p, row0 + TQ, row0 + 2 * TQ);
+                const uint32_t n_max = nb0 > nb1 ? nb0 : nb1;
+                if (n_max == 0) continue;
+                if (q_it > 0 && !(ok = mbar_wait(q_empty, (q_it - 1) & 1, abort_word))) break;
+                mbar_expect_tx(q_full, 2 * TILE_BYTES); arm(0, q_it & 1);
+                for (int t = 0; t < 2; ++t)
+                    for (int s = 0; s < 2; ++s)
+                        tma_load_4d(sq + t * TILE_BYTES + s * SLAB_BYTES, &map_q, q_full, s * 64, (int32_t)(row0 + t * TQ), (int32_t)h, (int32_t)b);
+                for (uint32_t j = 0; ok && j < n_max; ++j) {
+                    const uint32_t st = (kv_it + j) % KV_STAGES, ph = ((kv_it + j) / KV_STAGES) & 1;
+                    if (!(ok = mbar_wait(&k_empty[st], ph ^ 1, abort_word))) break;
+                    mbar_expect_tx(&k_full[st], TILE_BYTES); arm(1 + st, ph);
+                    for (int s = 0; s < 2; ++s)
+                        tma_load_4d(sk + st * TILE_BYTES + s * SLAB_BYTES, &map_k, &k_full[st], s * 64, (int32_t)(j * TK), (int32_t)kvh, (int32_t)b);
+                    if (!(ok = mbar_wait(&v_empty[st], ph ^ 1, abort_word))) break;
+                    mbar_expect_tx(&v_full[st], TILE_BYTES); arm(3 + st, ph);
+                    for (int s = 0; s < 2; ++s)
+                        tma_load_4d(sv + st * TILE_BYTES + s * SLAB_BYTES, &map_v, &v_full[st], s * 64, (int32_t)(j * TK), (int32_t)kvh, (int32_t)b);
+                }
+                kv_it += n_max; ++q_it;
             }
             if (!ok) {
                 // A wait expired: give the copies already issued a bounded time to land before the CTA retires.
-                for (uint32_t i = 0; i < (1u << 20) && !mbar_try_wait(q_full, 0); ++i) {}
-                for (uint32_t j = issued_k > KV_STAGES ? issued_k - KV_STAGES : 0; j < issued_k; ++j)
-                    for (uint32_t i = 0; i < (1u << 20) && !mbar_try_wait(&k_full[j % KV_STAGES], (j / KV_STAGES) & 1); ++i) {}
-                for (uint32_t j = issued_v > KV_STAGES ? issued_v - KV_STAGES : 0; j < issued_v; ++j)
-                    for (uint32_t i = 0; i < (1u << 20) && !mbar_try_wait(&v_full[j % KV_STAGES], (j / KV_STAGES) & 1); ++i) {}
+                for (uint32_t bit = 0; bit < 5; ++bit) {
+                    if (!(armed & (1u << bit))) continue;
+                    uint64_t* bar = bit == 0 ? q_full : (bit < 3 ? &k_full[bit - 1] : &v_full[bit - 3]);
+                    for (uint32_t i = 0; i < (1u << 20) && !mbar_try_wait(bar, (armed_parity >> bit) & 1u); ++i) {}
+                }
             }
-        }
-    } else if (warp == 9) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
-        // ---------------- MMA issuer ----------------
-        if (elect_one()) {
+        } else if (warp == 9 && elect_one()) {
+            // ---------------- MMA issuer ----------------
             const uint32_t idesc_qk = make_idesc_bf16(TQ, TK, 0, 0);   // A = Q (K-major), B = K tile (K-major)
             const uint32_t idesc_pv = make_idesc_bf16(TQ, D, 0, 1);    // A = P (TMEM), B = V tile, Dv-contiguous (MN-major)
-            bool ok = mbar_wait(q_full, 0, abort_word);
-            auto issue_s = [&](uint32_t t, uint32_t j) {
-                const uint32_t st = j % KV_STAGES;
-                const uint32_t qa = smem_u32(sq + t * TILE_BYTES), ka = smem_u32(sk + st * TILE_BYTES);
+            bool ok = true;
+            uint32_t kv_it = 0, q_it = 0;
+            uint32_t blk[2] = {0, 0};      // key blocks served per tile so far (parity of s_full / p_half / p_full)
+            uint32_t used[2] = {0, 0};     // items per tile so far (parity of o_full / o_free)
+            // descriptor lower halves of the tile bases; a step of 16 head-dim elements (or 16 keys of V) is a constant added to them
+            const uint32_t q_lo = desc_lo_kmajor(smem_u32(sq)), k_lo = desc_lo_kmajor(smem_u32(sk)), v_lo = desc_lo_mnmajor(smem_u32(sv), SLAB_BYTES);
+            auto issue_s = [&](uint32_t t, uint32_t st) {
+                const uint32_t qa = q_lo + t * (TILE_BYTES >> 4), ka = k_lo + st * (TILE_BYTES >> 4);
 #pragma unroll
                 for (uint32_t kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t off = (kk >> 2) * SLAB_BYTES + (kk & 3) * 32;  // 16 head-dim elements per step
-                    umma_bf16_ss(tmem_base + t * TK, make_kmajor_sw128_desc(qa + off), make_kmajor_sw128_desc(ka + off), idesc_qk, kk != 0);
+                    const uint32_t off = ((kk >> 2) * SLAB_BYTES + (kk & 3) * 32) >> 4;  // 16 head-dim elements per step
+                    umma_bf16_ss_lo(tmem_base + t * TK, qa + off, ka + off, idesc_qk, kk != 0);
                 }
                 umma_commit(&s_full[t]);
             };
-            if (ok && n_max > 0) {
-                ok = mbar_wait(&k_full[0], 0, abort_word);
-                if (ok) {
+            for (uint32_t item = blockIdx.x; ok && item < p.items; item += gridDim.x) {
+                uint32_t qb, h, b; item_coords(p, item, qb, h, b);
+                const uint32_t row0 = qb * 2 * TQ;
+                const uint32_t nb[2] = {blocks_for(p, row0, row0 + TQ), blocks_for(p, row0 + TQ, row0 + 2 * TQ)};
+                const uint32_t n_max = nb[0] > nb[1] ? nb[0] : nb[1];
+                if (n_max == 0) continue;
+                const uint32_t total_s = nb[0] + nb[1];
+                uint32_t s_done = 0;
+                const bool tr = trace_cta && item == blockIdx.x;
+                if (!(ok = mbar_wait(q_full, q_it & 1, abort_word))) break;
+                {
+                    const uint32_t st = kv_it % KV_STAGES, ph = (kv_it / KV_STAGES) & 1;
+                    if (!(ok = mbar_wait(&k_full[st], ph, abort_word))) break;
                     tc_fence_after();
-                    for (uint32_t t = 0; t < 2; ++t) if (n_blocks[t] > 0) issue_s(t, 0);
-                    umma_commit(&k_empty[0]);
-                }
-            }
-            for (uint32_t j = 0; ok && j < n_max; ++j) {
-                const uint32_t st = j % KV_STAGES, ph = (j / KV_STAGES) & 1;
-                for (uint32_t t = 0; ok && t < 2; ++t) {
-                    if (j >= n_blocks[t]) continue;
-                    if (!(ok = mbar_wait(&p_full[t], j & 1, abort_word))) break;
-                    if (!(ok = mbar_wait(&v_full[st], ph, abort_word))) break;
-                    tc_fence_after();
-                    const uint32_t va = smem_u32(sv + st * TILE_BYTES);
 #pragma unroll
-                    for (uint32_t kk = 0; kk < TK / 16; ++kk)   // 16 keys per step: 8 TMEM columns of packed BF16 pairs
-                        umma_bf16_ts(tmem_base + 256 + t * D, tmem_base + t * TK + kk * 8,
-                                     make_mnmajor_sw128_desc(va + kk * 2048, SLAB_BYTES), idesc_pv, (j | kk) != 0);
-                    const bool last_user = (t == 1) || (j >= n_blocks[1]);
-                    if (last_user) umma_commit(&v_empty[st]);
-                    if (j + 1 < n_blocks[t]) {
-                        const uint32_t st1 = (j + 1) % KV_STAGES, ph1 = ((j + 1) / KV_STAGES) & 1;
-                        if (!(ok = mbar_wait(&k_full[st1], ph1, abort_word))) break;
+                    for (uint32_t t = 0; t < 2; ++t) if (nb[t] > 0) { issue_s(t, st); ++s_done; }
+                    umma_commit(&k_empty[st]);
+                    if (s_done == total_s) umma_commit(q_empty);
+                }
+                for (uint32_t j = 0; ok && j < n_max; ++j) {
+                    const uint32_t st = (kv_it + j) % KV_STAGES, ph = ((kv_it + j) / KV_STAGES) & 1;
+#pragma unroll
+                    for (uint32_t t = 0; t < 2; ++t) {
+                        if (!ok || j >= nb[t]) continue;
+                        const uint32_t par = blk[t] & 1;
+                        RB_TR(tr, 2 + t, j, 7);
+                        if (!(ok = wait_handoff(&p_half[t], par, abort_word))) continue;
+                        RB_TR(tr, 2 + t, j, 0);
+                        // the first P V of an item overwrites O: the epilogue must have read the previous item's O
+                        if (j == 0 && used[t] > 0 && !(ok = mbar_wait(&o_free[t], (used[t] - 1) & 1, abort_word))) continue;
+                        if (!(ok = mbar_wait(&v_full[st], ph, abort_word))) continue;
+                        RB_TR(tr, 2 + t, j, 1);
                         tc_fence_after();
-                        issue_s(t, j + 1);
-                        const bool last_k_user = (t == 1) || (j + 1 >= n_blocks[1]);
-                        if (last_k_user) umma_commit(&k_empty[st1]);
-                    } else {
-                        umma_commit(&o_full[t]);
+                        const uint32_t va = v_lo + st * (TILE_BYTES >> 4);
+#pragma unroll
+                        for (uint32_t kk = 0; kk < TK / 32; ++kk)   // 16 keys per step: 8 TMEM columns of packed BF16 pairs, 2048 B of V
+                            umma_bf16_ts_lo(tmem_base + 256 + t * D, tmem_base + t * TK + kk * 8, va + kk * (2048 >> 4), idesc_pv, kk != 0 ? 1u : j);
+                        RB_TR(tr, 2 + t, j, 2);
+                        if (!(ok = wait_handoff(&p_full[t], par, abort_word))) continue;
+                        RB_TR(tr, 2 + t, j, 3);
+                        tc_fence_after();
+#pragma unroll
+                        for (uint32_t kk = TK / 32; kk < TK / 16; ++kk)
+                            umma_bf16_ts_lo(tmem_base + 256 + t * D, tmem_base + t * TK + kk * 8, va + kk * (2048 >> 4), idesc_pv, 1u);
+                        ++blk[t];
+                        const bool last_user = (t == 1) || (j >= nb[1]);
+                        if (last_user) umma_commit(&v_empty[st]);
+                        RB_TR(tr, 2 + t, j, 4);
+                        if (j + 1 < nb[t]) {
+                            const uint32_t st1 = (kv_it + j + 1) % KV_STAGES, ph1 = ((kv_it + j + 1) / KV_STAGES) & 1;
+                            if (!(ok = mbar_wait(&k_full[st1], ph1, abort_word))) continue;
+                            RB_TR(tr, 2 + t, j, 5);
+                            tc_fence_after();
+                            issue_s(t, st1); ++s_done;
+                            const bool last_k_user = (t == 1) || (j + 1 >= nb[1]);
+                            if (last_k_user) umma_commit(&k_empty[st1]);
+                            if (s_done == total_s) umma_commit(q_empty);
+                            RB_TR(tr, 2 + t, j, 6);
+                        } else {
+                            umma_commit(&o_full[t]);
+                            ++used[t];
+                        }
                     }
                 }
+                kv_it += n_max; ++q_it;
             }
         }
-    } else if (warp >= 10) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
         // ---------------- softmax + epilogue: warps 0-3 own tile 0, warps 4-7 own tile 1 ----------------
         const uint32_t t = warp >> 2, quarter = warp & 3;
         const uint32_t row_in_tile = quarter * 32 + lane;
-        const uint32_t row = row0 + t * TQ + row_in_tile;          // query index inside the sequence
         const uint32_t lane_base = (quarter * 32) << 16;
         const uint32_t tmem_s = tmem_base + t * TK + lane_base;
         const uint32_t tmem_o = tmem_base + 256 + t * D + lane_base;
-        const uint32_t nb = n_blocks[t];
-        const int64_t q_limit = (int64_t)row + p.delta;            // keys with index > q_limit are masked (causal)
-        float m_used = 0.f, l = 0.f;
+        uint32_t blk = 0, used = 0;
         bool ok = true;
-        for (uint32_t j = 0; j < nb; ++j) {
-            ok = mbar_wait(&s_full[t], j & 1, abort_word);
-            if (!(ok = __all_sync(0xffffffffu, ok))) break;
-            tc_fence_after();
-            const uint32_t k0 = j * TK;
-            const bool partial = k0 + TK > p.N;
-            const bool diagonal = p.causal && (int64_t)(k0 + TK - 1) > (int64_t)(row0 + t * TQ) + p.delta;  // warp-uniform
-            int32_t visible = TK;   // keys of this block the row may see
-            if (partial || diagonal) {
-                int64_t limit = (int64_t)p.N - 1;
-                if (p.causal && q_limit < limit) limit = q_limit;
-                const int64_t v64 = limit - (int64_t)k0 + 1;
-                visible = (int32_t)(v64 > TK ? TK : (v64 < 0 ? 0 : v64));
-            }
-            if (partial || diagonal) softmax_block<true>(tmem_s, tmem_o, p.scale_log2, visible, j == 0, m_used, l);
-            else softmax_block<false>(tmem_s, tmem_o, p.scale_log2, visible, j == 0, m_used, l);
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(&p_full[t]);
-        }
-        if (ok && row0 + t * TQ < p.M) {
+        for (uint32_t item = blockIdx.x; ok && item < p.items; item += gridDim.x) {
+            uint32_t qb, h, b; item_coords(p, item, qb, h, b);
+            const uint32_t tile_row0 = qb * 2 * TQ + t * TQ;
+            if (tile_row0 >= p.M) continue;
+            const uint32_t nb = blocks_for(p, tile_row0, tile_row0 + TQ);
+            const uint32_t row = tile_row0 + row_in_tile;                  // query index inside the sequence
             bf* o = p.out + (uint64_t)b * p.o_stride_b + (uint64_t)h * p.o_stride_h + (uint64_t)row * p.o_stride_m;
             if (nb == 0) {
                 // No visible key for this tile: the reference's softmax over an empty set has no value; write zeros.
                 if (row < p.M) for (int i = 0; i < D / 8; ++i) reinterpret_cast<uint4*>(o)[i] = make_uint4(0, 0, 0, 0);
-            } else {
-                ok = mbar_wait(&o_full[t], 0, abort_word);
-                ok = __all_sync(0xffffffffu, ok);
-                if (ok) {
-                    tc_fence_after();
-                    const float inv = l > 0.f ? __fdiv_rn(1.0f, l) : 0.f;
+                continue;
+            }
+            const bool tr = trace_cta && item == blockIdx.x && quarter == 0 && lane == 0;
+            const int64_t q_limit0 = (int64_t)(tile_row0 + quarter * 32) + p.delta;   // last visible key of this warp's first row (causal)
+            float m_used = 0.f, l = 0.f;
+            for (uint32_t j = 0; j < nb; ++j, ++blk) {
+                ok = wait_handoff(&s_full[t], blk & 1, abort_word);
+                if (!(ok = __all_sync(0xffffffffu, ok))) break;
+                tc_fence_after();
+                RB_TR(tr, t, j, 0);
+                const uint32_t k0 = j * TK;
+                const bool partial = k0 + TK > p.N;
+                const bool diagonal = p.causal && (int64_t)(k0 + TK - 1) > (int64_t)tile_row0 + p.delta;  // CTA-tile-uniform
+                if (partial || diagonal) {
+                    // keys [0, nk) of the block exist; lane l of this warp sees keys [0, v0 + l) of them under the causal rule
+                    const int64_t nk64 = (int64_t)p.N - (int64_t)k0;
+                    const int32_t nk = (int32_t)(nk64 > TK ? TK : nk64);
+                    int32_t v0 = TK;   // without a causal rule every lane sees the whole block
+                    if (p.causal) {
+                        const int64_t v64 = q_limit0 - (int64_t)k0 + 1;
+                        v0 = (int32_t)(v64 > 2 * TK ? 2 * TK : (v64 < -TK ? -TK : v64));
+                    }
+                    int32_t visible = p.causal ? v0 + (int32_t)lane : TK;
+                    visible = visible > nk ? nk : (visible < 0 ? 0 : visible);
+                    softmax_block<true>(tmem_s, tmem_o, p.scale_log2, visible, v0, nk, j == 0, m_used, l, &p_half[t], &p_full[t], tr, t, j);
+                } else {
+                    softmax_block<false>(tmem_s, tmem_o, p.scale_log2, TK, TK, TK, j == 0, m_used, l, &p_half[t], &p_full[t], tr, t, j);
+                }
+            }
+            if (!ok) break;
+            // ---- epilogue of the item: O / l -> BF16 -> global ----
+            ok = mbar_wait(&o_full[t], used & 1, abort_word);
+            if (!(ok = __all_sync(0xffffffffu, ok))) break;
+            tc_fence_after();
+            const float inv = l > 0.f ? __fdiv_rn(1.0f, l) : 0.f;
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        uint32_t r[32];
-                        tmem_ld_32x32(tmem_o + c * 32, r);
-                        tmem_wait_ld();
-                        if (row < p.M) {
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32(tmem_o + c * 32, r);
+                tmem_wait_ld();
+                if (c == 3) { tc_fence_before(); mbar_arrive(&o_free[t]); }   // O is in registers: the next item may overwrite it
+                if (row < p.M) {
 #pragma unroll
-                            for (int i = 0; i < 32; i += 8) {
-                                uint4 w;
-                                w.x = pack_bf16(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
-                                w.y = pack_bf16(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
-                                w.z = pack_bf16(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
-                                w.w = pack_bf16(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
-                                *reinterpret_cast<uint4*>(o + c * 32 + i) = w;
-                            }
-                        }
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 w;
+                        w.x = pack_bf16(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+                        w.y = pack_bf16(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+                        w.z = pack_bf16(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+                        w.w = pack_bf16(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+                        *reinterpret_cast<uint4*>(o + c * 32 + i) = w;
                     }
                 }
             }
+            ++used;
         }
     }
 
@@ -553,6 +706,7 @@ int32_t rb_attention(rb_ctx* ctx, const rb_tensor* q, const rb_tensor* k, const 
     AttnParams p{};
     p.B = (uint32_t)B; p.Hq = (uint32_t)Hq; p.Hkv = (uint32_t)Hkv; p.M = (uint32_t)M; p.N = (uint32_t)N;
     p.scale_log2 = scale * 1.4426950408889634f; p.causal = causal ? 1 : 0; p.delta = causal ? delta : 0;
+    p.q_blocks = (uint32_t)((M + 2 * TQ - 1) / (2 * TQ)); p.heads_total = (uint32_t)flat; p.items = p.q_blocks * p.heads_total;
     p.out = (bf*)po; p.o_stride_b = o_stride_b; p.o_stride_h = o_stride_h; p.o_stride_m = o_stride_m;
     RB_TRY(kernel_status_word(ctx, &p.status));
     CUtensorMap mq, mk, mv;
@@ -564,9 +718,17 @@ int32_t rb_attention(rb_ctx* ctx, const rb_tensor* q, const rb_tensor* k, const 
         if (e != cudaSuccess) return fail(RB_STATUS, "cudaFuncSetAttribute(attention) failed with CUDA status %d (%s)", (int)e, cudaGetErrorString(e));
         configured = true;
     }
-    dim3 grid((unsigned)((M + 2 * TQ - 1) / (2 * TQ)), (unsigned)Hq, (unsigned)B);
-    attention_fwd_kernel<<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(mq, mk, mv, p);
+    const uint32_t sms = ctx->sm_limit > 0 ? (uint32_t)ctx->sm_limit : (uint32_t)ctx->sm_count;
+    attention_fwd_kernel<<<p.items < sms ? p.items : sms, THREADS, SMEM_BYTES, ctx->stream>>>(mq, mk, mv, p);
     return after_launch(ctx, "attention");
 }
+
+#ifdef RB_ATTN_TRACE
+// Developer builds only: copies the cycle trace of the last attention launch to the host.
+__attribute__((visibility("default"))) int32_t rb_debug_attention_trace(unsigned long long* out, uint64_t words) {
+    if (words > 5 * 64 * 8) words = 5 * 64 * 8;
+    return cudaMemcpyFromSymbol(out, g_attn_trace, words * 8) == cudaSuccess ? 0 : 3;
+}
+#endif
 
 }  // extern "C"

@@ -11,6 +11,11 @@
 // memory), warps 2..5 are the epilogue.  Two TMEM accumulators let the epilogue of tile i overlap the
 // main loop of tile i+1.  The epilogue is fused: identity, + bias[n], or SiLU(gate)*up where the gate and
 // up projections are accumulated side by side in one UMMA of N = BN from two weight matrices.
+// Tail wave: when the tiles left for the last round of the persistent loop would occupy at most half of the CTAs, each
+// of them is cut into two half-width tiles (UMMA N = BN/2, loaded through half-height B boxes), so that the last round
+// takes about half a tile's time on twice as many SMs instead of a full tile's time on a few (4096^3: 512 tiles on 148
+// CTAs = 3 rounds + 68 tiles -> 136 half tiles).  No partial sums are exchanged; every output element is still the
+// result of one accumulator in one fixed K order.
 // Operands that are not K-major (A transposed, B not transposed) are first rewritten K-major by a tiled
 // transpose kernel; the hot Linear layout (X [M,K], W [N,K]) needs no rewrite.
 #include "common.cuh"
@@ -31,6 +36,8 @@ constexpr int THREADS = 192;
 struct GemmParams {
     uint32_t m, n, k, batches;      // n = output columns
     uint32_t tiles_m, tiles_n;
+    uint32_t split;                 // work items below this index are whole tiles; from it on, item = half of tile split + (i - split) / 2
+    uint32_t items;                 // whole tiles + half tiles
     uint32_t epilogue;              // rb_epilogue
     uint32_t out_f32;               // 1: FP32 output, 0: BF16
     uint32_t bias_bf16;             // bias storage: 1 BF16, 0 FP32
@@ -49,7 +56,9 @@ template <int BN> struct Config {
     static constexpr int TMEM_COLS = 2 * BN;
 };
 
-__device__ __forceinline__ void tile_coords(uint32_t t, const GemmParams& p, uint32_t& batch, uint32_t& tm, uint32_t& tn) {
+// Work item -> tile coordinates; `half` is 0 or 1 for a half-width tile and 2 for a whole tile.
+__device__ __forceinline__ void tile_coords(uint32_t item, const GemmParams& p, uint32_t& batch, uint32_t& tm, uint32_t& tn, uint32_t& half) {
+    uint32_t t; rb_gemm_item(item, p.split, t, half);
     rb_tile_coords(t, p.tiles_m, p.tiles_n, GROUP_M, batch, tm, tn);
 }
 
@@ -60,7 +69,8 @@ __device__ __forceinline__ float bias_at(const GemmParams& p, uint32_t col) {
 template <int BN>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                 const __grid_constant__ CUtensorMap map_b2, const GemmParams p) {
+                 const __grid_constant__ CUtensorMap map_b2, const __grid_constant__ CUtensorMap map_bh,
+                 const __grid_constant__ CUtensorMap map_b2h, const GemmParams p) {
     using C = Config<BN>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -74,9 +84,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool swiglu = p.epilogue == RB_EPILOGUE_SWIGLU;
-    const uint32_t bn_out = swiglu ? BN / 2 : BN;
+    const uint32_t bn_out = swiglu ? BN / 2 : BN;      // output columns of a whole tile
     const uint32_t num_kb = (p.k + BK - 1) / BK;
-    const uint32_t num_tiles = p.tiles_m * p.tiles_n * p.batches;
+    const uint32_t num_tiles = p.items;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -84,6 +94,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         *abort_word = 0;
         fence_barrier_init();
         prefetch_tmap(&map_a); prefetch_tmap(&map_b); if (swiglu) prefetch_tmap(&map_b2);
+        if (p.items > p.split) { prefetch_tmap(&map_bh); if (swiglu) prefetch_tmap(&map_b2h); }
     }
     if (warp == 1) { tmem_alloc(tmem_slot, C::TMEM_COLS); tmem_relinquish(); }
     tc_fence_before();
@@ -97,19 +108,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             uint32_t stage = 0, phase = 0, armed = 0, armed_parity = 0;
             bool ok = true;
             for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
-                uint32_t batch, tm, tn; tile_coords(t, p, batch, tm, tn);
+                uint32_t batch, tm, tn, half; tile_coords(t, p, batch, tm, tn, half);
+                const bool whole = half == 2;
+                // B rows of this item: a whole tile takes bn_out rows of each weight, a half tile half as many, starting
+                // in the middle of the tile's range for the second half.
+                const uint32_t b_rows = whole ? bn_out : bn_out / 2;
+                const int32_t b_row0 = (int32_t)(tn * bn_out + (whole ? 0 : half * b_rows));
+                const uint32_t b_bytes = b_rows * BK * 2;
+                const CUtensorMap* mb = whole ? &map_b : &map_bh;
+                const CUtensorMap* mb2 = whole ? &map_b2 : &map_b2h;
                 for (uint32_t kb = 0; kb < num_kb; ++kb) {
                     if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_word))) break;
                     uint8_t* sa = smem + stage * C::STAGE_BYTES; uint8_t* sb = sa + C::A_BYTES;
-                    mbar_expect_tx(&full_bar[stage], C::STAGE_BYTES);
+                    mbar_expect_tx(&full_bar[stage], C::A_BYTES + (swiglu ? 2 * b_bytes : b_bytes));
                     armed |= 1u << stage; armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
                     tma_load_3d(sa, &map_a, &full_bar[stage], (int32_t)(kb * BK), (int32_t)(tm * BM), (int32_t)batch);
-                    if (swiglu) {
-                        tma_load_3d(sb, &map_b, &full_bar[stage], (int32_t)(kb * BK), (int32_t)(tn * (BN / 2)), (int32_t)batch);
-                        tma_load_3d(sb + C::B_BYTES / 2, &map_b2, &full_bar[stage], (int32_t)(kb * BK), (int32_t)(tn * (BN / 2)), (int32_t)batch);
-                    } else {
-                        tma_load_3d(sb, &map_b, &full_bar[stage], (int32_t)(kb * BK), (int32_t)(tn * BN), (int32_t)batch);
-                    }
+                    tma_load_3d(sb, mb, &full_bar[stage], (int32_t)(kb * BK), b_row0, (int32_t)batch);
+                    if (swiglu) tma_load_3d(sb + b_bytes, mb2, &full_bar[stage], (int32_t)(kb * BK), b_row0, (int32_t)batch);
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -123,11 +138,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (elect_one()) {
-            const uint32_t idesc = make_idesc_bf16(BM, BN);
+            const uint32_t idesc_whole = make_idesc_bf16(BM, BN), idesc_half = make_idesc_bf16(BM, BN / 2);
             uint32_t stage = 0, phase = 0, iter = 0;
             bool ok = true;
             for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++iter) {
                 const uint32_t acc = iter & 1, acc_phase = (iter >> 1) & 1;
+                const uint32_t idesc = t < p.split ? idesc_whole : idesc_half;
                 if (!(ok = mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_word))) break;
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + acc * BN;
@@ -152,29 +168,31 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         bool ok = true;
         for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++iter) {
             const uint32_t acc = iter & 1, acc_phase = (iter >> 1) & 1;
-            uint32_t batch, tm, tn; tile_coords(t, p, batch, tm, tn);
+            uint32_t batch, tm, tn, half; tile_coords(t, p, batch, tm, tn, half);
+            const uint32_t width = half == 2 ? bn_out : bn_out / 2;                    // output columns of this item
+            const uint32_t col0 = tn * bn_out + (half == 2 ? 0 : half * width);
+            const uint32_t up_at = half == 2 ? BN / 2 : BN / 4;                         // TMEM column where the up half starts (SwiGLU)
             float* sbias = bias_smem + (quarter * 2 + acc) * 256;
             if (p.epilogue == RB_EPILOGUE_BIAS) {
                 // Each warp stages this tile's bias row for itself (warp-level sync only, so no CTA barrier can
                 // be left waiting if a bounded wait expires).
-                for (uint32_t j = lane; j < bn_out; j += 32) sbias[j] = tn * bn_out + j < p.n ? bias_at(p, tn * bn_out + j) : 0.f;
+                for (uint32_t j = lane; j < width; j += 32) sbias[j] = col0 + j < p.n ? bias_at(p, col0 + j) : 0.f;
                 __syncwarp();
             }
             ok = mbar_wait(&tmem_full[acc], acc_phase, abort_word);
             if (!(ok = __all_sync(0xffffffffu, ok))) break;  // keep the warp converged
             tc_fence_after();
             const uint32_t row = tm * BM + quarter * 32 + lane;
-            const uint32_t col0 = tn * bn_out;
             const uint32_t taddr = tmem_base + acc * BN + ((quarter * 32) << 16);
             const size_t out_off = ((size_t)batch * p.m + row) * p.n;
-            for (uint32_t c = 0; c < bn_out; c += 32) {
+            for (uint32_t c = 0; c < width; c += 32) {
                 if (col0 + c >= p.n) break;  // warp-uniform
                 uint32_t r[32];
                 tmem_ld_32x32(taddr + c, r);
                 float v[32];
                 if (swiglu) {
                     uint32_t u[32];
-                    tmem_ld_32x32(taddr + BN / 2 + c, u);
+                    tmem_ld_32x32(taddr + up_at + c, u);
                     tmem_wait_ld();
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
@@ -243,7 +261,8 @@ __global__ void __launch_bounds__(256) transpose_bf16_kernel(const uint16_t* in,
 struct GemmState { uint32_t* status = nullptr; bool attrs_set = false; };
 
 template <int BN>
-int32_t launch(rb_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2, GemmParams& p) {
+int32_t launch(rb_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2, const CUtensorMap& mbh,
+               const CUtensorMap& mb2h, GemmParams& p) {
     using C = Config<BN>;
     static bool configured = false;
     if (!configured) {
@@ -251,11 +270,16 @@ int32_t launch(rb_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const 
         if (e != cudaSuccess) return rb::fail(RB_STATUS, "cudaFuncSetAttribute(GEMM) failed with CUDA status %d (%s)", (int)e, cudaGetErrorString(e));
         configured = true;
     }
-    uint32_t tiles = p.tiles_m * p.tiles_n * p.batches;
     const uint32_t sms = ctx->sm_limit > 0 ? (uint32_t)ctx->sm_limit : (uint32_t)ctx->sm_count;
-    uint32_t grid = tiles < sms ? tiles : sms;
-    gemm_bf16_kernel<BN><<<grid, THREADS, C::SMEM_BYTES, ctx->stream>>>(ma, mb, mb2, p);
+    const uint32_t grid = p.items < sms ? p.items : sms;
+    gemm_bf16_kernel<BN><<<grid, THREADS, C::SMEM_BYTES, ctx->stream>>>(ma, mb, mb2, mbh, mb2h, p);
     return rb::after_launch(ctx, "gemm");
+}
+
+// Decides whether the last round of the persistent loop runs as half-width tiles (see the note at the top of the file).
+void plan_tail(rb_ctx* ctx, GemmParams& p, uint32_t bn_out) {
+    const uint32_t sms = ctx->sm_limit > 0 ? (uint32_t)ctx->sm_limit : (uint32_t)ctx->sm_count;
+    rb_gemm_plan(p.tiles_m * p.tiles_n * p.batches, sms, (bn_out / 2) % 32 == 0, p.split, p.items);
 }
 
 bool make_operand_map(CUtensorMap* map, const void* base, uint64_t batches, uint64_t rows, uint64_t k, uint32_t box_rows) {
@@ -313,13 +337,15 @@ int32_t gemm_kmajor(rb_ctx* ctx, const void* a, const void* b, const void* b_up,
     if (swiglu && n <= 64) bn = 128;
     const uint32_t bn_out = swiglu ? bn / 2 : bn;
     p.tiles_m = (m + BM - 1) / BM; p.tiles_n = (n + bn_out - 1) / bn_out;
-    CUtensorMap ma, mb, mb2;
+    plan_tail(ctx, p, bn_out);
+    CUtensorMap ma, mb, mb2, mbh, mb2h;
     if (!make_operand_map(&ma, a, batches, m, k, BM) || !make_operand_map(&mb, b, batches, n, k, bn_out) ||
-        !make_operand_map(&mb2, swiglu ? b_up : b, batches, n, k, bn_out))
+        !make_operand_map(&mb2, swiglu ? b_up : b, batches, n, k, bn_out) || !make_operand_map(&mbh, b, batches, n, k, bn_out / 2) ||
+        !make_operand_map(&mb2h, swiglu ? b_up : b, batches, n, k, bn_out / 2))
         return fail(RB_STATUS, "cuTensorMapEncodeTiled failed for a GEMM operand (m=%u n=%u k=%u)", m, n, k);
-    if (bn == 256) return launch<256>(ctx, ma, mb, mb2, p);
-    if (bn == 128) return launch<128>(ctx, ma, mb, mb2, p);
-    return launch<64>(ctx, ma, mb, mb2, p);
+    if (bn == 256) return launch<256>(ctx, ma, mb, mb2, mbh, mb2h, p);
+    if (bn == 128) return launch<128>(ctx, ma, mb, mb2, mbh, mb2h, p);
+    return launch<64>(ctx, ma, mb, mb2, mbh, mb2h, p);
 }
 
 }  // namespace rb
@@ -470,10 +496,11 @@ extern "C" int32_t rb_gemm_no_alloc(rb_ctx* ctx, const rb_tensor* a, const rb_te
     p.out_f32 = out->dtype == RB_F32; p.out = po; p.status = status;
     const int bn = n > 128 ? 256 : (n > 64 ? 128 : 64);
     p.tiles_m = (p.m + BM - 1) / BM; p.tiles_n = (p.n + bn - 1) / bn;
-    CUtensorMap ma, mb;
-    if (!make_operand_map(&ma, ka, ba, m, k, BM) || !make_operand_map(&mb, kbp, ba, n, k, (uint32_t)bn))
+    plan_tail(ctx, p, (uint32_t)bn);
+    CUtensorMap ma, mb, mbh;
+    if (!make_operand_map(&ma, ka, ba, m, k, BM) || !make_operand_map(&mb, kbp, ba, n, k, (uint32_t)bn) || !make_operand_map(&mbh, kbp, ba, n, k, (uint32_t)bn / 2))
         return fail(RB_STATUS, "cuTensorMapEncodeTiled failed for a GEMM operand");
-    int32_t launched = bn == 256 ? launch<256>(ctx, ma, mb, mb, p) : (bn == 128 ? launch<128>(ctx, ma, mb, mb, p) : launch<64>(ctx, ma, mb, mb, p));
+    int32_t launched = bn == 256 ? launch<256>(ctx, ma, mb, mb, mbh, mbh, p) : (bn == 128 ? launch<128>(ctx, ma, mb, mb, mbh, mbh, p) : launch<64>(ctx, ma, mb, mb, mbh, mbh, p));
     RB_TRY(launched);
     // Report an expired wait without any state outside the array: drain the stream and read the status word.
     ctx->stats.synchronizations++;

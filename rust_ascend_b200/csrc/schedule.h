@@ -22,6 +22,24 @@ RB_HD void rb_tile_coords(uint32_t t, uint32_t tiles_m, uint32_t tiles_n, uint32
     tm = first_m + r % rows; tn = r / rows;
 }
 
+// Tail wave of the persistent GEMM.  `tiles` whole tiles are walked by `ctas` persistent CTAs in rounds; when the last
+// round would hold r tiles with 0 < 2r <= ctas, those r tiles become 2r half-width work items so that the last round takes
+// about half a tile's time.  Items [0, split) are whole tiles (item == tile), item split + i is half (i & 1) of tile
+// split + i / 2.  `allow_halves` is false where half a tile would not be a whole number of 32-column epilogue chunks.
+RB_HD void rb_gemm_plan(uint32_t tiles, uint32_t ctas, bool allow_halves, uint32_t& split, uint32_t& items) {
+    split = tiles; items = tiles;
+    if (!allow_halves || ctas == 0 || tiles == 0) return;
+    const uint32_t r = tiles % ctas;
+    if (r == 0 || 2 * r > ctas) return;
+    split = tiles - r; items = split + 2 * r;
+}
+// `half` = 2 for a whole tile, else which half (0: left columns, 1: right columns).
+RB_HD void rb_gemm_item(uint32_t item, uint32_t split, uint32_t& tile, uint32_t& half) {
+    if (item < split) { tile = item; half = 2; return; }
+    const uint32_t i = item - split;
+    tile = split + (i >> 1); half = i & 1u;
+}
+
 // Key blocks of `block` keys that query rows [row0, row_end) of an M-row, N-key problem must visit.  Under the causal
 // rule of mask_programs.rs:30-37 key k is hidden from query q iff k > q + delta (delta = query_start - key_start), so
 // the last visible key of the tile is (min(row_end, M) - 1) + delta.
@@ -33,6 +51,15 @@ RB_HD uint32_t rb_attention_blocks(uint32_t M, uint32_t N, int causal, int64_t d
     if (last_q < 0) return 0;
     const int64_t need = last_q / block + 1;
     return need < (int64_t)all ? (uint32_t)need : all;
+}
+
+// Work items of the persistent attention kernel: one item = one block of query rows of one (batch, head).  Items are numbered
+// so that the query blocks with the most visible keys (the last ones under a causal mask) come first and the heads of one
+// batch entry, and therefore of one KV group, are neighbours; CTA c of a grid of G takes items c, c + G, c + 2G, ...
+RB_HD void rb_attention_item(uint32_t item, uint32_t q_blocks, uint32_t heads_total, uint32_t heads, uint32_t& qb, uint32_t& h, uint32_t& b) {
+    qb = q_blocks - 1 - item / heads_total;
+    const uint32_t r = item % heads_total;
+    h = r % heads; b = r / heads;
 }
 
 // Scatter GEMM (row-parallel projection whose output rows belong to `world` owners of rows_per_owner rows each).

@@ -36,6 +36,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
                  : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
 // Every wait is bounded: after `WAIT_LIMIT` polls the waiter raises the CTA's abort word and returns
 // false; every role polls that word and leaves its loop, so a lost signal ends the kernel with an error
 // status instead of hanging the GPU.
@@ -44,6 +50,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 255u) == 255u && *abort_word) return false;
+    }
+    *abort_word = 1u;
+    return false;
+}
+
+// The same bound for a waiter that polls without suspending (test_wait): it sees the phase flip a few cycles after the
+// arrival instead of after the hardware's wake-up time, at the price of issue slots; used only on hand-offs that sit on a
+// kernel's critical path.
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_word) {
+    for (uint32_t i = 0; i < (WAIT_LIMIT << 2); ++i) {
+        if (mbar_test_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_word) return false;
     }
     *abort_word = 1u;
     return false;
@@ -100,6 +118,14 @@ __device__ __forceinline__ uint64_t make_mnmajor_sw128_desc(uint32_t smem_addr, 
     d |= (uint64_t)2 << 61;
     return d;
 }
+// The two 32-bit halves of those descriptors.  The upper half is the same for every 128-byte-swizzled tile whose 8-row
+// groups are 1024 B apart; the lower half is the start address (16-byte units) plus the leading byte offset, so stepping
+// through a tile is one 32-bit add on the lower half.
+constexpr uint32_t DESC_HI_SW128 = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo_kmajor(uint32_t smem_addr) { return ((smem_addr & 0x3ffffu) >> 4) | (1u << 16); }
+__device__ __forceinline__ uint32_t desc_lo_mnmajor(uint32_t smem_addr, uint32_t slab_bytes) {
+    return ((smem_addr & 0x3ffffu) >> 4) | (((slab_bytes >> 4) & 0x3fffu) << 16);
+}
 // Instruction descriptor of tcgen05.mma.kind::f16: D=F32 (bits 4-5 = 1), A=B=BF16 (bits 7-9, 10-12 = 1),
 // major bits 15/16 (0 = K-major), N>>3 at bits 17-22, M>>4 at bits 24-28.
 __host__ __device__ constexpr uint32_t make_idesc_bf16(uint32_t m, uint32_t n, uint32_t a_mn_major = 0, uint32_t b_mn_major = 0) {
@@ -118,6 +144,18 @@ __device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, u
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
                  ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// The same two instructions with descriptors given as (lower half, shared upper half); `accumulate` is usually a
+// compile-time constant at the call site, which leaves three instructions per MMA for the issuing thread.
+__device__ __forceinline__ void umma_bf16_ss_lo(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+                 ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(DESC_HI_SW128), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_ts_lo(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b64 db, {%2, %3};\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+                 ::"r"(tmem_d), "r"(tmem_a), "r"(b_lo), "r"(DESC_HI_SW128), "r"(idesc), "r"(accumulate) : "memory");
 }
 // The mbarrier receives one arrival when every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {

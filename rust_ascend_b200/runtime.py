@@ -9,6 +9,7 @@ computes on the host.
 from __future__ import annotations
 
 import ctypes as C
+import weakref
 import enum
 from dataclasses import dataclass, field
 
@@ -97,14 +98,31 @@ def _contiguous_strides(shape) -> tuple:
     return tuple(reversed(strides))
 
 
+class _Owner:
+    """Stands for one device allocation.  Tensors made by `ComputeClient.tensor` / `upload` and every view derived from them
+    share one owner; when the last of them is dropped the storage is released, as ComputeStorage::dealloc does when the
+    reference drops a handle (runtime/mod.rs:501-515).  Storages taken with `ComputeClient.empty` have no owner and are
+    released with `free` only."""
+    __slots__ = ("__weakref__",)
+
+
+def _release(lib, ctx_value: int, handle: int) -> None:
+    rt = B200Runtime
+    if rt._ctx is None or rt._ctx.value != ctx_value:
+        return                                   # the context this storage belonged to is gone, and its memory with it
+    lib.rb_free(rt._ctx, C.c_uint64(handle))     # an explicit free may have come first: the status is not an error here
+
+
 @dataclass
 class TensorBuffer:
-    """TensorBuffer{handle, shape, strides, dtype} (ruda_runtime); strides in elements."""
+    """TensorBuffer{handle, shape, strides, dtype} (ruda_runtime); strides in elements.  A tensor built by hand over another
+    tensor's handle is a non-owning view: pass `_owner=base._owner` (as `reshape` does) or keep the base alive while it is used."""
     handle: int
     shape: tuple
     dtype: DType
     strides: tuple = field(default=None)
     offset: int = 0
+    _owner: object = field(default=None, repr=False, compare=False)
 
     def __post_init__(self):
         self.shape = tuple(int(d) for d in self.shape)
@@ -130,7 +148,7 @@ class TensorBuffer:
             n *= d
         if n != self.elements:
             raise InvalidTensor("reshape must keep the element count")
-        return TensorBuffer(self.handle, shape, self.dtype, None, self.offset)
+        return TensorBuffer(self.handle, shape, self.dtype, None, self.offset, self._owner)
 
     def _c(self) -> rb_tensor:
         if not 1 <= len(self.shape) <= 8:
@@ -213,14 +231,19 @@ class ComputeClient:
                      np.dtype(np.int32): DType.I32, np.dtype(np.int64): DType.I64, np.dtype(np.uint8): DType.U8}[arr.dtype]
         if arr.dtype != np.dtype(DType(dtype).numpy):
             raise InvalidTensor(f"host array dtype {arr.dtype} does not carry {DType(dtype).name}")
-        return TensorBuffer(self.create_from_slice(arr), arr.shape if arr.ndim else (1,), dtype)
+        return self._owned(self.create_from_slice(arr), arr.shape if arr.ndim else (1,), dtype)
 
     def tensor(self, shape, dtype: DType) -> TensorBuffer:
         shape = tuple(int(d) for d in shape)
         n = 1
         for d in shape:
             n *= d
-        return TensorBuffer(self.empty(n * DType(dtype).size), shape, dtype)
+        return self._owned(self.empty(n * DType(dtype).size), shape, dtype)
+
+    def _owned(self, handle: int, shape, dtype) -> TensorBuffer:
+        owner = _Owner()
+        weakref.finalize(owner, _release, self._lib, self._ctx.value, handle).atexit = False
+        return TensorBuffer(handle, shape, dtype, None, 0, owner)
 
     def pinned(self, shape, dtype) -> np.ndarray:
         """Page-locked host array for asynchronous rb_write / rb_read."""
@@ -548,6 +571,18 @@ class B200Runtime:
         return out
 
     @staticmethod
+    def linear_host(client, host_x: np.ndarray, x: TensorBuffer, w: TensorBuffer, y: TensorBuffer, host_y: np.ndarray,
+                    bias: TensorBuffer | None = None, row_chunks: int = 8) -> None:
+        """rb_linear_host: host_y = host_x . w^T (+ bias) with upload, GEMM and read-back of row chunks overlapped on three
+        streams (the reference's write -> launch -> read, runtime/mod.rs:767-845, as one pipelined call).  `host_x` / `host_y`
+        are host arrays (pinned ones from `client.pinned` for full speed) holding BF16 bit patterns (and FP32 for an FP32 `y`);
+        `x` and `y` are device staging tensors of the same shapes.  Returns when `host_y` is complete."""
+        if host_x.nbytes != x.nbytes or host_y.nbytes != y.nbytes or not host_x.flags.c_contiguous or not host_y.flags.c_contiguous:
+            raise InvalidTensor("host buffers must be contiguous and as large as their staging tensors")
+        _check(client._lib.rb_linear_host(client._ctx, C.c_void_p(host_x.ctypes.data), _ref(x), _ref(w), _ref(bias), _ref(y),
+                                          C.c_void_p(host_y.ctypes.data), C.c_uint32(row_chunks)))
+
+    @staticmethod
     def gemm_no_alloc(client, a: TensorBuffer, b: TensorBuffer, ta: Transpose, tb: Transpose, out: TensorBuffer) -> None:
         """rb_gemm_no_alloc: GEMM into `out` that takes its scratch from a fixed array inside the library instead of
         cudaMalloc, for hosts that may not allocate device memory while running.  Operands stored against the K-major
@@ -645,7 +680,7 @@ class B200Runtime:
         same_batches = tuple(a.shape[:-2]) == tuple(b.shape[:-2]) and no <= 4096
 
         def slab(t, index, rows, cols):
-            return TensorBuffer(t.handle, (rows, cols), t.dtype, None, offset=t.offset + index * rows * cols * t.dtype.size)
+            return TensorBuffer(t.handle, (rows, cols), t.dtype, None, offset=t.offset + index * rows * cols * t.dtype.size, _owner=t._owner)
 
         def products(out_t, first):
             """out_t (+)= sum over the part pairs, for one batched launch set or one batch entry."""
@@ -714,9 +749,9 @@ class B200Runtime:
         for group, end in enumerate(ends):
             rows = end - start
             if rows:
-                a_g = TensorBuffer(a.handle, (rows, k), DType.BF16, None, offset=a.offset + start * k * 2)
-                w_g = TensorBuffer(weights.handle, (n, k), DType.BF16, None, offset=weights.offset + group * n * k * 2)
-                o_g = TensorBuffer(out.handle, (rows, n), dtype, None, offset=start * n * size)
+                a_g = TensorBuffer(a.handle, (rows, k), DType.BF16, None, offset=a.offset + start * k * 2, _owner=a._owner)
+                w_g = TensorBuffer(weights.handle, (n, k), DType.BF16, None, offset=weights.offset + group * n * k * 2, _owner=weights._owner)
+                o_g = TensorBuffer(out.handle, (rows, n), dtype, None, offset=start * n * size, _owner=out._owner)
                 B200Runtime.gemm_into(client, a_g, w_g, Transpose.No, Transpose.Yes, o_g)
             start = end
         return out

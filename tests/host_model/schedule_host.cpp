@@ -12,6 +12,8 @@ uint32_t host_scatter_shift(uint32_t rank, uint32_t world, uint32_t rows_per_own
 }
 void host_scatter_owner(uint32_t row, uint32_t rows_per_owner, uint32_t* out2) { rb_scatter_owner(row, rows_per_owner, out2[0], out2[1]); }
 void host_scatter_word(uint32_t it, uint32_t lane, uint32_t* out2) { rb_scatter_word(it, lane, out2[0], out2[1]); }
+void host_gemm_plan(uint32_t tiles, uint32_t ctas, int allow_halves, uint32_t* out2) { rb_gemm_plan(tiles, ctas, allow_halves != 0, out2[0], out2[1]); }
+void host_gemm_item(uint32_t item, uint32_t split, uint32_t* out2) { rb_gemm_item(item, split, out2[0], out2[1]); }
 uint32_t host_attention_blocks(uint32_t M, uint32_t N, int causal, int64_t delta, uint32_t row0, uint32_t row_end, uint32_t block) {
     return rb_attention_blocks(M, N, causal, delta, row0, row_end, block);
 }

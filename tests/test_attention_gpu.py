@@ -125,7 +125,7 @@ def test_strided_bshd_inputs(client, oracle):
         phys = np.ascontiguousarray(x.transpose(0, 2, 1, 3))  # [B,S,H,D]
         t = up16(client, phys)
         bb, ss, hh, dd = phys.shape
-        return TensorBuffer(t.handle, (bb, hh, ss, dd), DType.BF16, (ss * hh * dd, dd, hh * dd, 1))
+        return TensorBuffer(t.handle, (bb, hh, ss, dd), DType.BF16, (ss * hh * dd, dd, hh * dd, 1), _owner=t._owner)   # the view keeps the storage alive
     out = RT.attention(client, strided(q), strided(k), strided(v), SCALE, causal=True, bmhd_output=True)
     got = bf16_bits_to_f32(client.read(out)).transpose(0, 2, 1, 3)
     check_bf16(got, oracle.attention(q, k, v, SCALE, causal=True))

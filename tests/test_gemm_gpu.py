@@ -203,3 +203,45 @@ def test_config2b_full_size_swiglu_against_oracle_rows(client, oracle):
     bf16_tolerance(got[rows], oracle.linear(x[rows], wg, w_up=wu))
     assert np.all(np.isfinite(got))
     client.free(out.handle)
+
+
+@pytest.mark.parametrize("m,n,k,mode", [(19200, 256, 64, "bias"), (19200, 272, 80, "none"), (19200, 128, 64, "swiglu"), (9600, 400, 48, "swiglu"),
+                                        (128, 256, 128, "bias"), (2048, 4096 + 512, 64, "none")])
+def test_tail_round_of_half_tiles(client, oracle, m, n, k, mode):
+    """Shapes whose last round of the persistent loop is cut into half-width tiles (150 or 300 tiles on 148 SMs, a single tile, and
+    a grid with a ragged last column of tiles), with every epilogue: all rows against the oracle."""
+    rng = np.random.default_rng(m + n + k)
+    x = _normal_bf16(rng.integers(1 << 30), (m, k))
+    w = _normal_bf16(rng.integers(1 << 30), (n, k), 0.1)
+    if mode == "swiglu":
+        wu = _normal_bf16(rng.integers(1 << 30), (n, k), 0.1)
+        got = read(client, RT.gemm(client, up16(client, x), up16(client, w), Transpose.No, Transpose.Yes, DType.F32, b_up=up16(client, wu)))
+        want = oracle.linear(x, w, w_up=wu)
+    elif mode == "bias":
+        bias = rng.standard_normal(n).astype(np.float32)
+        got = read(client, RT.gemm(client, up16(client, x), up16(client, w), Transpose.No, Transpose.Yes, DType.F32, bias=client.upload(bias)))
+        want = oracle.linear(x, w, bias=bias)
+    else:
+        got = read(client, RT.gemm(client, up16(client, x), up16(client, w), Transpose.No, Transpose.Yes, DType.F32))
+        want = oracle.linear(x, w)
+    assert np.abs(got - want).max() <= 2e-4 * max(1.0, np.abs(want).max())
+
+
+@pytest.mark.parametrize("m,n,k,chunks,out", [(2048, 768, 512, 8, DType.BF16), (400, 272, 144, 3, DType.F32), (128, 128, 64, 8, DType.BF16)])
+def test_linear_on_host_buffers_matches_write_gemm_read(client, oracle, m, n, k, chunks, out):
+    """The pipelined host-buffer call gives the bits of rb_write + rb_gemm + rb_read, and meets the oracle."""
+    rng = np.random.default_rng(m + chunks)
+    x = f32_to_bf16_bits(rng.standard_normal((m, k), dtype=np.float32)); w = f32_to_bf16_bits(rng.standard_normal((n, k), dtype=np.float32) * 0.05)
+    bias = rng.standard_normal(n).astype(np.float32)
+    hx = client.pinned((m, k), np.uint16); hx[...] = x
+    hy = client.pinned((m, n), np.uint16 if out == DType.BF16 else np.float32); hy[...] = 0
+    tx, tw, tb, ty = client.tensor((m, k), DType.BF16), client.upload(w), client.upload(bias), client.tensor((m, n), out)
+    RT.linear_host(client, hx, tx, tw, ty, hy, bias=tb, row_chunks=chunks)
+    want = client.read(RT.gemm(client, client.upload(x), tw, Transpose.No, Transpose.Yes, out, bias=tb))
+    np.testing.assert_array_equal(np.array(hy), want)
+    got = bf16_bits_to_f32(np.array(hy)) if out == DType.BF16 else np.array(hy)
+    ref = oracle.linear(bf16_bits_to_f32(x), bf16_bits_to_f32(w), bias=bias)
+    if out == DType.BF16:
+        bf16_tolerance(got, ref)
+    else:
+        assert np.abs(got - ref).max() <= 1e-4 * max(1.0, np.abs(ref).max())

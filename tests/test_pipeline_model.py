@@ -55,6 +55,32 @@ def test_tile_raster_keeps_a_wave_inside_few_rows(host):
     assert len(rows) <= 16 and len(cols) == 16
 
 
+@pytest.mark.parametrize("tiles,ctas", [(512, 148), (68, 148), (1, 148), (74, 148), (75, 148), (148, 148), (444, 148), (2752, 148), (512, 132), (3, 4), (0, 148)])
+def test_gemm_tail_plan_covers_every_tile_once(host, tiles, ctas):
+    """The last round of the persistent GEMM becomes half-width tiles when it would fill at most half of the CTAs: every tile is
+    then covered either whole or by exactly its two halves, the halves come last, and the number of rounds does not grow."""
+    out = (C.c_uint32 * 2)()
+    host.host_gemm_plan(tiles, ctas, 1, out)
+    split, items = out[0], out[1]
+    r = tiles % ctas if ctas else 0
+    if 0 < 2 * r <= ctas:
+        assert (split, items) == (tiles - r, tiles + r)
+    else:
+        assert (split, items) == (tiles, tiles)
+    cover = {}
+    for item in range(items):
+        host.host_gemm_item(item, split, out)
+        tile, half = out[0], out[1]
+        assert tile < tiles and (half == 2) == (item < split)
+        cover.setdefault(tile, []).append(half)
+    assert sorted(cover) == list(range(tiles))
+    assert all(v == [2] or v == [0, 1] for v in cover.values())
+    if ctas:
+        assert -(-items // ctas) == -(-tiles // ctas)          # same number of rounds; the last one is the cheap one
+    host.host_gemm_plan(tiles, ctas, 0, out)
+    assert (out[0], out[1]) == (tiles, tiles)                  # shapes whose half tiles would be too narrow keep whole tiles
+
+
 @pytest.mark.parametrize("M,N,delta", [(128, 128, 0), (256, 384, 128), (400, 416, 16), (48, 96, 48), (2048, 2048, 0), (128, 1024, 896), (64, 64, -100), (272, 2048, 1776)])
 def test_attention_block_count_matches_the_causal_rule(host, M, N, delta):
     for row0 in range(0, M + 256, 128):
@@ -163,75 +189,123 @@ def test_gemm_ring_and_accumulator_handshake(stages, tiles, kblocks, seed):
     assert all(b.idle() for b in full + empty + tmem_full + tmem_empty) and all(s is None for s in smem)
 
 
-@pytest.mark.parametrize("n0,n1,seed", [(3, 4, 0), (8, 8, 1), (1, 2, 2), (5, 0, 3), (0, 0, 4), (16, 17, 5)])
-def test_attention_barrier_protocol(n0, n1, seed):
-    """Two query tiles, K/V rings of two stages, S/P aliased in TMEM (P overwrites the scores it was computed from)."""
+@pytest.mark.parametrize("items,seed", [([(3, 4)], 0), ([(8, 8), (1, 2), (5, 0)], 1), ([(0, 0), (2, 2), (0, 0), (1, 1)], 2), ([(1, 1)] * 5, 3),
+                                        ([(16, 17), (0, 3), (4, 4), (1, 0)], 4), ([(2, 3), (2, 3), (7, 8), (1, 2), (6, 6)], 5)])
+def test_attention_barrier_protocol(items, seed):
+    """The persistent attention kernel's protocol over a CTA's list of work items (each: key blocks of tile 0 and of tile 1):
+    one Q buffer handed back after the item's last score GEMM, K/V rings of two stages that run on across items, S/P aliased
+    in TMEM (P overwrites the scores it was computed from) and handed over in two halves, O read out by the softmax warps at
+    the end of an item and handed back before the next item's first P V overwrites it."""
     KV = 2
-    n = [n0, n1]; n_max = max(n)
+    q_full, q_empty = Barrier(1), Barrier(1)
     k_full = [Barrier(1) for _ in range(KV)]; k_empty = [Barrier(1) for _ in range(KV)]
     v_full = [Barrier(1) for _ in range(KV)]; v_empty = [Barrier(1) for _ in range(KV)]
-    s_full = [Barrier(1), Barrier(1)]; p_full = [Barrier(128), Barrier(128)]; o_full = [Barrier(1), Barrier(1)]
+    s_full = [Barrier(1), Barrier(1)]; p_half = [Barrier(128), Barrier(128)]; p_full = [Barrier(128), Barrier(128)]
+    o_full = [Barrier(1), Barrier(1)]; o_free = [Barrier(128), Barrier(128)]
+    qsm = [None]                     # item whose Q the shared-memory buffer holds
     ksm, vsm = [None] * KV, [None] * KV
-    s_tmem = [None, None]            # ("S", j) after the score GEMM, ("P", j) after the softmax
-    o_acc = [[], []]
-    done = [False, False]
+    s_tmem = [None, None]            # ("S", item, j) after the score GEMM, ("P", item, j) after the softmax
+    p_state = [0, 0]                 # halves of P the softmax threads have completed for the current block
+    o_tmem = [None, None]            # (item, [blocks accumulated]) or None once read out
+    stored = [[], []]
 
     def producer():
-        for j in range(n_max):
-            st, ph = j % KV, (j // KV) & 1
-            yield from wait(k_empty[st], ph ^ 1)
-            assert ksm[st] is None; ksm[st] = j; k_full[st].arrive(); yield True
-            yield from wait(v_empty[st], ph ^ 1)
-            assert vsm[st] is None; vsm[st] = j; v_full[st].arrive(); yield True
-
-    def issue_s(t, j):
-        assert ksm[j % KV] == j, "score GEMM read a K stage that holds another block"
-        assert s_tmem[t] is None or s_tmem[t] == ("consumed", j - 1), "scores overwritten while P was still needed"
-        s_tmem[t] = ("S", j); s_full[t].arrive()
+        kv_it = q_it = 0
+        for i, n in enumerate(items):
+            n_max = max(n)
+            if n_max == 0: continue
+            if q_it > 0:
+                yield from wait(q_empty, (q_it - 1) & 1)
+            assert qsm[0] is None, "Q overwritten while score GEMMs of the previous item could still read it"
+            qsm[0] = i; q_full.arrive(); yield True
+            for j in range(n_max):
+                st, ph = (kv_it + j) % KV, ((kv_it + j) // KV) & 1
+                yield from wait(k_empty[st], ph ^ 1)
+                assert ksm[st] is None; ksm[st] = (i, j); k_full[st].arrive(); yield True
+                yield from wait(v_empty[st], ph ^ 1)
+                assert vsm[st] is None; vsm[st] = (i, j); v_full[st].arrive(); yield True
+            kv_it += n_max; q_it += 1
 
     def mma():
-        if n_max > 0:
-            yield from wait(k_full[0], 0)
+        kv_it = q_it = 0
+        blk, used = [0, 0], [0, 0]
+        for i, n in enumerate(items):
+            n_max = max(n)
+            if n_max == 0: continue
+            total_s, s_done = n[0] + n[1], 0
+
+            def issue_s(t, j, st):
+                assert qsm[0] == i and ksm[st] == (i, j), "score GEMM read a Q or K buffer that holds something else"
+                assert s_tmem[t] is None or s_tmem[t][0] == "consumed", "scores overwritten while P was still needed"
+                s_tmem[t] = ("S", i, j); p_state[t] = 0; s_full[t].arrive()
+
+            yield from wait(q_full, q_it & 1)
+            st, ph = kv_it % KV, (kv_it // KV) & 1
+            yield from wait(k_full[st], ph)
             for t in range(2):
-                if n[t] > 0: issue_s(t, 0)
-            ksm[0] = None; k_empty[0].arrive(); yield True
-        for j in range(n_max):
-            st, ph = j % KV, (j // KV) & 1
-            for t in range(2):
-                if j >= n[t]: continue
-                yield from wait(p_full[t], j & 1)
-                yield from wait(v_full[st], ph)
-                assert s_tmem[t] == ("P", j) and vsm[st] == j
-                o_acc[t].append(j); s_tmem[t] = ("consumed", j)
-                if t == 1 or j >= n[1]:
-                    vsm[st] = None; v_empty[st].arrive()
-                yield True
-                if j + 1 < n[t]:
-                    st1, ph1 = (j + 1) % KV, ((j + 1) // KV) & 1
-                    yield from wait(k_full[st1], ph1)
-                    issue_s(t, j + 1)
-                    if t == 1 or j + 1 >= n[1]:
-                        ksm[st1] = None; k_empty[st1].arrive()
+                if n[t] > 0: issue_s(t, 0, st); s_done += 1
+            ksm[st] = None; k_empty[st].arrive()
+            if s_done == total_s: qsm[0] = None; q_empty.arrive()
+            yield True
+            for j in range(n_max):
+                st, ph = (kv_it + j) % KV, ((kv_it + j) // KV) & 1
+                for t in range(2):
+                    if j >= n[t]: continue
+                    par = blk[t] & 1
+                    yield from wait(p_half[t], par)
+                    if j == 0 and used[t] > 0:
+                        yield from wait(o_free[t], (used[t] - 1) & 1)
+                    yield from wait(v_full[st], ph)
+                    assert p_state[t] >= 1 and vsm[st] == (i, j)
+                    if j == 0:
+                        assert o_tmem[t] is None, "O overwritten before the previous item's rows were read out"
+                        o_tmem[t] = (i, [])
                     yield True
-                else:
-                    o_full[t].arrive(); yield True
+                    yield from wait(p_full[t], par)
+                    assert s_tmem[t] == ("P", i, j) and p_state[t] == 2
+                    o_tmem[t][1].append(j); s_tmem[t] = ("consumed", i, j)
+                    blk[t] += 1
+                    if t == 1 or j >= n[1]:
+                        vsm[st] = None; v_empty[st].arrive()
+                    yield True
+                    if j + 1 < n[t]:
+                        st1, ph1 = (kv_it + j + 1) % KV, ((kv_it + j + 1) // KV) & 1
+                        yield from wait(k_full[st1], ph1)
+                        issue_s(t, j + 1, st1); s_done += 1
+                        if t == 1 or j + 1 >= n[1]:
+                            ksm[st1] = None; k_empty[st1].arrive()
+                        if s_done == total_s: qsm[0] = None; q_empty.arrive()
+                        yield True
+                    else:
+                        o_full[t].arrive(); used[t] += 1; yield True
+            kv_it += n_max; q_it += 1
 
     def softmax_thread(t, tid):
-        for j in range(n[t]):
-            yield from wait(s_full[t], j & 1)
-            assert s_tmem[t] in (("S", j), ("P", j))      # ("P", j): another thread of the tile already finished this block
+        blk = used = 0
+        for i, n in enumerate(items):
+            if n[t] == 0: continue
+            for j in range(n[t]):
+                yield from wait(s_full[t], blk & 1)
+                assert s_tmem[t][1:] == (i, j) and s_tmem[t][0] in ("S", "P")
+                yield True
+                p_half[t].arrive()
+                if p_half[t].idle(): p_state[t] = 1
+                yield True
+                p_full[t].arrive()
+                if p_full[t].idle(): p_state[t] = 2; s_tmem[t] = ("P", i, j)
+                yield True
+                blk += 1
+            yield from wait(o_full[t], used & 1)
+            assert o_tmem[t] == (i, list(range(n[t]))), "epilogue read an accumulator that is not this item's finished O"
+            if tid == 0: stored[t].append(i)
             yield True
-            p_full[t].arrive()
-            if p_full[t].idle():
-                s_tmem[t] = ("P", j)
+            o_free[t].arrive()
+            if o_free[t].idle(): o_tmem[t] = None
             yield True
-        if n[t] > 0:
-            yield from wait(o_full[t], 0)
-            assert o_acc[t] == list(range(n[t]))
-        if tid == 0:
-            done[t] = True
+            used += 1
 
-    run([producer(), mma()] + [softmax_thread(t, i) for t in range(2) for i in range(128)], seed)
-    assert done == [True, True] and o_acc == [list(range(n0)), list(range(n1))]
-    assert all(b.idle() for b in k_full + k_empty + v_full + v_empty + s_full + p_full + o_full)
+    run([producer(), mma()] + [softmax_thread(t, i) for t in range(2) for i in range(128)], seed, limit=2000000)
+    for t in range(2):
+        assert stored[t] == [i for i, n in enumerate(items) if n[t] > 0]
+    assert all(b.idle() for b in [q_full] + k_full + k_empty + v_full + v_empty + s_full + p_half + p_full + o_full)
     assert all(x is None for x in ksm + vsm)

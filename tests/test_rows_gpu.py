@@ -211,11 +211,13 @@ def test_validation_errors_are_invalid_tensor_not_fallback(client):
 def test_counters_and_storage(client):
     before = client.stats()
     x = client.upload(np.arange(64, dtype=np.float32).reshape(2, 32))
-    RT.softmax(client, x); RT.softmax(client, client.upload(np.zeros((0, 32), np.float32)))
+    y = RT.softmax(client, x); empty = client.upload(np.zeros((0, 32), np.float32)); y_empty = RT.softmax(client, empty)
     client.sync()
     after = client.stats()
     assert after["launches"] == before["launches"] + 1 and after["empty_calls"] == before["empty_calls"] + 1
-    assert after["allocations"] >= before["allocations"] + 3
+    assert after["allocations"] >= before["allocations"] + 3      # x, y, empty (a zero-byte tensor still owns storage), y_empty
+    del y, y_empty, empty
+    assert client.stats()["allocations"] == before["allocations"] + 1   # dropping a tensor releases its storage; x is still held
     assert client.read_one(x.handle) == np.arange(64, dtype=np.float32).tobytes()
     client.free(x.handle)
     from rust_ascend_b200.runtime import NullHandle

@@ -310,3 +310,28 @@ def test_padded_attention_logical_keys_only(client):
     close(nn.scaled_dot_product_attention_padded_bf16_fp32(q, k, v, 0.25).into_data(), [[[2.0]]], 2e-3, 3e-3)   # three equal BF16 probabilities
     masked = nn.scaled_dot_product_attention_padded_bf16_fp32(q, k, v, 0.25, t(np.full((1, 1, 3), -np.inf)))
     assert np.isnan(masked.into_data()).all()                       # every key excluded: no value, as in the reference
+
+
+def test_composed_operators_reach_a_steady_state_of_device_memory(client):
+    """A training loop drops its intermediate tensors every step, as the reference's handles release their storage on drop
+    (runtime/mod.rs:501-515).  Fifty calls of the dtype-preserving matmul and of the padded attention must leave the bytes in use
+    where they were after the first call."""
+    import gc
+    import rust_ascend_b200.nn as nn
+    from rust_ascend_b200 import B200Runtime as RT
+    rng = np.random.default_rng(4)
+    a, b = client.upload(rng.standard_normal((3, 17, 33)).astype(np.float32)), client.upload(rng.standard_normal((3, 33, 20)).astype(np.float32))
+    t = lambda x: nn.Tensor.from_data(client, x.astype(np.float32))
+    q, k, v = t(rng.standard_normal((2, 5, 7))), t(rng.standard_normal((2, 9, 7))), t(rng.standard_normal((2, 9, 3)))
+
+    def step():
+        y = RT.tensor_matmul(client, a, b)
+        z = nn.scaled_dot_product_attention_padded_bf16_fp32(q, k, v, 0.25)
+        return y.shape, z.dims()
+
+    step(); gc.collect(); client.sync()
+    in_use = client.stats()["bytes_in_use"]
+    for _ in range(50):
+        step()
+    gc.collect(); client.sync()
+    assert client.stats()["bytes_in_use"] == in_use
