@@ -177,6 +177,10 @@ RB_API int32_t rb_bias_add(rb_ctx* ctx, const rb_tensor* x, const rb_tensor* bia
 RB_API int32_t rb_add(rb_ctx* ctx, const rb_tensor* a, const rb_tensor* b, const rb_tensor* y);
 /* Division by a scalar, in place allowed: the Mean step after a Sum collective (src/distributed.rs:150-154,267-271). */
 RB_API int32_t rb_div_scalar(rb_ctx* ctx, const rb_tensor* x, float divisor, const rb_tensor* y);
+/* Multiplication by a scalar, in place allowed: the `matmul(q, k^T) * scale` of the composed attention
+ * (src/nn/padded_attention.rs:43, src/nn/attention.rs:10-29).  One FP32 multiply per element, so any finite scale
+ * (zero and non-powers of two included) gives the reference's bits. */
+RB_API int32_t rb_mul_scalar(rb_ctx* ctx, const rb_tensor* x, float factor, const rb_tensor* y);
 /* AscendRuntime::rotary / rotary_backward, runtime/mod.rs:259-268 -> rotary.rs:15-30, IR rotary_programs.rs:47-97. */
 RB_API int32_t rb_rotary(rb_ctx* ctx, const rb_tensor* x, const rb_tensor* cos, const rb_tensor* sin,
                          int32_t layout, int32_t backward, const rb_tensor* y);

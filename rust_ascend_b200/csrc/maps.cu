@@ -130,6 +130,12 @@ __global__ void __launch_bounds__(256) div_scalar_kernel(const T* x, T* y, uint6
     for (uint64_t i = (uint64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += stride) st(y, i, __fdiv_rn(ld(x, i), divisor));
 }
 
+template <typename T>
+__global__ void __launch_bounds__(256) mul_scalar_kernel(const T* x, T* y, uint64_t n, float factor) {
+    uint64_t stride = (uint64_t)gridDim.x * 256;
+    for (uint64_t i = (uint64_t)blockIdx.x * 256 + threadIdx.x; i < n; i += stride) st(y, i, __fmul_rn(ld(x, i), factor));
+}
+
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(256) cast_kernel(const TI* x, TO* y, uint64_t n) {
     uint64_t stride = (uint64_t)gridDim.x * 256;
@@ -338,6 +344,20 @@ int32_t rb_div_scalar(rb_ctx* ctx, const rb_tensor* x, float divisor, const rb_t
     else if (x->dtype == RB_F16) div_scalar_kernel<__half><<<grid_for(ctx, n), 256, 0, ctx->stream>>>((const __half*)px, (__half*)py, n, divisor);
     else return fail(RB_INVALID_TENSOR, "div_scalar supports FP32, FP16 and BF16");
     return after_launch(ctx, "div_scalar");
+}
+
+int32_t rb_mul_scalar(rb_ctx* ctx, const rb_tensor* x, float factor, const rb_tensor* y) {
+    RB_TRY(check_ctx(ctx));
+    void *px, *py;
+    RB_TRY(resolve(ctx, x, "mul_scalar input", &px)); RB_TRY(resolve(ctx, y, "mul_scalar output", &py));
+    if (!same_shape(x, y) || x->dtype != y->dtype) return fail(RB_INVALID_TENSOR, "mul_scalar keeps shape and dtype");
+    uint64_t n = elements(x);
+    if (n == 0) return empty_call(ctx);
+    if (x->dtype == RB_F32) mul_scalar_kernel<float><<<grid_for(ctx, n), 256, 0, ctx->stream>>>((const float*)px, (float*)py, n, factor);
+    else if (x->dtype == RB_BF16) mul_scalar_kernel<bf><<<grid_for(ctx, n), 256, 0, ctx->stream>>>((const bf*)px, (bf*)py, n, factor);
+    else if (x->dtype == RB_F16) mul_scalar_kernel<__half><<<grid_for(ctx, n), 256, 0, ctx->stream>>>((const __half*)px, (__half*)py, n, factor);
+    else return fail(RB_INVALID_TENSOR, "mul_scalar supports FP32, FP16 and BF16");
+    return after_launch(ctx, "mul_scalar");
 }
 
 int32_t rb_embedding(rb_ctx* ctx, const rb_tensor* table, const rb_tensor* ids, const rb_tensor* out) {

@@ -377,8 +377,8 @@ class B200Runtime:
 
     @staticmethod
     def scale_in_place(client, t: TensorBuffer, scale: float) -> TensorBuffer:
-        """t *= scale, issued as a division by 1/scale (exact for powers of two, within one ulp otherwise)."""
-        _check(client._lib.rb_div_scalar(client._ctx, _ref(t), C.c_float(1.0 / scale), _ref(t)))
+        """t *= scale: one FP32 multiply per element, as the reference's `matmul(...) * scale` (src/nn/padded_attention.rs:43)."""
+        _check(client._lib.rb_mul_scalar(client._ctx, _ref(t), C.c_float(scale), _ref(t)))
         return t
 
     @staticmethod
@@ -645,7 +645,7 @@ class B200Runtime:
             parts.append(part)
             if index + 1 < (2 if t.dtype == DType.F16 else 3):
                 negative = RT.cast(client, part, DType.F32)
-                _check(client._lib.rb_div_scalar(client._ctx, _ref(negative), C.c_float(-1.0), _ref(negative)))
+                _check(client._lib.rb_mul_scalar(client._ctx, _ref(negative), C.c_float(-1.0), _ref(negative)))
                 rest = RT.add(client, rest, negative)              # exact: the part holds the leading bits of `rest`
         return parts
 
@@ -965,8 +965,8 @@ class B200Runtime:
         kb = bf(RT.repeat_kv_heads(client, k, hq), (flat, n, d))
         vb = bf(RT.repeat_kv_heads(client, v, hq), (flat, n, dv))
 
-        def times_scale(t):   # t * scale as a division by 1/scale (exact for the power-of-two scales of the reference examples)
-            _check(client._lib.rb_div_scalar(client._ctx, _ref(t), C.c_float(1.0 / scale), _ref(t)))
+        def times_scale(t):   # t * scale, one FP32 multiply per element like the reference's graph
+            _check(client._lib.rb_mul_scalar(client._ctx, _ref(t), C.c_float(scale), _ref(t)))
             return t
         scores = times_scale(RT.gemm(client, qb, kb, no, yes, DType.F32))
         additive = mask.reshape((flat, m, n)) if mask is not None else None
