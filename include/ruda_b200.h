@@ -253,6 +253,43 @@ RB_API int32_t rb_causal_cross_entropy(rb_ctx* ctx, const rb_tensor* logits, con
 RB_API int32_t rb_gemm(rb_ctx* ctx, const rb_tensor* a, const rb_tensor* b, int32_t transpose_a, int32_t transpose_b,
                        const rb_tensor* bias, const rb_tensor* b_up, int32_t epilogue, const rb_tensor* out);
 
+/* AscendRuntime::linear_bf16_fp32, runtime/mod.rs:367-370 -> matrix.rs:84-93,129-133 (tensor level src/nn.rs:73-88,375-413):
+ * Y = bf16(X) bf16(W)^T for FP32 X [M,K] and W [N,K], FP32 Y [M,N]; x_bf16 / w_bf16 receive the BF16 operands the
+ * reference returns beside Y for the backward pass.  One conversion launch covers both operands, then one GEMM. */
+RB_API int32_t rb_linear_bf16_fp32(rb_ctx* ctx, const rb_tensor* x, const rb_tensor* w, const rb_tensor* y,
+                                   const rb_tensor* x_bf16, const rb_tensor* w_bf16);
+/* Frozen-weight linear, runtime/mod.rs:383-385 -> matrix.rs:147-159 (src/nn/frozen.rs:44-59): Y = bf16(X) W^T with the
+ * BF16 weight used in place.  x_bf16 (BF16 [M,K]) receives the converted input, or may be NULL. */
+RB_API int32_t rb_linear_frozen_bf16(rb_ctx* ctx, const rb_tensor* x, const rb_tensor* w, const rb_tensor* y, const rb_tensor* x_bf16);
+/* RudaAscend::float_matmul, src/backend.rs:692-703 -> generic_matrix::matmul, runtime/generic_matrix.rs:17-54 (the vendor
+ * aclnnMatmul with KEEP_DTYPE, worker.rs:128-162): A [.., M, K] @ B [.., K, N] in the operands' own dtype (FP32, FP16 or
+ * BF16), ranks 2..6, singleton batch axes broadcast, any sizes (an empty contraction gives zeros).  `out` has the
+ * broadcast shape and the operands' dtype.  One pass packs each operand K-major and 16-aligned; one tensor-core launch
+ * multiplies: BF16 and FP16 operands in their own format, FP32 operands as three BF16 parts whose six leading cross
+ * products accumulate in one FP32 accumulator, smallest first (relative error about 2^-24 per product term). */
+RB_API int32_t rb_tensor_matmul(rb_ctx* ctx, const rb_tensor* a, const rb_tensor* b, const rb_tensor* out);
+/* M-grouped GEMM, GemmSpec::grouped_nt, deepgemm/plan.rs:61-67 with GroupEnds (plan.rs:15-29) and the tile walk of
+ * rust-ascend-kernels/src/scheduler.rs:21-33: A [M,K] BF16, weights [G,N,K] BF16, `ends` = G nondecreasing row prefix sums
+ * (host array, multiples of 256, last = M); rows [ends[g-1], ends[g]) meet weight g; out [M,N] BF16 or FP32.  One
+ * persistent launch covers all groups, empty ones included. */
+RB_API int32_t rb_gemm_grouped_nt(rb_ctx* ctx, const rb_tensor* a, const rb_tensor* weights, const int64_t* ends, uint32_t groups,
+                                  const rb_tensor* out);
+/* gemm_padded_bf16_fp32, runtime/mod.rs:188-191 -> padded_matrix.rs:40-50, PaddedGemmSpec deepgemm/padded.rs:12-50: FP32 (or
+ * BF16) A and B of any positive sizes, rank 2 or equal-batch rank 3, all four transposes; `out` is FP32 with the logical
+ * M x N; a_bf16 / b_bf16 receive the zero-padded BF16 operands (both matrix axes rounded up to multiples of 16) that the
+ * reference saves for the backward pass. */
+RB_API int32_t rb_gemm_padded(rb_ctx* ctx, const rb_tensor* a, const rb_tensor* b, int32_t transpose_a, int32_t transpose_b,
+                              const rb_tensor* out, const rb_tensor* a_bf16, const rb_tensor* b_bf16);
+/* Backward of the composed attention (the autodiff graph of src/nn/attention.rs:10-29,49-67) with the reference's rounding
+ * points (examples/grouped_attention_tensor.rs:14-44): P = softmax(scale bf16(Q) bf16(K)^T + mask), dP = bf16(dY) bf16(V)^T,
+ * dS = P (dP - sum(P dP)) in FP32, bf16(scale dS) feeds dQ and dK, bf16(P) feeds dV, and a KV head's gradients sum over
+ * its query heads (heads_programs.rs:59-86).  FP32 q [B,Hq,M,D], k [B,Hkv,N,D], v [B,Hkv,N,Dv], grad [B,Hq,M,Dv]; mask
+ * (nullable) FP32 [B,Hq,M,N]; the causal rule uses the absolute positions as rb_causal_mask does; dmask (nullable)
+ * receives dS.  Scores are materialised, as in the reference. */
+RB_API int32_t rb_attention_backward(rb_ctx* ctx, const rb_tensor* q, const rb_tensor* k, const rb_tensor* v, const rb_tensor* grad,
+                                     const rb_tensor* mask, float scale, int32_t causal, uint64_t query_start, uint64_t key_start,
+                                     const rb_tensor* dq, const rb_tensor* dk, const rb_tensor* dv, const rb_tensor* dmask);
+
 /* Linear on host buffers: Y_host = X_host W^T (+ bias), the reference's write -> launch -> read sequence for one call
  * (AscendServer::write / read, runtime/mod.rs:767-845; launch + stream sync, worker.rs:404-415) as ONE call whose three
  * steps overlap: X is cut into `row_chunks` groups of rows, and while one group multiplies on the tensor cores the next
@@ -295,6 +332,9 @@ RB_API int32_t rb_attention(rb_ctx* ctx, const rb_tensor* q, const rb_tensor* k,
                             float scale, int32_t causal, uint64_t query_start, uint64_t key_start,
                             const rb_tensor* cos, const rb_tensor* sin, int32_t rotary_layout, int32_t out_layout,
                             const rb_tensor* out);
+/* How many rb_attention calls of this context ran on the tensor-core kernel and how many on the general row kernel
+ * (introspection for tests and profiling, in the spirit of KernelStats, deepgemm/mod.rs:16). */
+RB_API int32_t rb_attention_launch_counts(rb_ctx* ctx, uint64_t* tensor_core, uint64_t* general);
 
 /* ---- a side stream beside the compute stream (no counterpart in the reference, where every operation is a launch followed
  * by a stream synchronisation, runtime/worker.rs:404-415) ------------------------------------------------------------ */

@@ -44,12 +44,16 @@ struct AttnParams {
     uint32_t B, Hq, Hkv, M, N;
     uint32_t items, heads_total;  // work items = query block pairs x B x Hq; heads_total = B * Hq
     uint32_t q_blocks;            // 256-row query blocks per head
+    uint32_t wave_heads;          // heads per wave of the item order
     float scale_log2;             // scale * log2(e)
     int32_t causal;
     int64_t delta;                // query_start - key_start (saturated): key k is masked iff k > q + delta
-    bf* out; uint64_t o_stride_b, o_stride_h, o_stride_m;   // elements
+    void* out; uint64_t o_stride_b, o_stride_h, o_stride_m;  // BF16 or FP32 (kernel template); strides in elements
+    const float* mask;            // additive FP32 [B*Hq, M, N] or null (kernel template)
     uint32_t* status;
 };
+
+constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ float ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
@@ -61,8 +65,9 @@ __device__ __forceinline__ uint32_t blocks_for(const AttnParams& p, uint32_t row
     return rb_attention_blocks(p.M, p.N, p.causal, p.delta, row0, row_end, TK);
 }
 // Work item -> (query block, head, batch): heaviest query blocks first, heads of one KV group next to each other.
-__device__ __forceinline__ void item_coords(const AttnParams& p, uint32_t item, uint32_t& qb, uint32_t& h, uint32_t& b) {
-    rb_attention_item(item, p.q_blocks, p.heads_total, p.Hq, qb, h, b);
+// `round` is the CTA's step number; returns false when the CTA has no item in that step.
+__device__ __forceinline__ bool item_coords(const AttnParams& p, uint32_t round, uint32_t& qb, uint32_t& h, uint32_t& b) {
+    return rb_attention_item(round, blockIdx.x, gridDim.x, p.q_blocks, p.heads_total, p.Hq, p.wave_heads, qb, h, b);
 }
 
 // Packed FP32 pairs (fma.rn.f32x2 / add.rn.f32x2) and the three-input max halve the issue slots of the softmax.
@@ -73,14 +78,14 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) { u
 __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) { uint64_t d; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b)); return d; }
 __device__ __forceinline__ float max3(float a, float b, float c) { float d; asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c)); return d; }
 
-// Waits on the three hand-offs of the per-tile chain (scores ready, P half ready, P ready): polling by default, since the
-// hardware's wake-up of a suspended waiter costs a few hundred cycles per hand-off.  -DRB_ATTN_SUSPEND selects the
-// suspending wait instead.
+// Waits on the three hand-offs of the per-tile chain (scores ready, P half ready, P ready).  The suspending wait measured
+// 1.5-2 % faster than polling with test_wait on B200 (the pollers take issue slots from the softmax warps of the other
+// tile); -DRB_ATTN_SPIN selects polling.
 __device__ __forceinline__ bool wait_handoff(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_word) {
-#ifdef RB_ATTN_SUSPEND
-    return mbar_wait(bar, parity, abort_word);
-#else
+#ifdef RB_ATTN_SPIN
     return mbar_wait_spin(bar, parity, abort_word);
+#else
+    return mbar_wait(bar, parity, abort_word);
 #endif
 }
 
@@ -173,15 +178,37 @@ __device__ __forceinline__ int chunk_class(int32_t v0, int32_t nk, int c) {
 // TMEM once (four loads in flight, one wait) and stay in registers; P goes back to TMEM as BF16 pairs over the scores
 // already consumed, and the MMA warp is told after the first 64 keys and again after all 128 so that P V can start
 // early.  MASKED is false for blocks entirely below the causal diagonal and inside the key range.
-template <bool MASKED>
+// r = r * sc + mask * log2(e) for one 32-key chunk: the additive mask joins the scores before the row maximum is taken.
+__device__ __forceinline__ void chunk_add_mask(uint32_t (&r)[32], float sc, const float* mask_row) {
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+        const float4 mk = __ldg(reinterpret_cast<const float4*>(mask_row + i));
+        r[i] = __float_as_uint(__fmaf_rn(__uint_as_float(r[i]), sc, mk.x * LOG2E));
+        r[i + 1] = __float_as_uint(__fmaf_rn(__uint_as_float(r[i + 1]), sc, mk.y * LOG2E));
+        r[i + 2] = __float_as_uint(__fmaf_rn(__uint_as_float(r[i + 2]), sc, mk.z * LOG2E));
+        r[i + 3] = __float_as_uint(__fmaf_rn(__uint_as_float(r[i + 3]), sc, mk.w * LOG2E));
+    }
+}
+
+template <bool MASKED, bool HAS_MASK>
 __device__ __forceinline__ void softmax_block(uint32_t tmem_s, uint32_t tmem_o, float sc, int32_t visible, int32_t v0, int32_t nk, bool first,
-                                              float& m_used, float& l, uint64_t* p_half, uint64_t* p_full, bool tr, uint32_t tr_role, uint32_t tr_j) {
+                                              float& m_used, float& l, uint64_t* p_half, uint64_t* p_full, const float* mask_row,
+                                              bool tr, uint32_t tr_role, uint32_t tr_j) {
     uint32_t r0[32], r1[32], r2[32], r3[32];
     tmem_ld_32x32(tmem_s, r0); tmem_ld_32x32(tmem_s + 32, r1); tmem_ld_32x32(tmem_s + 64, r2); tmem_ld_32x32(tmem_s + 96, r3);
     tmem_wait_ld();
     RB_TR(tr, tr_role, tr_j, 1);
     int c0 = 2, c1 = 2, c2 = 2, c3 = 2;
     if (MASKED) { c0 = chunk_class(v0, nk, 0); c1 = chunk_class(v0, nk, 1); c2 = chunk_class(v0, nk, 2); c3 = chunk_class(v0, nk, 3); }
+    if (HAS_MASK) {
+        // chunks that exist (the key count is a multiple of 32) take their mask values now; from here on the scores are final
+        // and already in the exp2 domain, so the scale that follows is 1
+        if (c0) chunk_add_mask(r0, sc, mask_row);
+        if (c1) chunk_add_mask(r1, sc, mask_row + 32);
+        if (c2) chunk_add_mask(r2, sc, mask_row + 64);
+        if (c3) chunk_add_mask(r3, sc, mask_row + 96);
+        sc = 1.0f;
+    }
     float mx = -INFINITY;
 #define RB_MAX(R, CLS, BASE) { if (!MASKED || CLS == 2) chunk_max<2>(R, 32, mx); else if (CLS == 1) chunk_max<1>(R, visible - BASE, mx); }
     RB_MAX(r0, c0, 0) RB_MAX(r1, c1, 32) RB_MAX(r2, c2, 64) RB_MAX(r3, c3, 96)
@@ -232,6 +259,7 @@ __device__ __forceinline__ void softmax_block(uint32_t tmem_s, uint32_t tmem_o, 
     l += s0 + s1;
 }
 
+template <bool HAS_MASK, bool OUT_F32>
 __global__ void __launch_bounds__(THREADS, 1)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                      const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
@@ -273,6 +301,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    const uint32_t rounds = rb_attention_steps(p.q_blocks, p.heads_total, p.wave_heads, gridDim.x);
 #ifdef RB_ATTN_TRACE
     const bool trace_cta = blockIdx.x == 0;
 #else
@@ -289,8 +318,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             uint32_t kv_it = 0, q_it = 0;
             uint32_t armed = 0, armed_parity = 0;      // bit 0: Q, bits 1-2: K stages, bits 3-4: V stages
             auto arm = [&](uint32_t bit, uint32_t parity) { armed |= 1u << bit; armed_parity = (armed_parity & ~(1u << bit)) | (parity << bit); };
-            for (uint32_t item = blockIdx.x; ok && item < p.items; item += gridDim.x) {
-                uint32_t qb, h, b; item_coords(p, item, qb, h, b);
+            for (uint32_t round = 0; ok && round < rounds; ++round) {
+                uint32_t qb, h, b;
+                if (!item_coords(p, round, qb, h, b)) continue;
                 const uint32_t kvh = h / (p.Hq / p.Hkv), row0 = qb * 2 * TQ;
                 const uint32_t nb0 = blocks_for(p, row0, row0 + TQ), nb1 = blocks_for(p, row0 + TQ, row0 + 2 * TQ);
                 const uint32_t n_max = nb0 > nb1 ? nb0 : nb1;
@@ -340,15 +370,16 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 }
                 umma_commit(&s_full[t]);
             };
-            for (uint32_t item = blockIdx.x; ok && item < p.items; item += gridDim.x) {
-                uint32_t qb, h, b; item_coords(p, item, qb, h, b);
+            for (uint32_t round = 0; ok && round < rounds; ++round) {
+                uint32_t qb, h, b;
+                if (!item_coords(p, round, qb, h, b)) continue;
                 const uint32_t row0 = qb * 2 * TQ;
                 const uint32_t nb[2] = {blocks_for(p, row0, row0 + TQ), blocks_for(p, row0 + TQ, row0 + 2 * TQ)};
                 const uint32_t n_max = nb[0] > nb[1] ? nb[0] : nb[1];
                 if (n_max == 0) continue;
                 const uint32_t total_s = nb[0] + nb[1];
                 uint32_t s_done = 0;
-                const bool tr = trace_cta && item == blockIdx.x;
+                const bool tr = trace_cta && round == 0;
                 if (!(ok = mbar_wait(q_full, q_it & 1, abort_word))) break;
                 {
                     const uint32_t st = kv_it % KV_STAGES, ph = (kv_it / KV_STAGES) & 1;
@@ -417,19 +448,27 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         const uint32_t tmem_o = tmem_base + 256 + t * D + lane_base;
         uint32_t blk = 0, used = 0;
         bool ok = true;
-        for (uint32_t item = blockIdx.x; ok && item < p.items; item += gridDim.x) {
-            uint32_t qb, h, b; item_coords(p, item, qb, h, b);
+        for (uint32_t round = 0; ok && round < rounds; ++round) {
+            uint32_t qb, h, b;
+            if (!item_coords(p, round, qb, h, b)) continue;
             const uint32_t tile_row0 = qb * 2 * TQ + t * TQ;
             if (tile_row0 >= p.M) continue;
             const uint32_t nb = blocks_for(p, tile_row0, tile_row0 + TQ);
             const uint32_t row = tile_row0 + row_in_tile;                  // query index inside the sequence
-            bf* o = p.out + (uint64_t)b * p.o_stride_b + (uint64_t)h * p.o_stride_h + (uint64_t)row * p.o_stride_m;
+            const uint64_t o_at = (uint64_t)b * p.o_stride_b + (uint64_t)h * p.o_stride_h + (uint64_t)row * p.o_stride_m;
+            // row of the additive mask [B*Hq, M, N]; rows past M are never dereferenced beyond the mask because their loads are
+            // clamped to row M - 1
+            const float* mask_row = HAS_MASK ? p.mask + ((uint64_t)(b * p.Hq + h) * p.M + (row < p.M ? row : p.M - 1)) * p.N : nullptr;
             if (nb == 0) {
-                // No visible key for this tile: the reference's softmax over an empty set has no value; write zeros.
-                if (row < p.M) for (int i = 0; i < D / 8; ++i) reinterpret_cast<uint4*>(o)[i] = make_uint4(0, 0, 0, 0);
+                // No visible key for this tile: a softmax over an empty set has no value.  The reference's composition gives NaN
+                // there (its mask is -inf everywhere in the row, mask_programs.rs:5), and so does this kernel.
+                if (row < p.M) {
+                    if (OUT_F32) { float* o = static_cast<float*>(p.out) + o_at; for (int i = 0; i < D / 4; ++i) reinterpret_cast<uint4*>(o)[i] = make_uint4(0x7fc00000u, 0x7fc00000u, 0x7fc00000u, 0x7fc00000u); }
+                    else { bf* o = static_cast<bf*>(p.out) + o_at; for (int i = 0; i < D / 8; ++i) reinterpret_cast<uint4*>(o)[i] = make_uint4(0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u, 0x7fc07fc0u); }
+                }
                 continue;
             }
-            const bool tr = trace_cta && item == blockIdx.x && quarter == 0 && lane == 0;
+            const bool tr = trace_cta && round == 0 && quarter == 0 && lane == 0;
             const int64_t q_limit0 = (int64_t)(tile_row0 + quarter * 32) + p.delta;   // last visible key of this warp's first row (causal)
             float m_used = 0.f, l = 0.f;
             for (uint32_t j = 0; j < nb; ++j, ++blk) {
@@ -451,9 +490,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     }
                     int32_t visible = p.causal ? v0 + (int32_t)lane : TK;
                     visible = visible > nk ? nk : (visible < 0 ? 0 : visible);
-                    softmax_block<true>(tmem_s, tmem_o, p.scale_log2, visible, v0, nk, j == 0, m_used, l, &p_half[t], &p_full[t], tr, t, j);
+                    softmax_block<true, HAS_MASK>(tmem_s, tmem_o, p.scale_log2, visible, v0, nk, j == 0, m_used, l, &p_half[t], &p_full[t], mask_row + k0, tr, t, j);
                 } else {
-                    softmax_block<false>(tmem_s, tmem_o, p.scale_log2, TK, TK, TK, j == 0, m_used, l, &p_half[t], &p_full[t], tr, t, j);
+                    softmax_block<false, HAS_MASK>(tmem_s, tmem_o, p.scale_log2, TK, TK, TK, j == 0, m_used, l, &p_half[t], &p_full[t], mask_row + k0, tr, t, j);
                 }
             }
             if (!ok) break;
@@ -461,7 +500,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             ok = mbar_wait(&o_full[t], used & 1, abort_word);
             if (!(ok = __all_sync(0xffffffffu, ok))) break;
             tc_fence_after();
-            const float inv = l > 0.f ? __fdiv_rn(1.0f, l) : 0.f;
+            // a row that saw no key at all (every key hidden by the causal rule or by -inf mask values) has no value: NaN, as the
+            // reference's softmax of a row of -inf gives
+            const float inv = l > 0.f ? __fdiv_rn(1.0f, l) : __uint_as_float(0x7fc00000u);
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 uint32_t r[32];
@@ -469,14 +510,23 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 tmem_wait_ld();
                 if (c == 3) { tc_fence_before(); mbar_arrive(&o_free[t]); }   // O is in registers: the next item may overwrite it
                 if (row < p.M) {
+                    if (OUT_F32) {
+                        float* o = static_cast<float*>(p.out) + o_at + c * 32;
 #pragma unroll
-                    for (int i = 0; i < 32; i += 8) {
-                        uint4 w;
-                        w.x = pack_bf16(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
-                        w.y = pack_bf16(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
-                        w.z = pack_bf16(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
-                        w.w = pack_bf16(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
-                        *reinterpret_cast<uint4*>(o + c * 32 + i) = w;
+                        for (int i = 0; i < 32; i += 4)
+                            *reinterpret_cast<float4*>(o + i) = make_float4(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv,
+                                                                           __uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+                    } else {
+                        bf* o = static_cast<bf*>(p.out) + o_at + c * 32;
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            uint4 w;
+                            w.x = pack_bf16(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+                            w.y = pack_bf16(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+                            w.z = pack_bf16(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+                            w.w = pack_bf16(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+                            *reinterpret_cast<uint4*>(o + i) = w;
+                        }
                     }
                 }
             }
@@ -573,6 +623,14 @@ __global__ void __launch_bounds__(128) attention_rows_kernel(const T* q, const T
     }
 }
 
+// Per-context bookkeeping of this translation unit: which kernels have had their shared-memory limit raised, and how many
+// calls took each path (read by rb_attention_launch_counts).
+struct AttnState {
+    bool configured[4] = {false, false, false, false};
+    bool rows_f32 = false, rows_bf16 = false;
+    uint64_t tensor_core_launches = 0, general_launches = 0;
+};
+
 bool make_qkv_map(CUtensorMap* map, const void* base, const rb_tensor* t) {
     // logical [B, H, S, 128] with element strides; TMA dims innermost first: {d, s, h, b}
     uint64_t dims[4] = {t->shape[3], t->shape[2], t->shape[1], t->shape[0]};
@@ -652,75 +710,107 @@ int32_t rb_attention(rb_ctx* ctx, const rb_tensor* q, const rb_tensor* k, const 
         if (!cos || !sin) return fail(RB_INVALID_TENSOR, "fused rotary needs both tables");
         RB_TRY(resolve(ctx, cos, "attention cos table", &pc)); RB_TRY(resolve(ctx, sin, "attention sin table", &ps));
         const int64_t q_off = delta;
-        if (cos->dtype != RB_F32 || sin->dtype != RB_F32 || !same_shape(cos, sin) || cos->shape[cos->rank - 1] != 64 || Dq != 128 || q->dtype != RB_BF16 ||
+        if (cos->dtype != RB_F32 || sin->dtype != RB_F32 || !same_shape(cos, sin) || cos->shape[cos->rank - 1] != 64 || Dq != 128 ||
             q_off < 0 || elements(cos) / 64 < N || elements(cos) / 64 < M + (uint64_t)q_off)
-            return fail(RB_INVALID_TENSOR, "fused rotary needs BF16 head dim 128 and FP32 tables [positions >= max(N, M + query_start - key_start), 64]");
+            return fail(RB_INVALID_TENSOR, "fused rotary needs head dim 128 and FP32 tables [positions >= max(N, M + query_start - key_start), 64]");
         if (rotary_layout != RB_ROTARY_SPLIT_HALF && rotary_layout != RB_ROTARY_INTERLEAVED) return fail(RB_INVALID_TENSOR, "unknown rotary layout");
     }
 
-    const bool fast = q->dtype == RB_BF16 && Dq == 128 && Dv == 128 && !additive_mask && scale > 0.0f;
+    AttnState* state = static_cast<AttnState*>(ctx->attention_state);
+    if (!state) { state = new AttnState(); ctx->attention_state = state; }
+    const bool f32 = q->dtype == RB_F32;
+    // The tensor-core kernel takes head dim 128 and a positive scale (it takes row maxima before scaling); FP32 tensors, the
+    // reference's own contract (src/nn/attention.rs:10-80), are rounded to BF16 on the way in, which is where the reference
+    // rounds them too, and leave as FP32.
+    const bool fast = Dq == 128 && Dv == 128 && scale > 0.0f && (!f32 || (is_contiguous4(q) && is_contiguous4(k) && is_contiguous4(v)));
     if (!fast) {
-        if (rope) return fail(RB_INVALID_TENSOR, "fused rotary is only available on the BF16 head-dim-128 path");
+        if (rope) return fail(RB_INVALID_TENSOR, "fused rotary is only available on the head-dim-128 path");
         if (!is_contiguous4(q) || !is_contiguous4(k) || !is_contiguous4(v)) return fail(RB_INVALID_TENSOR, "general attention path requires contiguous [B,H,S,D] tensors");
         if (Dq > 256) return fail(RB_INVALID_TENSOR, "general attention path supports head dims up to 256");
         const size_t smem = N * sizeof(float);
-        if (smem > 200 * 1024) return fail(RB_INVALID_TENSOR, "general attention path supports up to 51200 keys; use BF16 head dim 128 for longer sequences");
+        if (smem > 200 * 1024) return fail(RB_INVALID_TENSOR, "general attention path supports up to 51200 keys; use head dim 128 for longer sequences");
         const uint64_t rows = flat * M;
-        if (q->dtype == RB_F32) {
-            static bool set32 = false;
-            if (!set32) { cudaFuncSetAttribute(attention_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); set32 = true; }
+        if (f32) {
+            if (!state->rows_f32) { cudaFuncSetAttribute(attention_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); state->rows_f32 = true; }
             attention_rows_kernel<float><<<(unsigned)rows, 128, smem, ctx->stream>>>((const float*)pq, (const float*)pk, (const float*)pv, (const float*)pm, (float*)po,
                 (uint32_t)Hq, (uint32_t)Hkv, (uint32_t)M, (uint32_t)N, (uint32_t)Dq, (uint32_t)Dv, scale, causal, delta, o_stride_b, o_stride_h, o_stride_m);
         } else {
-            static bool set16 = false;
-            if (!set16) { cudaFuncSetAttribute(attention_rows_kernel<bf>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); set16 = true; }
+            if (!state->rows_bf16) { cudaFuncSetAttribute(attention_rows_kernel<bf>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); state->rows_bf16 = true; }
             attention_rows_kernel<bf><<<(unsigned)rows, 128, smem, ctx->stream>>>((const bf*)pq, (const bf*)pk, (const bf*)pv, (const float*)pm, (bf*)po,
                 (uint32_t)Hq, (uint32_t)Hkv, (uint32_t)M, (uint32_t)N, (uint32_t)Dq, (uint32_t)Dv, scale, causal, delta, o_stride_b, o_stride_h, o_stride_m);
         }
+        state->general_launches++;
         return after_launch(ctx, "attention (general path)");
     }
 
     // ---- tensor-core path ----
-    rb_tensor qt = *q, kt = *k;
-    if (rope) {
-        // K is rotated once per KV head and Q once per query head into the context workspace; doing it inside the
-        // attention CTAs would repeat the K rotation for every query head of the group and every query block.
-        const uint64_t qn = flat * M * 128, kn = B * Hkv * N * 128;
-        RB_TRY(ensure_workspace(ctx, 1024 + (qn + kn) * 2));
-        bf* wq = reinterpret_cast<bf*>(static_cast<uint8_t*>(ctx->workspace) + 1024); bf* wk = wq + qn;
-        const uint32_t q_off = (uint32_t)delta;
-        rope_bf16_kernel<<<(unsigned)((flat * M * 8 + 255) / 256), 256, 0, ctx->stream>>>((const bf*)pq, q->strides[0], q->strides[1], q->strides[2], (const float*)pc,
-            (const float*)ps, wq, (uint32_t)Hq, (uint32_t)M, flat * M, q_off, rotary_layout);
-        RB_TRY(after_launch(ctx, "attention rotary(Q)"));
-        rope_bf16_kernel<<<(unsigned)((B * Hkv * N * 8 + 255) / 256), 256, 0, ctx->stream>>>((const bf*)pk, k->strides[0], k->strides[1], k->strides[2], (const float*)pc,
-            (const float*)ps, wk, (uint32_t)Hkv, (uint32_t)N, B * Hkv * N, 0, rotary_layout);
-        RB_TRY(after_launch(ctx, "attention rotary(K)"));
-        pq = wq; pk = wk;
-        qt.strides[0] = Hq * M * 128; qt.strides[1] = M * 128; qt.strides[2] = 128; qt.strides[3] = 1;
-        kt.strides[0] = Hkv * N * 128; kt.strides[1] = N * 128; kt.strides[2] = 128; kt.strides[3] = 1;
+    Scratch scratch(ctx);
+    rb_tensor qt = *q, kt = *k, vt = *v;
+    if (f32) {
+        // FP32 Q/K/V -> BF16 copies (Cast, as the reference's composition does before its two GEMMs)
+        rb_tensor q16, k16, v16; void *c16q, *c16k, *c16v;
+        RB_TRY(scratch.tensor(RB_BF16, {B, Hq, M, 128}, &q16, &c16q)); RB_TRY(scratch.tensor(RB_BF16, {B, Hkv, N, 128}, &k16, &c16k));
+        RB_TRY(scratch.tensor(RB_BF16, {B, Hkv, N, 128}, &v16, &c16v));
+        RB_TRY(rb_cast(ctx, q, &q16)); RB_TRY(rb_cast(ctx, k, &k16)); RB_TRY(rb_cast(ctx, v, &v16));
+        qt = q16; kt = k16; vt = v16; pq = c16q; pk = c16k; pv = c16v;
     }
-    const rb_tensor* operands[3] = {&qt, &kt, v};
+    if (rope) {
+        // K is rotated once per KV head and Q once per query head into temporaries; doing it inside the attention CTAs
+        // would repeat the K rotation for every query head of the group and every query block.
+        rb_tensor rq, rk; void *wq, *wk;
+        RB_TRY(scratch.tensor(RB_BF16, {B, Hq, M, 128}, &rq, &wq)); RB_TRY(scratch.tensor(RB_BF16, {B, Hkv, N, 128}, &rk, &wk));
+        const uint32_t q_off = (uint32_t)delta;
+        rope_bf16_kernel<<<(unsigned)((flat * M * 8 + 255) / 256), 256, 0, ctx->stream>>>((const bf*)pq, qt.strides[0], qt.strides[1], qt.strides[2], (const float*)pc,
+            (const float*)ps, (bf*)wq, (uint32_t)Hq, (uint32_t)M, flat * M, q_off, rotary_layout);
+        RB_TRY(after_launch(ctx, "attention rotary(Q)"));
+        rope_bf16_kernel<<<(unsigned)((B * Hkv * N * 8 + 255) / 256), 256, 0, ctx->stream>>>((const bf*)pk, kt.strides[0], kt.strides[1], kt.strides[2], (const float*)pc,
+            (const float*)ps, (bf*)wk, (uint32_t)Hkv, (uint32_t)N, B * Hkv * N, 0, rotary_layout);
+        RB_TRY(after_launch(ctx, "attention rotary(K)"));
+        pq = wq; pk = wk; qt = rq; kt = rk;
+    }
+    const rb_tensor* operands[3] = {&qt, &kt, &vt};
     for (const rb_tensor* t : operands)
         for (int i = 0; i < 3; ++i)
             if (t->strides[i] % 8 != 0) return fail(RB_INVALID_TENSOR, "attention strides must be multiples of 8 elements");
     AttnParams p{};
     p.B = (uint32_t)B; p.Hq = (uint32_t)Hq; p.Hkv = (uint32_t)Hkv; p.M = (uint32_t)M; p.N = (uint32_t)N;
-    p.scale_log2 = scale * 1.4426950408889634f; p.causal = causal ? 1 : 0; p.delta = causal ? delta : 0;
+    p.scale_log2 = scale * LOG2E; p.causal = causal ? 1 : 0; p.delta = causal ? delta : 0;
     p.q_blocks = (uint32_t)((M + 2 * TQ - 1) / (2 * TQ)); p.heads_total = (uint32_t)flat; p.items = p.q_blocks * p.heads_total;
-    p.out = (bf*)po; p.o_stride_b = o_stride_b; p.o_stride_h = o_stride_h; p.o_stride_m = o_stride_m;
+    const uint32_t sms = ctx->sm_limit > 0 ? (uint32_t)ctx->sm_limit : (uint32_t)ctx->sm_count;
+    const uint32_t grid = p.items < sms ? p.items : sms;
+    p.wave_heads = rb_attention_wave_heads(p.q_blocks, p.heads_total, grid);
+    p.out = po; p.o_stride_b = o_stride_b; p.o_stride_h = o_stride_h; p.o_stride_m = o_stride_m;
+    p.mask = static_cast<const float*>(pm);
     RB_TRY(kernel_status_word(ctx, &p.status));
     CUtensorMap mq, mk, mv;
-    if (!make_qkv_map(&mq, pq, &qt) || !make_qkv_map(&mk, pk, &kt) || !make_qkv_map(&mv, pv, v))
+    if (!make_qkv_map(&mq, pq, &qt) || !make_qkv_map(&mk, pk, &kt) || !make_qkv_map(&mv, pv, &vt))
         return fail(RB_STATUS, "cuTensorMapEncodeTiled failed for an attention operand");
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        if (e != cudaSuccess) return fail(RB_STATUS, "cudaFuncSetAttribute(attention) failed with CUDA status %d (%s)", (int)e, cudaGetErrorString(e));
-        configured = true;
+    const int variant = (pm ? 2 : 0) | (f32 ? 1 : 0);
+    auto launch = [&](auto kernel) -> int32_t {
+        if (!state->configured[variant]) {
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+            if (e != cudaSuccess) return fail(RB_STATUS, "cudaFuncSetAttribute(attention) failed with CUDA status %d (%s)", (int)e, cudaGetErrorString(e));
+            state->configured[variant] = true;
+        }
+        kernel<<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(mq, mk, mv, p);
+        return RB_OK;
+    };
+    switch (variant) {
+        case 0: RB_TRY(launch(attention_fwd_kernel<false, false>)); break;
+        case 1: RB_TRY(launch(attention_fwd_kernel<false, true>)); break;
+        case 2: RB_TRY(launch(attention_fwd_kernel<true, false>)); break;
+        default: RB_TRY(launch(attention_fwd_kernel<true, true>)); break;
     }
-    const uint32_t sms = ctx->sm_limit > 0 ? (uint32_t)ctx->sm_limit : (uint32_t)ctx->sm_count;
-    attention_fwd_kernel<<<p.items < sms ? p.items : sms, THREADS, SMEM_BYTES, ctx->stream>>>(mq, mk, mv, p);
+    state->tensor_core_launches++;
     return after_launch(ctx, "attention");
+}
+
+int32_t rb_attention_launch_counts(rb_ctx* ctx, uint64_t* tensor_core, uint64_t* general) {
+    RB_TRY(check_ctx(ctx));
+    const AttnState* state = static_cast<const AttnState*>(ctx->attention_state);
+    if (tensor_core) *tensor_core = state ? state->tensor_core_launches : 0;
+    if (general) *general = state ? state->general_launches : 0;
+    return RB_OK;
 }
 
 #ifdef RB_ATTN_TRACE

@@ -12,6 +12,7 @@
 #include <mutex>
 #include <string>
 #include <unordered_map>
+#include <initializer_list>
 #include <vector>
 
 #include "ruda_b200.h"
@@ -77,8 +78,70 @@ int32_t poll_kernel_status(rb_ctx* ctx);
 int32_t kernel_status_word(rb_ctx* ctx, uint32_t** out);
 // True between rb_aux_begin and rb_aux_end: launches are going to the side stream, beside the compute stream's kernels.
 bool aux_active(rb_ctx* ctx);
+// One launch of the tensor-core GEMM on K-major operands (A [.., m, k], B [.., n, k], both 16-bit), with every option the
+// kernel has.  Operands that were split into parts store the parts as consecutive batch entries (z = batch * parts + part).
+struct GemmCall {
+    const void* a = nullptr; const void* b = nullptr; const void* b_up = nullptr;
+    uint32_t batches = 1, m = 0, n = 0, k = 0;
+    uint32_t a_rows = 0, b_rows = 0;                   // rows each batch entry of A / B occupies in memory (0: m / n); more when padded
+    int epilogue = 0; const void* bias = nullptr; bool bias_bf16 = false;
+    void* out = nullptr; uint32_t out_kind = 0;        // 0 BF16, 1 FP32, 2 FP16
+    bool f16_operands = false;                         // operands are FP16 bit patterns instead of BF16
+    bool ragged = false;                               // n * element size is not a multiple of 16 bytes
+    uint32_t nseg = 1, parts_a = 1, parts_b = 1;
+    uint32_t seg_a[6] = {0, 0, 0, 0, 0, 0}, seg_b[6] = {0, 0, 0, 0, 0, 0};
+    bool a_bcast = false, b_bcast = false;             // the operand has one batch entry used by every output batch
+    const int32_t* group_ends = nullptr; uint32_t groups = 0;   // M-grouped NT: B is [groups, n, k], device array of row prefix sums
+};
+int32_t gemm_run(rb_ctx* ctx, const GemmCall& call);
 int32_t gemm_kmajor(rb_ctx* ctx, const void* a, const void* b, const void* b_up, uint32_t batches, uint32_t m, uint32_t n, uint32_t k,
                     int epilogue, const void* bias, bool bias_bf16, void* out, bool out_f32);
+
+}  // namespace rb
+
+namespace rb {
+
+// Device temporaries of one call.  Each is registered as a non-owning storage so that the other entry points can be called on
+// it through an ordinary tensor descriptor; the destructor drops the registrations and queues the frees behind the work.
+struct Scratch {
+    rb_ctx* ctx;
+    struct Item { void* ptr; uint64_t handle; };
+    std::vector<Item> items;
+    explicit Scratch(rb_ctx* c) : ctx(c) {}
+    ~Scratch() {
+        for (auto& it : items) { rb_free(ctx, it.handle); cudaFreeAsync(it.ptr, ctx->stream); }
+    }
+    int32_t tensor(uint32_t dtype, std::initializer_list<uint64_t> shape, rb_tensor* out, void** ptr_out = nullptr) {
+        *out = rb_tensor{};
+        out->dtype = dtype; out->rank = (uint32_t)shape.size();
+        uint64_t n = 1; int i = 0;
+        for (uint64_t d : shape) { out->shape[i++] = d; n *= d; }
+        uint64_t stride = 1;
+        for (int a = (int)out->rank - 1; a >= 0; --a) { out->strides[a] = stride; stride *= out->shape[a]; }
+        const uint64_t bytes = n * dtype_size(dtype);
+        void* p = nullptr;
+        cudaError_t e = cudaMallocAsync(&p, bytes ? bytes : 16, ctx->stream);
+        if (e != cudaSuccess) return fail(RB_STATUS, "temporary of %llu bytes: cudaMallocAsync failed with CUDA status %d (%s)", (unsigned long long)bytes, (int)e, cudaGetErrorString(e));
+        uint64_t h = 0;
+        int32_t rc = rb_import(ctx, p, bytes ? bytes : 16, &h);
+        if (rc != RB_OK) { cudaFreeAsync(p, ctx->stream); return rc; }
+        items.push_back({p, h});
+        out->handle = h;
+        if (ptr_out) *ptr_out = p;
+        return RB_OK;
+    }
+};
+
+// The same storage seen with another shape (contiguous).
+inline rb_tensor view(const rb_tensor& t, std::initializer_list<uint64_t> shape) {
+    rb_tensor v = t;
+    v.rank = (uint32_t)shape.size();
+    int i = 0;
+    for (uint64_t d : shape) v.shape[i++] = d;
+    uint64_t stride = 1;
+    for (int a = (int)v.rank - 1; a >= 0; --a) { v.strides[a] = stride; stride *= v.shape[a]; }
+    return v;
+}
 
 }  // namespace rb
 

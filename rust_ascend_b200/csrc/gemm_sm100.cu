@@ -39,8 +39,17 @@ struct GemmParams {
     uint32_t split;                 // work items below this index are whole tiles; from it on, item = half of tile split + (i - split) / 2
     uint32_t items;                 // whole tiles + half tiles
     uint32_t epilogue;              // rb_epilogue
-    uint32_t out_f32;               // 1: FP32 output, 0: BF16
+    uint32_t out_f32;               // output storage: 0 BF16, 1 FP32, 2 FP16
     uint32_t bias_bf16;             // bias storage: 1 BF16, 0 FP32
+    uint32_t f16_operands;          // 1: the 16-bit operands are FP16 instead of BF16 (UMMA operand format)
+    uint32_t ragged;                // 1: output rows are not multiples of 16 bytes, stored element by element
+    // K passes: pass s multiplies part seg_a[s] of A with part seg_b[s] of B into the same accumulator (an FP32 operand
+    // split into BF16 parts); an operand with `parts` parts stores them as consecutive batch entries: z = batch * parts + part
+    uint32_t nseg, parts_a, parts_b;
+    uint32_t seg_a[6], seg_b[6];
+    uint32_t a_bcast, b_bcast;      // 1: the operand has one batch entry that every output batch uses
+    const int32_t* group_ends;      // M-grouped NT: B's batch entry is the group that owns the tile's rows (row prefix sums); else null
+    uint32_t groups;
     void* out;
     const void* bias;
     uint32_t* status;               // device status word: non-zero when a bounded wait expired
@@ -86,6 +95,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const bool swiglu = p.epilogue == RB_EPILOGUE_SWIGLU;
     const uint32_t bn_out = swiglu ? BN / 2 : BN;      // output columns of a whole tile
     const uint32_t num_kb = (p.k + BK - 1) / BK;
+    const uint32_t total_kb = num_kb * p.nseg;          // K blocks of all passes
     const uint32_t num_tiles = p.items;
 
     if (threadIdx.x == 0) {
@@ -117,14 +127,19 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 const uint32_t b_bytes = b_rows * BK * 2;
                 const CUtensorMap* mb = whole ? &map_b : &map_bh;
                 const CUtensorMap* mb2 = whole ? &map_b2 : &map_b2h;
-                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                const uint32_t za0 = (p.a_bcast ? 0u : batch) * p.parts_a;
+                uint32_t zb0 = (p.b_bcast ? 0u : batch) * p.parts_b;
+                if (p.group_ends) zb0 = rb_group_of(p.group_ends, p.groups, tm * BM);
+                for (uint32_t kt = 0; kt < total_kb; ++kt) {
+                    const uint32_t seg = kt / num_kb, kb = kt - seg * num_kb;
+                    const int32_t za = (int32_t)(za0 + p.seg_a[seg]), zb = (int32_t)(zb0 + p.seg_b[seg]);
                     if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_word))) break;
                     uint8_t* sa = smem + stage * C::STAGE_BYTES; uint8_t* sb = sa + C::A_BYTES;
                     mbar_expect_tx(&full_bar[stage], C::A_BYTES + (swiglu ? 2 * b_bytes : b_bytes));
                     armed |= 1u << stage; armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
-                    tma_load_3d(sa, &map_a, &full_bar[stage], (int32_t)(kb * BK), (int32_t)(tm * BM), (int32_t)batch);
-                    tma_load_3d(sb, mb, &full_bar[stage], (int32_t)(kb * BK), b_row0, (int32_t)batch);
-                    if (swiglu) tma_load_3d(sb + b_bytes, mb2, &full_bar[stage], (int32_t)(kb * BK), b_row0, (int32_t)batch);
+                    tma_load_3d(sa, &map_a, &full_bar[stage], (int32_t)(kb * BK), (int32_t)(tm * BM), za);
+                    tma_load_3d(sb, mb, &full_bar[stage], (int32_t)(kb * BK), b_row0, zb);
+                    if (swiglu) tma_load_3d(sb + b_bytes, mb2, &full_bar[stage], (int32_t)(kb * BK), b_row0, zb);
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -138,7 +153,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (elect_one()) {
-            const uint32_t idesc_whole = make_idesc_bf16(BM, BN), idesc_half = make_idesc_bf16(BM, BN / 2);
+            // FP16 operands clear the two operand-format fields (bits 7-9 and 10-12: 1 = BF16, 0 = FP16)
+            const uint32_t fmt_mask = p.f16_operands ? ~((1u << 7) | (1u << 10)) : ~0u;
+            const uint32_t idesc_whole = make_idesc_bf16(BM, BN) & fmt_mask, idesc_half = make_idesc_bf16(BM, BN / 2) & fmt_mask;
             uint32_t stage = 0, phase = 0, iter = 0;
             bool ok = true;
             for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x, ++iter) {
@@ -147,7 +164,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 if (!(ok = mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_word))) break;
                 tc_fence_after();
                 const uint32_t tmem_d = tmem_base + acc * BN;
-                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                for (uint32_t kb = 0; kb < total_kb; ++kb) {
                     if (!(ok = mbar_wait(&full_bar[stage], phase, abort_word))) break;
                     tc_fence_after();
                     uint8_t* sa = smem + stage * C::STAGE_BYTES;
@@ -209,8 +226,32 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], sbias[c + j]);
                     }
                 }
-                if (row < p.m) {
-                    if (p.out_f32) {
+                if (row < p.m && p.ragged) {
+                    // rows that are not multiples of 16 bytes: one element per store
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        if (col0 + c + j < p.n) {
+                            const size_t at = out_off + col0 + c + j;
+                            if (p.out_f32 == 1) static_cast<float*>(p.out)[at] = v[j];
+                            else if (p.out_f32 == 2) static_cast<__half*>(p.out)[at] = __float2half_rn(v[j]);
+                            else static_cast<bf*>(p.out)[at] = __float2bfloat16_rn(v[j]);
+                        }
+                    }
+                } else if (row < p.m) {
+                    if (p.out_f32 == 2) {
+                        __half* o = static_cast<__half*>(p.out) + out_off + col0 + c;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            if (col0 + c + j < p.n) {
+                                __half2 q0 = __floats2half2_rn(v[j], v[j + 1]), q1 = __floats2half2_rn(v[j + 2], v[j + 3]);
+                                __half2 q2 = __floats2half2_rn(v[j + 4], v[j + 5]), q3 = __floats2half2_rn(v[j + 6], v[j + 7]);
+                                uint4 w;
+                                w.x = *reinterpret_cast<uint32_t*>(&q0); w.y = *reinterpret_cast<uint32_t*>(&q1);
+                                w.z = *reinterpret_cast<uint32_t*>(&q2); w.w = *reinterpret_cast<uint32_t*>(&q3);
+                                *reinterpret_cast<uint4*>(o + j) = w;
+                            }
+                        }
+                    } else if (p.out_f32) {
                         float* o = static_cast<float*>(p.out) + out_off + col0 + c;
 #pragma unroll
                         for (int j = 0; j < 32; j += 4)
@@ -324,28 +365,41 @@ int32_t poll_kernel_status(rb_ctx* ctx) {
     return RB_OK;
 }
 
-// C[batches, m, n] = A_k[batches, m, k] * B_k[batches, n, k]^T with both operands already K-major.
-int32_t gemm_kmajor(rb_ctx* ctx, const void* a, const void* b, const void* b_up, uint32_t batches, uint32_t m, uint32_t n, uint32_t k,
-                    int epilogue, const void* bias, bool bias_bf16, void* out, bool out_f32) {
+int32_t gemm_run(rb_ctx* ctx, const GemmCall& c) {
     GemmParams p{};
-    p.m = m; p.n = n; p.k = k; p.batches = batches; p.epilogue = (uint32_t)epilogue; p.out_f32 = out_f32; p.bias_bf16 = bias_bf16;
-    p.out = out; p.bias = bias;
+    p.m = c.m; p.n = c.n; p.k = c.k; p.batches = c.batches; p.epilogue = (uint32_t)c.epilogue; p.out_f32 = c.out_kind; p.bias_bf16 = c.bias_bf16;
+    p.out = c.out; p.bias = c.bias;
+    p.f16_operands = c.f16_operands; p.ragged = c.ragged; p.nseg = c.nseg; p.parts_a = c.parts_a; p.parts_b = c.parts_b;
+    for (int i = 0; i < 6; ++i) { p.seg_a[i] = c.seg_a[i]; p.seg_b[i] = c.seg_b[i]; }
+    p.a_bcast = c.a_bcast; p.b_bcast = c.b_bcast; p.group_ends = c.group_ends; p.groups = c.groups;
     RB_TRY(kernel_status_word(ctx, &p.status));
-    const bool swiglu = epilogue == RB_EPILOGUE_SWIGLU;
+    const bool swiglu = c.epilogue == RB_EPILOGUE_SWIGLU;
     // Tile width: the widest accumulator that does not leave most of the tile empty.
-    int bn = n > 128 || swiglu ? 256 : (n > 64 ? 128 : 64);
-    if (swiglu && n <= 64) bn = 128;
+    int bn = c.n > 128 || swiglu ? 256 : (c.n > 64 ? 128 : 64);
+    if (swiglu && c.n <= 64) bn = 128;
     const uint32_t bn_out = swiglu ? bn / 2 : bn;
-    p.tiles_m = (m + BM - 1) / BM; p.tiles_n = (n + bn_out - 1) / bn_out;
+    p.tiles_m = (c.m + BM - 1) / BM; p.tiles_n = (c.n + bn_out - 1) / bn_out;
     plan_tail(ctx, p, bn_out);
+    const uint64_t za = (uint64_t)(c.a_bcast ? 1 : c.batches) * c.parts_a;
+    const uint64_t zb = c.group_ends ? c.groups : (uint64_t)(c.b_bcast ? 1 : c.batches) * c.parts_b;
+    const uint64_t ar = c.a_rows ? c.a_rows : c.m, br = c.b_rows ? c.b_rows : c.n;
     CUtensorMap ma, mb, mb2, mbh, mb2h;
-    if (!make_operand_map(&ma, a, batches, m, k, BM) || !make_operand_map(&mb, b, batches, n, k, bn_out) ||
-        !make_operand_map(&mb2, swiglu ? b_up : b, batches, n, k, bn_out) || !make_operand_map(&mbh, b, batches, n, k, bn_out / 2) ||
-        !make_operand_map(&mb2h, swiglu ? b_up : b, batches, n, k, bn_out / 2))
-        return fail(RB_STATUS, "cuTensorMapEncodeTiled failed for a GEMM operand (m=%u n=%u k=%u)", m, n, k);
+    if (!make_operand_map(&ma, c.a, za, ar, c.k, BM) || !make_operand_map(&mb, c.b, zb, br, c.k, bn_out) ||
+        !make_operand_map(&mb2, swiglu ? c.b_up : c.b, zb, br, c.k, bn_out) || !make_operand_map(&mbh, c.b, zb, br, c.k, bn_out / 2) ||
+        !make_operand_map(&mb2h, swiglu ? c.b_up : c.b, zb, br, c.k, bn_out / 2))
+        return fail(RB_STATUS, "cuTensorMapEncodeTiled failed for a GEMM operand (m=%u n=%u k=%u)", c.m, c.n, c.k);
     if (bn == 256) return launch<256>(ctx, ma, mb, mb2, mbh, mb2h, p);
     if (bn == 128) return launch<128>(ctx, ma, mb, mb2, mbh, mb2h, p);
     return launch<64>(ctx, ma, mb, mb2, mbh, mb2h, p);
+}
+
+// C[batches, m, n] = A_k[batches, m, k] * B_k[batches, n, k]^T with both operands already K-major.
+int32_t gemm_kmajor(rb_ctx* ctx, const void* a, const void* b, const void* b_up, uint32_t batches, uint32_t m, uint32_t n, uint32_t k,
+                    int epilogue, const void* bias, bool bias_bf16, void* out, bool out_f32) {
+    GemmCall c;
+    c.a = a; c.b = b; c.b_up = b_up; c.batches = batches; c.m = m; c.n = n; c.k = k; c.epilogue = epilogue; c.bias = bias; c.bias_bf16 = bias_bf16;
+    c.out = out; c.out_kind = out_f32 ? 1 : 0;
+    return gemm_run(ctx, c);
 }
 
 }  // namespace rb
@@ -494,6 +548,7 @@ extern "C" int32_t rb_gemm_no_alloc(rb_ctx* ctx, const rb_tensor* a, const rb_te
     GemmParams p{};
     p.m = (uint32_t)m; p.n = (uint32_t)n; p.k = (uint32_t)k; p.batches = (uint32_t)ba; p.epilogue = RB_EPILOGUE_NONE;
     p.out_f32 = out->dtype == RB_F32; p.out = po; p.status = status;
+    p.nseg = 1; p.parts_a = 1; p.parts_b = 1;
     const int bn = n > 128 ? 256 : (n > 64 ? 128 : 64);
     p.tiles_m = (p.m + BM - 1) / BM; p.tiles_n = (p.n + bn - 1) / bn;
     plan_tail(ctx, p, (uint32_t)bn);

@@ -40,6 +40,17 @@ RB_HD void rb_gemm_item(uint32_t item, uint32_t split, uint32_t& tile, uint32_t&
     tile = split + (i >> 1); half = i & 1u;
 }
 
+// M-grouped GEMM (GroupEnds, deepgemm/plan.rs:15-29): `ends` are nondecreasing row prefix sums, group g owns rows
+// [ends[g-1], ends[g]).  Returns the group that owns `row` (the first g with row < ends[g]); empty groups own nothing.
+RB_HD uint32_t rb_group_of(const int32_t* ends, uint32_t groups, uint32_t row) {
+    uint32_t lo = 0, hi = groups;            // invariant: the answer is in [lo, hi)
+    while (lo + 1 < hi) {
+        const uint32_t mid = (lo + hi) / 2;
+        if ((uint32_t)ends[mid - 1] <= row) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
 // Key blocks of `block` keys that query rows [row0, row_end) of an M-row, N-key problem must visit.  Under the causal
 // rule of mask_programs.rs:30-37 key k is hidden from query q iff k > q + delta (delta = query_start - key_start), so
 // the last visible key of the tile is (min(row_end, M) - 1) + delta.
@@ -53,13 +64,42 @@ RB_HD uint32_t rb_attention_blocks(uint32_t M, uint32_t N, int causal, int64_t d
     return need < (int64_t)all ? (uint32_t)need : all;
 }
 
-// Work items of the persistent attention kernel: one item = one block of query rows of one (batch, head).  Items are numbered
-// so that the query blocks with the most visible keys (the last ones under a causal mask) come first and the heads of one
-// batch entry, and therefore of one KV group, are neighbours; CTA c of a grid of G takes items c, c + G, c + 2G, ...
-RB_HD void rb_attention_item(uint32_t item, uint32_t q_blocks, uint32_t heads_total, uint32_t heads, uint32_t& qb, uint32_t& h, uint32_t& b) {
-    qb = q_blocks - 1 - item / heads_total;
-    const uint32_t r = item % heads_total;
-    h = r % heads; b = r / heads;
+// Work items of the persistent attention kernel: one item = one block of query rows of one (batch, head).  The order serves
+// two ends.  Cache reuse: the heads are taken in waves of a few neighbouring heads (about two rounds of work for the grid), so
+// the K and V tiles of a head are read from DRAM once and then found in L2 by the other query blocks of that head and by the
+// other query heads of its KV group.  Load balance: inside a wave the items are sorted by cost (under a causal mask the last
+// query blocks see the most keys, so they come first) and the CTAs walk the wave's list in a zigzag: place r * G + c in even
+// rounds r, r * G + (G - 1 - c) in odd rounds, so a CTA that drew an expensive item in one round draws a cheap one in the next.
+// Heads per wave: at most two rounds of work, and the same number in every wave (a short last wave would leave the CTAs that drew
+// its expensive items without cheap ones to pair them with).
+RB_HD uint32_t rb_attention_wave_heads(uint32_t q_blocks, uint32_t heads_total, uint32_t ctas) {
+    uint32_t most = (2 * ctas) / (q_blocks ? q_blocks : 1);
+    if (most == 0) most = 1;
+    if (heads_total == 0) return 1;
+    const uint32_t waves = (heads_total + most - 1) / most;
+    return (heads_total + waves - 1) / waves;
+}
+// Steps every CTA of the grid walks: waves x rounds per (full) wave.
+RB_HD uint32_t rb_attention_steps(uint32_t q_blocks, uint32_t heads_total, uint32_t wave_heads, uint32_t ctas) {
+    const uint32_t waves = (heads_total + wave_heads - 1) / wave_heads;
+    const uint32_t in_wave = wave_heads < heads_total ? wave_heads : heads_total;
+    return waves * ((in_wave * q_blocks + ctas - 1) / ctas);
+}
+// Item of CTA `cta` in step `step`; false when the CTA has nothing to do in that step (the end of a wave's list).
+RB_HD bool rb_attention_item(uint32_t step, uint32_t cta, uint32_t ctas, uint32_t q_blocks, uint32_t heads_total, uint32_t heads, uint32_t wave_heads,
+                             uint32_t& qb, uint32_t& h, uint32_t& b) {
+    const uint32_t in_full = wave_heads < heads_total ? wave_heads : heads_total;
+    const uint32_t rounds = (in_full * q_blocks + ctas - 1) / ctas;
+    const uint32_t wave = step / rounds, r = step - wave * rounds;
+    const uint32_t first = wave * wave_heads;
+    if (first >= heads_total) return false;
+    const uint32_t in_wave = heads_total - first < wave_heads ? heads_total - first : wave_heads;   // the last wave may be short
+    const uint32_t place = r * ctas + ((r & 1u) ? ctas - 1 - cta : cta);
+    if (place >= in_wave * q_blocks) return false;
+    qb = q_blocks - 1 - place / in_wave;
+    const uint32_t head = first + place % in_wave;
+    h = head % heads; b = head / heads;
+    return true;
 }
 
 // Scatter GEMM (row-parallel projection whose output rows belong to `world` owners of rows_per_owner rows each).

@@ -604,14 +604,21 @@ class B200Runtime:
         (runtime/mod.rs:367-370 -> matrix.rs:129-133)."""
         if len(input.shape) != 2 or len(weight.shape) != 2:
             raise InvalidTensor("linear requires rank-2 X[M,K] and W[N,K]")
-        return B200Runtime.gemm_bf16_fp32(client, input, weight, Transpose.No, Transpose.Yes)
+        if input.dtype != DType.F32 or weight.dtype != DType.F32:
+            raise InvalidTensor("gemm_bf16_fp32 requires FP32 inputs")
+        y = client.tensor((input.shape[0], weight.shape[0]), DType.F32)
+        x16, w16 = client.tensor(input.shape, DType.BF16), client.tensor(weight.shape, DType.BF16)
+        _check(client._lib.rb_linear_bf16_fp32(client._ctx, _ref(input), _ref(weight), _ref(y), _ref(x16), _ref(w16)))
+        return [y, x16, w16]
 
     @staticmethod
     def linear_frozen_bf16_fp32(client, input: TensorBuffer, weight: TensorBuffer) -> TensorBuffer:
         """FP32 X times a fixed BF16 W^T, FP32 result, no weight copy (runtime/mod.rs:383-385 -> matrix.rs:147-159)."""
-        if input.dtype != DType.F32 or weight.dtype != DType.BF16:
+        if input.dtype != DType.F32 or weight.dtype != DType.BF16 or len(input.shape) != 2 or len(weight.shape) != 2:
             raise InvalidTensor("frozen linear requires FP32 input and BF16 weight storage")
-        return B200Runtime.gemm(client, B200Runtime.cast(client, input, DType.BF16), weight, Transpose.No, Transpose.Yes, DType.F32)
+        y = client.tensor((input.shape[0], weight.shape[0]), DType.F32)
+        _check(client._lib.rb_linear_frozen_bf16(client._ctx, _ref(input), _ref(weight), _ref(y), None))
+        return y
 
 
     # -- dtype-preserving broadcast matmul (runtime/generic_matrix.rs; the vendor aclnnMatmul(KEEP_DTYPE) in the reference) ----
@@ -632,76 +639,17 @@ class B200Runtime:
         return tuple(batch) + (a_shape[-2], b_shape[-1])
 
     @staticmethod
-    def _bf16_parts(client, t: TensorBuffer):
-        """t as a sum of BF16 tensors, exactly for finite values: one part for BF16 storage, two for FP16 (11 significant bits),
-        three for FP32 (24 bits).  Built from the cast, scalar-division and add entry points."""
-        RT = B200Runtime
-        if t.dtype == DType.BF16:
-            return [t]
-        rest = t if t.dtype == DType.F32 else RT.cast(client, t, DType.F32)
-        parts = []
-        for index in range(2 if t.dtype == DType.F16 else 3):
-            part = RT.cast(client, rest, DType.BF16)
-            parts.append(part)
-            if index + 1 < (2 if t.dtype == DType.F16 else 3):
-                negative = RT.cast(client, part, DType.F32)
-                _check(client._lib.rb_mul_scalar(client._ctx, _ref(negative), C.c_float(-1.0), _ref(negative)))
-                rest = RT.add(client, rest, negative)              # exact: the part holds the leading bits of `rest`
-        return parts
-
-    @staticmethod
     def tensor_matmul(client, a: TensorBuffer, b: TensorBuffer) -> TensorBuffer:
         """A[..., M, K] @ B[..., K, N] in the operands' own dtype (FP32, FP16 or BF16), ranks 2..6, singleton batch axes
-        broadcasting, any non-negative sizes (runtime/mod.rs:156-158 -> generic_matrix.rs:17-54).  The products run on the BF16
-        tensor-core GEMM with FP32 accumulation: BF16 operands directly; FP16 and FP32 operands as exact sums of two or three
-        BF16 parts, whose cross products are accumulated in FP32 smallest first (FP32: the three terms below 2^-26 of the
-        result are dropped), so the result carries the precision of the storage type rather than BF16's.  Finite inputs."""
-        RT = B200Runtime
+        broadcasting, any non-negative sizes (runtime/mod.rs:156-158 -> generic_matrix.rs:17-54): rb_tensor_matmul.  BF16 and FP16
+        operands go to the tensor cores in their own format; FP32 operands as three BF16 parts whose six leading cross products
+        accumulate in one FP32 accumulator, smallest first, so the result carries FP32's precision rather than BF16's."""
         floats = (DType.F32, DType.F16, DType.BF16)
         if a.dtype not in floats or b.dtype != a.dtype or not 2 <= len(a.shape) <= 6 or not 2 <= len(b.shape) <= 6:
             raise InvalidTensor("generic Ascend matmul requires matching floating dtypes and rank 2..6")
-        out_shape = RT.matmul_shape(a.shape, b.shape)
-        m, k, n = a.shape[-2], a.shape[-1], b.shape[-1]
-        if 0 in out_shape or k == 0:                     # an empty result, or an empty contraction: zeros
-            out = client.tensor(out_shape, a.dtype)
-            if out.elements:
-                client.memset(out, 0)
-            return out
-        batch = out_shape[:-2]
-        count = lambda dims: int(np.prod(dims)) if len(dims) else 1
-        na, nb, no = count(a.shape[:-2]), count(b.shape[:-2]), count(batch)
-        up = lambda d: (d + 15) // 16 * 16
-        mp, kp, np_ = up(m), up(k), up(n)
-        pa = [RT.resize_prefix(client, t.reshape((na, m, k)), (na, mp, kp)) for t in RT._bf16_parts(client, a)]
-        pb = [RT.resize_prefix(client, t.reshape((nb, k, n)), (nb, kp, np_)) for t in RT._bf16_parts(client, b)]
-        limit = max(len(pa), len(pb)) - 1
-        pairs = sorted(((i, j) for i in range(len(pa)) for j in range(len(pb)) if i + j <= limit), key=lambda ij: -(ij[0] + ij[1]))
-        acc = client.tensor((no, mp, np_), DType.F32)
-        same_batches = tuple(a.shape[:-2]) == tuple(b.shape[:-2]) and no <= 4096
-
-        def slab(t, index, rows, cols):
-            return TensorBuffer(t.handle, (rows, cols), t.dtype, None, offset=t.offset + index * rows * cols * t.dtype.size, _owner=t._owner)
-
-        def products(out_t, first):
-            """out_t (+)= sum over the part pairs, for one batched launch set or one batch entry."""
-            for number, (i, j) in enumerate(pairs):
-                x, y = first(pa[i], True), first(pb[j], False)
-                if number == 0:
-                    RT.gemm_into(client, x, y, Transpose.No, Transpose.No, out_t)
-                else:
-                    term = RT.gemm(client, x, y, Transpose.No, Transpose.No, DType.F32)
-                    RT.add(client, out_t, term, out=out_t)
-        if same_batches:
-            products(acc, lambda t, is_a: t)
-        else:
-            ba = (1,) * (len(batch) - len(a.shape[:-2])) + tuple(a.shape[:-2])
-            bb = (1,) * (len(batch) - len(b.shape[:-2])) + tuple(b.shape[:-2])
-            for flat, index in enumerate(np.ndindex(*batch)):
-                ia = int(np.ravel_multi_index([0 if d == 1 else i for i, d in zip(index, ba)], ba)) if ba else 0
-                ib = int(np.ravel_multi_index([0 if d == 1 else i for i, d in zip(index, bb)], bb)) if bb else 0
-                products(slab(acc, flat, mp, np_), lambda t, is_a: slab(t, ia, mp, kp) if is_a else slab(t, ib, kp, np_))
-        cropped = RT.resize_prefix(client, acc, (no, m, n)).reshape(out_shape)
-        return cropped if a.dtype == DType.F32 else RT.cast(client, cropped, a.dtype)
+        out = client.tensor(B200Runtime.matmul_shape(a.shape, b.shape), a.dtype)
+        _check(client._lib.rb_tensor_matmul(client._ctx, _ref(a), _ref(b), _ref(out)))
+        return out
 
     @staticmethod
     def matmul_fp32(client, a: TensorBuffer, b: TensorBuffer) -> TensorBuffer:
@@ -729,9 +677,8 @@ class B200Runtime:
     @staticmethod
     def gemm_grouped_nt(client, a: TensorBuffer, weights: TensorBuffer, ends, dtype: DType) -> TensorBuffer:
         """M-grouped GEMM of GemmSpec::grouped_nt (deepgemm/plan.rs:61-67, tile walk scheduler.rs:21-33): A [M,K], weights
-        [G,N,K], rows [ends[g-1], ends[g]) of A meet expert g's weight; output [M,N].  One launch of the dense kernel per
-        non-empty group on row slices of A and of the output (groups start on 256-row boundaries, so every slice is a
-        whole number of 128-row tiles)."""
+        [G,N,K], rows [ends[g-1], ends[g]) of A meet expert g's weight; output [M,N].  rb_gemm_grouped_nt: one persistent launch
+        over all groups (groups start on 256-row boundaries, so every 128-row tile belongs to one group)."""
         ends = B200Runtime.group_ends(ends)
         if len(a.shape) != 2 or len(weights.shape) != 3:
             raise InvalidTensor("grouped NT requires [M,K] and [G,N,K]")
@@ -744,16 +691,7 @@ class B200Runtime:
         if any(x <= 0 or x % 16 or x > 2**31 - 1 for x in (m, n, k)):
             raise InvalidTensor("M/N/K must be positive multiples of 16 <= INT32_MAX; batches/groups 1..=4096")
         out = client.tensor((m, n), dtype)
-        size = DType(dtype).size
-        start = 0
-        for group, end in enumerate(ends):
-            rows = end - start
-            if rows:
-                a_g = TensorBuffer(a.handle, (rows, k), DType.BF16, None, offset=a.offset + start * k * 2, _owner=a._owner)
-                w_g = TensorBuffer(weights.handle, (n, k), DType.BF16, None, offset=weights.offset + group * n * k * 2, _owner=weights._owner)
-                o_g = TensorBuffer(out.handle, (rows, n), dtype, None, offset=start * n * size, _owner=out._owner)
-                B200Runtime.gemm_into(client, a_g, w_g, Transpose.No, Transpose.Yes, o_g)
-            start = end
+        _check(client._lib.rb_gemm_grouped_nt(client._ctx, _ref(a), _ref(weights), (C.c_int64 * len(ends))(*ends), C.c_uint32(len(ends)), _ref(out)))
         return out
 
     # -- matrices whose axes are not multiples of 16 (runtime/padded_matrix.rs, deepgemm/padded.rs) --------------
@@ -794,9 +732,9 @@ class B200Runtime:
         if a.dtype != DType.F32 or b.dtype != DType.F32:
             raise InvalidTensor("padded trainable matmul requires FP32 inputs")
         out_shape, pa, pb = B200Runtime._padded_spec(a.shape, b.shape, a.dtype, b.dtype, ta, tb)
-        a16, b16 = B200Runtime._rounded(client, a, pa), B200Runtime._rounded(client, b, pb)
-        y = B200Runtime.gemm(client, a16, b16, ta, tb, DType.F32)
-        return [B200Runtime.resize_prefix(client, y, out_shape), a16, b16]
+        y, a16, b16 = client.tensor(out_shape, DType.F32), client.tensor(pa, DType.BF16), client.tensor(pb, DType.BF16)
+        _check(client._lib.rb_gemm_padded(client._ctx, _ref(a), _ref(b), C.c_int32(int(ta)), C.c_int32(int(tb)), _ref(y), _ref(a16), _ref(b16)))
+        return [y, a16, b16]
 
     @staticmethod
     def gemm_padded_bf16_fp32_backward(client, a: TensorBuffer, b: TensorBuffer, grad: TensorBuffer, a_shape, b_shape, ta: Transpose, tb: Transpose):
@@ -954,39 +892,25 @@ class B200Runtime:
         _, hkv, n, dv = v.shape
         if hkv == 0 or hq % hkv or k.shape != (b, hkv, n, d) or v.shape[0] != b or grad.shape != (b, hq, m, dv):
             raise InvalidTensor("GQA requires matching batches, positive divisible Q/KV heads and matching K/V lengths and Q/K widths")
-        if not np.isfinite(scale) or scale == 0.0:
-            raise InvalidTensor("attention backward needs a finite non-zero scale")
+        if not np.isfinite(scale):
+            raise InvalidTensor("attention backward needs a finite scale")
         flat = b * hq
         if mask is not None and (mask.dtype != DType.F32 or mask.elements != flat * m * n):
             raise InvalidTensor("attention additive mask must be FP32 [B,Hq,M,N]")
-        bf = lambda t, shape: RT.cast(client, t, DType.BF16).reshape(shape)
-        no, yes = Transpose.No, Transpose.Yes
-        qb, gb = bf(q, (flat, m, d)), bf(grad, (flat, m, dv))
-        kb = bf(RT.repeat_kv_heads(client, k, hq), (flat, n, d))
-        vb = bf(RT.repeat_kv_heads(client, v, hq), (flat, n, dv))
-
-        def times_scale(t):   # t * scale, one FP32 multiply per element like the reference's graph
-            _check(client._lib.rb_mul_scalar(client._ctx, _ref(t), C.c_float(scale), _ref(t)))
-            return t
-        scores = times_scale(RT.gemm(client, qb, kb, no, yes, DType.F32))
-        additive = mask.reshape((flat, m, n)) if mask is not None else None
-        if causal:
-            tri = RT.causal_mask(client, flat, m, n, query_start, key_start)
-            additive = tri if additive is None else RT.add(client, additive, tri)
-        if additive is not None:
-            RT.add(client, scores, additive, out=scores)
-        p = RT.softmax(client, scores)
-        dp = RT.gemm(client, gb, vb, no, yes, DType.F32)
-        ds = RT.softmax_backward(client, p, dp)
-        dmask = RT.copy_contiguous(client, ds).reshape((b, hq, m, n)) if want_mask_grad else None
-        dsb = RT.cast(client, times_scale(ds), DType.BF16)
-        pb = RT.cast(client, p, DType.BF16)
-        dq = RT.gemm(client, dsb, kb, no, no, DType.F32).reshape((b, hq, m, d))
-        dk = RT.repeat_kv_heads_backward(client, k.shape, hq, RT.gemm(client, dsb, qb, yes, no, DType.F32).reshape((b, hq, n, d)))
-        dv_ = RT.repeat_kv_heads_backward(client, v.shape, hq, RT.gemm(client, pb, gb, yes, no, DType.F32).reshape((b, hq, n, dv)))
+        dq, dk, dv_ = client.tensor(q.shape, DType.F32), client.tensor(k.shape, DType.F32), client.tensor(v.shape, DType.F32)
+        dmask = client.tensor((b, hq, m, n), DType.F32) if want_mask_grad else None
+        _check(client._lib.rb_attention_backward(client._ctx, _ref(q), _ref(k), _ref(v), _ref(grad), _ref(mask), C.c_float(scale), C.c_int32(int(causal)),
+                                                 C.c_uint64(query_start), C.c_uint64(key_start), _ref(dq), _ref(dk), _ref(dv_), _ref(dmask)))
         return [dq, dk, dv_] + ([dmask] if want_mask_grad else [])
 
     # -- attention -------------------------------------------------------------------------------
+    @staticmethod
+    def attention_launch_counts(client) -> dict:
+        """How many attention calls of this context ran on the tensor-core kernel and how many on the general row kernel."""
+        fast, general = C.c_uint64(), C.c_uint64()
+        _check(client._lib.rb_attention_launch_counts(client._ctx, C.byref(fast), C.byref(general)))
+        return {"tensor_core": fast.value, "general": general.value}
+
     @staticmethod
     def attention(client, q: TensorBuffer, k: TensorBuffer, v: TensorBuffer, scale: float, mask: TensorBuffer | None = None,
                   causal: bool = False, query_start: int = 0, key_start: int = 0, cos: TensorBuffer | None = None,

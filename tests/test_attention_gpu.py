@@ -200,3 +200,78 @@ def test_config4_as_stated_rows_sample(client, oracle):
             qr = oracle.bf16(oracle.rotary(q[bi:bi + 1, h:h + 1, r0:r1], tq[0], tq[1], "split_half"))
             want = oracle.attention(qr, kr, v[bi:bi + 1, kvh:kvh + 1], SCALE, causal=True, query_start=r0)
             check_bf16(got[bi:bi + 1, h:h + 1, r0:r1], want)
+
+
+# ---- the reference's own contract (FP32 tensors) on the tensor-core kernel ---------------------------------------
+def test_fp32_contract_at_head_dim_128_runs_on_the_tensor_core_kernel(client, oracle):
+    """nn.causal_grouped_query_attention_bf16_fp32 (src/nn/attention.rs:69-80) takes FP32 Q/K/V; at head dim 128 the call must
+    reach the tcgen05 kernel (launch counter), and its FP32 output must meet the BF16 tolerance against the oracle, which rounds
+    the operands and P to BF16 where the reference does."""
+    rng = np.random.default_rng(21)
+    b, hq, hkv, m, n = 2, 8, 2, 384, 512
+    q = rng.standard_normal((b, hq, m, 128), dtype=np.float32); k = rng.standard_normal((b, hkv, n, 128), dtype=np.float32)
+    v = rng.standard_normal((b, hkv, n, 128), dtype=np.float32)
+    T = lambda a: nn.Tensor.from_data(client, a)
+    before = RT.attention_launch_counts(client)
+    out = nn.causal_grouped_query_attention_bf16_fp32(T(q), T(k), T(v), float(SCALE), n - m, 0)
+    after = RT.attention_launch_counts(client)
+    assert after["tensor_core"] == before["tensor_core"] + 1 and after["general"] == before["general"]
+    assert out.dtype() == DType.F32 and out.dims() == [b, hq, m, 128]
+    check_bf16(out.into_data(), oracle.attention(q, k, v, SCALE, causal=True, query_start=n - m))
+    # the plain and the grouped non-causal entry points take the same route
+    out2 = nn.grouped_query_attention_bf16_fp32(T(q), T(k), T(v), float(SCALE), None)
+    assert RT.attention_launch_counts(client)["tensor_core"] == after["tensor_core"] + 1
+    check_bf16(out2.into_data(), oracle.attention(q, k, v, SCALE))
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+def test_additive_mask_tiles_on_the_tensor_core_kernel(client, oracle, dtype):
+    """An additive FP32 mask [B,Hq,M,N] (src/nn/attention.rs:10-29) joins the scores inside the tensor-core kernel: finite
+    biases, -inf entries, a key block cut by the end of the keys, and one row whose keys are all excluded (no value: NaN, as
+    the reference's softmax of a row of -inf gives)."""
+    rng = np.random.default_rng(22)
+    b, hq, hkv, m, n = 1, 4, 2, 272, 416
+    q, k, v = rand_qkv(23, b, hq, hkv, m, n)
+    mask = rng.standard_normal((b, hq, m, n)).astype(np.float32)
+    mask[rng.random(mask.shape) < 0.3] = -np.inf
+    mask[0, 1, 5, :] = -np.inf                                   # a row without any visible key
+    mask[0, 2, 100, :300] = -np.inf                              # whole key blocks hidden, the tail visible
+    before = RT.attention_launch_counts(client)["tensor_core"]
+    if dtype == "bf16":
+        out = RT.attention(client, up16(client, q), up16(client, k), up16(client, v), SCALE, mask=client.upload(mask))
+        got = bf16_bits_to_f32(client.read(out))
+    else:
+        out = RT.attention(client, client.upload(q), client.upload(k), client.upload(v), SCALE, mask=client.upload(mask))
+        got = client.read(out)
+    assert RT.attention_launch_counts(client)["tensor_core"] == before + 1
+    want = oracle.attention(q, k, v, SCALE, mask=mask)
+    assert np.isnan(got[0, 1, 5]).all() and np.isnan(want[0, 1, 5]).all()
+    keep = np.ones((b, hq, m), bool); keep[0, 1, 5] = False
+    check_bf16(got[keep], want[keep])
+
+
+def test_rows_without_visible_keys_have_no_value(client, oracle):
+    """Causal attention whose first queries lie before every key (key_start > query_start + row): the reference's mask is -inf
+    over the whole row and its softmax gives NaN; the tensor-core kernel and the oracle agree with that, tile by tile and row by row."""
+    q, k, v = rand_qkv(31, 1, 2, 2, 384, 256)
+    out = RT.attention(client, up16(client, q), up16(client, k), up16(client, v), SCALE, causal=True, query_start=0, key_start=200)
+    got = bf16_bits_to_f32(client.read(out))
+    want = oracle.attention(q, k, v, SCALE, causal=True, query_start=0, key_start=200)
+    assert np.isnan(got[:, :, :200]).all() and np.isnan(want[:, :, :200]).all()      # rows 0..199 see no key (a whole tile and part of the next)
+    check_bf16(got[:, :, 200:], want[:, :, 200:])
+
+
+def test_fp32_contract_with_fused_rotary(client, oracle):
+    b, hq, hkv, m, n = 1, 4, 2, 256, 256
+    rng = np.random.default_rng(41)
+    q = rng.standard_normal((b, hq, m, 128), dtype=np.float32); k = rng.standard_normal((b, hkv, n, 128), dtype=np.float32)
+    v = rng.standard_normal((b, hkv, n, 128), dtype=np.float32)
+    pos = np.arange(n, dtype=np.float64)[:, None]
+    inv = 10000.0 ** (-np.arange(64, dtype=np.float64) * 2 / 128)
+    cos, sin = np.cos(pos * inv).astype(np.float32), np.sin(pos * inv).astype(np.float32)
+    out = RT.attention(client, client.upload(q), client.upload(k), client.upload(v), SCALE, causal=True, cos=client.upload(cos), sin=client.upload(sin),
+                       rotary_layout=RotaryLayout.SplitHalf)
+    tq = np.broadcast_to(cos[:m], (b, hq, m, 64)), np.broadcast_to(sin[:m], (b, hq, m, 64))
+    tk = np.broadcast_to(cos[:n], (b, hkv, n, 64)), np.broadcast_to(sin[:n], (b, hkv, n, 64))
+    qr = oracle.bf16(oracle.rotary(oracle.bf16(q), tq[0], tq[1], "split_half")); kr = oracle.bf16(oracle.rotary(oracle.bf16(k), tk[0], tk[1], "split_half"))
+    check_bf16(client.read(out), oracle.attention(qr, kr, v, SCALE, causal=True))

@@ -81,6 +81,43 @@ def test_gemm_tail_plan_covers_every_tile_once(host, tiles, ctas):
     assert (out[0], out[1]) == (tiles, tiles)                  # shapes whose half tiles would be too narrow keep whole tiles
 
 
+@pytest.mark.parametrize("q_blocks,batch,heads,ctas", [(8, 4, 32, 148), (16, 2, 32, 148), (32, 1, 32, 148), (1, 1, 1, 1), (3, 2, 5, 7), (8, 8, 4, 132), (1, 3, 7, 148), (40, 1, 2, 148)])
+def test_attention_item_order_is_a_balanced_bijection(host, q_blocks, batch, heads, ctas):
+    """Every (query block, head, batch) is visited exactly once over the CTAs' rounds; with the causal cost of an item (its number of
+    key-block pairs, growing with the query block) no CTA carries much more than the average; and the heads in flight at any
+    time are few, so that their K and V stay in L2."""
+    host.host_attention_wave_heads.restype = C.c_uint32; host.host_attention_steps.restype = C.c_uint32
+    heads_total = batch * heads
+    items = q_blocks * heads_total
+    grid = min(items, ctas)
+    wave = host.host_attention_wave_heads(q_blocks, heads_total, grid)
+    assert wave >= 1
+    out = (C.c_uint32 * 3)()
+    seen, load = set(), [0] * grid
+    for step in range(host.host_attention_steps(q_blocks, heads_total, wave, grid)):
+        in_flight = set()
+        for c in range(grid):
+            if not host.host_attention_item(step, c, grid, q_blocks, heads_total, heads, wave, out):
+                continue
+            qb, h, b = out[0], out[1], out[2]
+            assert qb < q_blocks and h < heads and b < batch
+            assert (qb, h, b) not in seen
+            seen.add((qb, h, b)); load[c] += 2 * qb + 2; in_flight.add((h, b))
+        assert len(in_flight) <= wave                    # one step stays inside one wave of heads
+    assert len(seen) == items
+    if items >= 4 * grid:
+        assert max(load) <= 1.10 * (sum(load) / grid) + 2 * q_blocks
+
+
+def test_group_lookup_matches_the_prefix_sums(host):
+    host.host_group_of.restype = C.c_uint32
+    ends = [256, 256, 768, 1024, 1024, 1280]
+    arr = (C.c_int32 * len(ends))(*ends)
+    for row in range(0, 1280, 128):
+        want = next(g for g, e in enumerate(ends) if row < e)
+        assert host.host_group_of(arr, len(ends), row) == want
+
+
 @pytest.mark.parametrize("M,N,delta", [(128, 128, 0), (256, 384, 128), (400, 416, 16), (48, 96, 48), (2048, 2048, 0), (128, 1024, 896), (64, 64, -100), (272, 2048, 1776)])
 def test_attention_block_count_matches_the_causal_rule(host, M, N, delta):
     for row0 in range(0, M + 256, 128):
