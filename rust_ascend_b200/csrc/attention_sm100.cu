@@ -380,7 +380,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 const uint32_t total_s = nb[0] + nb[1];
                 uint32_t s_done = 0;
                 const bool tr = trace_cta && round == 0;
+                RB_TR(trace_cta, 4, round, 0);                       // MMA: starts waiting for the item's Q
                 if (!(ok = mbar_wait(q_full, q_it & 1, abort_word))) break;
+                RB_TR(trace_cta, 4, round, 1);                       // MMA: Q has landed
                 {
                     const uint32_t st = kv_it % KV_STAGES, ph = (kv_it / KV_STAGES) & 1;
                     if (!(ok = mbar_wait(&k_full[st], ph, abort_word))) break;
@@ -389,6 +391,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     for (uint32_t t = 0; t < 2; ++t) if (nb[t] > 0) { issue_s(t, st); ++s_done; }
                     umma_commit(&k_empty[st]);
                     if (s_done == total_s) umma_commit(q_empty);
+                    RB_TR(trace_cta, 4, round, 2);                   // MMA: first score GEMMs issued
                 }
                 for (uint32_t j = 0; ok && j < n_max; ++j) {
                     const uint32_t st = (kv_it + j) % KV_STAGES, ph = ((kv_it + j) / KV_STAGES) & 1;
@@ -436,6 +439,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     }
                 }
                 kv_it += n_max; ++q_it;
+                RB_TR(trace_cta, 4, round, 3);                       // MMA: the item's last P V issued
             }
         }
     } else {
@@ -471,6 +475,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             const bool tr = trace_cta && round == 0 && quarter == 0 && lane == 0;
             const int64_t q_limit0 = (int64_t)(tile_row0 + quarter * 32) + p.delta;   // last visible key of this warp's first row (causal)
             float m_used = 0.f, l = 0.f;
+            const bool tri = trace_cta && t == 0 && quarter == 0 && lane == 0;
+            RB_TR(tri, 4, round, 4);                                 // softmax tile 0: item starts
             for (uint32_t j = 0; j < nb; ++j, ++blk) {
                 ok = wait_handoff(&s_full[t], blk & 1, abort_word);
                 if (!(ok = __all_sync(0xffffffffu, ok))) break;
@@ -496,9 +502,11 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 }
             }
             if (!ok) break;
+            RB_TR(tri, 4, round, 5);                                 // softmax tile 0: last P handed over
             // ---- epilogue of the item: O / l -> BF16 -> global ----
             ok = mbar_wait(&o_full[t], used & 1, abort_word);
             if (!(ok = __all_sync(0xffffffffu, ok))) break;
+            RB_TR(tri, 4, round, 6);                                 // softmax tile 0: O complete
             tc_fence_after();
             // a row that saw no key at all (every key hidden by the causal rule or by -inf mask values) has no value: NaN, as the
             // reference's softmax of a row of -inf gives
@@ -531,6 +539,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 }
             }
             ++used;
+            RB_TR(tri, 4, round, 7);                                 // softmax tile 0: epilogue stored
         }
     }
 

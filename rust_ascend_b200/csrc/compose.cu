@@ -107,13 +107,6 @@ __global__ void __launch_bounds__(256) pad_cast_kernel(const T* in, bf* out, uin
     }
 }
 
-int32_t matrix_batches(const rb_tensor* t, uint64_t* batches) {
-    uint64_t n = 1;
-    for (uint32_t i = 0; i + 2 < t->rank; ++i) n *= t->shape[i];
-    *batches = n;
-    return RB_OK;
-}
-
 }  // namespace
 
 extern "C" {

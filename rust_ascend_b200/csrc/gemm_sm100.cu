@@ -19,6 +19,8 @@
 // Operands that are not K-major (A transposed, B not transposed) are first rewritten K-major by a tiled
 // transpose kernel; the hot Linear layout (X [M,K], W [N,K]) needs no rewrite.
 #include "common.cuh"
+
+#include <cstdlib>
 #include "schedule.h"
 #include "sm100.cuh"
 
@@ -283,6 +285,196 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if (warp == 1) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem_base, C::TMEM_COLS); }
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// The same GEMM on pairs of CTAs (cluster of two, tcgen05 cta_group::2): one MMA covers a 256 x BN tile, each CTA of the pair
+// keeps 128 of its rows in its own TMEM and loads its own half of A and only HALF of B, since the tensor core reads the two
+// halves of B from the two CTAs' shared memory.  Per output tile that is a third less traffic from L2 into shared memory than
+// two independent 128 x BN tiles, and 32 KiB instead of 48 KiB per stage, so the ring is six stages deep instead of four.
+// Rank 0 of the pair (the leader) issues the MMAs; every completion is broadcast to the barriers of both CTAs.  Every CTA
+// fetches its own tiles (no cluster-broadcast load); it only reports their arrival to the leader's barrier.
+// Tail round: as above, a last round that would use at most half of the pairs runs as tiles of half the width.
+constexpr int PAIR_BN = 256;
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_A_BYTES = BM * BK * 2;                 // this CTA's 128 rows of A
+constexpr int PAIR_B_BYTES = (PAIR_BN / 2) * BK * 2;      // this CTA's half of B
+constexpr int PAIR_STAGE_BYTES = PAIR_A_BYTES + PAIR_B_BYTES;
+constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256 + 4 * 2 * 256 * 4;
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                      const __grid_constant__ CUtensorMap map_b2, const __grid_constant__ CUtensorMap map_bh,
+                      const __grid_constant__ CUtensorMap map_b2h, const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + PAIR_STAGES * PAIR_STAGE_BYTES);   // used in the leader only
+    uint64_t* empty_bar = full_bar + PAIR_STAGES;                                               // one copy per CTA
+    uint64_t* tmem_full = empty_bar + PAIR_STAGES;                                              // one copy per CTA
+    uint64_t* tmem_empty = tmem_full + 2;                                                       // used in the leader only: 256 arrivals
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    volatile uint32_t* abort_word = tmem_slot + 1;
+    float* bias_smem = reinterpret_cast<float*>(smem + PAIR_STAGES * PAIR_STAGE_BYTES + 256);
+
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();               // 0: leader
+    const uint32_t pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    const bool swiglu = p.epilogue == RB_EPILOGUE_SWIGLU;
+    const uint32_t bn_out = swiglu ? PAIR_BN / 2 : PAIR_BN;   // output columns of a whole tile
+    const uint32_t num_kb = (p.k + BK - 1) / BK;
+    const uint32_t num_tiles = p.items;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PAIR_STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full[a], 1); mbar_init(&tmem_empty[a], 256); }
+        *abort_word = 0;
+        fence_barrier_init();
+        prefetch_tmap(&map_a); prefetch_tmap(&map_b); if (swiglu) prefetch_tmap(&map_b2);
+        if (p.items > p.split) { prefetch_tmap(&map_bh); if (swiglu) prefetch_tmap(&map_b2h); }
+    }
+    if (warp == 1) { tmem_alloc_pair(tmem_slot, 2 * PAIR_BN); tmem_relinquish_pair(); }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();            // both CTAs' barriers exist before either reports to, or broadcasts into, the other
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer (one per CTA) ----------------
+        if (elect_one()) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (uint32_t t = pair; ok && t < num_tiles; t += pairs) {
+                uint32_t batch, tm, tn, half; tile_coords(t, p, batch, tm, tn, half);
+                const bool whole = half == 2;
+                // this CTA's rows of B: whole tile 128, half tile 64; with SwiGLU rank 0 holds gate rows and rank 1 up rows
+                const uint32_t b_rows = whole ? PAIR_BN / 2 : PAIR_BN / 4;
+                const uint32_t out_w = whole ? bn_out : bn_out / 2;          // output columns of this item
+                const uint32_t col0 = tn * bn_out + (whole ? 0 : half * out_w);
+                const int32_t b_row0 = (int32_t)(swiglu ? col0 : col0 + rank * b_rows);
+                const uint32_t b_bytes = b_rows * BK * 2;
+                const CUtensorMap* mb = swiglu && rank == 1 ? (whole ? &map_b2 : &map_b2h) : (whole ? &map_b : &map_bh);
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    if (!(ok = mbar_wait(&empty_bar[stage], phase ^ 1, abort_word))) break;
+                    uint8_t* sa = smem + stage * PAIR_STAGE_BYTES; uint8_t* sb = sa + PAIR_A_BYTES;
+                    const uint32_t leader_full = mapa_shared(smem_u32(&full_bar[stage]), 0);
+                    if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * (PAIR_A_BYTES + b_bytes));   // the bytes of both CTAs
+                    tma_load_3d_pair(sa, &map_a, leader_full, (int32_t)(kb * BK), (int32_t)(tm * 2 * BM + rank * BM), (int32_t)batch);
+                    tma_load_3d_pair(sb, mb, leader_full, (int32_t)(kb * BK), b_row0, (int32_t)batch);
+                    if (++stage == PAIR_STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (!ok) {
+                // A wait expired somewhere: give the copies in flight a bounded time to land before the CTA retires.
+                for (uint32_t i = 0; i < (1u << 22); ++i) __nanosleep(32);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (leader only) ----------------
+        if (rank == 0 && elect_one()) {
+            const uint32_t idesc_whole = make_idesc_bf16(2 * BM, PAIR_BN), idesc_half = make_idesc_bf16(2 * BM, PAIR_BN / 2);
+            uint32_t stage = 0, phase = 0, iter = 0;
+            bool ok = true;
+            for (uint32_t t = pair; ok && t < num_tiles; t += pairs, ++iter) {
+                const uint32_t acc = iter & 1, acc_phase = (iter >> 1) & 1;
+                const uint32_t idesc = t < p.split ? idesc_whole : idesc_half;
+                if (!(ok = mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_word))) break;
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + acc * PAIR_BN;
+                for (uint32_t kb = 0; kb < num_kb; ++kb) {
+                    if (!(ok = mbar_wait(&full_bar[stage], phase, abort_word))) break;
+                    tc_fence_after();
+                    uint8_t* sa = smem + stage * PAIR_STAGE_BYTES;
+                    const uint64_t da = make_kmajor_sw128_desc(smem_u32(sa)), db = make_kmajor_sw128_desc(smem_u32(sa + PAIR_A_BYTES));
+#pragma unroll
+                    for (uint32_t k = 0; k < BK / UMMA_K; ++k)
+                        umma_bf16_ss_pair(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0);
+                    umma_commit_pair(&empty_bar[stage]);       // frees the stage in both CTAs
+                    if (++stage == PAIR_STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (ok) umma_commit_pair(&tmem_full[acc]);     // wakes the epilogue warps of both CTAs
+            }
+        }
+    } else {
+        // ---------------- epilogue: 4 warps per CTA, one TMEM lane (= output row) per thread ----------------
+        const uint32_t quarter = warp & 3;
+        uint32_t iter = 0;
+        bool ok = true;
+        for (uint32_t t = pair; ok && t < num_tiles; t += pairs, ++iter) {
+            const uint32_t acc = iter & 1, acc_phase = (iter >> 1) & 1;
+            uint32_t batch, tm, tn, half; tile_coords(t, p, batch, tm, tn, half);
+            const bool whole = half == 2;
+            const uint32_t width = whole ? bn_out : bn_out / 2;
+            const uint32_t col0 = tn * bn_out + (whole ? 0 : half * width);
+            const uint32_t up_at = whole ? PAIR_BN / 2 : PAIR_BN / 4;     // TMEM column where the up half starts (SwiGLU)
+            float* sbias = bias_smem + (quarter * 2 + acc) * 256;
+            if (p.epilogue == RB_EPILOGUE_BIAS) {
+                for (uint32_t j = lane; j < width; j += 32) sbias[j] = col0 + j < p.n ? bias_at(p, col0 + j) : 0.f;
+                __syncwarp();
+            }
+            ok = mbar_wait(&tmem_full[acc], acc_phase, abort_word);
+            if (!(ok = __all_sync(0xffffffffu, ok))) break;
+            tc_fence_after();
+            const uint32_t row = tm * 2 * BM + rank * BM + quarter * 32 + lane;
+            const uint32_t taddr = tmem_base + acc * PAIR_BN + ((quarter * 32) << 16);
+            const size_t out_off = ((size_t)batch * p.m + row) * p.n;
+            for (uint32_t c = 0; c < width; c += 32) {
+                if (col0 + c >= p.n) break;  // warp-uniform
+                uint32_t r[32];
+                tmem_ld_32x32(taddr + c, r);
+                float v[32];
+                if (swiglu) {
+                    uint32_t u[32];
+                    tmem_ld_32x32(taddr + up_at + c, u);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        float g = __uint_as_float(r[j]);
+                        float sg = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-g)));
+                        v[j] = __fmul_rn(__fmul_rn(g, sg), __uint_as_float(u[j]));
+                    }
+                } else {
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                    if (p.epilogue == RB_EPILOGUE_BIAS) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) v[j] = __fadd_rn(v[j], sbias[c + j]);
+                    }
+                }
+                if (row < p.m) {
+                    if (p.out_f32) {
+                        float* o = static_cast<float*>(p.out) + out_off + col0 + c;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4)
+                            if (col0 + c + j < p.n) *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    } else {
+                        bf* o = static_cast<bf*>(p.out) + out_off + col0 + c;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            if (col0 + c + j < p.n) {
+                                __nv_bfloat162 q0 = __floats2bfloat162_rn(v[j], v[j + 1]), q1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+                                __nv_bfloat162 q2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), q3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+                                uint4 w;
+                                w.x = *reinterpret_cast<uint32_t*>(&q0); w.y = *reinterpret_cast<uint32_t*>(&q1);
+                                w.z = *reinterpret_cast<uint32_t*>(&q2); w.w = *reinterpret_cast<uint32_t*>(&q3);
+                                *reinterpret_cast<uint4*>(o + j) = w;
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            // hand the accumulator back to the leader's MMA thread: 128 arrivals from each CTA of the pair
+            mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty[acc]), 0));
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_word) atomicExch(p.status, 1u);
+    cluster_sync_all();            // nothing may still be reporting to this CTA's barriers when its shared memory goes away
+    if (warp == 1) { __syncwarp(); tc_fence_after(); tmem_dealloc_pair(tmem_base, 2 * PAIR_BN); }
+}
+
 // Batched BF16 transpose [batches, R, C] -> [batches, C, R] through a padded shared-memory tile.
 __global__ void __launch_bounds__(256) transpose_bf16_kernel(const uint16_t* in, uint16_t* out, uint32_t rows, uint32_t cols) {
     __shared__ uint16_t tile[64][66];
@@ -299,7 +491,7 @@ __global__ void __launch_bounds__(256) transpose_bf16_kernel(const uint16_t* in,
     }
 }
 
-struct GemmState { uint32_t* status = nullptr; bool attrs_set = false; };
+struct GemmState { uint32_t* status = nullptr; bool attrs_set = false; bool pair_configured = false; uint32_t max_pairs = 0; int use_pairs = -1; };
 
 template <int BN>
 int32_t launch(rb_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2, const CUtensorMap& mbh,
@@ -321,6 +513,34 @@ int32_t launch(rb_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const 
 void plan_tail(rb_ctx* ctx, GemmParams& p, uint32_t bn_out) {
     const uint32_t sms = ctx->sm_limit > 0 ? (uint32_t)ctx->sm_limit : (uint32_t)ctx->sm_count;
     rb_gemm_plan(p.tiles_m * p.tiles_n * p.batches, sms, (bn_out / 2) % 32 == 0, p.split, p.items);
+}
+
+// Launch on CTA pairs.  The number of pairs that can be resident at once comes from the occupancy query for clusters (not
+// every SM of the chip can be paired), capped by the context's SM limit.
+int32_t launch_pair(rb_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2, const CUtensorMap& mbh,
+                    const CUtensorMap& mb2h, GemmParams& p, uint32_t bn_out) {
+    GemmState* st = static_cast<GemmState*>(ctx->gemm_state);
+    if (!st->pair_configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES);
+        if (e != cudaSuccess) return rb::fail(RB_STATUS, "cudaFuncSetAttribute(pair GEMM) failed with CUDA status %d (%s)", (int)e, cudaGetErrorString(e));
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(2 * (unsigned)ctx->sm_count, 1, 1); cfg.blockDim = dim3(THREADS, 1, 1); cfg.dynamicSmemBytes = PAIR_SMEM_BYTES;
+        cudaLaunchAttribute attr{};
+        attr.id = cudaLaunchAttributeClusterDimension; attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr; cfg.numAttrs = 1;
+        int clusters = 0;
+        e = cudaOccupancyMaxActiveClusters(&clusters, gemm_bf16_pair_kernel, &cfg);
+        if (e != cudaSuccess || clusters < 1) return rb::fail(RB_STATUS, "cudaOccupancyMaxActiveClusters(pair GEMM) failed with CUDA status %d (%s)", (int)e, cudaGetErrorString(e));
+        st->max_pairs = (uint32_t)clusters;
+        st->pair_configured = true;
+    }
+    uint32_t pairs = st->max_pairs;
+    if (ctx->sm_limit > 0 && (uint32_t)ctx->sm_limit / 2 < pairs) pairs = (uint32_t)ctx->sm_limit / 2;
+    if (pairs == 0) pairs = 1;
+    rb_gemm_plan(p.tiles_m * p.tiles_n * p.batches, pairs, (bn_out / 2) % 32 == 0, p.split, p.items);
+    if (p.items < pairs) pairs = p.items;
+    gemm_bf16_pair_kernel<<<2 * pairs, THREADS, PAIR_SMEM_BYTES, ctx->stream>>>(ma, mb, mb2, mbh, mb2h, p);
+    return rb::after_launch(ctx, "gemm (CTA pairs)");
 }
 
 bool make_operand_map(CUtensorMap* map, const void* base, uint64_t batches, uint64_t rows, uint64_t k, uint32_t box_rows) {
@@ -378,6 +598,21 @@ int32_t gemm_run(rb_ctx* ctx, const GemmCall& c) {
     int bn = c.n > 128 || swiglu ? 256 : (c.n > 64 ? 128 : 64);
     if (swiglu && c.n <= 64) bn = 128;
     const uint32_t bn_out = swiglu ? bn / 2 : bn;
+    GemmState* st = static_cast<GemmState*>(ctx->gemm_state);
+    { const char* env = std::getenv("RUDA_GEMM_PAIRS"); st->use_pairs = env && env[0] == '1' ? 1 : 0; }
+    // CTA pairs take the plain shapes of the hot path: wide outputs, one K pass, BF16 operands, 16-byte rows.
+    const bool pairs_ok = st->use_pairs == 1 && bn == 256 && c.m >= 256 && c.nseg == 1 && !c.group_ends && !c.f16_operands && !c.ragged &&
+                          c.out_kind <= 1 && !c.a_bcast && !c.b_bcast && c.parts_a == 1 && c.parts_b == 1;
+    if (pairs_ok) {
+        p.tiles_m = (c.m + 2 * BM - 1) / (2 * BM); p.tiles_n = (c.n + bn_out - 1) / bn_out;
+        const uint64_t ar2 = c.a_rows ? c.a_rows : c.m, br2 = c.b_rows ? c.b_rows : c.n;
+        CUtensorMap ma, mb, mb2, mbh, mb2h;
+        if (!make_operand_map(&ma, c.a, c.batches, ar2, c.k, BM) || !make_operand_map(&mb, c.b, c.batches, br2, c.k, PAIR_BN / 2) ||
+            !make_operand_map(&mb2, swiglu ? c.b_up : c.b, c.batches, br2, c.k, PAIR_BN / 2) || !make_operand_map(&mbh, c.b, c.batches, br2, c.k, PAIR_BN / 4) ||
+            !make_operand_map(&mb2h, swiglu ? c.b_up : c.b, c.batches, br2, c.k, PAIR_BN / 4))
+            return fail(RB_STATUS, "cuTensorMapEncodeTiled failed for a GEMM operand (m=%u n=%u k=%u)", c.m, c.n, c.k);
+        return launch_pair(ctx, ma, mb, mb2, mbh, mb2h, p, bn_out);
+    }
     p.tiles_m = (c.m + BM - 1) / BM; p.tiles_n = (c.n + bn_out - 1) / bn_out;
     plan_tail(ctx, p, bn_out);
     const uint64_t za = (uint64_t)(c.a_bcast ? 1 : c.batches) * c.parts_a;

@@ -245,3 +245,43 @@ def test_linear_on_host_buffers_matches_write_gemm_read(client, oracle, m, n, k,
         bf16_tolerance(got, ref)
     else:
         assert np.abs(got - ref).max() <= 1e-4 * max(1.0, np.abs(ref).max())
+
+
+@pytest.fixture
+def cta_pairs():
+    """Routes eligible GEMMs to the kernel that runs on pairs of CTAs (clusters of two) for the duration of a test."""
+    import os
+    before = os.environ.get("RUDA_GEMM_PAIRS")
+    os.environ["RUDA_GEMM_PAIRS"] = "1"
+    yield
+    if before is None:
+        del os.environ["RUDA_GEMM_PAIRS"]
+    else:
+        os.environ["RUDA_GEMM_PAIRS"] = before
+
+
+@pytest.mark.parametrize("batches,m,n,k,mode", [(1, 512, 512, 256, "none"), (1, 4096, 1024, 512, "bias"), (1, 1024, 1376, 512, "swiglu"), (1, 400, 272, 144, "bias"),
+                                                (1, 19200, 256, 64, "none"), (1, 19200, 128, 64, "swiglu"), (2, 768, 512, 192, "none"), (1, 256, 256, 4096, "none")])
+def test_cta_pair_kernel_against_oracle(client, oracle, cta_pairs, batches, m, n, k, mode):
+    """The 256-row tiles of the CTA-pair kernel: whole and half-width tiles (75 tiles on 74 pairs), ragged last tiles in both
+    directions, every epilogue, batches, a long K: all rows against the oracle, FP32 and BF16 outputs."""
+    rng = np.random.default_rng(batches + m + n + k)
+    shape = lambda *s: ((batches,) + s) if batches > 1 else s
+    x = _normal_bf16(rng.integers(1 << 30), shape(m, k)); w = _normal_bf16(rng.integers(1 << 30), shape(n, k), 0.1)
+    flat = lambda a: a.reshape(-1, a.shape[-2], a.shape[-1])
+    kwargs, want = {}, None
+    if mode == "swiglu":
+        wu = _normal_bf16(rng.integers(1 << 30), shape(n, k), 0.1)
+        kwargs["b_up"] = up16(client, wu)
+        want = np.stack([oracle.linear(a, b, w_up=u) for a, b, u in zip(flat(x), flat(w), flat(wu))])
+    elif mode == "bias":
+        bias = rng.standard_normal(n).astype(np.float32)
+        kwargs["bias"] = client.upload(bias)
+        want = np.stack([oracle.linear(a, b, bias=bias) for a, b in zip(flat(x), flat(w))])
+    else:
+        want = np.stack([oracle.linear(a, b) for a, b in zip(flat(x), flat(w))])
+    want = want.reshape(shape(m, n))
+    got = read(client, RT.gemm(client, up16(client, x), up16(client, w), Transpose.No, Transpose.Yes, DType.F32, **kwargs))
+    assert np.abs(got - want).max() <= 2e-4 * max(1.0, np.abs(want).max())
+    got16 = read(client, RT.gemm(client, up16(client, x), up16(client, w), Transpose.No, Transpose.Yes, DType.BF16, **kwargs))
+    bf16_tolerance(got16, want)

@@ -64,7 +64,9 @@ def test_attention_backward_seeded_case_and_rejections(client, oracle):
     with pytest.raises(InvalidTensor):
         RT.attention_backward(client, up(q), up(k), up(v), up(dy[:, :, :32]), scale)                           # upstream shape
     with pytest.raises(InvalidTensor):
-        RT.attention_backward(client, up(q), up(k), up(v), up(dy), 0.0)
+        RT.attention_backward(client, up(q), up(k), up(v), up(dy), float("nan"))                                # the scale must be finite
+    zero = RT.attention_backward(client, up(q), up(k), up(v), up(dy), 0.0)                                       # scale 0: uniform attention, no gradient into Q and K
+    assert not client.read(zero[0]).any() and not client.read(zero[1]).any() and np.isfinite(client.read(zero[2])).all()
 
 
 def test_grouped_gemm_matches_per_group_products(client, oracle):
