@@ -7,16 +7,17 @@
 //
 // Persistent kernel, one CTA per SM.  A work item is 256 query rows of one (batch, head), handled as two 128-row tiles
 // that ping-pong on the tensor core; items are numbered heaviest first (under a causal mask the last query blocks see the
-// most keys) and CTA c takes items c, c + grid, c + 2 grid, ...  Roles (384 threads):
-//   warps 0-3 / 4-7  softmax of tile 0 / tile 1: one query row per thread, running max and sum in FP32, exp2 with the
+// most keys); see schedule.h for the order in which the CTAs take them.  Roles (384 threads, twelve warps: four control warps and
+// two softmax warpgroups; the order of the groups is a build option):
+//   softmax warps    four for tile 0, four for tile 1: one query row per thread, running max and sum in FP32, exp2 with the
 //                    scale folded in, P written back to TMEM as BF16 over the scores, handed to the MMA warp in two halves;
 //                    at the end of an item the same warps normalise O and store it, while the TMA and MMA warps already
 //                    load and multiply the first key block of the next item
-//   warp 8           TMA producer: Q of the next item as soon as the last score GEMM of this one has read it, K and V
+//   TMA warp          Q of the next item as soon as the last score GEMM of this one has read it, K and V
 //                    tiles of 128 keys through two 2-stage rings
-//   warp 9           issues tcgen05.mma:  S_t = Q_t K^T (operands in shared memory),  O_t += P_t V (P from TMEM, V consumed
+//   MMA warp         issues tcgen05.mma:  S_t = Q_t K^T (operands in shared memory),  O_t += P_t V (P from TMEM, V consumed
 //                    as stored, Dv-contiguous)
-//   warps 10-11      idle; they only donate their registers to the softmax warps (setmaxnreg)
+//   two more warps   idle; they only donate their registers to the softmax warps (setmaxnreg)
 // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_t aliases the first 64 columns of S_t.
 // The running maximum is only refreshed when it grows by more than 2^8 (the accumulator and the sum are then rescaled),
 // so most key blocks need no pass over O.  A key block that the causal rule or the end of the keys cuts is processed in
@@ -35,10 +36,20 @@ constexpr int D = 128;            // head dim (Q/K) and value dim
 constexpr int TQ = 128;           // query rows per tile
 constexpr int TK = 128;           // keys per block
 constexpr int KV_STAGES = 2;
-constexpr int THREADS = 384;   // warps 0-7 softmax + epilogue, 8 TMA, 9 MMA, 10-11 only donate registers
+constexpr int THREADS = 384;
+// Warp roles.  The warp that issues the MMAs is a single thread with a long dependent instruction stream; which warp slot it
+// sits in decides how often the scheduler lets it issue beside the two busy softmax warps of its SM sub-partition
+// (-DRB_ATTN_MMA_LAST puts the control warps behind the softmax warps instead of in front of them).
+#ifdef RB_ATTN_MMA_LAST
+constexpr uint32_t W_SOFTMAX = 0, W_CONTROL = 8;
+#else
+constexpr uint32_t W_SOFTMAX = 4, W_CONTROL = 0;
+#endif
+constexpr uint32_t W_MMA = W_CONTROL, W_TMA = W_CONTROL + 1;   // the other two control warps only donate registers
 constexpr int TILE_BYTES = 128 * D * 2;       // 32 KiB: one [128 x 128] BF16 tile = two 64-wide swizzle slabs
 constexpr int SLAB_BYTES = 128 * 64 * 2;      // 16 KiB
-constexpr int SMEM_BYTES = 2 * TILE_BYTES + 2 * KV_STAGES * TILE_BYTES + 1024 + 256;
+constexpr int ITEM_TAB = 512;                 // steps whose items are tabulated in shared memory; later steps compute theirs
+constexpr int SMEM_BYTES = 2 * TILE_BYTES + 2 * KV_STAGES * TILE_BYTES + 1024 + 256 + ITEM_TAB * 8;
 
 struct AttnParams {
     uint32_t B, Hq, Hkv, M, N;
@@ -66,7 +77,12 @@ __device__ __forceinline__ uint32_t blocks_for(const AttnParams& p, uint32_t row
 }
 // Work item -> (query block, head, batch): heaviest query blocks first, heads of one KV group next to each other.
 // `round` is the CTA's step number; returns false when the CTA has no item in that step.
-__device__ __forceinline__ bool item_coords(const AttnParams& p, uint32_t round, uint32_t& qb, uint32_t& h, uint32_t& b) {
+__device__ __forceinline__ bool item_coords(const AttnParams& p, const uint2* item_tab, uint32_t round, uint32_t& qb, uint32_t& h, uint32_t& b) {
+    if (round < ITEM_TAB) {
+        const uint2 e = item_tab[round];
+        qb = e.x & 0x7fffffffu; h = e.y & 0xffffu; b = e.y >> 16;
+        return (e.x >> 31) != 0;
+    }
     return rb_attention_item(round, blockIdx.x, gridDim.x, p.q_blocks, p.heads_total, p.Hq, p.wave_heads, qb, h, b);
 }
 
@@ -282,8 +298,17 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     uint64_t* o_free = o_full + 2;              // [2 tiles]  softmax warps -> MMA: O has been read out of TMEM
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_free + 2);
     volatile uint32_t* abort_word = tmem_slot + 1;
+    // this CTA's work items, one entry per step: (query block | valid << 31, head | batch << 16).  Filled by all threads at once
+    // before the roles part, so that no role spends its own (single-thread) instruction stream on the index arithmetic.
+    uint2* item_tab = reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(bars) + 256);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rounds = rb_attention_steps(p.q_blocks, p.heads_total, p.wave_heads, gridDim.x);
+    for (uint32_t step = threadIdx.x; step < rounds && step < ITEM_TAB; step += THREADS) {
+        uint32_t qb = 0, h = 0, b = 0;
+        const bool valid = rb_attention_item(step, blockIdx.x, gridDim.x, p.q_blocks, p.heads_total, p.Hq, p.wave_heads, qb, h, b);
+        item_tab[step] = make_uint2(qb | (valid ? 0x80000000u : 0u), h | (b << 16));
+    }
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1); mbar_init(q_empty, 1);
@@ -296,12 +321,11 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         fence_barrier_init();
         prefetch_tmap(&map_q); prefetch_tmap(&map_k); prefetch_tmap(&map_v);
     }
-    if (warp == 9) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
+    if (warp == W_MMA) { tmem_alloc(tmem_slot, 512); tmem_relinquish(); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t rounds = rb_attention_steps(p.q_blocks, p.heads_total, p.wave_heads, gridDim.x);
 #ifdef RB_ATTN_TRACE
     const bool trace_cta = blockIdx.x == 0;
 #else
@@ -310,9 +334,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 
     // Register budget: the two softmax warpgroups keep a whole score row in registers, the third warpgroup (TMA, MMA and
     // two idle warps) needs few.  256 * 224 + 128 * 56 = 64512 registers.
-    if (warp >= 8) {
+    if (warp >= W_CONTROL && warp < W_CONTROL + 4) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
-        if (warp == 8 && elect_one()) {
+        if (warp == W_TMA && elect_one()) {
             // ---------------- TMA producer ----------------
             bool ok = true;
             uint32_t kv_it = 0, q_it = 0;
@@ -320,7 +344,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             auto arm = [&](uint32_t bit, uint32_t parity) { armed |= 1u << bit; armed_parity = (armed_parity & ~(1u << bit)) | (parity << bit); };
             for (uint32_t round = 0; ok && round < rounds; ++round) {
                 uint32_t qb, h, b;
-                if (!item_coords(p, round, qb, h, b)) continue;
+                if (!item_coords(p, item_tab, round, qb, h, b)) continue;
                 const uint32_t kvh = h / (p.Hq / p.Hkv), row0 = qb * 2 * TQ;
                 const uint32_t nb0 = blocks_for(p, row0, row0 + TQ), nb1 = blocks_for(p, row0 + TQ, row0 + 2 * TQ);
                 const uint32_t n_max = nb0 > nb1 ? nb0 : nb1;
@@ -351,7 +375,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     for (uint32_t i = 0; i < (1u << 20) && !mbar_try_wait(bar, (armed_parity >> bit) & 1u); ++i) {}
                 }
             }
-        } else if (warp == 9 && elect_one()) {
+        } else if (warp == W_MMA && elect_one()) {
             // ---------------- MMA issuer ----------------
             const uint32_t idesc_qk = make_idesc_bf16(TQ, TK, 0, 0);   // A = Q (K-major), B = K tile (K-major)
             const uint32_t idesc_pv = make_idesc_bf16(TQ, D, 0, 1);    // A = P (TMEM), B = V tile, Dv-contiguous (MN-major)
@@ -372,7 +396,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             };
             for (uint32_t round = 0; ok && round < rounds; ++round) {
                 uint32_t qb, h, b;
-                if (!item_coords(p, round, qb, h, b)) continue;
+                if (!item_coords(p, item_tab, round, qb, h, b)) continue;
                 const uint32_t row0 = qb * 2 * TQ;
                 const uint32_t nb[2] = {blocks_for(p, row0, row0 + TQ), blocks_for(p, row0 + TQ, row0 + 2 * TQ)};
                 const uint32_t n_max = nb[0] > nb[1] ? nb[0] : nb[1];
@@ -445,7 +469,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
         // ---------------- softmax + epilogue: warps 0-3 own tile 0, warps 4-7 own tile 1 ----------------
-        const uint32_t t = warp >> 2, quarter = warp & 3;
+        const uint32_t t = (warp - W_SOFTMAX) >> 2, quarter = warp & 3;
         const uint32_t row_in_tile = quarter * 32 + lane;
         const uint32_t lane_base = (quarter * 32) << 16;
         const uint32_t tmem_s = tmem_base + t * TK + lane_base;
@@ -454,7 +478,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         bool ok = true;
         for (uint32_t round = 0; ok && round < rounds; ++round) {
             uint32_t qb, h, b;
-            if (!item_coords(p, round, qb, h, b)) continue;
+            if (!item_coords(p, item_tab, round, qb, h, b)) continue;
             const uint32_t tile_row0 = qb * 2 * TQ + t * TQ;
             if (tile_row0 >= p.M) continue;
             const uint32_t nb = blocks_for(p, tile_row0, tile_row0 + TQ);
@@ -546,7 +570,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     tc_fence_before();
     __syncthreads();
     if (threadIdx.x == 0 && *abort_word) atomicExch(p.status, 2u);
-    if (warp == 9) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+    if (warp == W_MMA) { __syncwarp(); tc_fence_after(); tmem_dealloc(tmem_base, 512); }
 }
 
 // Rotary encoding of a BF16 [B,H,S,128] tensor (any strides with a contiguous last axis) into a contiguous

@@ -599,7 +599,7 @@ int32_t gemm_run(rb_ctx* ctx, const GemmCall& c) {
     if (swiglu && c.n <= 64) bn = 128;
     const uint32_t bn_out = swiglu ? bn / 2 : bn;
     GemmState* st = static_cast<GemmState*>(ctx->gemm_state);
-    { const char* env = std::getenv("RUDA_GEMM_PAIRS"); st->use_pairs = env && env[0] == '1' ? 1 : 0; }
+    { const char* env = std::getenv("RUDA_GEMM_PAIRS"); st->use_pairs = env && env[0] == '0' ? 0 : 1; }   // RUDA_GEMM_PAIRS=0 keeps every GEMM on single CTAs
     // CTA pairs take the plain shapes of the hot path: wide outputs, one K pass, BF16 operands, 16-byte rows.
     const bool pairs_ok = st->use_pairs == 1 && bn == 256 && c.m >= 256 && c.nseg == 1 && !c.group_ends && !c.f16_operands && !c.ragged &&
                           c.out_kind <= 1 && !c.a_bcast && !c.b_bcast && c.parts_a == 1 && c.parts_b == 1;

@@ -260,3 +260,101 @@ def test_peer_buffer_exchange_orders_handles_by_rank_and_fails_on_every_rank(fai
             assert sorted(closed) == [100 + r for r in range(world) if r != rank] and freed == [7]
         else:
             assert results[rank][0] == "error" and f"NCCL rank {fail_rank}:" in results[rank][1]
+
+
+# ---- TCP rendezvous, RUDA_* process configuration and the data-parallel layer, on host-side stand-ins -------------------------
+class HostTensor:
+    """A tensor of a CPU rank: the shape / dtype surface of TensorBuffer over a NumPy array."""
+
+    def __init__(self, array):
+        from rust_ascend_b200 import DType
+        self.array = np.ascontiguousarray(array)
+        self.shape = self.array.shape
+        self.dtype = {np.dtype(np.float32): DType.F32, np.dtype(np.float16): DType.F16, np.dtype(np.int64): DType.I64,
+                      np.dtype(np.int32): DType.I32, np.dtype(np.uint8): DType.U8}[self.array.dtype]
+
+
+class HostCommunicator:
+    """The NcclCommunicator surface with the tensor payloads carried by the control plane (a CPU rank has no NCCL)."""
+
+    def __init__(self, control):
+        self.control, self.rank, self.world_size = control, control.rank, control.world_size
+
+    def all_gather_bytes(self, payload):
+        return self.control.all_gather_bytes(payload)
+
+    def _everyone(self, value):
+        return [np.frombuffer(b, dtype=value.array.dtype).reshape(value.shape) for b in self.control.all_gather_bytes(value.array.tobytes())]
+
+    def broadcast_float(self, value, root): return HostTensor(self._everyone(value)[root].copy())
+    broadcast_int = broadcast_bool = broadcast_float
+
+    def all_reduce_float(self, value, operation="sum"):
+        total = sum(self._everyone(value))
+        return HostTensor((total / self.world_size if operation == "mean" else total).astype(value.array.dtype))
+
+    def zeros_fp32(self, shape): return HostTensor(np.zeros(shape, np.float32))
+    def to_fp32(self, value): return HostTensor(value.array.astype(np.float32))
+    def divide(self, value, divisor): return HostTensor((value.array / np.float32(divisor)).astype(np.float32))
+
+
+def _data_parallel_worker(rank, world, port, results):
+    from rust_ascend_b200.distributed import ContractError, DataParallel, TcpControl, process_configuration
+    env = {"RUDA_RANK": str(rank), "RUDA_WORLD_SIZE": str(world), "RUDA_RENDEZVOUS": f"127.0.0.1:{port}",
+           "RUDA_RENDEZVOUS_ID": "00000000000000000000000000002077"}
+    cfg = process_configuration(env)
+    assert cfg["device"] == rank and cfg["rendezvous_id"] == bytes.fromhex(env["RUDA_RENDEZVOUS_ID"])
+    control = TcpControl(cfg["rank"], cfg["world_size"], cfg["address"], cfg["rendezvous_id"], timeout=30)
+    out = {"gather": control.all_gather_bytes(bytes([rank]) * (rank + 1))}
+    comm = HostCommunicator(control)
+    root = world - 1
+    ddp = DataParallel(comm, root)
+    # examples/hccl_data_parallel.rs:77-104: float weight, an I64 counter beyond 2^53 and Bool flags leave with the root's values
+    synced = ddp.initialize_with_buffers({"weight": HostTensor(np.full(4, rank + 1, np.float32)),
+                                          "counter": HostTensor(np.array([9_007_199_254_740_993 + rank], np.int64)),
+                                          "flags": HostTensor(np.array([rank == root, rank != root], np.uint8))})
+    out["weight"], out["counter"], out["flags"] = synced["weight"].array.tolist(), synced["counter"].array.tolist(), synced["flags"].array.tolist()
+    # :105-124: local loss weight^2 * sum(w) -> local gradient (rank+1)^2, local weight rank+1 -> (2 world + 1) / 3
+    local_weight = rank + 1
+    grads, global_weight = ddp.reduce_fp32({"weight": HostTensor(np.full(4, local_weight * local_weight, np.float16))}, local_weight)
+    out["reduced"], out["global_weight"], out["dtype"] = grads["weight"].array.tolist(), global_weight, str(grads["weight"].array.dtype)
+    # a rank without the gradient: an error under the strict policy (on every rank), zeros under the lenient one
+    mine = {} if rank == 0 else {"weight": HostTensor(np.ones(4, np.float32))}
+    try:
+        ddp.reduce_fp32(mine, 1)
+        out["strict"] = "passed"
+    except ContractError as error:
+        out["strict"] = str(error)
+    lenient, _ = ddp.reduce_fp32(mine, 1, missing="zero")
+    out["lenient"] = lenient["weight"].array.tolist()
+    control.close()
+    results[rank] = out
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_tcp_rendezvous_and_data_parallel_reduction(world):
+    port = _free_port()
+    with mp.Manager() as manager:
+        results = manager.dict()
+        mp.spawn(_data_parallel_worker, args=(world, port, results), nprocs=world, join=True)
+        r = {k: dict(v) for k, v in results.items()}
+    root = world - 1
+    for rank in range(world):
+        assert r[rank]["gather"] == [bytes([i]) * (i + 1) for i in range(world)]
+        assert r[rank]["weight"] == [float(root + 1)] * 4
+        assert r[rank]["counter"] == [9_007_199_254_740_993 + root] and r[rank]["flags"] == [1, 0]
+        assert r[rank]["global_weight"] == world * (world + 1) // 2 and r[rank]["dtype"] == "float32"
+        assert np.allclose(r[rank]["reduced"], (2 * world + 1) / 3, atol=1e-2)
+        assert "missing" in r[rank]["strict"]
+        assert np.allclose(r[rank]["lenient"], (world - 1) / world)
+
+
+def test_process_configuration_rejects_bad_settings():
+    from rust_ascend_b200.distributed import ContractError, process_configuration
+    good = {"RUDA_RANK": "1", "RUDA_WORLD_SIZE": "2", "RUDA_RENDEZVOUS": "127.0.0.1:29500", "RUDA_RENDEZVOUS_ID": "0" * 32, "RUDA_CUDA_DEVICE": "5"}
+    assert process_configuration(good)["device"] == 5
+    for key, value in (("RUDA_RENDEZVOUS_ID", "abc"), ("RUDA_RENDEZVOUS_ID", "g" * 32), ("RUDA_RANK", "2"), ("RUDA_RENDEZVOUS", "nowhere"), ("RUDA_WORLD_SIZE", "x")):
+        with pytest.raises(ContractError):
+            process_configuration(dict(good, **{key: value}))
+    with pytest.raises(ContractError, match="RUDA_RANK"):
+        process_configuration({k: v for k, v in good.items() if k != "RUDA_RANK"})

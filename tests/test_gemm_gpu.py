@@ -178,6 +178,11 @@ def _normal_bf16(seed, shape, std=1.0):
     return bf16_bits_to_f32(f32_to_bf16_bits(x))
 
 
+def test_config2a_full_size_on_single_ctas(client, oracle, single_ctas):
+    """The same configuration on the single-CTA kernel (512 tiles on 148 CTAs: three rounds of whole tiles and a last round of 136 half tiles)."""
+    test_config2a_full_size_against_oracle_rows(client, oracle)
+
+
 def test_config2a_full_size_against_oracle_rows(client, oracle):
     """BASELINE configuration 2a as stated: X [4096,4096] ~ N(0,1), W [4096,4096] ~ N(0,0.02) stored [N,K], FP32 bias
     ~ N(0,0.02), BF16 output.  The whole output is computed on the GPU; the oracle recomputes 48 sampled rows."""
@@ -207,7 +212,7 @@ def test_config2b_full_size_swiglu_against_oracle_rows(client, oracle):
 
 @pytest.mark.parametrize("m,n,k,mode", [(19200, 256, 64, "bias"), (19200, 272, 80, "none"), (19200, 128, 64, "swiglu"), (9600, 400, 48, "swiglu"),
                                         (128, 256, 128, "bias"), (2048, 4096 + 512, 64, "none")])
-def test_tail_round_of_half_tiles(client, oracle, m, n, k, mode):
+def test_tail_round_of_half_tiles(client, oracle, single_ctas, m, n, k, mode):
     """Shapes whose last round of the persistent loop is cut into half-width tiles (150 or 300 tiles on 148 SMs, a single tile, and
     a grid with a ragged last column of tiles), with every epilogue: all rows against the oracle."""
     rng = np.random.default_rng(m + n + k)
@@ -247,17 +252,27 @@ def test_linear_on_host_buffers_matches_write_gemm_read(client, oracle, m, n, k,
         assert np.abs(got - ref).max() <= 1e-4 * max(1.0, np.abs(ref).max())
 
 
-@pytest.fixture
-def cta_pairs():
-    """Routes eligible GEMMs to the kernel that runs on pairs of CTAs (clusters of two) for the duration of a test."""
+def _with_pairs(value):
     import os
     before = os.environ.get("RUDA_GEMM_PAIRS")
-    os.environ["RUDA_GEMM_PAIRS"] = "1"
+    os.environ["RUDA_GEMM_PAIRS"] = value
     yield
     if before is None:
         del os.environ["RUDA_GEMM_PAIRS"]
     else:
         os.environ["RUDA_GEMM_PAIRS"] = before
+
+
+@pytest.fixture
+def cta_pairs():
+    """Wide GEMMs run on pairs of CTAs (clusters of two); this is the default, stated here so that the test says what it covers."""
+    yield from _with_pairs("1")
+
+
+@pytest.fixture
+def single_ctas():
+    """Keeps every GEMM of the test on the single-CTA kernel, which otherwise only narrow or short shapes reach."""
+    yield from _with_pairs("0")
 
 
 @pytest.mark.parametrize("batches,m,n,k,mode", [(1, 512, 512, 256, "none"), (1, 4096, 1024, 512, "bias"), (1, 1024, 1376, 512, "swiglu"), (1, 400, 272, 144, "bias"),
