@@ -3,8 +3,9 @@
 
 Headline (one JSON line on rank 0): BF16 Linear GEMM  Y = bf16(X W^T + bias),  X [4096,4096], W [4096,4096]
 (stored [N,K]), FP32 accumulate, bias FP32 — the configuration the reference's metric is quoted on.  One step
-is one pass of that GEMM over one synthetic batch.  At N > 1 every rank runs the same shape on its own rows of
-a batch that is N times taller (independent row shards, no data-path collective): weak scaling.
+is one pass of that GEMM over one synthetic batch.  At N > 1 the same Linear runs as a row-parallel layer: every rank
+multiplies its own K shard (one 4096^3 product per rank, so the work per GPU stays that of the one-GPU step: weak
+scaling) and the partial products are summed on every rank, which is the exchange step tensor parallelism has.
 
 `--impl reference` times the reference's arithmetic for the same step on the host cores instead (the CPU
 oracle port, since the reference has no CPU execution path of its own and its Rust sources do not build here).
@@ -33,8 +34,68 @@ NCCL_CTAS = 16                           # SMs left to NCCL while tensor-paralle
 
 def workload_config(world: int) -> dict:
     """The `config` object both arms print (identical keys and values, so the two lines describe one workload)."""
-    return {"workload": "linear_bf16_4096x4096x4096_bias", "m": M, "n": N, "k": K, "rows_per_gpu": M,
-            "l2": f"rotating {SETS} operand sets (384 MiB) > 126 MB L2", "parallelism": f"row shards x{world}, no collective"}
+    parallelism = "one GPU" if world == 1 else (f"row-parallel Linear: K sharded x{world} (one 4096^3 product per GPU and step), the partial products "
+                                                "summed on every rank (one exchange of the 32 MiB BF16 result per step)")
+    return {"workload": "linear_bf16_4096x4096x4096_bias", "m": M, "n": N, "k": K, "k_total": K * world,
+            "l2": f"rotating {SETS} operand sets (384 MiB) > 126 MB L2", "parallelism": parallelism}
+
+
+class RowParallelHeadline:
+    """The N > 1 headline step: Y = sum_r X_r W_r^T + bias on every rank (rank 0's partial product carries the bias)."""
+
+    def __init__(self, client, RT, dist, rank, world, sets, args):
+        import ctypes as C
+        from rust_ascend_b200.distributed import NcclCommunicator, TorchControl
+        from rust_ascend_b200.fused import GATHER, SCATTER, FusedExchange
+        from rust_ascend_b200.runtime import _check
+        self.client, self.dist, self.rank, self.world, self.args = client, dist, rank, world, args
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        control = TorchControl()
+        lib, keep = client._lib, []
+        self._keep = keep
+        self.candidates = {}
+        try:
+            ex = FusedExchange(client, control, M, N)
+            self.exchange = ex
+            scatter = [ex.scatter_bias_args(st[0], st[1], st[2] if rank == 0 else None, keep) for st in sets]
+            wait_s, wait_g = ex.wait_args(SCATTER, ex.signals, keep), ex.wait_args(GATHER, 1, keep)
+            push = ex.push_args(True, None, None, 1e-5, None, keep)
+
+            def fused(i):
+                _check(lib.rb_gemm_scatter_bias(*scatter[i % SETS])); _check(lib.rb_peer_wait(*wait_s))
+                _check(lib.rb_reduce_norm_push(*push)); _check(lib.rb_peer_wait(*wait_g))
+            self.candidates["fused scatter-GEMM + owner-side sum + push over peer memory"] = (fused, 4)
+        except Exception as error:           # peer memory unavailable: the NCCL form still runs
+            self.fused_error = f"{type(error).__name__}: {error}"
+        comm = NcclCommunicator.initialize(control, client)
+        self.comm = comm
+        descs = [[t._c() for t in st] for st in sets]
+        keep.append(descs)
+        gemms = [(client._ctx, C.byref(k[0]), C.byref(k[1]), C.c_int32(0), C.c_int32(1), C.byref(k[2]) if rank == 0 else None, None,
+                  C.c_int32(1 if rank == 0 else 0), C.byref(k[3])) for k in descs]
+        reduces = [(comm.native._comm, C.byref(k[3]), C.c_int32(0), C.byref(k[3]), C.c_int32(0)) for k in descs]
+
+        def nccl(i):
+            _check(lib.rb_gemm(*gemms[i % SETS])); _check(lib.rb_all_reduce(*reduces[i % SETS]))
+        self.candidates["GEMM + NCCL all-reduce"] = (nccl, 1)
+        self.chosen, self.timings = None, {}
+
+    def choose(self):
+        for name, (fn, _) in self.candidates.items():
+            for i in range(max(3, self.args.warmup)):
+                fn(i)
+            self.client.sync(); self.dist.barrier()
+            self.client.start_profile()
+            for i in range(20):
+                fn(i)
+            self.timings[name] = max_over_ranks(self.dist, self.client.end_profile() / 20)
+        self.chosen = min(self.timings, key=self.timings.get)
+        return self.candidates[self.chosen]
+
+    def result(self, i):
+        """Device tensor that holds Y after step i."""
+        return self.exchange.gathered() if self.chosen.startswith("fused") else None
+
 
 
 def peaks():
@@ -184,6 +245,14 @@ def run_ours(args):
     def step(i):
         _check(rb_gemm(*calls[i % SETS]))   # Y = X W^T + bias through the C ABI
 
+    exchange, launches_per_step = None, 1
+    if world > 1:
+        # N > 1: the same Linear as a row-parallel layer.  Every rank holds its own K shard (X_r [4096,4096], W_r [4096,4096]: one
+        # 4096^3 product per rank and step, so the work per GPU is that of the one-GPU step) and every rank ends with
+        # Y = sum over ranks of X_r W_r^T + bias.  Two ways to make that sum are timed in warm-up and the faster one is kept:
+        # the exchange fused into the kernels over peer memory, and the plain GEMM followed by an NCCL all-reduce.
+        exchange = RowParallelHeadline(client, RT, dist, rank, world, sets, args)
+        step, launches_per_step = exchange.choose()
     for i in range(args.warmup):
         step(i)
     client.sync()
@@ -213,24 +282,43 @@ def run_ours(args):
     hy = client.pinned((M, N), np.uint16)
     hx[...] = f32_to_bf16_bits(rng.standard_normal((M, K), dtype=np.float32))
     x, w, b, y = sets[0]
-    for _ in range(3):
-        RT.linear_host(client, hx, x, w, y, hy, bias=b, row_chunks=chunks)
-    if dist is not None:
+    if exchange is None:
+        for _ in range(3):
+            RT.linear_host(client, hx, x, w, y, hy, bias=b, row_chunks=chunks)
+        t0 = time.perf_counter()
+        for i in range(e2e_steps):
+            x, w, b, y = sets[i % SETS]
+            RT.linear_host(client, hx, x, w, y, hy, bias=b, row_chunks=chunks)   # returns when Y is in host memory
+        e2e_s = (time.perf_counter() - t0) / e2e_steps
+        # the same three steps one after the other (rb_write, rb_gemm, rb_read), for comparison
+        t0 = time.perf_counter()
+        for i in range(min(e2e_steps, 10)):
+            x, w, b, y = sets[i % SETS]
+            client.write(x.handle, hx)
+            RT.gemm_into(client, x, w, Transpose.No, Transpose.Yes, y, bias=b)
+            client.read_into(y.handle, hy)
+        serial_s = (time.perf_counter() - t0) / min(e2e_steps, 10)
+        e2e_note = (f"rb_linear_host: every byte of X uploaded and of Y read back inside every timed step, in {chunks} row chunks whose H2D copy, GEMM "
+                    "and D2H copy overlap on three streams; W and bias stay resident as module parameters")
+    else:
+        # row-parallel: every rank uploads its K shard of X, the ranks exchange, every rank reads the whole Y back
+        def e2e_step(i):
+            st = sets[i % SETS]
+            client.write(st[0].handle, hx)
+            step(i)
+            out = exchange.result(i) or st[3]
+            client.read_into(out.handle, hy, out.offset)
+        for i in range(3):
+            e2e_step(i)
         dist.barrier()
-    t0 = time.perf_counter()
-    for i in range(e2e_steps):
-        x, w, b, y = sets[i % SETS]
-        RT.linear_host(client, hx, x, w, y, hy, bias=b, row_chunks=chunks)   # returns when Y is in host memory
-    e2e_s = max_over_ranks(dist, (time.perf_counter() - t0) / e2e_steps)
+        t0 = time.perf_counter()
+        for i in range(e2e_steps):
+            e2e_step(i)
+        e2e_s = max_over_ranks(dist, (time.perf_counter() - t0) / e2e_steps)
+        serial_s = e2e_s
+        e2e_note = ("every rank uploads its K shard of X (rb_write), runs the row-parallel step and reads the whole Y back (rb_read) inside every timed step; "
+                    "W and bias stay resident as module parameters")
     e2e_value = world * FLOPS_PER_STEP / e2e_s / 1e12
-    # the same three steps one after the other (rb_write, rb_gemm, rb_read), for comparison
-    t0 = time.perf_counter()
-    for i in range(min(e2e_steps, 10)):
-        x, w, b, y = sets[i % SETS]
-        client.write(x.handle, hx)
-        RT.gemm_into(client, x, w, Transpose.No, Transpose.Yes, y, bias=b)
-        client.read_into(y.handle, hy)
-    serial_s = max_over_ranks(dist, (time.perf_counter() - t0) / min(e2e_steps, 10))
 
     kernel_tflops = FLOPS_PER_STEP / (ms_per_step * 1e-3) / 1e12
     sustained = total_ms > 1000.0
@@ -242,14 +330,16 @@ def run_ours(args):
         "config": workload_config(world),
         "clocks": clocks, "gpu_launches": int(gpu_launches),
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": int(hx.nbytes), "d2h_bytes_per_step": int(hy.nbytes),
-                "steps": e2e_steps, "ms_per_step": e2e_s * 1e3, "serial_write_gemm_read_ms": serial_s * 1e3,
-                "note": f"rb_linear_host: every byte of X uploaded and of Y read back inside every timed step, in {chunks} row chunks whose H2D copy, GEMM "
-                        "and D2H copy overlap on three streams; W and bias stay resident as module parameters"},
+                "steps": e2e_steps, "ms_per_step": e2e_s * 1e3, "serial_write_gemm_read_ms": serial_s * 1e3, "note": e2e_note},
         "roofline": {"bound": "tensor", "achieved": kernel_tflops, "peak": peak, "unit": "TFLOP/s", "frac": kernel_tflops / peak,
-                     "traffic": 80.9e6, "traffic_source": "ncu dram__bytes_read+write per launch of this shape (profiles/gemm_bf16_linear4096.txt); algorithmic bytes are 100.7e6, the output tail stays in L2", "kernel": "gemm_bf16_kernel<256>", "peak_kind": ("sustained" if sustained else "burst") + " of " + pk["source"],
+                     "traffic": 80.9e6, "traffic_source": "ncu dram__bytes_read+write per launch of this shape (profiles/gemm_bf16_linear4096.txt); algorithmic bytes are 100.7e6, the output tail stays in L2", "kernel": "gemm_bf16_pair_kernel", "peak_kind": ("sustained" if sustained else "burst") + " of " + pk["source"],
                      "frac_of_burst": kernel_tflops / pk["bf16_tflops"], "frac_of_sustained": kernel_tflops / pk["bf16_tflops_sustained"],
                      "frac_of_nominal_2250": kernel_tflops / 2250.0},
     }
+    if exchange is not None:
+        line["exchange"] = {"chosen": exchange.chosen, "us_per_step_in_warm_up": {k: v * 1e3 for k, v in exchange.timings.items()},
+                            "bytes_per_rank_and_step": M * N * 2, "fused_error": getattr(exchange, "fused_error", None)}
+        line["roofline"]["note"] = "the step is one 4096^3 GEMM per GPU plus the exchange of its result; achieved counts the GEMM's flops over the whole step"
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         import oracle as orc
         orc.build()
@@ -586,8 +676,8 @@ def attention_extra(client, RT, pk):
 
 def row_parallel_extra(client, pk, rank, world, dist):
     """Config 2a as a row-parallel Linear: every rank holds K/world columns of X [4096, 4096] and W [4096, 4096] and the
-    partial products are summed by one all-reduce of the BF16 [4096, 4096] result; timed sequentially and with the rows cut
-    into chunks whose all-reduces run under the next chunk's GEMM.  Whole-job flops are those of the full product."""
+    partial products are summed on every rank: by one NCCL all-reduce of the BF16 [4096, 4096] result, and by the exchange fused
+    into the kernels over peer memory.  Strong scaling: whole-job flops are those of the one full product."""
     from rust_ascend_b200 import DType
     from rust_ascend_b200.distributed import NcclCommunicator, TorchControl
     from rust_ascend_b200.runtime import f32_to_bf16_bits
@@ -605,16 +695,23 @@ def row_parallel_extra(client, pk, rank, world, dist):
 
     def call(overlap):
         _check(client._lib.rb_row_parallel_linear_allreduce(comm.native._comm, C.byref(keep[0]), C.byref(keep[1]), C.byref(keep[2]), C.c_int32(int(overlap))))
-    for name, overlap in (("sequential", False), ("row_chunks_overlapped", True)):
+    variants = {"gemm_then_nccl_all_reduce": lambda: call(False)}
+    try:
+        from rust_ascend_b200.fused import FusedExchange, row_parallel_linear_allreduce
+        ex = FusedExchange(client, TorchControl(), M, N)
+        variants["fused_scatter_reduce_push"] = lambda: row_parallel_linear_allreduce(ex, x, w)
+    except Exception as error:
+        result["fused_error"] = f"{type(error).__name__}: {error}"
+    for name, fn in variants.items():
         for _ in range(5):
-            call(overlap)
+            fn()
         client.sync()
         if dist is not None:
             dist.barrier()
         steps = 20
         client.start_profile()
         for _ in range(steps):
-            call(overlap)
+            fn()
         ms = max_over_ranks(dist, client.end_profile() / steps)
         result[name] = {"us": ms * 1e3, "value": 2.0 * M * N * K / (ms * 1e-3) / 1e12}
     return result

@@ -367,6 +367,10 @@ RB_API int32_t rb_peer_close(rb_ctx* ctx, uint64_t handle);
  * number of announcements one call makes per owner. */
 RB_API int32_t rb_gemm_scatter(rb_ctx* ctx, const rb_tensor* a, const rb_tensor* b, uint32_t rank, uint32_t world,
                                const rb_tensor* const* staging, const rb_tensor* const* flags);
+/* The same with an FP32 bias [H] folded into this rank's partial product (NULL: none).  A row-parallel Linear adds its bias
+ * once, so exactly one rank of the group passes it (src/nn.rs:77-79 adds the bias after the product). */
+RB_API int32_t rb_gemm_scatter_bias(rb_ctx* ctx, const rb_tensor* a, const rb_tensor* b, const rb_tensor* bias, uint32_t rank, uint32_t world,
+                                    const rb_tensor* const* staging, const rb_tensor* const* flags);
 /* This entry has no counterpart in the reference.  Announcements per owner of one rb_gemm_scatter call with T tokens and H columns (0 when
  * the shape is not accepted). */
 RB_API uint32_t rb_gemm_scatter_signals(uint64_t tokens, uint64_t hidden, uint32_t world);

@@ -47,6 +47,7 @@ struct ScatterParams {
     uint32_t world;
     uint32_t tile_shift;            // tile rows this rank starts ahead of rank order, so that at any moment the ranks write to
                                     // different owners instead of all to the same one
+    const float* bias;              // FP32 [n] added to this rank's partial product before it is rounded and stored, or null
     uint8_t* dst[MAX_PEERS];        // owner o's staging slot for this rank: [rows_per_owner, n] BF16
     uint32_t* flag[MAX_PEERS];      // owner o's flag word for this rank
     uint32_t* status;
@@ -192,6 +193,14 @@ gemm_scatter_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 tmem_ld_32x32(taddr + c, r0);
                 tmem_ld_32x32(taddr + c + 32, r1);
                 tmem_wait_ld();
+                if (p.bias) {
+                    // the bias of a row-parallel Linear is added once: the rank that is given it folds it into its partial product
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        r0[j] = __float_as_uint(__fadd_rn(__uint_as_float(r0[j]), __ldg(p.bias + col0 + c + j)));
+                        r1[j] = __float_as_uint(__fadd_rn(__uint_as_float(r1[j]), __ldg(p.bias + col0 + c + 32 + j)));
+                    }
+                }
                 if (c + CHUNK >= BN || col0 + c + CHUNK >= p.n) {    // last read of this accumulator: hand it back early
                     tc_fence_before();
                     mbar_arrive(&tmem_empty[acc]);
@@ -456,6 +465,11 @@ extern "C" {
 
 int32_t rb_gemm_scatter(rb_ctx* ctx, const rb_tensor* a, const rb_tensor* b, uint32_t rank, uint32_t world,
                         const rb_tensor* const* staging, const rb_tensor* const* flags) {
+    return rb_gemm_scatter_bias(ctx, a, b, nullptr, rank, world, staging, flags);
+}
+
+int32_t rb_gemm_scatter_bias(rb_ctx* ctx, const rb_tensor* a, const rb_tensor* b, const rb_tensor* bias, uint32_t rank, uint32_t world,
+                             const rb_tensor* const* staging, const rb_tensor* const* flags) {
     RB_TRY(check_ctx(ctx));
     if (world < 1 || world > MAX_PEERS || rank >= world || !staging || !flags) return fail(RB_INVALID_TENSOR, "scatter GEMM needs 1..%d ranks and their staging and flag tensors", MAX_PEERS);
     void *pa, *pb;
@@ -466,6 +480,12 @@ int32_t rb_gemm_scatter(rb_ctx* ctx, const rb_tensor* a, const rb_tensor* b, uin
     if (m == 0 || n == 0 || k == 0 || k % 16 || n % CHUNK || m % ((uint64_t)world * BM) || m > 0x7fffffffull || n > 0x7fffffffull || k > 0x7fffffffull)
         return fail(RB_INVALID_TENSOR, "scatter GEMM needs T a multiple of 128 * world, H a multiple of 64 and K a multiple of 16");
     ScatterParams p{};
+    if (bias) {
+        void* pbias = nullptr;
+        RB_TRY(resolve(ctx, bias, "scatter GEMM bias", &pbias));
+        if (bias->dtype != RB_F32 || elements(bias) != n) return fail(RB_INVALID_TENSOR, "scatter GEMM bias is FP32 [H]");
+        p.bias = static_cast<const float*>(pbias);
+    }
     p.m = (uint32_t)m; p.n = (uint32_t)n; p.k = (uint32_t)k; p.world = world; p.rows_per_owner = (uint32_t)(m / world);
     const uint64_t slot = (uint64_t)p.rows_per_owner * n * 2;
     for (uint32_t o = 0; o < world; ++o) {

@@ -147,6 +147,15 @@ class FusedExchange:
         return (self.client._ctx, C.byref(sa), C.byref(sw), C.c_uint32(self.rank), C.c_uint32(self.world),
                 tensor_array(self.staging_views(), keep), tensor_array(self.flag_views(SCATTER), keep))
 
+    def scatter_bias_args(self, a: TensorBuffer, w: TensorBuffer, bias: TensorBuffer | None, keep: list):
+        """Arguments of rb_gemm_scatter_bias; `bias` (FP32 [hidden]) is given by exactly one rank of the group."""
+        args = self.scatter_args(a, w, keep)
+        sb = None
+        if bias is not None:
+            sb = bias._c()
+            keep.append(sb)
+        return args[:3] + (C.byref(sb) if sb is not None else None,) + args[3:]
+
     def wait_args(self, group: int, count: int, keep: list):
         f = self.local_flags(group)._c()
         keep.append(f)
