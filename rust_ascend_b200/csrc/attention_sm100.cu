@@ -49,7 +49,13 @@ constexpr uint32_t W_MMA = W_CONTROL, W_TMA = W_CONTROL + 1;   // the other two 
 constexpr int TILE_BYTES = 128 * D * 2;       // 32 KiB: one [128 x 128] BF16 tile = two 64-wide swizzle slabs
 constexpr int SLAB_BYTES = 128 * 64 * 2;      // 16 KiB
 constexpr int ITEM_TAB = 512;                 // steps whose items are tabulated in shared memory; later steps compute theirs
-constexpr int SMEM_BYTES = 2 * TILE_BYTES + 2 * KV_STAGES * TILE_BYTES + 1024 + 256 + ITEM_TAB * 8;
+constexpr int SMEM_BYTES = 2 * TILE_BYTES + 2 * KV_STAGES * TILE_BYTES + 1024 + 256 + ITEM_TAB * 16;
+#ifdef RB_ATTN_TILE0_FIRST
+constexpr uint32_t FIRST_TILE = 0;
+#else
+constexpr uint32_t FIRST_TILE = 1;
+#endif                                        // tile served first in every round of the ping-pong: under a causal mask tile 1 has one key
+                                              // block more than tile 0, so it leads and its extra block overlaps tile 0's lag
 
 struct AttnParams {
     uint32_t B, Hq, Hkv, M, N;
@@ -76,14 +82,38 @@ __device__ __forceinline__ uint32_t blocks_for(const AttnParams& p, uint32_t row
     return rb_attention_blocks(p.M, p.N, p.causal, p.delta, row0, row_end, TK);
 }
 // Work item -> (query block, head, batch): heaviest query blocks first, heads of one KV group next to each other.
-// `round` is the CTA's step number; returns false when the CTA has no item in that step.
-__device__ __forceinline__ bool item_coords(const AttnParams& p, const uint2* item_tab, uint32_t round, uint32_t& qb, uint32_t& h, uint32_t& b) {
-    if (round < ITEM_TAB) {
-        const uint2 e = item_tab[round];
-        qb = e.x & 0x7fffffffu; h = e.y & 0xffffu; b = e.y >> 16;
-        return (e.x >> 31) != 0;
+// One work item of this CTA: (query block | valid << 31, head | batch << 16, key blocks of tile 0, key blocks of tile 1).
+__device__ __forceinline__ uint4 make_item(const AttnParams& p, uint32_t step) {
+    uint32_t qb = 0, h = 0, b = 0;
+    const bool valid = rb_attention_item(step, blockIdx.x, gridDim.x, p.q_blocks, p.heads_total, p.Hq, p.wave_heads, qb, h, b);
+    const uint32_t row0 = qb * 2 * TQ;
+    return make_uint4(qb | (valid ? 0x80000000u : 0u), h | (b << 16), valid ? blocks_for(p, row0, row0 + TQ) : 0u,
+                      valid ? blocks_for(p, row0 + TQ, row0 + 2 * TQ) : 0u);
+}
+// `round` is the CTA's step number; returns false when the CTA has no item in that step.  nb0 / nb1 are the key blocks the
+// item's two tiles visit.
+__device__ __forceinline__ bool item_coords(const AttnParams& p, const uint4* item_tab, uint32_t round, uint32_t& qb, uint32_t& h, uint32_t& b,
+                                            uint32_t& nb0, uint32_t& nb1) {
+    const uint4 e = round < ITEM_TAB ? item_tab[round] : make_item(p, round);
+    qb = e.x & 0x7fffffffu; h = e.y & 0xffffu; b = e.y >> 16; nb0 = e.z; nb1 = e.w;
+    return (e.x >> 31) != 0;
+}
+
+// The MMA warp's two issue sequences as functions of their own: every call site (first block of an item, steady state, either
+// tile) runs the same instructions, which therefore stay in the instruction cache beside the softmax warps' long unrolled code.
+__device__ __noinline__ void issue_scores(uint32_t tmem_s, uint32_t qa, uint32_t ka, uint32_t idesc, uint64_t* done) {
+#pragma unroll
+    for (uint32_t kk = 0; kk < D / 16; ++kk) {
+        const uint32_t off = ((kk >> 2) * SLAB_BYTES + (kk & 3) * 32) >> 4;  // 16 head-dim elements per step
+        umma_bf16_ss_lo(tmem_s, qa + off, ka + off, idesc, kk != 0);
     }
-    return rb_attention_item(round, blockIdx.x, gridDim.x, p.q_blocks, p.heads_total, p.Hq, p.wave_heads, qb, h, b);
+    umma_commit(done);
+}
+// Half of O += P V: keys [64 * half, 64 * half + 64) of the block.  16 keys per step: 8 TMEM columns of packed BF16 pairs, 2048 B of V.
+__device__ __noinline__ void issue_pv_half(uint32_t tmem_o, uint32_t tmem_p, uint32_t va, uint32_t idesc, uint32_t accumulate_first) {
+#pragma unroll
+    for (uint32_t kk = 0; kk < TK / 32; ++kk)
+        umma_bf16_ts_lo(tmem_o, tmem_p + kk * 8, va + kk * (2048 >> 4), idesc, kk != 0 ? 1u : accumulate_first);
 }
 
 // Packed FP32 pairs (fma.rn.f32x2 / add.rn.f32x2) and the three-input max halve the issue slots of the softmax.
@@ -298,17 +328,13 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     uint64_t* o_free = o_full + 2;              // [2 tiles]  softmax warps -> MMA: O has been read out of TMEM
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_free + 2);
     volatile uint32_t* abort_word = tmem_slot + 1;
-    // this CTA's work items, one entry per step: (query block | valid << 31, head | batch << 16).  Filled by all threads at once
+    // this CTA's work items, one entry per step (see make_item).  Filled by all threads at once
     // before the roles part, so that no role spends its own (single-thread) instruction stream on the index arithmetic.
-    uint2* item_tab = reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(bars) + 256);
+    uint4* item_tab = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(bars) + 256);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rounds = rb_attention_steps(p.q_blocks, p.heads_total, p.wave_heads, gridDim.x);
-    for (uint32_t step = threadIdx.x; step < rounds && step < ITEM_TAB; step += THREADS) {
-        uint32_t qb = 0, h = 0, b = 0;
-        const bool valid = rb_attention_item(step, blockIdx.x, gridDim.x, p.q_blocks, p.heads_total, p.Hq, p.wave_heads, qb, h, b);
-        item_tab[step] = make_uint2(qb | (valid ? 0x80000000u : 0u), h | (b << 16));
-    }
+    for (uint32_t step = threadIdx.x; step < rounds && step < ITEM_TAB; step += THREADS) item_tab[step] = make_item(p, step);
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1); mbar_init(q_empty, 1);
@@ -343,10 +369,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             uint32_t armed = 0, armed_parity = 0;      // bit 0: Q, bits 1-2: K stages, bits 3-4: V stages
             auto arm = [&](uint32_t bit, uint32_t parity) { armed |= 1u << bit; armed_parity = (armed_parity & ~(1u << bit)) | (parity << bit); };
             for (uint32_t round = 0; ok && round < rounds; ++round) {
-                uint32_t qb, h, b;
-                if (!item_coords(p, item_tab, round, qb, h, b)) continue;
+                uint32_t qb, h, b, nb0, nb1;
+                if (!item_coords(p, item_tab, round, qb, h, b, nb0, nb1)) continue;
                 const uint32_t kvh = h / (p.Hq / p.Hkv), row0 = qb * 2 * TQ;
-                const uint32_t nb0 = blocks_for(p, row0, row0 + TQ), nb1 = blocks_for(p, row0 + TQ, row0 + 2 * TQ);
                 const uint32_t n_max = nb0 > nb1 ? nb0 : nb1;
                 if (n_max == 0) continue;
                 if (q_it > 0 && !(ok = mbar_wait(q_empty, (q_it - 1) & 1, abort_word))) break;
@@ -386,19 +411,12 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             // descriptor lower halves of the tile bases; a step of 16 head-dim elements (or 16 keys of V) is a constant added to them
             const uint32_t q_lo = desc_lo_kmajor(smem_u32(sq)), k_lo = desc_lo_kmajor(smem_u32(sk)), v_lo = desc_lo_mnmajor(smem_u32(sv), SLAB_BYTES);
             auto issue_s = [&](uint32_t t, uint32_t st) {
-                const uint32_t qa = q_lo + t * (TILE_BYTES >> 4), ka = k_lo + st * (TILE_BYTES >> 4);
-#pragma unroll
-                for (uint32_t kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t off = ((kk >> 2) * SLAB_BYTES + (kk & 3) * 32) >> 4;  // 16 head-dim elements per step
-                    umma_bf16_ss_lo(tmem_base + t * TK, qa + off, ka + off, idesc_qk, kk != 0);
-                }
-                umma_commit(&s_full[t]);
+                issue_scores(tmem_base + t * TK, q_lo + t * (TILE_BYTES >> 4), k_lo + st * (TILE_BYTES >> 4), idesc_qk, &s_full[t]);
             };
             for (uint32_t round = 0; ok && round < rounds; ++round) {
-                uint32_t qb, h, b;
-                if (!item_coords(p, item_tab, round, qb, h, b)) continue;
-                const uint32_t row0 = qb * 2 * TQ;
-                const uint32_t nb[2] = {blocks_for(p, row0, row0 + TQ), blocks_for(p, row0 + TQ, row0 + 2 * TQ)};
+                uint32_t qb, h, b, nb0, nb1;
+                if (!item_coords(p, item_tab, round, qb, h, b, nb0, nb1)) continue;
+                const uint32_t nb[2] = {nb0, nb1};
                 const uint32_t n_max = nb[0] > nb[1] ? nb[0] : nb[1];
                 if (n_max == 0) continue;
                 const uint32_t total_s = nb[0] + nb[1];
@@ -412,7 +430,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     if (!(ok = mbar_wait(&k_full[st], ph, abort_word))) break;
                     tc_fence_after();
 #pragma unroll
-                    for (uint32_t t = 0; t < 2; ++t) if (nb[t] > 0) { issue_s(t, st); ++s_done; }
+                    for (uint32_t ti = 0; ti < 2; ++ti) { const uint32_t t = ti ^ FIRST_TILE; if (nb[t] > 0) { issue_s(t, st); ++s_done; } }
                     umma_commit(&k_empty[st]);
                     if (s_done == total_s) umma_commit(q_empty);
                     RB_TR(trace_cta, 4, round, 2);                   // MMA: first score GEMMs issued
@@ -420,7 +438,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 for (uint32_t j = 0; ok && j < n_max; ++j) {
                     const uint32_t st = (kv_it + j) % KV_STAGES, ph = ((kv_it + j) / KV_STAGES) & 1;
 #pragma unroll
-                    for (uint32_t t = 0; t < 2; ++t) {
+                    for (uint32_t ti = 0; ti < 2; ++ti) {
+                        const uint32_t t = ti ^ FIRST_TILE, other = t ^ 1u;     // `other` is served first when t is the second tile
                         if (!ok || j >= nb[t]) continue;
                         const uint32_t par = blk[t] & 1;
                         RB_TR(tr, 2 + t, j, 7);
@@ -432,18 +451,15 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                         RB_TR(tr, 2 + t, j, 1);
                         tc_fence_after();
                         const uint32_t va = v_lo + st * (TILE_BYTES >> 4);
-#pragma unroll
-                        for (uint32_t kk = 0; kk < TK / 32; ++kk)   // 16 keys per step: 8 TMEM columns of packed BF16 pairs, 2048 B of V
-                            umma_bf16_ts_lo(tmem_base + 256 + t * D, tmem_base + t * TK + kk * 8, va + kk * (2048 >> 4), idesc_pv, kk != 0 ? 1u : j);
+                        issue_pv_half(tmem_base + 256 + t * D, tmem_base + t * TK, va, idesc_pv, j);
                         RB_TR(tr, 2 + t, j, 2);
                         if (!(ok = wait_handoff(&p_full[t], par, abort_word))) continue;
                         RB_TR(tr, 2 + t, j, 3);
                         tc_fence_after();
-#pragma unroll
-                        for (uint32_t kk = TK / 32; kk < TK / 16; ++kk)
-                            umma_bf16_ts_lo(tmem_base + 256 + t * D, tmem_base + t * TK + kk * 8, va + kk * (2048 >> 4), idesc_pv, 1u);
+                        issue_pv_half(tmem_base + 256 + t * D, tmem_base + t * TK + 32, va + 4 * (2048 >> 4), idesc_pv, 1u);
                         ++blk[t];
-                        const bool last_user = (t == 1) || (j >= nb[1]);
+                        // the stage is released by the tile served second, or by this one when the other tile does not use the block
+                        const bool last_user = (ti == 1) || (j >= nb[other]);
                         if (last_user) umma_commit(&v_empty[st]);
                         RB_TR(tr, 2 + t, j, 4);
                         if (j + 1 < nb[t]) {
@@ -452,7 +468,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                             RB_TR(tr, 2 + t, j, 5);
                             tc_fence_after();
                             issue_s(t, st1); ++s_done;
-                            const bool last_k_user = (t == 1) || (j + 1 >= nb[1]);
+                            const bool last_k_user = (ti == 1) || (j + 1 >= nb[other]);
                             if (last_k_user) umma_commit(&k_empty[st1]);
                             if (s_done == total_s) umma_commit(q_empty);
                             RB_TR(tr, 2 + t, j, 6);
@@ -477,11 +493,11 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         uint32_t blk = 0, used = 0;
         bool ok = true;
         for (uint32_t round = 0; ok && round < rounds; ++round) {
-            uint32_t qb, h, b;
-            if (!item_coords(p, item_tab, round, qb, h, b)) continue;
+            uint32_t qb, h, b, nb0, nb1;
+            if (!item_coords(p, item_tab, round, qb, h, b, nb0, nb1)) continue;
             const uint32_t tile_row0 = qb * 2 * TQ + t * TQ;
             if (tile_row0 >= p.M) continue;
-            const uint32_t nb = blocks_for(p, tile_row0, tile_row0 + TQ);
+            const uint32_t nb = t ? nb1 : nb0;
             const uint32_t row = tile_row0 + row_in_tile;                  // query index inside the sequence
             const uint64_t o_at = (uint64_t)b * p.o_stride_b + (uint64_t)h * p.o_stride_h + (uint64_t)row * p.o_stride_m;
             // row of the additive mask [B*Hq, M, N]; rows past M are never dereferenced beyond the mask because their loads are

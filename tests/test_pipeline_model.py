@@ -279,14 +279,14 @@ def test_attention_barrier_protocol(items, seed):
             yield from wait(q_full, q_it & 1)
             st, ph = kv_it % KV, (kv_it // KV) & 1
             yield from wait(k_full[st], ph)
-            for t in range(2):
+            for t in (1, 0):                                   # tile 1 leads: it has the extra key block under a causal mask
                 if n[t] > 0: issue_s(t, 0, st); s_done += 1
             ksm[st] = None; k_empty[st].arrive()
             if s_done == total_s: qsm[0] = None; q_empty.arrive()
             yield True
             for j in range(n_max):
                 st, ph = (kv_it + j) % KV, ((kv_it + j) // KV) & 1
-                for t in range(2):
+                for t in (1, 0):
                     if j >= n[t]: continue
                     par = blk[t] & 1
                     yield from wait(p_half[t], par)
@@ -302,14 +302,14 @@ def test_attention_barrier_protocol(items, seed):
                     assert s_tmem[t] == ("P", i, j) and p_state[t] == 2
                     o_tmem[t][1].append(j); s_tmem[t] = ("consumed", i, j)
                     blk[t] += 1
-                    if t == 1 or j >= n[1]:
+                    if t == 0 or j >= n[0]:                    # released by the tile served second, or by the only user
                         vsm[st] = None; v_empty[st].arrive()
                     yield True
                     if j + 1 < n[t]:
                         st1, ph1 = (kv_it + j + 1) % KV, ((kv_it + j + 1) // KV) & 1
                         yield from wait(k_full[st1], ph1)
                         issue_s(t, j + 1, st1); s_done += 1
-                        if t == 1 or j + 1 >= n[1]:
+                        if t == 0 or j + 1 >= n[0]:
                             ksm[st1] = None; k_empty[st1].arrive()
                         if s_done == total_s: qsm[0] = None; q_empty.arrive()
                         yield True
