@@ -111,6 +111,12 @@ RB_API int32_t rb_device_properties(rb_ctx* ctx, char* name, size_t name_bytes, 
  * zero-byte requests still own a minimal allocation (tensor/mod.rs:106-111).  rb_free synchronises first. */
 RB_API int32_t rb_alloc(rb_ctx* ctx, uint64_t bytes, uint64_t* handle);
 RB_API int32_t rb_free(rb_ctx* ctx, uint64_t handle);
+/* Debug option (environment RUDA_GUARD_BANDS=1 at rb_init_exclusive): every rb_alloc is surrounded by 256-byte guard bands
+ * and starts filled with all-ones bytes (NaN in every float format).  rb_check_guards drains the stream and counts the
+ * live allocations whose guard bands a kernel has written into; rb_free checks its allocation too and reports damage as a
+ * sticky error.  Stands in for a memory checker where none can run (the reference's test VM poisons local memory in the
+ * same spirit, rust-ascend-kernels/src/tests.rs:20-88). */
+RB_API int32_t rb_check_guards(rb_ctx* ctx, uint64_t* damaged);
 /* Registers caller-owned device memory (for example a torch tensor) as a non-owning storage handle. */
 RB_API int32_t rb_import(rb_ctx* ctx, void* device_pointer, uint64_t bytes, uint64_t* handle);
 /* AscendStorage::get, runtime/mod.rs:494-500: resolves a handle to its device address and size. */

@@ -25,6 +25,7 @@ struct Storage {
     void* ptr = nullptr;
     uint64_t bytes = 0;
     bool owned = false;
+    uint32_t guard = 0;      // bytes of guard band in front of and behind `ptr` (debug option), 0 when off
 };
 
 }  // namespace rb
@@ -48,6 +49,7 @@ struct rb_ctx {
     size_t smem_optin = 0;
     void* workspace = nullptr;         // lazily grown scratch owned by the context
     uint64_t workspace_bytes = 0;
+    uint32_t guard_bytes = 0;          // RUDA_GUARD_BANDS=1: every allocation gets guard bands and starts filled with NaN patterns
     void* gemm_state = nullptr;        // tensor-map cache owned by the GEMM translation unit
     void* attention_state = nullptr;
 };

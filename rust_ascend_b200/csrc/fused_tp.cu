@@ -425,12 +425,11 @@ __global__ void __launch_bounds__(PUSH_THREADS) reduce_norm_push_kernel(const Pu
 template <int BN>
 int32_t launch_scatter(rb_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const ScatterParams& p) {
     using C = Config<BN>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_scatter_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
-        if (e != cudaSuccess) return rb::fail(RB_STATUS, "cudaFuncSetAttribute(scatter GEMM) failed with CUDA status %d (%s)", (int)e, cudaGetErrorString(e));
-        configured = true;
-    }
+    // raised once per process and template instance; std::call_once makes the first use safe from any thread
+    static std::once_flag once;
+    static cudaError_t configured = cudaSuccess;
+    std::call_once(once, [] { configured = cudaFuncSetAttribute(gemm_scatter_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES); });
+    if (configured != cudaSuccess) return rb::fail(RB_STATUS, "cudaFuncSetAttribute(scatter GEMM) failed with CUDA status %d (%s)", (int)configured, cudaGetErrorString(configured));
     const uint32_t tiles = p.tiles_m * p.tiles_n;
     const uint32_t sms = ctx->sm_limit > 0 ? (uint32_t)ctx->sm_limit : (uint32_t)ctx->sm_count;
     gemm_scatter_kernel<BN><<<tiles < sms ? tiles : sms, THREADS, C::SMEM_BYTES, ctx->stream>>>(ma, mb, p);

@@ -497,12 +497,11 @@ template <int BN>
 int32_t launch(rb_ctx* ctx, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2, const CUtensorMap& mbh,
                const CUtensorMap& mb2h, GemmParams& p) {
     using C = Config<BN>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
-        if (e != cudaSuccess) return rb::fail(RB_STATUS, "cudaFuncSetAttribute(GEMM) failed with CUDA status %d (%s)", (int)e, cudaGetErrorString(e));
-        configured = true;
-    }
+    // raised once per process and template instance; std::call_once makes the first use safe from any thread
+    static std::once_flag once;
+    static cudaError_t configured = cudaSuccess;
+    std::call_once(once, [] { configured = cudaFuncSetAttribute(gemm_bf16_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES); });
+    if (configured != cudaSuccess) return rb::fail(RB_STATUS, "cudaFuncSetAttribute(GEMM) failed with CUDA status %d (%s)", (int)configured, cudaGetErrorString(configured));
     const uint32_t sms = ctx->sm_limit > 0 ? (uint32_t)ctx->sm_limit : (uint32_t)ctx->sm_count;
     const uint32_t grid = p.items < sms ? p.items : sms;
     gemm_bf16_kernel<BN><<<grid, THREADS, C::SMEM_BYTES, ctx->stream>>>(ma, mb, mb2, mbh, mb2h, p);

@@ -2,6 +2,8 @@
 // rust-ascend-driver/src/tensor/runtime/mod.rs:485-877).
 #include "common.cuh"
 
+#include <cstdlib>
+
 namespace rb {
 
 static thread_local char g_error[1024] = "";
@@ -130,6 +132,22 @@ static rb_ctx* g_ctx = nullptr;
 
 using namespace rb;
 
+namespace {
+
+constexpr int GUARD_PATTERN = 0xA5;
+
+// Reads both guard bands of an allocation back and compares them with the pattern (the stream has been drained by the caller).
+bool guards_damaged(const Storage& s) {
+    const uint64_t body = ((s.bytes ? s.bytes : 1) + 255) & ~uint64_t(255);
+    std::vector<unsigned char> host(2ull * s.guard);
+    if (cudaMemcpy(host.data(), static_cast<const char*>(s.ptr) - s.guard, s.guard, cudaMemcpyDeviceToHost) != cudaSuccess) return true;
+    if (cudaMemcpy(host.data() + s.guard, static_cast<const char*>(s.ptr) + body, s.guard, cudaMemcpyDeviceToHost) != cudaSuccess) return true;
+    for (unsigned char c : host) if (c != GUARD_PATTERN) return true;
+    return false;
+}
+
+}  // namespace
+
 extern "C" {
 
 const char* rb_last_error(void) { return g_error; }
@@ -152,6 +170,7 @@ int32_t rb_init_exclusive(const rb_options* options, rb_ctx** out) {
     rb_ctx* ctx = new rb_ctx();
     ctx->device = device;
     ctx->synchronous = options && options->synchronous;
+    { const char* env = std::getenv("RUDA_GUARD_BANDS"); ctx->guard_bytes = env && env[0] == '1' ? 256u : 0u; }
     ctx->sm_count = prop.multiProcessorCount;
     ctx->smem_optin = prop.sharedMemPerBlockOptin;
     e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
@@ -191,15 +210,44 @@ int32_t rb_device_properties(rb_ctx* ctx, char* name, size_t name_bytes, int32_t
     return RB_OK;
 }
 
+int32_t rb_check_guards(rb_ctx* ctx, uint64_t* damaged) {
+    RB_TRY(check_ctx(ctx));
+    if (!damaged) return fail(RB_NULL_HANDLE, "null pointer");
+    *damaged = 0;
+    if (!ctx->guard_bytes) return RB_OK;
+    ctx->stats.synchronizations++;
+    RB_CUDA(ctx, "cudaStreamSynchronize", cudaStreamSynchronize(ctx->stream));
+    std::vector<Storage> owned;
+    {
+        std::lock_guard<std::mutex> g(ctx->lock);
+        for (auto& kv : ctx->storage) if (kv.second.owned && kv.second.guard) owned.push_back(kv.second);
+    }
+    for (const Storage& s : owned) if (guards_damaged(s)) ++*damaged;
+    return RB_OK;
+}
+
 int32_t rb_alloc(rb_ctx* ctx, uint64_t bytes, uint64_t* handle) {
     RB_TRY(check_ctx(ctx));
     if (!handle) return fail(RB_NULL_HANDLE, "null handle pointer");
     void* p = nullptr;
     uint64_t real = bytes ? bytes : 1;  // empty tensors still own an allocation
-    RB_CUDA(ctx, "cudaMalloc", cudaMalloc(&p, real));
+    const uint32_t guard = ctx->guard_bytes;
+    if (guard) {
+        // Debug option: [guard | body rounded up to 256 B | guard].  The guards hold a fixed pattern that rb_check_guards and
+        // rb_free verify; the body starts as all-ones bytes (NaN in every float format), so an output element that a kernel
+        // never wrote shows up in any comparison.
+        const uint64_t body = (real + 255) & ~uint64_t(255);
+        RB_CUDA(ctx, "cudaMalloc", cudaMalloc(&p, body + 2ull * guard));
+        RB_CUDA(ctx, "cudaMemsetAsync", cudaMemsetAsync(p, GUARD_PATTERN, guard, ctx->stream));
+        RB_CUDA(ctx, "cudaMemsetAsync", cudaMemsetAsync(static_cast<char*>(p) + guard, 0xFF, body, ctx->stream));
+        RB_CUDA(ctx, "cudaMemsetAsync", cudaMemsetAsync(static_cast<char*>(p) + guard + body, GUARD_PATTERN, guard, ctx->stream));
+        p = static_cast<char*>(p) + guard;
+    } else {
+        RB_CUDA(ctx, "cudaMalloc", cudaMalloc(&p, real));
+    }
     std::lock_guard<std::mutex> g(ctx->lock);
     uint64_t id = ctx->next_handle++;
-    ctx->storage[id] = Storage{p, bytes, true};
+    ctx->storage[id] = Storage{p, bytes, true, guard};
     ctx->stats.bytes_in_use += bytes; ctx->stats.allocations++;
     *handle = id;
     return RB_OK;
@@ -230,6 +278,15 @@ int32_t rb_free(rb_ctx* ctx, uint64_t handle) {
     ctx->stats.synchronizations++;
     cudaError_t e = cudaStreamSynchronize(ctx->stream);
     if (e != cudaSuccess) { ctx->poisoned = true; return fail(RB_COMPLETION, "dealloc: stream did not drain (CUDA status %d); memory is leaked, not freed", (int)e); }
+    if (s.guard) {
+        if (guards_damaged(s)) {
+            std::lock_guard<std::mutex> g(ctx->lock);
+            char msg[160]; snprintf(msg, sizeof(msg), "a kernel wrote outside storage %llu (%llu bytes): its guard band is damaged", (unsigned long long)handle, (unsigned long long)s.bytes);
+            ctx->sticky.emplace_back(msg);
+        }
+        RB_CUDA(ctx, "cudaFree", cudaFree(static_cast<char*>(s.ptr) - s.guard));
+        return RB_OK;
+    }
     RB_CUDA(ctx, "cudaFree", cudaFree(s.ptr));
     return RB_OK;
 }

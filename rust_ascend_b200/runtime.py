@@ -264,6 +264,12 @@ class ComputeClient:
 
     flush = sync
 
+    def check_guards(self) -> int:
+        """With RUDA_GUARD_BANDS=1: drains the stream and returns how many live allocations had a kernel write outside them."""
+        n = C.c_uint64()
+        _check(self._lib.rb_check_guards(self._ctx, C.byref(n)))
+        return n.value
+
     def take_errors(self) -> list[str]:
         buf = C.create_string_buffer(4096)
         n = C.c_uint32()
