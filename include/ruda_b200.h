@@ -355,7 +355,7 @@ RB_API int32_t rb_aux_wait(rb_ctx* ctx, uint32_t slot);
 /* ---- peer memory and the fused tensor-parallel exchange (no counterpart in the reference: its row-parallel projection is a
  * GEMM followed by a vendor all-reduce, runtime/hccl.rs:386-548; src/distributed.rs:139-156) ------------------------- */
 #define RB_MAX_PEERS 8
-#define RB_PEER_TOKEN_BYTES 72 /* 64-byte CUDA IPC handle of the allocation + 8-byte offset of the storage inside it */
+#define RB_PEER_TOKEN_BYTES 80 /* 64-byte CUDA IPC handle of the allocation + 8-byte offset of the storage inside it + 8-byte length of the storage */
 /* This entry has no counterpart in the reference.  Exports a storage of this process as a token (CUDA IPC) that another process of
  * the node passes to rb_peer_open; tokens travel over the control plane that carries the communicator's root id
  * (src/distributed.rs:74-110). */

@@ -17,7 +17,7 @@
 namespace {
 
 constexpr size_t HANDLE_BYTES = sizeof(cudaIpcMemHandle_t);
-static_assert(HANDLE_BYTES == 64 && RB_PEER_TOKEN_BYTES == HANDLE_BYTES + 8, "token = 64-byte IPC handle + 8-byte offset");
+static_assert(HANDLE_BYTES == 64 && RB_PEER_TOKEN_BYTES == HANDLE_BYTES + 16, "token = 64-byte IPC handle + 8-byte offset + 8-byte length");
 
 struct Mapping { void* base = nullptr; int refs = 0; };
 struct Opened { std::string key; };
@@ -61,6 +61,7 @@ int32_t rb_peer_export(rb_ctx* ctx, uint64_t handle, uint8_t token[RB_PEER_TOKEN
     const uint64_t offset = (uint64_t)((uintptr_t)p - (uintptr_t)base);
     std::memcpy(token, &h, HANDLE_BYTES);
     std::memcpy(token + HANDLE_BYTES, &offset, 8);
+    std::memcpy(token + HANDLE_BYTES + 8, &bytes, 8);        // the opener may not claim more than the exporter owns
     return RB_OK;
 }
 
@@ -71,6 +72,9 @@ int32_t rb_peer_open(rb_ctx* ctx, const uint8_t token[RB_PEER_TOKEN_BYTES], uint
     uint64_t offset = 0;
     std::memcpy(&h, token, HANDLE_BYTES);
     std::memcpy(&offset, token + HANDLE_BYTES, 8);
+    uint64_t exported = 0;
+    std::memcpy(&exported, token + HANDLE_BYTES + 8, 8);
+    if (bytes > exported) return fail(RB_INVALID_TENSOR, "the token names a storage of %llu bytes; %llu were asked for", (unsigned long long)exported, (unsigned long long)bytes);
     const std::string key(reinterpret_cast<const char*>(token), HANDLE_BYTES);
     std::lock_guard<std::mutex> g(g_lock);
     Mapping& m = g_mappings[key];

@@ -24,7 +24,7 @@ from .distributed import check_replies, failure_bytes
 from .runtime import ComputeClient, DType, InvalidTensor, TensorBuffer, _check, _ref
 
 MAX_PEERS = 8
-TOKEN_BYTES = 72                     # RB_PEER_TOKEN_BYTES
+TOKEN_BYTES = 80                     # RB_PEER_TOKEN_BYTES
 FLAG_WORDS = 16                      # words per flag group: world counters, the running target, padding
 SCATTER, GATHER, BARRIER = 0, 1, 2   # flag groups inside one flags buffer; word 48 is the local block counter
 
