@@ -316,9 +316,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     uint8_t* sk = smem + 2 * TILE_BYTES;                  // [stages][2 slabs][128 keys][64 d]
     uint8_t* sv = sk + KV_STAGES * TILE_BYTES;            // [stages][2 slabs][128 keys][64 dv]
     uint64_t* bars = reinterpret_cast<uint64_t*>(sv + KV_STAGES * TILE_BYTES);
-    uint64_t* q_full = bars;                    // [2 tiles]  TMA -> MMA: the tile's Q rows of an item have landed
-    uint64_t* q_empty = bars + 2;               // [2 tiles]  MMA -> TMA: the tile's last score GEMM of an item has read them
-    uint64_t* k_full = bars + 4;                // [stages]
+    uint64_t* q_full = bars;                    // [1]  TMA -> MMA: Q of the item has landed
+    uint64_t* q_empty = bars + 1;               // [1]  MMA -> TMA: the item's last score GEMM has read Q
+    uint64_t* k_full = bars + 2;                // [stages]
     uint64_t* k_empty = k_full + KV_STAGES;
     uint64_t* v_full = k_empty + KV_STAGES;
     uint64_t* v_empty = v_full + KV_STAGES;
@@ -338,7 +338,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     for (uint32_t step = threadIdx.x; step < rounds && step < ITEM_TAB; step += THREADS) item_tab[step] = make_item(p, step);
 
     if (threadIdx.x == 0) {
-        for (int t = 0; t < 2; ++t) { mbar_init(&q_full[t], 1); mbar_init(&q_empty[t], 1); }
+        mbar_init(q_full, 1); mbar_init(q_empty, 1);
         for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
         for (int t = 0; t < 2; ++t) {
             mbar_init(&s_full[t], 1); mbar_init(&p_half[t], 128); mbar_init(&p_full[t], 128); mbar_init(&o_full[t], 1);
@@ -366,49 +366,38 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         if (warp == W_TMA && elect_one()) {
             // ---------------- TMA producer ----------------
             bool ok = true;
-            uint32_t kv_it = 0;
-            uint32_t q_it[2] = {0, 0};                 // Q loads issued per tile
-            uint32_t armed = 0, armed_parity = 0;      // bits 0-1: Q tiles, bits 2-3: K stages, bits 4-5: V stages
+            uint32_t kv_it = 0, q_it = 0;
+            uint32_t armed = 0, armed_parity = 0;      // bit 0: Q, bits 1-2: K stages, bits 3-4: V stages
             auto arm = [&](uint32_t bit, uint32_t parity) { armed |= 1u << bit; armed_parity = (armed_parity & ~(1u << bit)) | (parity << bit); };
             for (uint32_t round = 0; ok && round < rounds; ++round) {
                 uint32_t qb, h, b, nb0, nb1;
                 if (!item_coords(p, item_tab, round, qb, h, b, nb0, nb1)) continue;
                 const uint32_t kvh = h / (p.Hq / p.Hkv), row0 = qb * 2 * TQ;
-                const uint32_t nb[2] = {nb0, nb1};
                 const uint32_t n_max = nb0 > nb1 ? nb0 : nb1;
                 if (n_max == 0) continue;
-                // Q rows of one tile, as soon as the tile's last score GEMM of the item before has read the buffer
-                auto load_q = [&](uint32_t t) -> bool {
-                    if (nb[t] == 0) return true;
-                    if (q_it[t] > 0 && !mbar_wait(&q_empty[t], (q_it[t] - 1) & 1, abort_word)) return false;
-                    mbar_expect_tx(&q_full[t], TILE_BYTES); arm(t, q_it[t] & 1);
+                if (q_it > 0 && !(ok = mbar_wait(q_empty, (q_it - 1) & 1, abort_word))) break;
+                mbar_expect_tx(q_full, 2 * TILE_BYTES); arm(0, q_it & 1);
+                for (int t = 0; t < 2; ++t)
                     for (int s = 0; s < 2; ++s)
-                        tma_load_4d(sq + t * TILE_BYTES + s * SLAB_BYTES, &map_q, &q_full[t], s * 64, (int32_t)(row0 + t * TQ), (int32_t)h, (int32_t)b);
-                    ++q_it[t];
-                    return true;
-                };
-                // Order: tile 0 finishes an item first (it has the fewer key blocks), so its Q and the first K tile go out before
-                // the copy waits for tile 1's buffer; the MMA warp can then start tile 0's next item while tile 1 still works.
-                if (!(ok = load_q(0))) break;
+                        tma_load_4d(sq + t * TILE_BYTES + s * SLAB_BYTES, &map_q, q_full, s * 64, (int32_t)(row0 + t * TQ), (int32_t)h, (int32_t)b);
                 for (uint32_t j = 0; ok && j < n_max; ++j) {
                     const uint32_t st = (kv_it + j) % KV_STAGES, ph = ((kv_it + j) / KV_STAGES) & 1;
                     if (!(ok = mbar_wait(&k_empty[st], ph ^ 1, abort_word))) break;
-                    mbar_expect_tx(&k_full[st], TILE_BYTES); arm(2 + st, ph);
+                    mbar_expect_tx(&k_full[st], TILE_BYTES); arm(1 + st, ph);
                     for (int s = 0; s < 2; ++s)
                         tma_load_4d(sk + st * TILE_BYTES + s * SLAB_BYTES, &map_k, &k_full[st], s * 64, (int32_t)(j * TK), (int32_t)kvh, (int32_t)b);
-                    if (j == 0 && !(ok = load_q(1))) break;
                     if (!(ok = mbar_wait(&v_empty[st], ph ^ 1, abort_word))) break;
-                    mbar_expect_tx(&v_full[st], TILE_BYTES); arm(4 + st, ph);
+                    mbar_expect_tx(&v_full[st], TILE_BYTES); arm(3 + st, ph);
                     for (int s = 0; s < 2; ++s)
                         tma_load_4d(sv + st * TILE_BYTES + s * SLAB_BYTES, &map_v, &v_full[st], s * 64, (int32_t)(j * TK), (int32_t)kvh, (int32_t)b);
                 }
-                kv_it += n_max;
+                kv_it += n_max; ++q_it;
             }
             if (!ok) {
                 // A wait expired: give the copies already issued a bounded time to land before the CTA retires.
-                for (uint32_t bit = 0; bit < 6; ++bit) {
+                for (uint32_t bit = 0; bit < 5; ++bit) {
                     if (!(armed & (1u << bit))) continue;
-                    uint64_t* bar = bit < 2 ? &q_full[bit] : (bit < 4 ? &k_full[bit - 2] : &v_full[bit - 4]);
+                    uint64_t* bar = bit == 0 ? q_full : (bit < 3 ? &k_full[bit - 1] : &v_full[bit - 3]);
                     for (uint32_t i = 0; i < (1u << 20) && !mbar_try_wait(bar, (armed_parity >> bit) & 1u); ++i) {}
                 }
             }
@@ -417,43 +406,13 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             const uint32_t idesc_qk = make_idesc_bf16(TQ, TK, 0, 0);   // A = Q (K-major), B = K tile (K-major)
             const uint32_t idesc_pv = make_idesc_bf16(TQ, D, 0, 1);    // A = P (TMEM), B = V tile, Dv-contiguous (MN-major)
             bool ok = true;
-            uint32_t kv_it = 0;
-            // Per-tile phase bits, packed into one register each (bit t = tile t): the parity of the tile's next Q, of its next key
-            // block (s_full / p_half / p_full) and of its next item (o_full / o_free), and whether the tile has finished an item yet.
-            uint32_t q_par = 0, blk_par = 0, used_par = 0, used_any = 0;
+            uint32_t kv_it = 0, q_it = 0;
+            uint32_t blk[2] = {0, 0};      // key blocks served per tile so far (parity of s_full / p_half / p_full)
+            uint32_t used[2] = {0, 0};     // items per tile so far (parity of o_full / o_free)
             // descriptor lower halves of the tile bases; a step of 16 head-dim elements (or 16 keys of V) is a constant added to them
             const uint32_t q_lo = desc_lo_kmajor(smem_u32(sq)), k_lo = desc_lo_kmajor(smem_u32(sk)), v_lo = desc_lo_mnmajor(smem_u32(sv), SLAB_BYTES);
             auto issue_s = [&](uint32_t t, uint32_t st) {
                 issue_scores(tmem_base + t * TK, q_lo + t * (TILE_BYTES >> 4), k_lo + st * (TILE_BYTES >> 4), idesc_qk, &s_full[t]);
-            };
-            // Items overlap: a tile that has finished its last key block of an item gets the first score GEMM of the NEXT item
-            // issued as soon as that item's Q rows and first K tile are there, while the other tile still finishes the current one.
-            uint32_t pre = 0;              // bit t: block 0 of the item about to start has already been issued for tile t
-            uint32_t pending = 0;          // bit t: tile t is done with the current item and waits for such an early issue
-            uint32_t next_has = 0;         // bit t: the next item has key blocks for tile t; bit 2 + t: exactly one
-            uint32_t next_stage = 0, next_phase = 0;
-            auto try_early = [&]() {
-#pragma unroll
-                for (uint32_t t = 0; t < 2; ++t) {
-                    if (!(pending & (1u << t))) continue;
-                    if (!mbar_test_wait(&q_full[t], (q_par >> t) & 1) || !mbar_test_wait(&k_full[next_stage], next_phase)) continue;
-                    tc_fence_after();
-                    issue_s(t, next_stage);
-                    if (next_has & (4u << t)) umma_commit(&q_empty[t]);
-                    pre |= 1u << t; pending &= ~(1u << t);
-                }
-            };
-            // Waits for a hand-off of the softmax warps; while a tile is waiting for its early issue the wait polls, so that
-            // whichever becomes possible first is served.
-            auto wait_serving = [&](uint64_t* bar, uint32_t parity) -> bool {
-                if (!pending) return wait_handoff(bar, parity, abort_word);
-                for (uint32_t i = 0; i < (WAIT_LIMIT << 2); ++i) {
-                    if (mbar_test_wait(bar, parity)) return true;
-                    if (pending) try_early();
-                    if ((i & 1023u) == 1023u && *abort_word) return false;
-                }
-                *abort_word = 1u;
-                return false;
             };
             for (uint32_t round = 0; ok && round < rounds; ++round) {
                 uint32_t qb, h, b, nb0, nb1;
@@ -461,59 +420,45 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 const uint32_t nb[2] = {nb0, nb1};
                 const uint32_t n_max = nb[0] > nb[1] ? nb[0] : nb[1];
                 if (n_max == 0) continue;
+                const uint32_t total_s = nb[0] + nb[1];
+                uint32_t s_done = 0;
                 const bool tr = trace_cta && round == 0;
-                RB_TR(trace_cta, 4, round, 0);                       // MMA: item starts
+                RB_TR(trace_cta, 4, round, 0);                       // MMA: starts waiting for the item's Q
+                if (!(ok = mbar_wait(q_full, q_it & 1, abort_word))) break;
+                RB_TR(trace_cta, 4, round, 1);                       // MMA: Q has landed
                 {
-                    // first score GEMMs of the item for the tiles that did not get theirs early
                     const uint32_t st = kv_it % KV_STAGES, ph = (kv_it / KV_STAGES) & 1;
+                    if (!(ok = mbar_wait(&k_full[st], ph, abort_word))) break;
+                    tc_fence_after();
 #pragma unroll
-                    for (uint32_t ti = 0; ti < 2; ++ti) {
-                        const uint32_t t = ti ^ FIRST_TILE;
-                        if (!ok || nb[t] == 0 || (pre & (1u << t))) continue;
-                        if (!(ok = mbar_wait(&q_full[t], (q_par >> t) & 1, abort_word))) continue;
-                        if (!(ok = mbar_wait(&k_full[st], ph, abort_word))) continue;
-                        tc_fence_after();
-                        issue_s(t, st);
-                        if (nb[t] == 1) umma_commit(&q_empty[t]);
-                    }
-                    if (!ok) break;
+                    for (uint32_t ti = 0; ti < 2; ++ti) { const uint32_t t = ti ^ FIRST_TILE; if (nb[t] > 0) { issue_s(t, st); ++s_done; } }
                     umma_commit(&k_empty[st]);
+                    if (s_done == total_s) umma_commit(q_empty);
                     RB_TR(trace_cta, 4, round, 2);                   // MMA: first score GEMMs issued
                 }
-                pre = 0; pending = 0;
-                // the item after this one (for the early issue): its block counts and where its first K tile will be
-                next_has = 0;
-                for (uint32_t r2 = round + 1; r2 < rounds; ++r2) {
-                    uint32_t q2, h2, b2, m0, m1;
-                    if (item_coords(p, item_tab, r2, q2, h2, b2, m0, m1) && (m0 | m1)) {
-                        next_has = (m0 ? 1u : 0u) | (m1 ? 2u : 0u) | (m0 == 1 ? 4u : 0u) | (m1 == 1 ? 8u : 0u);
-                        break;
-                    }
-                }
-                next_stage = (kv_it + n_max) % KV_STAGES; next_phase = ((kv_it + n_max) / KV_STAGES) & 1;
                 for (uint32_t j = 0; ok && j < n_max; ++j) {
                     const uint32_t st = (kv_it + j) % KV_STAGES, ph = ((kv_it + j) / KV_STAGES) & 1;
 #pragma unroll
                     for (uint32_t ti = 0; ti < 2; ++ti) {
                         const uint32_t t = ti ^ FIRST_TILE, other = t ^ 1u;     // `other` is served first when t is the second tile
                         if (!ok || j >= nb[t]) continue;
-                        const uint32_t par = (blk_par >> t) & 1;
+                        const uint32_t par = blk[t] & 1;
                         RB_TR(tr, 2 + t, j, 7);
-                        if (!(ok = wait_serving(&p_half[t], par))) continue;
+                        if (!(ok = wait_handoff(&p_half[t], par, abort_word))) continue;
                         RB_TR(tr, 2 + t, j, 0);
                         // the first P V of an item overwrites O: the epilogue must have read the previous item's O
-                        if (j == 0 && (used_any & (1u << t)) && !(ok = mbar_wait(&o_free[t], ((used_par >> t) & 1) ^ 1, abort_word))) continue;
+                        if (j == 0 && used[t] > 0 && !(ok = mbar_wait(&o_free[t], (used[t] - 1) & 1, abort_word))) continue;
                         if (!(ok = mbar_wait(&v_full[st], ph, abort_word))) continue;
                         RB_TR(tr, 2 + t, j, 1);
                         tc_fence_after();
                         const uint32_t va = v_lo + st * (TILE_BYTES >> 4);
                         issue_pv_half(tmem_base + 256 + t * D, tmem_base + t * TK, va, idesc_pv, j);
                         RB_TR(tr, 2 + t, j, 2);
-                        if (!(ok = wait_serving(&p_full[t], par))) continue;
+                        if (!(ok = wait_handoff(&p_full[t], par, abort_word))) continue;
                         RB_TR(tr, 2 + t, j, 3);
                         tc_fence_after();
                         issue_pv_half(tmem_base + 256 + t * D, tmem_base + t * TK + 32, va + 4 * (2048 >> 4), idesc_pv, 1u);
-                        blk_par ^= 1u << t;
+                        ++blk[t];
                         // the stage is released by the tile served second, or by this one when the other tile does not use the block
                         const bool last_user = (ti == 1) || (j >= nb[other]);
                         if (last_user) umma_commit(&v_empty[st]);
@@ -523,22 +468,18 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                             if (!(ok = mbar_wait(&k_full[st1], ph1, abort_word))) continue;
                             RB_TR(tr, 2 + t, j, 5);
                             tc_fence_after();
-                            issue_s(t, st1);
+                            issue_s(t, st1); ++s_done;
                             const bool last_k_user = (ti == 1) || (j + 1 >= nb[other]);
                             if (last_k_user) umma_commit(&k_empty[st1]);
-                            if (j + 2 == nb[t]) umma_commit(&q_empty[t]);    // that was the tile's last score GEMM of the item
+                            if (s_done == total_s) umma_commit(q_empty);
                             RB_TR(tr, 2 + t, j, 6);
                         } else {
                             umma_commit(&o_full[t]);
-                            used_par ^= 1u << t; used_any |= 1u << t; q_par ^= 1u << t;
-#ifndef RB_ATTN_NO_EARLY
-                            if (next_has & (1u << t)) pending |= 1u << t;
-#endif
+                            ++used[t];
                         }
-                        if (pending) try_early();
                     }
                 }
-                kv_it += n_max;
+                kv_it += n_max; ++q_it;
                 RB_TR(trace_cta, 4, round, 3);                       // MMA: the item's last P V issued
             }
         }

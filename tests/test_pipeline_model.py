@@ -227,97 +227,69 @@ def test_gemm_ring_and_accumulator_handshake(stages, tiles, kblocks, seed):
 
 
 @pytest.mark.parametrize("items,seed", [([(3, 4)], 0), ([(8, 8), (1, 2), (5, 0)], 1), ([(0, 0), (2, 2), (0, 0), (1, 1)], 2), ([(1, 1)] * 5, 3),
-                                        ([(16, 17), (0, 3), (4, 4), (1, 0)], 4), ([(2, 3), (2, 3), (7, 8), (1, 2), (6, 6)], 5),
-                                        ([(1, 2), (1, 2), (3, 4), (0, 1), (1, 2)], 6), ([(15, 16), (13, 14), (1, 2)], 7)])
+                                        ([(16, 17), (0, 3), (4, 4), (1, 0)], 4), ([(2, 3), (2, 3), (7, 8), (1, 2), (6, 6)], 5)])
 def test_attention_barrier_protocol(items, seed):
     """The persistent attention kernel's protocol over a CTA's list of work items (each: key blocks of tile 0 and of tile 1):
-    one Q buffer per tile, handed back after the tile's last score GEMM of an item; K/V rings of two stages that run on across
-    items; S/P aliased in TMEM (P overwrites the scores it was computed from) and handed over in two halves; O read out by the
-    softmax warps at the end of an item and handed back before the next item's first P V overwrites it; and the overlap of
-    items: a tile that is done with an item gets the next item's first score GEMM issued early, while the other tile still works."""
+    one Q buffer handed back after the item's last score GEMM, K/V rings of two stages that run on across items, S/P aliased
+    in TMEM (P overwrites the scores it was computed from) and handed over in two halves, O read out by the softmax warps at
+    the end of an item and handed back before the next item's first P V overwrites it."""
     KV = 2
-    q_full = [Barrier(1), Barrier(1)]; q_empty = [Barrier(1), Barrier(1)]
+    q_full, q_empty = Barrier(1), Barrier(1)
     k_full = [Barrier(1) for _ in range(KV)]; k_empty = [Barrier(1) for _ in range(KV)]
     v_full = [Barrier(1) for _ in range(KV)]; v_empty = [Barrier(1) for _ in range(KV)]
     s_full = [Barrier(1), Barrier(1)]; p_half = [Barrier(128), Barrier(128)]; p_full = [Barrier(128), Barrier(128)]
     o_full = [Barrier(1), Barrier(1)]; o_free = [Barrier(128), Barrier(128)]
-    qsm = [None, None]               # item whose Q rows the tile's shared-memory buffer holds
+    qsm = [None]                     # item whose Q the shared-memory buffer holds
     ksm, vsm = [None] * KV, [None] * KV
     s_tmem = [None, None]            # ("S", item, j) after the score GEMM, ("P", item, j) after the softmax
     p_state = [0, 0]                 # halves of P the softmax threads have completed for the current block
     o_tmem = [None, None]            # (item, [blocks accumulated]) or None once read out
     stored = [[], []]
-    early = [0]                      # how many first score GEMMs were issued early
-    work = [(i, n) for i, n in enumerate(items) if max(n) > 0]
 
     def producer():
-        kv_it, q_it = 0, [0, 0]
-
-        def load_q(t, i, n):
-            if n[t] == 0:
-                return
-            if q_it[t] > 0:
-                yield from wait(q_empty[t], (q_it[t] - 1) & 1)
-            assert qsm[t] is None, "Q overwritten while score GEMMs of the previous item could still read it"
-            qsm[t] = i; q_full[t].arrive(); q_it[t] += 1
-            yield True
-
-        for i, n in work:
+        kv_it = q_it = 0
+        for i, n in enumerate(items):
             n_max = max(n)
-            yield from load_q(0, i, n)
+            if n_max == 0: continue
+            if q_it > 0:
+                yield from wait(q_empty, (q_it - 1) & 1)
+            assert qsm[0] is None, "Q overwritten while score GEMMs of the previous item could still read it"
+            qsm[0] = i; q_full.arrive(); yield True
             for j in range(n_max):
                 st, ph = (kv_it + j) % KV, ((kv_it + j) // KV) & 1
                 yield from wait(k_empty[st], ph ^ 1)
                 assert ksm[st] is None; ksm[st] = (i, j); k_full[st].arrive(); yield True
-                if j == 0:
-                    yield from load_q(1, i, n)
                 yield from wait(v_empty[st], ph ^ 1)
                 assert vsm[st] is None; vsm[st] = (i, j); v_full[st].arrive(); yield True
-            kv_it += n_max
+            kv_it += n_max; q_it += 1
 
     def mma():
-        kv_it = 0
-        q_par, blk, used = [0, 0], [0, 0], [0, 0]
-        pre, pending = set(), set()
-
-        def issue_s(t, i, j, st, n):
-            assert qsm[t] == i and ksm[st] == (i, j), "score GEMM read a Q or K buffer that holds something else"
-            assert s_tmem[t] is None or s_tmem[t][0] == "consumed", "scores overwritten while P was still needed"
-            s_tmem[t] = ("S", i, j); p_state[t] = 0; s_full[t].arrive()
-            if j == n[t] - 1:
-                qsm[t] = None; q_empty[t].arrive()
-
-        for w, (i, n) in enumerate(work):
+        kv_it = q_it = 0
+        blk, used = [0, 0], [0, 0]
+        for i, n in enumerate(items):
             n_max = max(n)
-            nxt = work[w + 1] if w + 1 < len(work) else None
+            if n_max == 0: continue
+            total_s, s_done = n[0] + n[1], 0
+
+            def issue_s(t, j, st):
+                assert qsm[0] == i and ksm[st] == (i, j), "score GEMM read a Q or K buffer that holds something else"
+                assert s_tmem[t] is None or s_tmem[t][0] == "consumed", "scores overwritten while P was still needed"
+                s_tmem[t] = ("S", i, j); p_state[t] = 0; s_full[t].arrive()
+
+            yield from wait(q_full, q_it & 1)
             st, ph = kv_it % KV, (kv_it // KV) & 1
-            for t in (1, 0):
-                if n[t] == 0 or t in pre: continue
-                yield from wait(q_full[t], q_par[t])
-                yield from wait(k_full[st], ph)
-                issue_s(t, i, 0, st, n)
-            ksm[st] = None; k_empty[st].arrive(); yield True
-            pre, pending = set(), set()
-            nst, nph = (kv_it + n_max) % KV, ((kv_it + n_max) // KV) & 1
-
-            def try_early():
-                for t in sorted(pending):
-                    if q_full[t].passed(q_par[t]) and k_full[nst].passed(nph):
-                        issue_s(t, nxt[0], 0, nst, nxt[1]); pre.add(t); pending.discard(t); early[0] += 1
-
-            def wait_serving(bar, parity):
-                while not bar.passed(parity):
-                    if pending: try_early()
-                    yield False
-                yield True
-
+            yield from wait(k_full[st], ph)
+            for t in (1, 0):                                   # tile 1 leads: it has the extra key block under a causal mask
+                if n[t] > 0: issue_s(t, 0, st); s_done += 1
+            ksm[st] = None; k_empty[st].arrive()
+            if s_done == total_s: qsm[0] = None; q_empty.arrive()
+            yield True
             for j in range(n_max):
                 st, ph = (kv_it + j) % KV, ((kv_it + j) // KV) & 1
                 for t in (1, 0):
                     if j >= n[t]: continue
-                    other = t ^ 1
                     par = blk[t] & 1
-                    yield from wait_serving(p_half[t], par)
+                    yield from wait(p_half[t], par)
                     if j == 0 and used[t] > 0:
                         yield from wait(o_free[t], (used[t] - 1) & 1)
                     yield from wait(v_full[st], ph)
@@ -326,26 +298,24 @@ def test_attention_barrier_protocol(items, seed):
                         assert o_tmem[t] is None, "O overwritten before the previous item's rows were read out"
                         o_tmem[t] = (i, [])
                     yield True
-                    yield from wait_serving(p_full[t], par)
+                    yield from wait(p_full[t], par)
                     assert s_tmem[t] == ("P", i, j) and p_state[t] == 2
                     o_tmem[t][1].append(j); s_tmem[t] = ("consumed", i, j)
                     blk[t] += 1
-                    if t == 0 or j >= n[other]:                # released by the tile served second, or by the only user
+                    if t == 0 or j >= n[0]:                    # released by the tile served second, or by the only user
                         vsm[st] = None; v_empty[st].arrive()
                     yield True
                     if j + 1 < n[t]:
                         st1, ph1 = (kv_it + j + 1) % KV, ((kv_it + j + 1) // KV) & 1
                         yield from wait(k_full[st1], ph1)
-                        issue_s(t, i, j + 1, st1, n)
-                        if t == 0 or j + 1 >= n[other]:
+                        issue_s(t, j + 1, st1); s_done += 1
+                        if t == 0 or j + 1 >= n[0]:
                             ksm[st1] = None; k_empty[st1].arrive()
+                        if s_done == total_s: qsm[0] = None; q_empty.arrive()
                         yield True
                     else:
-                        o_full[t].arrive(); used[t] += 1; q_par[t] ^= 1
-                        if nxt is not None and nxt[1][t] > 0: pending.add(t)
-                        yield True
-                    if pending: try_early()
-            kv_it += n_max
+                        o_full[t].arrive(); used[t] += 1; yield True
+            kv_it += n_max; q_it += 1
 
     def softmax_thread(t, tid):
         blk = used = 0
@@ -374,5 +344,5 @@ def test_attention_barrier_protocol(items, seed):
     run([producer(), mma()] + [softmax_thread(t, i) for t in range(2) for i in range(128)], seed, limit=2000000)
     for t in range(2):
         assert stored[t] == [i for i, n in enumerate(items) if n[t] > 0]
-    assert all(b.idle() for b in q_full + k_full + k_empty + v_full + v_empty + s_full + p_half + p_full + o_full)
+    assert all(b.idle() for b in [q_full] + k_full + k_empty + v_full + v_empty + s_full + p_half + p_full + o_full)
     assert all(x is None for x in ksm + vsm)
