@@ -65,6 +65,22 @@ class RowParallelHeadline:
                 _check(lib.rb_gemm_scatter_bias(*scatter[i % SETS])); _check(lib.rb_peer_wait(*wait_s))
                 _check(lib.rb_reduce_norm_push(*push)); _check(lib.rb_peer_wait(*wait_g))
             self.candidates["fused scatter-GEMM + owner-side sum + push over peer memory"] = (fused, 4)
+            # pull form: the plain GEMM writes this rank's partial product, the owner-side kernel fetches its rows from every rank
+            px = FusedExchange(client, control, M, N, activations=ex.activations, pull=True)
+            self.pull_exchange = px
+            own = px.own_partial()._c()
+            keep.append(own)
+            pd = [[t._c() for t in st] for st in sets]
+            keep.append(pd)
+            pull_gemms = [(client._ctx, C.byref(k[0]), C.byref(k[1]), C.c_int32(0), C.c_int32(1), C.byref(k[2]) if rank == 0 else None, None,
+                           C.c_int32(1 if rank == 0 else 0), C.byref(own)) for k in pd]
+            announce, pull = px.signal_args(keep, SCATTER), px.pull_args(None, None, 1e-5, None, keep)
+            pwait_s, pwait_g = px.wait_args(SCATTER, 1, keep), px.wait_args(GATHER, 1, keep)
+
+            def pulled(i):
+                _check(lib.rb_gemm(*pull_gemms[i % SETS])); _check(lib.rb_peer_signal(*announce)); _check(lib.rb_peer_wait(*pwait_s))
+                _check(lib.rb_reduce_norm_push_pull(*pull)); _check(lib.rb_peer_wait(*pwait_g))
+            self.candidates["fused: plain GEMM, owner-side kernel pulls the partial products, sums and pushes over peer memory"] = (pulled, 5)
         except Exception as error:           # peer memory unavailable: the NCCL form still runs
             self.fused_error = f"{type(error).__name__}: {error}"
         comm = NcclCommunicator.initialize(control, client)
@@ -700,6 +716,8 @@ def row_parallel_extra(client, pk, rank, world, dist):
         from rust_ascend_b200.fused import FusedExchange, row_parallel_linear_allreduce
         ex = FusedExchange(client, TorchControl(), M, N)
         variants["fused_scatter_reduce_push"] = lambda: row_parallel_linear_allreduce(ex, x, w)
+        px = FusedExchange(client, TorchControl(), M, N, activations=ex.activations, pull=True)
+        variants["gemm_then_pull_reduce_push"] = lambda: row_parallel_linear_allreduce(px, x, w)
     except Exception as error:
         result["fused_error"] = f"{type(error).__name__}: {error}"
     for name, fn in variants.items():
@@ -728,6 +746,11 @@ def decoder_candidates(world: int, sequences: int = 8, fused: bool = False):
     out = [dict(overlap, tp=world), dict(plain, tp=world), dict(plain, tp=world, micro_batches=2)]
     if fused:   # exchange fused into the kernels over peer memory: on one stream, and with the owner-side step on the side stream
         out += [dict(plain, tp=world, fused=True), dict(overlap, tp=world, fused=True, overlap_exchange=True, nccl_max_ctas=0)]
+        # pull form: plain GEMMs, the owner-side kernel fetches the partial products (all link traffic on the side stream)
+        out += [dict(plain, tp=world, fused=True, pull_exchange=True),
+                dict(overlap, tp=world, fused=True, overlap_exchange=True, pull_exchange=True, nccl_max_ctas=0)]
+        if sequences % 4 == 0 and (sequences // 4 * 2048) % (128 * world) == 0:
+            out.append(dict(overlap, tp=world, fused=True, overlap_exchange=True, pull_exchange=True, nccl_max_ctas=0, micro_batches=4))
     tp = world // 2
     while tp >= 1:
         per_group = sequences * tp // world
@@ -791,9 +814,10 @@ def decoder_extra(client, pk, rank, world, dist, sink, candidates, results):
                 other.close()
             models[tp] = TensorParallelDecoder(client, cfg, per_group, seq, comm=comm, rank=tp_rank, world=tp, micro_batches=cand["micro_batches"],
                                                sm_reserve=cand["sms_left_to_nccl"], use_graph=True, fused=cand.get("fused", False),
-                                               overlap_exchange=cand.get("overlap_exchange", False))
+                                               overlap_exchange=cand.get("overlap_exchange", False), pull_exchange=cand.get("pull_exchange", False))
         else:
-            models[tp].configure(comm, cand["micro_batches"], cand["sms_left_to_nccl"], True, cand.get("fused", False), cand.get("overlap_exchange", False))
+            models[tp].configure(comm, cand["micro_batches"], cand["sms_left_to_nccl"], True, cand.get("fused", False), cand.get("overlap_exchange", False),
+                                 cand.get("pull_exchange", False))
         model = models[tp]
         model.forward(tokens[group * per_group:(group + 1) * per_group])
         for _ in range(2):
@@ -808,7 +832,10 @@ def decoder_extra(client, pk, rank, world, dist, sink, candidates, results):
         ms = max_over_ranks(dist, client.end_profile() / steps)
         label = f"tp{tp}" if groups == 1 else (f"tp{tp} x {groups} groups of {per_group} sequences" if tp > 1 else f"{groups} replicas of {per_group} sequences, no exchange")
         if cand.get("fused"):
-            label += ", exchange fused into the kernels" + (" and overlapped on the side stream" if cand.get("overlap_exchange") else "")
+            label += (", partial products pulled by the owner-side kernel" if cand.get("pull_exchange") else ", exchange fused into the kernels") \
+                + (" and overlapped on the side stream" if cand.get("overlap_exchange") else "")
+            if cand["micro_batches"] > 2:
+                label += f", {cand['micro_batches']} micro batches"
         results.append(dict(cand, parallelism=label, ms_per_forward=ms, launches_per_forward=model.launches_per_forward,
                             all_reduces_per_forward=model.collectives_per_forward, fused_exchanges_per_forward=model.fused_exchanges_per_forward))
         sink["tp_decoder"] = summary()

@@ -399,6 +399,16 @@ RB_API int32_t rb_reduce_norm_push(rb_ctx* ctx, const rb_tensor* staging, const 
                                    double epsilon, const rb_tensor* x_out, uint32_t rank, uint32_t world,
                                    const rb_tensor* const* destinations, const rb_tensor* const* flags,
                                    const rb_tensor* done);
+/* The same owner-side step in its pull form, for a row-parallel Linear that ran as a plain rb_gemm: partials[s] is rank s's
+ * whole partial product (BF16 [world * rows, width], rank s's memory mapped here), and this rank fetches rows
+ * [rank * rows, (rank + 1) * rows) of every one of them itself (asynchronous bulk copies into shared memory, several rows in
+ * flight per SM), sums them in rank order and continues exactly as rb_reduce_norm_push does, with the same bits.  The caller
+ * orders the step behind every rank's GEMM (rb_peer_signal after the GEMM, rb_peer_wait before this call); a rank may
+ * overwrite its partial product again once it has seen every owner's announcement in `flags`.  Stands where the reference runs
+ * all_reduce (src/distributed.rs:139-156) and rms_norm (runtime/mod.rs:405-408) after the Linear. */
+RB_API int32_t rb_reduce_norm_push_pull(rb_ctx* ctx, const rb_tensor* const* partials, const rb_tensor* x_in, const rb_tensor* weight,
+                                        double epsilon, const rb_tensor* x_out, uint32_t rank, uint32_t world,
+                                        const rb_tensor* const* destinations, const rb_tensor* const* flags, const rb_tensor* done);
 
 /* ---- collectives: NCCL over NVLink 5 / NVSwitch in place of HCCL ----------------------------------------------- */
 typedef struct rb_comm rb_comm;

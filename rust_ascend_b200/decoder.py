@@ -19,6 +19,8 @@ all-reduce of one group overlaps the GEMMs of the other (deferred fences on the 
 their partial rows into the staging area of the rank that owns those rows, the owner sums them, updates its rows of the
 residual stream (which is then sharded by rows), normalises and pushes the result into every rank's activation buffer;
 `overlap_exchange=True` moves the owner-side step to a side stream under the other micro batch's GEMMs.
+`pull_exchange=True` keeps the row-parallel GEMMs plain (each rank writes its partial product locally and announces it) and
+lets the owner-side step fetch the partial products itself, so that all link traffic is on the side stream.
 """
 from __future__ import annotations
 
@@ -160,7 +162,7 @@ class TensorParallelDecoder:
 
     def __init__(self, client: ComputeClient, cfg: LlamaConfig, batch: int, seq: int, comm=None, rank: int = 0, world: int = 1,
                  seed: int = 0, exact_weights: bool = False, micro_batches: int = 1, sm_reserve: int = 0, use_graph: bool = False,
-                 fused: bool = False, overlap_exchange: bool = False):
+                 fused: bool = False, overlap_exchange: bool = False, pull_exchange: bool = False):
         if world > 1 and comm is None:
             raise InvalidTensor("a communicator is required for tensor parallelism")
         if cfg.head_dim != 128:
@@ -204,10 +206,10 @@ class TensorParallelDecoder:
         self.scale = 1.0 / float(np.sqrt(d))
         self._graph = None
         self._exchanges, self._peer_h, self._x_own = [], None, None
-        self.configure(comm, micro_batches, sm_reserve, use_graph, fused, overlap_exchange)
+        self.configure(comm, micro_batches, sm_reserve, use_graph, fused, overlap_exchange, pull_exchange)
 
     def configure(self, comm, micro_batches: int = 1, sm_reserve: int = 0, use_graph: bool = False, fused: bool = False,
-                  overlap_exchange: bool = False) -> None:
+                  overlap_exchange: bool = False, pull_exchange: bool = False) -> None:
         """(Re)builds the launch plan, and the recorded graph if asked for, on the weights and buffers already resident.
         Lets a caller compare schedules (micro batches, SMs left to NCCL, communicators with different CTA limits)
         without loading the model again."""
@@ -219,6 +221,7 @@ class TensorParallelDecoder:
             raise InvalidTensor("fused exchange needs a communicator with a control plane and micro batches of a multiple of 128 * world tokens")
         self.close()
         self.comm, self.micro, self.fused, self.overlap_exchange = comm, micro_batches, fused, bool(fused and overlap_exchange)
+        self.pull_exchange = bool(fused and pull_exchange)
         self._keep = []          # ctypes structures referenced by the plan
         self._steps = []         # (function, argument tuple)
         self.launches_per_forward = 0
@@ -344,7 +347,8 @@ class TensorParallelDecoder:
         rows = tm // self.world                    # rows of it this rank owns
         control = self.comm.control
         self._peer_h = PeerBuffer(c, control, self.tokens * hidden * 2)
-        self._exchanges = [FusedExchange(c, control, tm, hidden, activations=self._peer_h, activation_offset=mb * tm * hidden * 2) for mb in range(n)]
+        self._exchanges = [FusedExchange(c, control, tm, hidden, activations=self._peer_h, activation_offset=mb * tm * hidden * 2, pull=self.pull_exchange)
+                           for mb in range(n)]
         self._x_own = c.tensor((n, rows, hidden), DType.BF16)
         eps = cfg.eps
         keep = self._keep
@@ -370,7 +374,7 @@ class TensorParallelDecoder:
                 ids = TensorBuffer(self.tokens_dev.handle, (rows,), DType.I32, None, offset=first * 4)
                 self._op("rb_embedding", ctx, self._t(self.embedding), self._t(ids), self._t(x_own(mb)))
             elif kind == "wait_scatter":
-                self._op("rb_peer_wait", *ex.wait_args(SCATTER, ex.signals, keep))
+                self._op("rb_peer_wait", *ex.wait_args(SCATTER, ex.scatter_count, keep))
             elif kind == "wait_gather":
                 self._op("rb_peer_wait", *ex.wait_args(GATHER, 1, keep))
             elif kind == "push":
@@ -378,7 +382,10 @@ class TensorParallelDecoder:
                 lw = self.layers[layer] if layer < cfg.layers else None
                 weight = self.final_norm if lw is None else (lw["norm1"] if which == 0 else lw["norm2"])
                 very_first = layer == 0 and which == 0     # nothing staged yet: normalise the embedding rows
-                self._op("rb_reduce_norm_push", *ex.push_args(not very_first, x_own(mb), weight, eps, None if very_first else x_own(mb), keep))
+                if self.pull_exchange and not very_first:
+                    self._op("rb_reduce_norm_push_pull", *ex.pull_args(x_own(mb), weight, eps, x_own(mb), keep))
+                else:
+                    self._op("rb_reduce_norm_push", *ex.push_args(not very_first, x_own(mb), weight, eps, None if very_first else x_own(mb), keep))
                 self.fused_exchanges_per_forward += 0 if very_first else 1
             elif kind == "attention_block":
                 lw = self.layers[step[2]]
@@ -394,7 +401,11 @@ class TensorParallelDecoder:
             elif kind == "scatter":
                 lw = self.layers[step[2]]
                 a = self._rows(self.attn, mb) if step[3] == "wo" else self._rows(self.ffn_act, mb)
-                self._op("rb_gemm_scatter", *ex.scatter_args(a, lw[step[3]], keep))
+                if self.pull_exchange:
+                    self._gemm(a, lw[step[3]], ex.own_partial())
+                    self._op("rb_peer_signal", *ex.signal_args(keep, SCATTER))
+                else:
+                    self._op("rb_gemm_scatter", *ex.scatter_args(a, lw[step[3]], keep))
             elif kind == "lm_head":
                 self._gemm(h, self.lm_head, self._rows(self.logits, mb))
             else:

@@ -10,6 +10,11 @@ other ranks of the node (`PeerBuffer`), and the two halves of the all-reduce bec
                         the rows into every rank's activation buffer (all-gather folded into the norm);
 * `rb_peer_wait`      - a one-warp kernel that waits, with a time limit, for the announcements of the other GPUs.
 
+The pull form (`FusedExchange(..., pull=True)`) keeps the GEMM plain: every rank writes its whole partial product into a
+buffer of its own that the others have mapped, announces it (`rb_peer_signal`), and the owner-side step
+(`rb_reduce_norm_push_pull`) fetches its rows of every partial product itself.  All link traffic then belongs to the
+owner-side kernel, which can run on a few SMs beside another micro batch's GEMMs, and the GEMM is never held up by the link.
+
 `FusedExchange` owns the buffers and flags of one stream of such projections; `row_parallel_linear_allreduce` is the
 all-reduce-equivalent composition (the entry the reference-shaped API asks for), and `decoder.TensorParallelDecoder` uses the
 pieces directly so that the residual stream stays sharded by rows between projections.
@@ -105,7 +110,7 @@ class FusedExchange:
     `activations` (a PeerBuffer holding at least tokens*hidden BF16 at `activation_offset`) receives the gathered rows."""
 
     def __init__(self, client: ComputeClient, control, tokens: int, hidden: int, activations: PeerBuffer | None = None,
-                 activation_offset: int = 0):
+                 activation_offset: int = 0, pull: bool = False):
         self.client, self.control = client, control
         self.rank, self.world = control.rank, control.world_size
         self.tokens, self.hidden = int(tokens), int(hidden)
@@ -113,7 +118,10 @@ class FusedExchange:
         if self.signals == 0 or hidden % 64:
             raise InvalidTensor("fused exchange needs tokens a multiple of 128 * world and hidden a multiple of 64")
         self.rows = tokens // self.world
-        self.staging = PeerBuffer(client, control, self.world * self.rows * hidden * 2)
+        self.pull = bool(pull)
+        # push form: a staging area the peers' GEMMs store into; pull form: this rank's whole partial product, read by the peers
+        self.staging = None if self.pull else PeerBuffer(client, control, self.world * self.rows * hidden * 2)
+        self.partial = PeerBuffer(client, control, tokens * hidden * 2) if self.pull else None
         self.flags = PeerBuffer(client, control, 256)
         self._own_activations = activations is None
         self.activations = activations or PeerBuffer(client, control, tokens * hidden * 2)
@@ -123,6 +131,13 @@ class FusedExchange:
     # -- descriptors -------------------------------------------------------------------------------------------
     def staging_views(self):
         return [self.staging.view(o, (self.world, self.rows, self.hidden), DType.BF16) for o in range(self.world)]
+
+    def partial_views(self):
+        return [self.partial.view(r, (self.tokens, self.hidden), DType.BF16) for r in range(self.world)]
+
+    def own_partial(self) -> TensorBuffer:
+        """Pull form: where this rank's row-parallel GEMM writes its partial product [tokens, hidden]."""
+        return self.partial.view(self.rank, (self.tokens, self.hidden), DType.BF16)
 
     def flag_views(self, group: int):
         return [self.flags.view(d, (FLAG_WORDS,), DType.I32, group * FLAG_WORDS * 4) for d in range(self.world)]
@@ -172,19 +187,48 @@ class FusedExchange:
         return (self.client._ctx, ref(staging), ref(x_in), ref(weight), C.c_double(eps), ref(x_out), C.c_uint32(self.rank), C.c_uint32(self.world),
                 tensor_array(self.activation_views(), keep), tensor_array(self.flag_views(GATHER), keep), ref(self.done_word()))
 
-    def signal_args(self, keep: list):
-        return (self.client._ctx, C.c_uint32(self.rank), C.c_uint32(self.world), tensor_array(self.flag_views(BARRIER), keep))
+    def pull_args(self, x_in, weight, eps: float, x_out, keep: list):
+        """Arguments of rb_reduce_norm_push_pull."""
+        def ref(t):
+            if t is None:
+                return None
+            s = t._c()
+            keep.append(s)
+            return C.byref(s)
+        return (self.client._ctx, tensor_array(self.partial_views(), keep), ref(x_in), ref(weight), C.c_double(eps), ref(x_out),
+                C.c_uint32(self.rank), C.c_uint32(self.world), tensor_array(self.activation_views(), keep),
+                tensor_array(self.flag_views(GATHER), keep), ref(self.done_word()))
+
+    def signal_args(self, keep: list, group: int = BARRIER):
+        return (self.client._ctx, C.c_uint32(self.rank), C.c_uint32(self.world), tensor_array(self.flag_views(group), keep))
+
+    @property
+    def scatter_count(self) -> int:
+        """What every peer adds to this rank's SCATTER flag words per projection: the slices its scatter GEMM stores here, or one
+        announcement of its finished partial product in the pull form."""
+        return 1 if self.pull else self.signals
 
     # -- eager calls ---------------------------------------------------------------------------------------------
     def gemm_scatter(self, a: TensorBuffer, w: TensorBuffer) -> None:
-        """Partial product a [tokens, K/world] x w [hidden, K/world]^T scattered to the owners' staging areas."""
-        _check(self.client._lib.rb_gemm_scatter(*self.scatter_args(a, w, self._keep)))
+        """Partial product a [tokens, K/world] x w [hidden, K/world]^T: scattered to the owners' staging areas, or (pull form)
+        written to this rank's partial-product buffer by the plain GEMM and announced to every rank."""
+        lib = self.client._lib
+        if self.pull:
+            sa, sw, so = a._c(), w._c(), self.own_partial()._c()
+            self._keep.extend([sa, sw, so])
+            _check(lib.rb_gemm(self.client._ctx, C.byref(sa), C.byref(sw), C.c_int32(0), C.c_int32(1), None, None, C.c_int32(0), C.byref(so)))
+            _check(lib.rb_peer_signal(*self.signal_args(self._keep, SCATTER)))
+        else:
+            _check(lib.rb_gemm_scatter(*self.scatter_args(a, w, self._keep)))
 
     def wait_scatter(self) -> None:
-        _check(self.client._lib.rb_peer_wait(*self.wait_args(SCATTER, self.signals, self._keep)))
+        _check(self.client._lib.rb_peer_wait(*self.wait_args(SCATTER, self.scatter_count, self._keep)))
 
     def reduce_norm_push(self, x_in=None, weight=None, eps: float = 1e-5, x_out=None, use_staging: bool = True) -> None:
-        _check(self.client._lib.rb_reduce_norm_push(*self.push_args(use_staging, x_in, weight, eps, x_out, self._keep)))
+        if self.pull and use_staging:
+            _check(self.client._lib.rb_reduce_norm_push_pull(*self.pull_args(x_in, weight, eps, x_out, self._keep)))
+        else:
+            _check(self.client._lib.rb_reduce_norm_push(*self.push_args(use_staging and not self.pull, x_in, weight, eps, x_out, self._keep)))
 
     def wait_gather(self) -> None:
         _check(self.client._lib.rb_peer_wait(*self.wait_args(GATHER, 1, self._keep)))
@@ -197,8 +241,9 @@ class FusedExchange:
     def close(self) -> None:
         self.client.sync()
         self._keep = []
-        for buf in ([self.activations] if self._own_activations else []) + [self.flags, self.staging]:
-            buf.close()
+        for buf in ([self.activations] if self._own_activations else []) + [self.flags, self.staging, self.partial]:
+            if buf is not None:
+                buf.close()
 
 
 class LocalGroup:

@@ -67,6 +67,14 @@ def _worker(rank, world, port, results):
     y1 = bf16_bits_to_f32(client.read(row_parallel_linear_allreduce(ex, xs, ws)))
     y2 = bf16_bits_to_f32(client.read(row_parallel_linear_allreduce(ex, xs, ws)))
     out["fused_linear"], out["fused_linear_again_equal"] = y1, bool(np.array_equal(y1, y2))
+    # pull form: plain GEMM into this rank's own buffer, the owner-side kernel fetches its rows from every rank; the second call
+    # runs on other inputs, so a stale read of a peer's buffer cannot go unnoticed
+    px = FusedExchange(client, control, x.shape[0], w.shape[0], pull=True)
+    out["pull_linear"] = bf16_bits_to_f32(client.read(row_parallel_linear_allreduce(px, xs, ws)))
+    xs2 = client.upload(f32_to_bf16_bits(-2.0 * x[:, rank * k:(rank + 1) * k]))
+    out["pull_linear_scaled"] = bf16_bits_to_f32(client.read(row_parallel_linear_allreduce(px, xs2, ws)))
+    client.sync()
+    px.close()
     # residual + RMSNorm folded into the owner-side step
     rows = x.shape[0] // world
     resid = np.random.default_rng(5).standard_normal((x.shape[0], w.shape[0])).astype(np.float32)
@@ -86,14 +94,16 @@ def _worker(rank, world, port, results):
         out[f"nccl_linear_{int(overlap)}"] = bf16_bits_to_f32(client.read(y))
     cfg = _cfg()
     tokens = np.random.default_rng(0).integers(0, cfg.vocab, size=(2, 128)).astype(np.int32)
-    for name, kwargs in (("nccl", {}), ("fused", {"fused": True}), ("fused_graph", {"fused": True, "use_graph": True})):
+    for name, kwargs in (("nccl", {}), ("fused", {"fused": True}), ("fused_graph", {"fused": True, "use_graph": True}),
+                         ("pull_graph", {"fused": True, "use_graph": True, "pull_exchange": True})):
         model = TensorParallelDecoder(client, cfg, 2, 128, comm=comm, rank=rank, world=world, seed=3, exact_weights=True, **kwargs)
         model.forward(tokens)
         out[name] = bf16_bits_to_f32(client.read(model.forward()))
         model.close()
     # overlapped exchange: two micro batches, the owner-side step on the side stream under the other batch's GEMMs
     tokens4 = np.random.default_rng(1).integers(0, cfg.vocab, size=(4, 128)).astype(np.int32)
-    for name, kwargs in (("fused4", {"fused": True}), ("fused4_overlap", {"fused": True, "micro_batches": 2, "overlap_exchange": True, "sm_reserve": 16, "use_graph": True})):
+    for name, kwargs in (("fused4", {"fused": True}), ("fused4_overlap", {"fused": True, "micro_batches": 2, "overlap_exchange": True, "sm_reserve": 16, "use_graph": True}),
+                         ("pull4_overlap", {"fused": True, "micro_batches": 2, "overlap_exchange": True, "pull_exchange": True, "sm_reserve": 16, "use_graph": True})):
         model = TensorParallelDecoder(client, cfg, 4, 128, comm=comm, rank=rank, world=world, seed=3, exact_weights=True, **kwargs)
         model.forward(tokens4)
         out[name] = bf16_bits_to_f32(client.read(model.forward()))
@@ -135,6 +145,8 @@ def test_two_gpu_fused_exchange(oracle):
         err = np.abs(got - total)
         assert err.max() <= 2.0 ** -7 * np.abs(total).max() and err.mean() <= 1e-3 * np.abs(total).mean() + 1e-6, (err.max(), err.mean())
         np.testing.assert_array_equal(got, r[0]["fused_linear"])          # every rank holds the same bits
+        np.testing.assert_array_equal(r[rank]["pull_linear"], got)        # the pull form sums the same partial products in the same order
+        np.testing.assert_array_equal(r[rank]["pull_linear_scaled"], -2.0 * got)   # exact: a power of two scales every BF16 value exactly
         for key in ("nccl_linear_0", "nccl_linear_1"):
             assert np.abs(r[rank][key] - total).max() <= 2.0 ** -7 * np.abs(total).max()
     rows = x.shape[0] // world
@@ -150,13 +162,15 @@ def test_two_gpu_fused_exchange(oracle):
     cfg = _cfg()
     tokens = np.random.default_rng(0).integers(0, cfg.vocab, size=(2, 128)).astype(np.int32)
     want = forward(oracle, cfg, full_weights(cfg, 3), tokens)
-    for name in ("nccl", "fused", "fused_graph"):
+    for name in ("nccl", "fused", "fused_graph", "pull_graph"):
         got = np.concatenate([r[0][name], r[1][name]], axis=1)
         err = np.abs(got - want)
         assert err.max() <= 0.04 * np.abs(want).max() and err.mean() <= 0.015 * np.abs(want).mean() + 1e-4, (name, err.max(), err.mean())
     np.testing.assert_array_equal(r[0]["fused"], r[0]["fused_graph"])
+    np.testing.assert_array_equal(r[0]["fused"], r[0]["pull_graph"])
     for rank in range(world):      # the schedule changes, the arithmetic does not
         assert np.abs(r[rank]["fused4"] - r[rank]["fused4_overlap"]).max() <= 2.0 ** -7 * np.abs(r[rank]["fused4"]).max()
+        assert np.abs(r[rank]["fused4"] - r[rank]["pull4_overlap"]).max() <= 2.0 ** -7 * np.abs(r[rank]["fused4"]).max()
 
 
 def test_single_gpu_fused_exchange(client, oracle):
@@ -176,6 +190,18 @@ def test_single_gpu_fused_exchange(client, oracle):
         for _ in range(2):                                           # twice: flags only count up, buffers are reused
             got = bf16_bits_to_f32(client.read(row_parallel_linear_allreduce(ex, xs, ws)))
             assert np.abs(got - want).max() <= 2.0 ** -7 * np.abs(want).max()
+        # pull form in a world of one: bulk copies from local memory, same bits
+        px = FusedExchange(client, SingleControl(), x.shape[0], w.shape[0], pull=True)
+        for _ in range(2):
+            np.testing.assert_array_equal(bf16_bits_to_f32(client.read(row_parallel_linear_allreduce(px, xs, ws))), got)
+        px.close()
+        # the scatter GEMM runs on CTA pairs for these sizes; single CTAs must give the same bits
+        os.environ["RUDA_GEMM_PAIRS"] = "0"
+        try:
+            single = bf16_bits_to_f32(client.read(row_parallel_linear_allreduce(ex, xs, ws)))
+        finally:
+            del os.environ["RUDA_GEMM_PAIRS"]
+        np.testing.assert_array_equal(single, got)
         resid = np.random.default_rng(5).standard_normal(want.shape).astype(np.float32)
         weight = np.random.default_rng(6).uniform(0.5, 1.5, want.shape[1]).astype(np.float32)
         x_own = client.upload(f32_to_bf16_bits(resid))
@@ -190,7 +216,8 @@ def test_single_gpu_fused_exchange(client, oracle):
         cfg = _cfg()
         tokens = np.random.default_rng(0).integers(0, cfg.vocab, size=(4, 128)).astype(np.int32)
         want_logits = forward(oracle, cfg, full_weights(cfg, 3), tokens)
-        for kwargs in ({}, {"use_graph": True}, {"micro_batches": 2, "overlap_exchange": True, "sm_reserve": 16, "use_graph": True}):
+        for kwargs in ({}, {"use_graph": True}, {"micro_batches": 2, "overlap_exchange": True, "sm_reserve": 16, "use_graph": True},
+                       {"pull_exchange": True, "use_graph": True}, {"micro_batches": 2, "overlap_exchange": True, "pull_exchange": True, "sm_reserve": 16, "use_graph": True}):
             model = TensorParallelDecoder(client, cfg, 4, 128, comm=LocalGroup(), seed=3, exact_weights=True, fused=True, **kwargs)
             model.forward(tokens)
             got = bf16_bits_to_f32(client.read(model.forward()))
