@@ -751,6 +751,7 @@ def decoder_candidates(world: int, sequences: int = 8, fused: bool = False):
                 dict(overlap, tp=world, fused=True, overlap_exchange=True, pull_exchange=True, nccl_max_ctas=0)]
         if sequences % 4 == 0 and (sequences // 4 * 2048) % (128 * world) == 0:
             out.append(dict(overlap, tp=world, fused=True, overlap_exchange=True, pull_exchange=True, nccl_max_ctas=0, micro_batches=4))
+        out.append(dict(overlap, tp=world, fused=True, overlap_exchange=True, pull_exchange=True, nccl_max_ctas=0, sms_left_to_nccl=2 * NCCL_CTAS))
     tp = world // 2
     while tp >= 1:
         per_group = sequences * tp // world
@@ -836,6 +837,8 @@ def decoder_extra(client, pk, rank, world, dist, sink, candidates, results):
                 + (" and overlapped on the side stream" if cand.get("overlap_exchange") else "")
             if cand["micro_batches"] > 2:
                 label += f", {cand['micro_batches']} micro batches"
+            if cand.get("overlap_exchange") and cand["sms_left_to_nccl"] != NCCL_CTAS:
+                label += f", {cand['sms_left_to_nccl']} SMs left to the side stream"
         results.append(dict(cand, parallelism=label, ms_per_forward=ms, launches_per_forward=model.launches_per_forward,
                             all_reduces_per_forward=model.collectives_per_forward, fused_exchanges_per_forward=model.fused_exchanges_per_forward))
         sink["tp_decoder"] = summary()

@@ -473,7 +473,8 @@ constexpr int PUSH_MAXV = 4;        // 16-byte vectors per thread: width <= 256 
 // What follows the sum of the partials for one row: round it once to BF16 (as the result of an all-reduce would be), add the
 // residual stream, store the new residual row, normalise, and store the row into every rank's activation buffer.
 // v[i][0..8) is the FP32 sum of 16-byte vector i * PUSH_THREADS + threadIdx.x of the row.  Called by all threads of the block.
-__device__ __forceinline__ void push_row(const PushParams& p, uint32_t row, float (&v)[PUSH_MAXV][8], const bool (&have)[PUSH_MAXV], float* red) {
+// xin[i] is the same vector of the residual stream's row (read when p.x_in is set).
+__device__ __forceinline__ void push_row(const PushParams& p, uint32_t row, const uint4 (&xin)[PUSH_MAXV], float (&v)[PUSH_MAXV][8], const bool (&have)[PUSH_MAXV], float* red) {
     if (p.partials) {
 #pragma unroll
         for (int i = 0; i < PUSH_MAXV; ++i)
@@ -481,10 +482,9 @@ __device__ __forceinline__ void push_row(const PushParams& p, uint32_t row, floa
             for (int j = 0; j < 8; ++j) v[i][j] = __bfloat162float(__float2bfloat16_rn(v[i][j]));
     }
     if (p.x_in) {
-        const uint4* src = reinterpret_cast<const uint4*>(p.x_in + (size_t)row * p.width);
 #pragma unroll
         for (int i = 0; i < PUSH_MAXV; ++i) if (have[i]) {
-            const uint4 w = src[i * PUSH_THREADS + threadIdx.x];
+            const uint4 w = xin[i];
             const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&w);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -594,7 +594,13 @@ __global__ void __launch_bounds__(PUSH_THREADS) reduce_norm_push_kernel(const Pu
                 for (int j = 0; j < 4; ++j) { float2 f = __bfloat1622float2(h2[j]); v[i][2 * j] += f.x; v[i][2 * j + 1] += f.y; }
             }
         }
-        push_row(p, row, v, have, red);
+        uint4 xin[PUSH_MAXV];
+        if (p.x_in) {
+            const uint4* src = reinterpret_cast<const uint4*>(p.x_in + (size_t)row * p.width);
+#pragma unroll
+            for (int i = 0; i < PUSH_MAXV; ++i) if (have[i]) xin[i] = src[i * PUSH_THREADS + threadIdx.x];
+        }
+        push_row(p, row, xin, v, have, red);
     }
     push_announce(p, &last);
 }
@@ -602,8 +608,9 @@ __global__ void __launch_bounds__(PUSH_THREADS) reduce_norm_push_kernel(const Pu
 // The pull form of the owner-side step: the partial products stay where the plain GEMM of each rank wrote them, and the owner
 // fetches its rows of all of them itself.  Remote reads have microseconds of latency, so the rows come in as bulk asynchronous
 // copies (one per source and row, straight into shared memory, completion counted by an mbarrier) that keep PULL_STAGES rows
-// of `world` sources in flight per block without holding them in registers.  The copies name one GPU's memory each and are
-// not cluster broadcasts.  Everything after the sum is push_row, so both forms give the same bits.
+// of `world` sources in flight per block without holding them in registers; the row of the residual stream travels the same
+// way, so that no thread waits for a load from global memory.  The copies name one GPU's memory each and are not cluster
+// broadcasts.  Everything after the sum is push_row, so both forms give the same bits.
 constexpr int PULL_STAGES = 3;
 
 __device__ __forceinline__ void bulk_load(void* smem_dst, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -619,7 +626,7 @@ __global__ void __launch_bounds__(PUSH_THREADS) pull_reduce_norm_push_kernel(con
     __shared__ bool last;
     __shared__ uint32_t step_lost, abort_word_s;
     volatile uint32_t* abort_word = &abort_word_s;
-    const uint32_t vecs = p.width / 8, row_bytes = p.width * 2, stage_bytes = p.partials * row_bytes;
+    const uint32_t vecs = p.width / 8, row_bytes = p.width * 2, stage_bytes = (p.partials + (p.x_in ? 1u : 0u)) * row_bytes;
     if (threadIdx.x == 0) {
         step_lost = *reinterpret_cast<const volatile uint32_t*>(p.status);
         abort_word_s = 0;
@@ -634,6 +641,7 @@ __global__ void __launch_bounds__(PUSH_THREADS) pull_reduce_norm_push_kernel(con
         mbar_expect_tx(&full[st], stage_bytes);
         for (uint32_t s = 0; s < p.partials; ++s)
             bulk_load(smem + (size_t)st * stage_bytes + (size_t)s * row_bytes, p.pull[s] + (size_t)row * p.width, row_bytes, &full[st]);
+        if (p.x_in) bulk_load(smem + (size_t)st * stage_bytes + (size_t)p.partials * row_bytes, p.x_in + (size_t)row * p.width, row_bytes, &full[st]);
     };
     if (threadIdx.x == 0)
         for (uint32_t it = 0; it < my_rows && it < p.stages; ++it) fetch(it);
@@ -664,9 +672,16 @@ __global__ void __launch_bounds__(PUSH_THREADS) pull_reduce_norm_push_kernel(con
                 for (int j = 0; j < 4; ++j) { float2 f = __bfloat1622float2(h2[j]); v[i][2 * j] += f.x; v[i][2 * j + 1] += f.y; }
             }
         }
+        // the residual row moves to registers before the stage is handed back
+        uint4 xin[PUSH_MAXV];
+        if (p.x_in) {
+            const uint4* src = reinterpret_cast<const uint4*>(smem + (size_t)st * stage_bytes + (size_t)p.partials * row_bytes);
+#pragma unroll
+            for (int i = 0; i < PUSH_MAXV; ++i) if (have[i]) xin[i] = src[i * PUSH_THREADS + threadIdx.x];
+        }
         __syncthreads();                 // every thread has read the stage: it may be filled again
         if (threadIdx.x == 0 && it + p.stages < my_rows) fetch(it + p.stages);
-        push_row(p, row, v, have, red);
+        push_row(p, row, xin, v, have, red);
     }
     if (!ok) {
         // A copy did not arrive within the bound (a peer's memory went away): raise the status word, give the copies that
@@ -795,19 +810,22 @@ int32_t reduce_norm_push_impl(rb_ctx* ctx, const rb_tensor* staging, const rb_te
     // Beside the compute stream's persistent GEMMs this kernel gets the SMs they leave free; alone it gets them all.
     const int sms = ctx->sm_limit > 0 ? (aux_active(ctx) ? ctx->sm_count - ctx->sm_limit : ctx->sm_limit) : ctx->sm_count;
     if (pulls) {
-        // one block per SM, each with up to PULL_STAGES rows of `world` sources in flight in shared memory
-        const uint64_t stage_bytes = (uint64_t)world * width * 2;
-        const uint64_t budget = 200 * 1024;
+        // every block keeps up to PULL_STAGES rows of (world partial products + the residual row) in flight in shared memory;
+        // as many blocks per SM as that leaves room for, so that the stores of one row overlap the sum of another
+        const uint64_t stage_bytes = (uint64_t)(world + (x_in ? 1 : 0)) * width * 2;
+        const uint64_t budget = 222 * 1024;
         uint32_t stages = (uint32_t)(budget / stage_bytes);
         if (stages > (uint32_t)PULL_STAGES) stages = PULL_STAGES;
         if (stages == 0) return fail(RB_INVALID_TENSOR, "pull form: one row of every rank's partial product (%llu bytes) does not fit shared memory", (unsigned long long)stage_bytes);
         p.stages = stages;
         const uint32_t smem = (uint32_t)(stages * stage_bytes + 128);
+        uint64_t per_sm = budget / (smem + 1024);
+        per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
         static std::once_flag once;
         static cudaError_t configured = cudaSuccess;
-        std::call_once(once, [] { configured = cudaFuncSetAttribute(pull_reduce_norm_push_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024 + 128); });
+        std::call_once(once, [] { configured = cudaFuncSetAttribute(pull_reduce_norm_push_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 222 * 1024 + 128); });
         if (configured != cudaSuccess) return fail(RB_STATUS, "cudaFuncSetAttribute(pull reduce+norm+push) failed with CUDA status %d (%s)", (int)configured, cudaGetErrorString(configured));
-        const uint64_t cap = (uint64_t)(sms > 0 ? sms : 1);
+        const uint64_t cap = (uint64_t)(sms > 0 ? sms : 1) * per_sm;
         pull_reduce_norm_push_kernel<<<(unsigned)(rows < cap ? rows : cap), PUSH_THREADS, smem, ctx->stream>>>(p);
         return after_launch(ctx, "reduce_norm_push (pull)");
     }
