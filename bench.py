@@ -437,6 +437,8 @@ def tp_summary(extras_out: dict, world: int, rank: int):
     t1, source = TP_N1_RECORDED_MS, "recorded constant"
     if world == 1:
         t1, source = tpd["ms_per_forward"], "this run"
+    elif tpd.get("t1_this_run_ms"):
+        t1, source = tpd["t1_this_run_ms"], "every GPU running the whole batch alone, this run"
     elif os.path.exists(TP_N1_FILE):
         try:
             t1, source = float(json.load(open(TP_N1_FILE))["ms_per_forward"]), "N=1 run on this box"
@@ -742,7 +744,9 @@ def decoder_candidates(world: int, sequences: int = 8, fused: bool = False):
     overlap = {"micro_batches": 2, "sms_left_to_nccl": NCCL_CTAS, "nccl_max_ctas": NCCL_CTAS}   # all-reduce under the other group's GEMMs
     plain = {"micro_batches": 1, "sms_left_to_nccl": 0, "nccl_max_ctas": 0}                      # sequential, NCCL at full width
     if world == 1:
-        return [dict(plain, tp=1)]
+        # one GPU: the whole batch at once, and in groups of sequences one after the other (smaller activations stay in L2
+        # between the kernels of a layer)
+        return [dict(plain, tp=1)] + [dict(plain, tp=1, micro_batches=n) for n in (2, 4) if sequences % n == 0]
     out = [dict(overlap, tp=world), dict(plain, tp=world), dict(plain, tp=world, micro_batches=2)]
     if fused:   # exchange fused into the kernels over peer memory: on one stream, and with the owner-side step on the side stream
         out += [dict(plain, tp=world, fused=True), dict(overlap, tp=world, fused=True, overlap_exchange=True, nccl_max_ctas=0)]
@@ -751,7 +755,8 @@ def decoder_candidates(world: int, sequences: int = 8, fused: bool = False):
                 dict(overlap, tp=world, fused=True, overlap_exchange=True, pull_exchange=True, nccl_max_ctas=0)]
         if sequences % 4 == 0 and (sequences // 4 * 2048) % (128 * world) == 0:
             out.append(dict(overlap, tp=world, fused=True, overlap_exchange=True, pull_exchange=True, nccl_max_ctas=0, micro_batches=4))
-        out.append(dict(overlap, tp=world, fused=True, overlap_exchange=True, pull_exchange=True, nccl_max_ctas=0, sms_left_to_nccl=2 * NCCL_CTAS))
+        for sms in (NCCL_CTAS // 2, NCCL_CTAS * 3 // 2, 2 * NCCL_CTAS):
+            out.append(dict(overlap, tp=world, fused=True, overlap_exchange=True, pull_exchange=True, nccl_max_ctas=0, sms_left_to_nccl=sms))
     tp = world // 2
     while tp >= 1:
         per_group = sequences * tp // world
@@ -760,6 +765,8 @@ def decoder_candidates(world: int, sequences: int = 8, fused: bool = False):
                 out.append(dict(overlap, tp=tp))
             out.append(dict(plain, tp=tp))
         tp //= 2
+    # T1 of the same run: every GPU runs the whole batch alone (what the efficiency of tensor parallelism is measured against)
+    out += [dict(plain, tp=1, whole_batch=True), dict(plain, tp=1, whole_batch=True, micro_batches=4)]
     return out
 
 
@@ -787,7 +794,10 @@ def decoder_extra(client, pk, rank, world, dist, sink, candidates, results):
                "parallelism": f"tp{world}", "schedule": best, "schedules_timed": list(results),
                "config": "8 layers, hidden 4096, 32q/8kv heads, ffn 14336, vocab 32000, batch 8 x seq 2048, BF16",
                "frac_of_sustained_peak_per_gpu": tf / world / pk["bf16_tflops_sustained"]}
-        mixed = [r for r in results if r["tp"] != world]
+        whole = [r for r in results if r.get("whole_batch")]
+        if whole:
+            out["t1_this_run_ms"] = min(r["ms_per_forward"] for r in whole)
+        mixed = [r for r in results if r["tp"] != world and not r.get("whole_batch")]
         if mixed:
             b = min(mixed, key=lambda r: r["ms_per_forward"])
             out["smaller_groups_best"] = {"parallelism": b["parallelism"], "ms_per_forward": b["ms_per_forward"],
@@ -809,18 +819,21 @@ def decoder_extra(client, pk, rank, world, dist, sink, candidates, results):
                 control = TorchControl() if tp == world else GroupControl(TorchControl(), tensor_parallel_groups(world, tp)[group])
                 comms[(tp, cap)] = NcclCommunicator.initialize(control, client)
             comm = comms[(tp, cap)]
-        per_group = sequences // groups
-        if tp not in models:
+        per_group = sequences if cand.get("whole_batch") else sequences // groups
+        first = 0 if cand.get("whole_batch") else group * per_group
+        key = (tp, per_group)
+        if key not in models:
             for other in models.values():
                 other.close()
-            models[tp] = TensorParallelDecoder(client, cfg, per_group, seq, comm=comm, rank=tp_rank, world=tp, micro_batches=cand["micro_batches"],
+            models.clear()
+            models[key] = TensorParallelDecoder(client, cfg, per_group, seq, comm=comm, rank=tp_rank, world=tp, micro_batches=cand["micro_batches"],
                                                sm_reserve=cand["sms_left_to_nccl"], use_graph=True, fused=cand.get("fused", False),
                                                overlap_exchange=cand.get("overlap_exchange", False), pull_exchange=cand.get("pull_exchange", False))
         else:
-            models[tp].configure(comm, cand["micro_batches"], cand["sms_left_to_nccl"], True, cand.get("fused", False), cand.get("overlap_exchange", False),
+            models[key].configure(comm, cand["micro_batches"], cand["sms_left_to_nccl"], True, cand.get("fused", False), cand.get("overlap_exchange", False),
                                  cand.get("pull_exchange", False))
-        model = models[tp]
-        model.forward(tokens[group * per_group:(group + 1) * per_group])
+        model = models[key]
+        model.forward(tokens[first:first + per_group])
         for _ in range(2):
             model.forward()
         client.sync()
@@ -831,7 +844,9 @@ def decoder_extra(client, pk, rank, world, dist, sink, candidates, results):
         for _ in range(steps):
             model.forward()
         ms = max_over_ranks(dist, client.end_profile() / steps)
-        label = f"tp{tp}" if groups == 1 else (f"tp{tp} x {groups} groups of {per_group} sequences" if tp > 1 else f"{groups} replicas of {per_group} sequences, no exchange")
+        label = "every GPU runs the whole batch alone (T1 of this run)" if cand.get("whole_batch") else f"tp{tp}" if groups == 1 else (f"tp{tp} x {groups} groups of {per_group} sequences" if tp > 1 else f"{groups} replicas of {per_group} sequences, no exchange")
+        if tp == 1 and cand["micro_batches"] > 1:
+            label += f", in {cand['micro_batches']} groups of sequences one after the other"
         if cand.get("fused"):
             label += (", partial products pulled by the owner-side kernel" if cand.get("pull_exchange") else ", exchange fused into the kernels") \
                 + (" and overlapped on the side stream" if cand.get("overlap_exchange") else "")

@@ -12,9 +12,11 @@ if ROOT not in sys.path:
 
 def test_decoder_candidates_cover_pure_and_grouped_tensor_parallelism():
     import bench
-    assert [c["tp"] for c in bench.decoder_candidates(1)] == [1]
+    assert [(c["tp"], c["micro_batches"]) for c in bench.decoder_candidates(1)] == [(1, 1), (1, 2), (1, 4)]   # one GPU: whole batch, then groups of sequences
     for world in (2, 4, 8):
         cands = bench.decoder_candidates(world)
+        assert [c["micro_batches"] for c in cands if c.get("whole_batch")] == [1, 4] and all(c.get("whole_batch") for c in cands[-2:])   # T1 of the same run, timed last
+        cands = cands[:-2]
         assert [c["tp"] for c in cands[:3]] == [world] * 3            # pure tensor parallelism is timed first
         degrees = [c["tp"] for c in cands]
         assert degrees == sorted(degrees, reverse=True) and degrees[-1] == 1 and set(degrees) == {world >> i for i in range(world.bit_length())}
@@ -30,7 +32,7 @@ def test_fused_candidates_are_added_on_request():
     import bench
     extra = [c for c in bench.decoder_candidates(8, fused=True) if c.get("fused")]
     assert [(c["tp"], c["micro_batches"], c.get("overlap_exchange", False), c.get("pull_exchange", False)) for c in extra] == [
-        (8, 1, False, False), (8, 2, True, False), (8, 1, False, True), (8, 2, True, True), (8, 4, True, True), (8, 2, True, True)]
+        (8, 1, False, False), (8, 2, True, False), (8, 1, False, True), (8, 2, True, True), (8, 4, True, True), (8, 2, True, True), (8, 2, True, True), (8, 2, True, True)]
     assert all(c["nccl_max_ctas"] == 0 for c in extra)                  # NCCL is not on this path
     assert bench.decoder_candidates(1, fused=True) == bench.decoder_candidates(1)
 
