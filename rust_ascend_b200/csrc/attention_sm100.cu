@@ -32,22 +32,10 @@ namespace {
 using namespace sm100;
 using bf = __nv_bfloat16;
 
-#ifndef RB_ATTN_CTRL_REGS
-#define RB_ATTN_CTRL_REGS 56
-#endif
-#ifndef RB_ATTN_SOFTMAX_REGS
-#define RB_ATTN_SOFTMAX_REGS 224
-#endif
-#define RB_STR2(x) #x
-#define RB_STR(x) RB_STR2(x)
 constexpr int D = 128;            // head dim (Q/K) and value dim
 constexpr int TQ = 128;           // query rows per tile
 constexpr int TK = 128;           // keys per block
-constexpr int KV_STAGES = 2;       // K ring
-#ifndef RB_ATTN_V_STAGES
-#define RB_ATTN_V_STAGES 2
-#endif
-constexpr int V_STAGES = RB_ATTN_V_STAGES;   // V ring (a third stage fits when the item table is short)
+constexpr int KV_STAGES = 2;
 constexpr int THREADS = 384;
 // Warp roles.  The warp that issues the MMAs is a single thread with a long dependent instruction stream; which warp slot it
 // sits in decides how often the scheduler lets it issue beside the two busy softmax warps of its SM sub-partition
@@ -57,12 +45,11 @@ constexpr uint32_t W_SOFTMAX = 0, W_CONTROL = 8;
 #else
 constexpr uint32_t W_SOFTMAX = 4, W_CONTROL = 0;
 #endif
-constexpr uint32_t W_MMA = W_CONTROL, W_TMA = W_CONTROL + 1, W_MMA1 = W_CONTROL + 2;   // MMA issuers of tile 0 and tile 1; the fourth control warp only donates registers
+constexpr uint32_t W_MMA = W_CONTROL, W_TMA = W_CONTROL + 1;   // the other two control warps only donate registers
 constexpr int TILE_BYTES = 128 * D * 2;       // 32 KiB: one [128 x 128] BF16 tile = two 64-wide swizzle slabs
 constexpr int SLAB_BYTES = 128 * 64 * 2;      // 16 KiB
-constexpr int ITEM_TAB = RB_ATTN_V_STAGES > 2 ? 64 : 512;   // steps whose items are tabulated in shared memory; later steps compute theirs
-constexpr int SMEM_BYTES = 2 * TILE_BYTES + (KV_STAGES + V_STAGES) * TILE_BYTES + 1024 + 256 + ITEM_TAB * 16;
-static_assert(SMEM_BYTES <= 227 * 1024, "shared memory of the attention kernel");
+constexpr int ITEM_TAB = 512;                 // steps whose items are tabulated in shared memory; later steps compute theirs
+constexpr int SMEM_BYTES = 2 * TILE_BYTES + 2 * KV_STAGES * TILE_BYTES + 1024 + 256 + ITEM_TAB * 16;
 #ifdef RB_ATTN_TILE0_FIRST
 constexpr uint32_t FIRST_TILE = 0;
 #else
@@ -103,11 +90,21 @@ __device__ __forceinline__ uint4 make_item(const AttnParams& p, uint32_t step) {
     return make_uint4(qb | (valid ? 0x80000000u : 0u), h | (b << 16), valid ? blocks_for(p, row0, row0 + TQ) : 0u,
                       valid ? blocks_for(p, row0 + TQ, row0 + 2 * TQ) : 0u);
 }
+// The same item for a step beyond the table: a real call, so that the index arithmetic (divisions, 64-bit compares) does not
+// become part of the roles' loops, whose single issuing threads have few registers.  Only very large problems get here.
+__device__ __noinline__ uint4 make_item_late(uint32_t step, uint32_t q_blocks, uint32_t heads_total, uint32_t Hq, uint32_t wave_heads,
+                                             uint32_t M, uint32_t N, int32_t causal, int64_t delta) {
+    uint32_t qb = 0, h = 0, b = 0;
+    const bool valid = rb_attention_item(step, blockIdx.x, gridDim.x, q_blocks, heads_total, Hq, wave_heads, qb, h, b);
+    const uint32_t row0 = qb * 2 * TQ;
+    return make_uint4(qb | (valid ? 0x80000000u : 0u), h | (b << 16), valid ? rb_attention_blocks(M, N, causal, delta, row0, row0 + TQ, TK) : 0u,
+                      valid ? rb_attention_blocks(M, N, causal, delta, row0 + TQ, row0 + 2 * TQ, TK) : 0u);
+}
 // `round` is the CTA's step number; returns false when the CTA has no item in that step.  nb0 / nb1 are the key blocks the
 // item's two tiles visit.
 __device__ __forceinline__ bool item_coords(const AttnParams& p, const uint4* item_tab, uint32_t round, uint32_t& qb, uint32_t& h, uint32_t& b,
                                             uint32_t& nb0, uint32_t& nb1) {
-    const uint4 e = round < ITEM_TAB ? item_tab[round] : make_item(p, round);
+    const uint4 e = round < ITEM_TAB ? item_tab[round] : make_item_late(round, p.q_blocks, p.heads_total, p.Hq, p.wave_heads, p.M, p.N, p.causal, p.delta);
     qb = e.x & 0x7fffffffu; h = e.y & 0xffffu; b = e.y >> 16; nb0 = e.z; nb1 = e.w;
     return (e.x >> 31) != 0;
 }
@@ -328,14 +325,14 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     uint8_t* sq = smem;                                   // [2 tiles][2 slabs][128][64]
     uint8_t* sk = smem + 2 * TILE_BYTES;                  // [stages][2 slabs][128 keys][64 d]
     uint8_t* sv = sk + KV_STAGES * TILE_BYTES;            // [stages][2 slabs][128 keys][64 dv]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sv + V_STAGES * TILE_BYTES);
-    uint64_t* q_full = bars;                    // [2 tiles]  TMA -> MMA: the tile's Q rows of the item have landed
-    uint64_t* q_empty = bars + 2;               // [2 tiles]  MMA -> TMA: the tile's last score GEMM of the item has read them
-    uint64_t* k_full = bars + 4;                // [stages]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sv + KV_STAGES * TILE_BYTES);
+    uint64_t* q_full = bars;                    // [1]  TMA -> MMA: Q of the item has landed
+    uint64_t* q_empty = bars + 1;               // [1]  MMA -> TMA: the item's last score GEMM has read Q
+    uint64_t* k_full = bars + 2;                // [stages]
     uint64_t* k_empty = k_full + KV_STAGES;
     uint64_t* v_full = k_empty + KV_STAGES;
-    uint64_t* v_empty = v_full + V_STAGES;
-    uint64_t* s_full = v_empty + V_STAGES;     // [2 tiles]  MMA -> softmax: scores of a block are in TMEM
+    uint64_t* v_empty = v_full + KV_STAGES;
+    uint64_t* s_full = v_empty + KV_STAGES;     // [2 tiles]  MMA -> softmax: scores of a block are in TMEM
     uint64_t* p_half = s_full + 2;              // [2 tiles]  softmax -> MMA: P of the first 64 keys is in TMEM
     uint64_t* p_full = p_half + 2;              // [2 tiles]  softmax -> MMA: all of P
     uint64_t* o_full = p_full + 2;              // [2 tiles]  MMA -> softmax warps: the item's last P V has completed
@@ -351,9 +348,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     for (uint32_t step = threadIdx.x; step < rounds && step < ITEM_TAB; step += THREADS) item_tab[step] = make_item(p, step);
 
     if (threadIdx.x == 0) {
-        for (int t = 0; t < 2; ++t) { mbar_init(&q_full[t], 1); mbar_init(&q_empty[t], 1); }
-        for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 2); }
-        for (int s = 0; s < V_STAGES; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 2); }
+        mbar_init(q_full, 1); mbar_init(q_empty, 1);
+        for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
         for (int t = 0; t < 2; ++t) {
             mbar_init(&s_full[t], 1); mbar_init(&p_half[t], 128); mbar_init(&p_full[t], 128); mbar_init(&o_full[t], 1);
             mbar_init(&o_free[t], 128);
@@ -376,147 +372,148 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     // Register budget: the two softmax warpgroups keep a whole score row in registers, the third warpgroup (TMA, MMA and
     // two idle warps) needs few.  256 * 224 + 128 * 56 = 64512 registers.
     if (warp >= W_CONTROL && warp < W_CONTROL + 4) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 " RB_STR(RB_ATTN_CTRL_REGS) ";");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
         if (warp == W_TMA && elect_one()) {
             // ---------------- TMA producer ----------------
-            // Per item: Q of tile 0, the first K block, Q of tile 1, then V(0), K(1), V(1), ...  Tile 0 finishes an item first
-            // under a causal mask, and the MMA warp starts the next item's first score GEMM for it while tile 1 is still in
-            // its last block: that needs Q of tile 0 and K(0) of the next item, and nothing else, as early as possible.
             bool ok = true;
-            uint32_t kv_it = 0;
-            uint32_t q_it[2] = {0, 0};
-            uint32_t armed = 0, armed_parity = 0;      // bits 0-1: Q tiles, bits 2-3: K stages, bits 4..: V stages
+            uint32_t kv_it = 0, q_it = 0;
+            uint32_t armed = 0, armed_parity = 0;      // bit 0: Q, bits 1-2: K stages, bits 3-4: V stages
             auto arm = [&](uint32_t bit, uint32_t parity) { armed |= 1u << bit; armed_parity = (armed_parity & ~(1u << bit)) | (parity << bit); };
             for (uint32_t round = 0; ok && round < rounds; ++round) {
                 uint32_t qb, h, b, nb0, nb1;
                 if (!item_coords(p, item_tab, round, qb, h, b, nb0, nb1)) continue;
                 const uint32_t kvh = h / (p.Hq / p.Hkv), row0 = qb * 2 * TQ;
-                const uint32_t nb[2] = {nb0, nb1};
                 const uint32_t n_max = nb0 > nb1 ? nb0 : nb1;
                 if (n_max == 0) continue;
-                auto load_q = [&](uint32_t t) {
-                    if (nb[t] == 0) return;
-                    if (q_it[t] > 0 && !(ok = mbar_wait(&q_empty[t], (q_it[t] - 1) & 1, abort_word))) return;
-                    mbar_expect_tx(&q_full[t], TILE_BYTES); arm(t, q_it[t] & 1);
-                    for (int sl = 0; sl < 2; ++sl)
-                        tma_load_4d(sq + t * TILE_BYTES + sl * SLAB_BYTES, &map_q, &q_full[t], sl * 64, (int32_t)(row0 + t * TQ), (int32_t)h, (int32_t)b);
-                    ++q_it[t];
-                };
-                auto load_k = [&](uint32_t j) {
-                    const uint32_t st = (kv_it + j) % KV_STAGES, ph = ((kv_it + j) / KV_STAGES) & 1;
-                    if (!(ok = mbar_wait(&k_empty[st], ph ^ 1, abort_word))) return;
-                    mbar_expect_tx(&k_full[st], TILE_BYTES); arm(2 + st, ph);
-                    for (int sl = 0; sl < 2; ++sl)
-                        tma_load_4d(sk + st * TILE_BYTES + sl * SLAB_BYTES, &map_k, &k_full[st], sl * 64, (int32_t)(j * TK), (int32_t)kvh, (int32_t)b);
-                };
-                load_q(0);
-                if (ok) load_k(0);
-                if (ok) load_q(1);
+                if (q_it > 0 && !(ok = mbar_wait(q_empty, (q_it - 1) & 1, abort_word))) break;
+                mbar_expect_tx(q_full, 2 * TILE_BYTES); arm(0, q_it & 1);
+                for (int t = 0; t < 2; ++t)
+                    for (int s = 0; s < 2; ++s)
+                        tma_load_4d(sq + t * TILE_BYTES + s * SLAB_BYTES, &map_q, q_full, s * 64, (int32_t)(row0 + t * TQ), (int32_t)h, (int32_t)b);
                 for (uint32_t j = 0; ok && j < n_max; ++j) {
-                    const uint32_t st = (kv_it + j) % V_STAGES, ph = ((kv_it + j) / V_STAGES) & 1;
-                    if (j > 0) { load_k(j); if (!ok) break; }
+                    const uint32_t st = (kv_it + j) % KV_STAGES, ph = ((kv_it + j) / KV_STAGES) & 1;
+                    if (!(ok = mbar_wait(&k_empty[st], ph ^ 1, abort_word))) break;
+                    mbar_expect_tx(&k_full[st], TILE_BYTES); arm(1 + st, ph);
+                    for (int s = 0; s < 2; ++s)
+                        tma_load_4d(sk + st * TILE_BYTES + s * SLAB_BYTES, &map_k, &k_full[st], s * 64, (int32_t)(j * TK), (int32_t)kvh, (int32_t)b);
                     if (!(ok = mbar_wait(&v_empty[st], ph ^ 1, abort_word))) break;
-                    mbar_expect_tx(&v_full[st], TILE_BYTES); arm(4 + st, ph);
-                    for (int sl = 0; sl < 2; ++sl)
-                        tma_load_4d(sv + st * TILE_BYTES + sl * SLAB_BYTES, &map_v, &v_full[st], sl * 64, (int32_t)(j * TK), (int32_t)kvh, (int32_t)b);
+                    mbar_expect_tx(&v_full[st], TILE_BYTES); arm(3 + st, ph);
+                    for (int s = 0; s < 2; ++s)
+                        tma_load_4d(sv + st * TILE_BYTES + s * SLAB_BYTES, &map_v, &v_full[st], s * 64, (int32_t)(j * TK), (int32_t)kvh, (int32_t)b);
                 }
-                kv_it += n_max;
+                kv_it += n_max; ++q_it;
             }
             if (!ok) {
                 // A wait expired: give the copies already issued a bounded time to land before the CTA retires.
-                for (uint32_t bit = 0; bit < 4 + (uint32_t)V_STAGES; ++bit) {
+                for (uint32_t bit = 0; bit < 5; ++bit) {
                     if (!(armed & (1u << bit))) continue;
-                    uint64_t* bar = bit < 2 ? &q_full[bit] : (bit < 4 ? &k_full[bit - 2] : &v_full[bit - 4]);
+                    uint64_t* bar = bit == 0 ? q_full : (bit < 3 ? &k_full[bit - 1] : &v_full[bit - 3]);
                     for (uint32_t i = 0; i < (1u << 20) && !mbar_try_wait(bar, (armed_parity >> bit) & 1u); ++i) {}
                 }
             }
-        } else if ((warp == W_MMA || warp == W_MMA1) && elect_one()) {
-            // ---------------- MMA issuers: one thread per tile ----------------
-            // Each tile has its own chain  S(j) -> softmax -> P V(j), S(j+1) -> ...  and its own issuing thread, so neither chain
-            // ever waits behind the other tile's instruction stream, and a tile that has finished an item goes straight on to the
-            // next item (its Q rows and the first K block are all the first score GEMM needs) while the other tile is still in
-            // its last block.  The two threads share only the K/V ring: a stage goes back to the TMA warp when BOTH have
-            // released it, and a thread releases every block of an item in ring order, also those its tile does not visit
-            // (under a causal mask tile 0 skips the item's last block).  It waits for the block's data first even then: that
-            // proves the stage's previous round has been closed, so the arrival cannot be counted for the round before.
-            const uint32_t t = warp == W_MMA ? 0u : 1u;
+        } else if (warp == W_MMA && elect_one()) {
+            // ---------------- MMA issuer ----------------
             const uint32_t idesc_qk = make_idesc_bf16(TQ, TK, 0, 0);   // A = Q (K-major), B = K tile (K-major)
             const uint32_t idesc_pv = make_idesc_bf16(TQ, D, 0, 1);    // A = P (TMEM), B = V tile, Dv-contiguous (MN-major)
             bool ok = true;
-            uint32_t kv_it = 0;            // ring position of the item's first block
-            uint32_t blk = 0;              // key blocks served so far (parity of s_full / p_half / p_full)
-            uint32_t used = 0;             // items served so far (parity of q_full / o_full / o_free)
+            uint32_t kv_it = 0, q_it = 0;
+            uint32_t blk[2] = {0, 0};      // key blocks served per tile so far (parity of s_full / p_half / p_full)
+            uint32_t used[2] = {0, 0};     // items per tile so far (parity of o_full / o_free)
             // descriptor lower halves of the tile bases; a step of 16 head-dim elements (or 16 keys of V) is a constant added to them
-            const uint32_t q_lo = desc_lo_kmajor(smem_u32(sq)) + t * (TILE_BYTES >> 4), k_lo = desc_lo_kmajor(smem_u32(sk)), v_lo = desc_lo_mnmajor(smem_u32(sv), SLAB_BYTES);
-            const uint32_t tmem_s = tmem_base + t * TK, tmem_o = tmem_base + 256 + t * D;
-            const bool tr = false;
+            const uint32_t q_lo = desc_lo_kmajor(smem_u32(sq)), k_lo = desc_lo_kmajor(smem_u32(sk)), v_lo = desc_lo_mnmajor(smem_u32(sv), SLAB_BYTES);
+            auto issue_s = [&](uint32_t t, uint32_t st) {
+                // The Q descriptor does not change from block to block, so the compiler would keep all eight per-step
+                // descriptors of both tiles in registers across the loop and spill other state of this 56-register thread;
+                // the empty volatile statement makes it add the step offsets at each use instead.
+                uint32_t qa = q_lo + t * (TILE_BYTES >> 4);
+                asm volatile("" : "+r"(qa));
+                uint32_t ka = k_lo + st * (TILE_BYTES >> 4);
+                asm volatile("" : "+r"(ka));
+                issue_scores(tmem_base + t * TK, qa, ka, idesc_qk, &s_full[t]);
+            };
             for (uint32_t round = 0; ok && round < rounds; ++round) {
                 uint32_t qb, h, b, nb0, nb1;
                 if (!item_coords(p, item_tab, round, qb, h, b, nb0, nb1)) continue;
-                const uint32_t nb = t ? nb1 : nb0;
-                const uint32_t n_max = nb0 > nb1 ? nb0 : nb1;
+                const uint32_t nb[2] = {nb0, nb1};
+                const uint32_t n_max = nb[0] > nb[1] ? nb[0] : nb[1];
                 if (n_max == 0) continue;
-                RB_TR(trace_cta && t == 0, 4, round, 0);               // MMA: starts waiting for the item's Q
+                const uint32_t total_s = nb[0] + nb[1];
+                uint32_t s_done = 0;
+                const bool tr = trace_cta && round == 0;
+                RB_TR(trace_cta, 4, round, 0);                       // MMA: starts waiting for the item's Q
+                if (!(ok = mbar_wait(q_full, q_it & 1, abort_word))) break;
+                RB_TR(trace_cta, 4, round, 1);                       // MMA: Q has landed
                 {
                     const uint32_t st = kv_it % KV_STAGES, ph = (kv_it / KV_STAGES) & 1;
-                    if (nb > 0 && !(ok = mbar_wait(&q_full[t], used & 1, abort_word))) break;
-                    RB_TR(trace_cta && t == 0, 4, round, 1);           // MMA: Q has landed
                     if (!(ok = mbar_wait(&k_full[st], ph, abort_word))) break;
-                    if (nb > 0) {
-                        tc_fence_after();
-                        issue_scores(tmem_s, q_lo, k_lo + st * (TILE_BYTES >> 4), idesc_qk, &s_full[t]);
-                        umma_commit(&k_empty[st]);
-                        if (nb == 1) umma_commit(&q_empty[t]);
-                    } else {
-                        mbar_arrive(&k_empty[st]);
-                    }
-                    RB_TR(trace_cta && t == 0, 4, round, 2);           // MMA: first score GEMM issued
+                    tc_fence_after();
+#pragma unroll
+                    for (uint32_t ti = 0; ti < 2; ++ti) { const uint32_t t = ti ^ FIRST_TILE; if (nb[t] > 0) { issue_s(t, st); ++s_done; } }
+                    umma_commit(&k_empty[st]);
+                    if (s_done == total_s) umma_commit(q_empty);
+                    RB_TR(trace_cta, 4, round, 2);                   // MMA: first score GEMMs issued
                 }
                 for (uint32_t j = 0; ok && j < n_max; ++j) {
-                    const uint32_t st = (kv_it + j) % V_STAGES, ph = ((kv_it + j) / V_STAGES) & 1;                 // V block j
-                    const uint32_t st1 = (kv_it + j + 1) % KV_STAGES, ph1 = ((kv_it + j + 1) / KV_STAGES) & 1;   // K block j + 1
-                    // the operand tiles first: they arrive long before P, so these waits cost nothing once P is there
-                    if (!(ok = mbar_wait(&v_full[st], ph, abort_word))) break;
-                    if (j + 1 < n_max && !(ok = mbar_wait(&k_full[st1], ph1, abort_word))) break;
-                    if (j < nb) {
-                        const uint32_t par = blk & 1;
-                        // the first P V of an item overwrites O: the epilogue must have read the previous item's O
-                        if (j == 0 && used > 0 && !(ok = mbar_wait(&o_free[t], (used - 1) & 1, abort_word))) break;
+                    const uint32_t st = (kv_it + j) % KV_STAGES, ph = ((kv_it + j) / KV_STAGES) & 1;
+#pragma unroll
+                    for (uint32_t ti = 0; ti < 2; ++ti) {
+                        const uint32_t t = ti ^ FIRST_TILE, other = t ^ 1u;     // `other` is served first when t is the second tile
+                        if (!ok || j >= nb[t]) continue;
+                        const uint32_t par = blk[t] & 1;
                         RB_TR(tr, 2 + t, j, 7);
-                        if (!(ok = wait_handoff(&p_half[t], par, abort_word))) break;
+#ifdef RB_ATTN_EARLY_WAITS
+                        // the operand tiles first: they arrive long before P, so these waits cost nothing once P is there
+                        if (!(ok = mbar_wait(&v_full[st], ph, abort_word))) continue;
+                        if (j + 1 < nb[t] && !(ok = mbar_wait(&k_full[(kv_it + j + 1) % KV_STAGES], ((kv_it + j + 1) / KV_STAGES) & 1, abort_word))) continue;
+                        if (j == 0 && used[t] > 0 && !(ok = mbar_wait(&o_free[t], (used[t] - 1) & 1, abort_word))) continue;
+                        if (!(ok = wait_handoff(&p_half[t], par, abort_word))) continue;
                         RB_TR(tr, 2 + t, j, 0);
+#else
+                        if (!(ok = wait_handoff(&p_half[t], par, abort_word))) continue;
+                        RB_TR(tr, 2 + t, j, 0);
+                        // the first P V of an item overwrites O: the epilogue must have read the previous item's O
+                        if (j == 0 && used[t] > 0 && !(ok = mbar_wait(&o_free[t], (used[t] - 1) & 1, abort_word))) continue;
+                        if (!(ok = mbar_wait(&v_full[st], ph, abort_word))) continue;
+#endif
+                        RB_TR(tr, 2 + t, j, 1);
                         tc_fence_after();
-                        const uint32_t va = v_lo + st * (TILE_BYTES >> 4);
-                        issue_pv_half(tmem_o, tmem_s, va, idesc_pv, j);
+                        uint32_t va = v_lo + st * (TILE_BYTES >> 4);
+                        asm volatile("" : "+r"(va));
+                        issue_pv_half(tmem_base + 256 + t * D, tmem_base + t * TK, va, idesc_pv, j);
                         RB_TR(tr, 2 + t, j, 2);
-                        if (!(ok = wait_handoff(&p_full[t], par, abort_word))) break;
+                        if (!(ok = wait_handoff(&p_full[t], par, abort_word))) continue;
                         RB_TR(tr, 2 + t, j, 3);
                         tc_fence_after();
-                        issue_pv_half(tmem_o, tmem_s + 32, va + 4 * (2048 >> 4), idesc_pv, 1u);
-                        ++blk;
-                        umma_commit(&v_empty[st]);
+                        issue_pv_half(tmem_base + 256 + t * D, tmem_base + t * TK + 32, va + 4 * (2048 >> 4), idesc_pv, 1u);
+                        ++blk[t];
+                        // the stage is released by the tile served second, or by this one when the other tile does not use the block
+                        const bool last_user = (ti == 1) || (j >= nb[other]);
+                        if (last_user) umma_commit(&v_empty[st]);
                         RB_TR(tr, 2 + t, j, 4);
-                        if (j + 1 < nb) {
-                            issue_scores(tmem_s, q_lo, k_lo + st1 * (TILE_BYTES >> 4), idesc_qk, &s_full[t]);
-                            umma_commit(&k_empty[st1]);
-                            if (j + 2 == nb) umma_commit(&q_empty[t]);     // that was the tile's last score GEMM of the item
+                        if (j + 1 < nb[t]) {
+                            const uint32_t st1 = (kv_it + j + 1) % KV_STAGES, ph1 = ((kv_it + j + 1) / KV_STAGES) & 1;
+#ifndef RB_ATTN_EARLY_WAITS
+                            if (!(ok = mbar_wait(&k_full[st1], ph1, abort_word))) continue;
+#endif
+                            RB_TR(tr, 2 + t, j, 5);
+                            tc_fence_after();
+                            issue_s(t, st1); ++s_done;
+                            const bool last_k_user = (ti == 1) || (j + 1 >= nb[other]);
+                            if (last_k_user) umma_commit(&k_empty[st1]);
+                            if (s_done == total_s) umma_commit(q_empty);
                             RB_TR(tr, 2 + t, j, 6);
                         } else {
                             umma_commit(&o_full[t]);
-                            ++used;
-                            if (j + 1 < n_max) mbar_arrive(&k_empty[st1]);
+                            ++used[t];
                         }
-                    } else {
-                        mbar_arrive(&v_empty[st]);
-                        if (j + 1 < n_max) mbar_arrive(&k_empty[st1]);
                     }
                 }
-                kv_it += n_max;
-                RB_TR(trace_cta && t == 0, 4, round, 3);               // MMA: the item's last P V issued
+                kv_it += n_max; ++q_it;
+                RB_TR(trace_cta, 4, round, 3);                       // MMA: the item's last P V issued
             }
         }
     } else {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 " RB_STR(RB_ATTN_SOFTMAX_REGS) ";");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
         // ---------------- softmax + epilogue: warps 0-3 own tile 0, warps 4-7 own tile 1 ----------------
         const uint32_t t = (warp - W_SOFTMAX) >> 2, quarter = warp & 3;
         const uint32_t row_in_tile = quarter * 32 + lane;

@@ -227,96 +227,73 @@ def test_gemm_ring_and_accumulator_handshake(stages, tiles, kblocks, seed):
 
 
 @pytest.mark.parametrize("items,seed", [([(3, 4)], 0), ([(8, 8), (1, 2), (5, 0)], 1), ([(0, 0), (2, 2), (0, 0), (1, 1)], 2), ([(1, 1)] * 5, 3),
-                                        ([(16, 17), (0, 3), (4, 4), (1, 0)], 4), ([(2, 3), (2, 3), (7, 8), (1, 2), (6, 6)], 5),
-                                        ([(1, 2)] * 6, 6), ([(0, 2), (3, 0), (0, 1), (2, 2)], 7)])
+                                        ([(16, 17), (0, 3), (4, 4), (1, 0)], 4), ([(2, 3), (2, 3), (7, 8), (1, 2), (6, 6)], 5)])
 def test_attention_barrier_protocol(items, seed):
     """The persistent attention kernel's protocol over a CTA's list of work items (each: key blocks of tile 0 and of tile 1):
-    one Q buffer per tile, handed back after the tile's last score GEMM of the item; K/V rings of two stages that run on
-    across items and are shared by two MMA-issuing threads, one per tile, each of which releases every block of an item in
-    ring order (also those its tile does not visit) after it has seen the block's data; S/P aliased in TMEM (P overwrites the
-    scores it was computed from) and handed over in two halves; O read out by the softmax warps at the end of an item and
-    handed back before the next item's first P V overwrites it.  A tile that has finished an item runs on into the next one."""
+    one Q buffer handed back after the item's last score GEMM, K/V rings of two stages that run on across items, S/P aliased
+    in TMEM (P overwrites the scores it was computed from) and handed over in two halves, O read out by the softmax warps at
+    the end of an item and handed back before the next item's first P V overwrites it."""
     KV = 2
-    q_full = [Barrier(1), Barrier(1)]; q_empty = [Barrier(1), Barrier(1)]
-    k_full = [Barrier(1) for _ in range(KV)]; k_empty = [Barrier(2) for _ in range(KV)]
-    v_full = [Barrier(1) for _ in range(KV)]; v_empty = [Barrier(2) for _ in range(KV)]
+    q_full, q_empty = Barrier(1), Barrier(1)
+    k_full = [Barrier(1) for _ in range(KV)]; k_empty = [Barrier(1) for _ in range(KV)]
+    v_full = [Barrier(1) for _ in range(KV)]; v_empty = [Barrier(1) for _ in range(KV)]
     s_full = [Barrier(1), Barrier(1)]; p_half = [Barrier(128), Barrier(128)]; p_full = [Barrier(128), Barrier(128)]
     o_full = [Barrier(1), Barrier(1)]; o_free = [Barrier(128), Barrier(128)]
-    qsm = [None, None]               # item whose Q rows each tile's shared-memory buffer holds
+    qsm = [None]                     # item whose Q the shared-memory buffer holds
     ksm, vsm = [None] * KV, [None] * KV
     s_tmem = [None, None]            # ("S", item, j) after the score GEMM, ("P", item, j) after the softmax
     p_state = [0, 0]                 # halves of P the softmax threads have completed for the current block
     o_tmem = [None, None]            # (item, [blocks accumulated]) or None once read out
     stored = [[], []]
 
-    def release(ring, bars, st):
-        bars[st].arrive()
-        if bars[st].idle():           # both threads have let go of the stage
-            ring[st] = None
-
     def producer():
-        kv_it = 0
-        q_it = [0, 0]
+        kv_it = q_it = 0
         for i, n in enumerate(items):
             n_max = max(n)
             if n_max == 0: continue
-
-            def load_q(t):
-                if n[t] == 0: return
-                if q_it[t] > 0:
-                    yield from wait(q_empty[t], (q_it[t] - 1) & 1)
-                assert qsm[t] is None, "Q overwritten while score GEMMs of the previous item could still read it"
-                qsm[t] = i; q_full[t].arrive(); q_it[t] += 1; yield True
-
-            def load_k(j):
+            if q_it > 0:
+                yield from wait(q_empty, (q_it - 1) & 1)
+            assert qsm[0] is None, "Q overwritten while score GEMMs of the previous item could still read it"
+            qsm[0] = i; q_full.arrive(); yield True
+            for j in range(n_max):
                 st, ph = (kv_it + j) % KV, ((kv_it + j) // KV) & 1
                 yield from wait(k_empty[st], ph ^ 1)
                 assert ksm[st] is None; ksm[st] = (i, j); k_full[st].arrive(); yield True
-
-            yield from load_q(0)
-            yield from load_k(0)
-            yield from load_q(1)
-            for j in range(n_max):
-                st, ph = (kv_it + j) % KV, ((kv_it + j) // KV) & 1
-                if j > 0:
-                    yield from load_k(j)
                 yield from wait(v_empty[st], ph ^ 1)
                 assert vsm[st] is None; vsm[st] = (i, j); v_full[st].arrive(); yield True
-            kv_it += n_max
+            kv_it += n_max; q_it += 1
 
-    def mma(t):
-        kv_it = blk = used = 0
-
-        def issue_s(i, j, st):
-            assert qsm[t] == i and ksm[st] == (i, j), "score GEMM read a Q or K buffer that holds something else"
-            assert s_tmem[t] is None or s_tmem[t][0] == "consumed", "scores overwritten while P was still needed"
-            s_tmem[t] = ("S", i, j); p_state[t] = 0; s_full[t].arrive()
-
+    def mma():
+        kv_it = q_it = 0
+        blk, used = [0, 0], [0, 0]
         for i, n in enumerate(items):
-            n_max, nb = max(n), n[t]
+            n_max = max(n)
             if n_max == 0: continue
+            total_s, s_done = n[0] + n[1], 0
+
+            def issue_s(t, j, st):
+                assert qsm[0] == i and ksm[st] == (i, j), "score GEMM read a Q or K buffer that holds something else"
+                assert s_tmem[t] is None or s_tmem[t][0] == "consumed", "scores overwritten while P was still needed"
+                s_tmem[t] = ("S", i, j); p_state[t] = 0; s_full[t].arrive()
+
+            yield from wait(q_full, q_it & 1)
             st, ph = kv_it % KV, (kv_it // KV) & 1
-            if nb > 0:
-                yield from wait(q_full[t], used & 1)
             yield from wait(k_full[st], ph)
-            if nb > 0:
-                issue_s(i, 0, st)
-                if nb == 1: qsm[t] = None; q_empty[t].arrive()
-            release(ksm, k_empty, st); yield True
+            for t in (1, 0):                                   # tile 1 leads: it has the extra key block under a causal mask
+                if n[t] > 0: issue_s(t, 0, st); s_done += 1
+            ksm[st] = None; k_empty[st].arrive()
+            if s_done == total_s: qsm[0] = None; q_empty.arrive()
+            yield True
             for j in range(n_max):
                 st, ph = (kv_it + j) % KV, ((kv_it + j) // KV) & 1
-                st1, ph1 = (kv_it + j + 1) % KV, ((kv_it + j + 1) // KV) & 1
-                yield from wait(v_full[st], ph)
-                assert vsm[st] == (i, j)
-                if j + 1 < n_max:
-                    yield from wait(k_full[st1], ph1)
-                    assert ksm[st1] == (i, j + 1)
-                if j < nb:
-                    par = blk & 1
-                    if j == 0 and used > 0:
-                        yield from wait(o_free[t], (used - 1) & 1)
+                for t in (1, 0):
+                    if j >= n[t]: continue
+                    par = blk[t] & 1
                     yield from wait(p_half[t], par)
-                    assert p_state[t] >= 1
+                    if j == 0 and used[t] > 0:
+                        yield from wait(o_free[t], (used[t] - 1) & 1)
+                    yield from wait(v_full[st], ph)
+                    assert p_state[t] >= 1 and vsm[st] == (i, j)
                     if j == 0:
                         assert o_tmem[t] is None, "O overwritten before the previous item's rows were read out"
                         o_tmem[t] = (i, [])
@@ -324,22 +301,21 @@ def test_attention_barrier_protocol(items, seed):
                     yield from wait(p_full[t], par)
                     assert s_tmem[t] == ("P", i, j) and p_state[t] == 2
                     o_tmem[t][1].append(j); s_tmem[t] = ("consumed", i, j)
-                    blk += 1
-                    release(vsm, v_empty, st); yield True
-                    if j + 1 < nb:
-                        issue_s(i, j + 1, st1)
-                        release(ksm, k_empty, st1)
-                        if j + 2 == nb: qsm[t] = None; q_empty[t].arrive()
+                    blk[t] += 1
+                    if t == 0 or j >= n[0]:                    # released by the tile served second, or by the only user
+                        vsm[st] = None; v_empty[st].arrive()
+                    yield True
+                    if j + 1 < n[t]:
+                        st1, ph1 = (kv_it + j + 1) % KV, ((kv_it + j + 1) // KV) & 1
+                        yield from wait(k_full[st1], ph1)
+                        issue_s(t, j + 1, st1); s_done += 1
+                        if t == 0 or j + 1 >= n[0]:
+                            ksm[st1] = None; k_empty[st1].arrive()
+                        if s_done == total_s: qsm[0] = None; q_empty.arrive()
                         yield True
                     else:
-                        o_full[t].arrive(); used += 1
-                        if j + 1 < n_max: release(ksm, k_empty, st1)
-                        yield True
-                else:
-                    release(vsm, v_empty, st)
-                    if j + 1 < n_max: release(ksm, k_empty, st1)
-                    yield True
-            kv_it += n_max
+                        o_full[t].arrive(); used[t] += 1; yield True
+            kv_it += n_max; q_it += 1
 
     def softmax_thread(t, tid):
         blk = used = 0
@@ -365,8 +341,8 @@ def test_attention_barrier_protocol(items, seed):
             yield True
             used += 1
 
-    run([producer(), mma(0), mma(1)] + [softmax_thread(t, i) for t in range(2) for i in range(128)], seed, limit=2000000)
+    run([producer(), mma()] + [softmax_thread(t, i) for t in range(2) for i in range(128)], seed, limit=2000000)
     for t in range(2):
         assert stored[t] == [i for i, n in enumerate(items) if n[t] > 0]
-    assert all(b.idle() for b in q_full + k_full + k_empty + v_full + v_empty + s_full + p_half + p_full + o_full)
+    assert all(b.idle() for b in [q_full] + k_full + k_empty + v_full + v_empty + s_full + p_half + p_full + o_full)
     assert all(x is None for x in ksm + vsm)
