@@ -413,18 +413,18 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             }
         } else if (warp == W_MMA && elect_one()) {
             // ---------------- MMA issuer ----------------
+            // This single thread's instruction stream is the scarcest resource of the kernel (every instruction costs it about
+            // 15 cycles beside two busy softmax warps on the same scheduler), so the per-tile step exists once, with the tile
+            // index as a variable and the per-tile counters packed into two registers: unrolled over the two tiles it measured
+            // 3 % slower, with rolled MMA loops 15 % slower.
             const uint32_t idesc_qk = make_idesc_bf16(TQ, TK, 0, 0);   // A = Q (K-major), B = K tile (K-major)
             const uint32_t idesc_pv = make_idesc_bf16(TQ, D, 0, 1);    // A = P (TMEM), B = V tile, Dv-contiguous (MN-major)
             bool ok = true;
             uint32_t kv_it = 0, q_it = 0;
-            uint32_t blk[2] = {0, 0};      // key blocks served per tile so far (parity of s_full / p_half / p_full)
-            uint32_t used[2] = {0, 0};     // items per tile so far (parity of o_full / o_free)
-            // descriptor lower halves of the tile bases; a step of 16 head-dim elements (or 16 keys of V) is a constant added to them
+            uint32_t bpar = 0;             // bit t: parity of the key blocks served for tile t (s_full / p_half / p_full)
+            uint32_t usedp = 0;            // 16 bits per tile: items served so far (parity of o_full / o_free)
             const uint32_t q_lo = desc_lo_kmajor(smem_u32(sq)), k_lo = desc_lo_kmajor(smem_u32(sk)), v_lo = desc_lo_mnmajor(smem_u32(sv), SLAB_BYTES);
             auto issue_s = [&](uint32_t t, uint32_t st) {
-                // The Q descriptor does not change from block to block, so the compiler would keep all eight per-step
-                // descriptors of both tiles in registers across the loop and spill other state of this 56-register thread;
-                // the empty volatile statement makes it add the step offsets at each use instead.
                 uint32_t qa = q_lo + t * (TILE_BYTES >> 4);
                 asm volatile("" : "+r"(qa));
                 uint32_t ka = k_lo + st * (TILE_BYTES >> 4);
@@ -434,82 +434,58 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             for (uint32_t round = 0; ok && round < rounds; ++round) {
                 uint32_t qb, h, b, nb0, nb1;
                 if (!item_coords(p, item_tab, round, qb, h, b, nb0, nb1)) continue;
-                const uint32_t nb[2] = {nb0, nb1};
-                const uint32_t n_max = nb[0] > nb[1] ? nb[0] : nb[1];
+                const uint32_t nbp = nb0 | (nb1 << 16);
+                const uint32_t n_max = nb0 > nb1 ? nb0 : nb1;
                 if (n_max == 0) continue;
-                const uint32_t total_s = nb[0] + nb[1];
-                uint32_t s_done = 0;
-                const bool tr = trace_cta && round == 0;
-                RB_TR(trace_cta, 4, round, 0);                       // MMA: starts waiting for the item's Q
+                uint32_t s_left = nb0 + nb1;
                 if (!(ok = mbar_wait(q_full, q_it & 1, abort_word))) break;
-                RB_TR(trace_cta, 4, round, 1);                       // MMA: Q has landed
                 {
                     const uint32_t st = kv_it % KV_STAGES, ph = (kv_it / KV_STAGES) & 1;
                     if (!(ok = mbar_wait(&k_full[st], ph, abort_word))) break;
                     tc_fence_after();
-#pragma unroll
-                    for (uint32_t ti = 0; ti < 2; ++ti) { const uint32_t t = ti ^ FIRST_TILE; if (nb[t] > 0) { issue_s(t, st); ++s_done; } }
+#pragma unroll 1
+                    for (uint32_t ti = 0; ti < 2; ++ti) { const uint32_t t = ti ^ FIRST_TILE; if (((nbp >> (16 * t)) & 0xffffu) > 0) { issue_s(t, st); --s_left; } }
                     umma_commit(&k_empty[st]);
-                    if (s_done == total_s) umma_commit(q_empty);
-                    RB_TR(trace_cta, 4, round, 2);                   // MMA: first score GEMMs issued
+                    if (s_left == 0) umma_commit(q_empty);
                 }
                 for (uint32_t j = 0; ok && j < n_max; ++j) {
                     const uint32_t st = (kv_it + j) % KV_STAGES, ph = ((kv_it + j) / KV_STAGES) & 1;
-#pragma unroll
+#pragma unroll 1
                     for (uint32_t ti = 0; ti < 2; ++ti) {
-                        const uint32_t t = ti ^ FIRST_TILE, other = t ^ 1u;     // `other` is served first when t is the second tile
-                        if (!ok || j >= nb[t]) continue;
-                        const uint32_t par = blk[t] & 1;
-                        RB_TR(tr, 2 + t, j, 7);
-#ifdef RB_ATTN_EARLY_WAITS
-                        // the operand tiles first: they arrive long before P, so these waits cost nothing once P is there
-                        if (!(ok = mbar_wait(&v_full[st], ph, abort_word))) continue;
-                        if (j + 1 < nb[t] && !(ok = mbar_wait(&k_full[(kv_it + j + 1) % KV_STAGES], ((kv_it + j + 1) / KV_STAGES) & 1, abort_word))) continue;
-                        if (j == 0 && used[t] > 0 && !(ok = mbar_wait(&o_free[t], (used[t] - 1) & 1, abort_word))) continue;
+                        const uint32_t t = ti ^ FIRST_TILE;
+                        const uint32_t nbt = (nbp >> (16 * t)) & 0xffffu, nbo = (nbp >> (16 * (t ^ 1u))) & 0xffffu;
+                        if (!ok || j >= nbt) continue;
+                        const uint32_t par = (bpar >> t) & 1u;
                         if (!(ok = wait_handoff(&p_half[t], par, abort_word))) continue;
-                        RB_TR(tr, 2 + t, j, 0);
-#else
-                        if (!(ok = wait_handoff(&p_half[t], par, abort_word))) continue;
-                        RB_TR(tr, 2 + t, j, 0);
                         // the first P V of an item overwrites O: the epilogue must have read the previous item's O
-                        if (j == 0 && used[t] > 0 && !(ok = mbar_wait(&o_free[t], (used[t] - 1) & 1, abort_word))) continue;
+                        const uint32_t used_t = (usedp >> (16 * t)) & 0xffffu;
+                        if (j == 0 && used_t > 0 && !(ok = mbar_wait(&o_free[t], (used_t - 1) & 1, abort_word))) continue;
                         if (!(ok = mbar_wait(&v_full[st], ph, abort_word))) continue;
-#endif
-                        RB_TR(tr, 2 + t, j, 1);
                         tc_fence_after();
                         uint32_t va = v_lo + st * (TILE_BYTES >> 4);
                         asm volatile("" : "+r"(va));
-                        issue_pv_half(tmem_base + 256 + t * D, tmem_base + t * TK, va, idesc_pv, j);
-                        RB_TR(tr, 2 + t, j, 2);
+                        const uint32_t tmem_o = tmem_base + 256 + t * D, tmem_p = tmem_base + t * TK;
+                        issue_pv_half(tmem_o, tmem_p, va, idesc_pv, j);
                         if (!(ok = wait_handoff(&p_full[t], par, abort_word))) continue;
-                        RB_TR(tr, 2 + t, j, 3);
                         tc_fence_after();
-                        issue_pv_half(tmem_base + 256 + t * D, tmem_base + t * TK + 32, va + 4 * (2048 >> 4), idesc_pv, 1u);
-                        ++blk[t];
+                        issue_pv_half(tmem_o, tmem_p + 32, va + 4 * (2048 >> 4), idesc_pv, 1u);
+                        bpar ^= 1u << t;
                         // the stage is released by the tile served second, or by this one when the other tile does not use the block
-                        const bool last_user = (ti == 1) || (j >= nb[other]);
-                        if (last_user) umma_commit(&v_empty[st]);
-                        RB_TR(tr, 2 + t, j, 4);
-                        if (j + 1 < nb[t]) {
+                        if (ti == 1 || j >= nbo) umma_commit(&v_empty[st]);
+                        if (j + 1 < nbt) {
                             const uint32_t st1 = (kv_it + j + 1) % KV_STAGES, ph1 = ((kv_it + j + 1) / KV_STAGES) & 1;
-#ifndef RB_ATTN_EARLY_WAITS
                             if (!(ok = mbar_wait(&k_full[st1], ph1, abort_word))) continue;
-#endif
-                            RB_TR(tr, 2 + t, j, 5);
                             tc_fence_after();
-                            issue_s(t, st1); ++s_done;
-                            const bool last_k_user = (ti == 1) || (j + 1 >= nb[other]);
-                            if (last_k_user) umma_commit(&k_empty[st1]);
-                            if (s_done == total_s) umma_commit(q_empty);
-                            RB_TR(tr, 2 + t, j, 6);
+                            issue_s(t, st1); --s_left;
+                            if (ti == 1 || j + 1 >= nbo) umma_commit(&k_empty[st1]);
+                            if (s_left == 0) umma_commit(q_empty);
                         } else {
                             umma_commit(&o_full[t]);
-                            ++used[t];
+                            usedp += 1u << (16 * t);
                         }
                     }
                 }
                 kv_it += n_max; ++q_it;
-                RB_TR(trace_cta, 4, round, 3);                       // MMA: the item's last P V issued
             }
         }
     } else {
