@@ -40,6 +40,11 @@ def workload_config(world: int) -> dict:
             "l2": f"rotating {SETS} operand sets (384 MiB) > 126 MB L2", "parallelism": parallelism}
 
 
+PIPELINED = "fused, pipelined: plain GEMM; the owner-side pull kernel of step i runs on the side stream beside the GEMM of step i+1"
+SIDE_SMS = int(os.environ.get("RUDA_BENCH_SIDE_SMS", "32"))      # SMs the pipelined form keeps free of the GEMM for the side stream
+PIPE_DEPTH = int(os.environ.get("RUDA_BENCH_PIPE_DEPTH", "2"))    # exchanges in flight in the pipelined form (2 or 4: divides the operand sets)
+
+
 class RowParallelHeadline:
     """The N > 1 headline step: Y = sum_r X_r W_r^T + bias on every rank (rank 0's partial product carries the bias)."""
 
@@ -81,6 +86,32 @@ class RowParallelHeadline:
                 _check(lib.rb_gemm(*pull_gemms[i % SETS])); _check(lib.rb_peer_signal(*announce)); _check(lib.rb_peer_wait(*pwait_s))
                 _check(lib.rb_reduce_norm_push_pull(*pull)); _check(lib.rb_peer_wait(*pwait_g))
             self.candidates["fused: plain GEMM, owner-side kernel pulls the partial products, sums and pushes over peer memory"] = (pulled, 5)
+            # pipelined pull form: consecutive steps are independent products (rotating operand sets), as consecutive micro
+            # batches of a layer are, so the exchange of step i (owner-side pull kernel on the side stream, on the SMs the GEMM
+            # leaves free) runs beside the GEMM of step i + 1.  Two exchanges alternate: a rank overwrites a partial-product
+            # buffer only after the exchange that read it has completed (rb_aux_wait).  Every step's sum is complete on every
+            # rank when the timed region ends (drain()).
+            self.pipe = [FusedExchange(client, control, M, N, pull=True) for _ in range(PIPE_DEPTH)]
+            self.sm_count = client.properties()["sm_count"]
+            owns = [e.own_partial()._c() for e in self.pipe]
+            keep.append(owns)
+            pipe_gemms = [(client._ctx, C.byref(k[0]), C.byref(k[1]), C.c_int32(0), C.c_int32(1), C.byref(k[2]) if rank == 0 else None, None,
+                           C.c_int32(1 if rank == 0 else 0), C.byref(owns[i % PIPE_DEPTH])) for i, k in enumerate(pd)]
+            pipe_args = [(e.signal_args(keep, SCATTER), e.wait_args(SCATTER, 1, keep), e.pull_args(None, None, 1e-5, None, keep), e.wait_args(GATHER, 1, keep))
+                         for e in self.pipe]
+            self._slot_used = [False] * PIPE_DEPTH
+
+            def pipelined(i):
+                slot = i % PIPE_DEPTH  # the depth divides SETS, so operand set i % SETS always meets the same exchange
+                announce_p, wait_sp, pull_p, wait_gp = pipe_args[slot]
+                if self._slot_used[slot]:
+                    _check(lib.rb_aux_wait(client._ctx, C.c_uint32(slot)))
+                _check(lib.rb_gemm(*pipe_gemms[i % SETS])); _check(lib.rb_peer_signal(*announce_p))
+                _check(lib.rb_aux_begin(client._ctx))
+                _check(lib.rb_peer_wait(*wait_sp)); _check(lib.rb_reduce_norm_push_pull(*pull_p)); _check(lib.rb_peer_wait(*wait_gp))
+                _check(lib.rb_aux_end(client._ctx, C.c_uint32(slot)))
+                self._slot_used[slot] = True
+            self.candidates[PIPELINED] = (pipelined, 5)
         except Exception as error:           # peer memory unavailable: the NCCL form still runs
             self.fused_error = f"{type(error).__name__}: {error}"
         comm = NcclCommunicator.initialize(control, client)
@@ -96,22 +127,55 @@ class RowParallelHeadline:
         self.candidates["GEMM + NCCL all-reduce"] = (nccl, 1)
         self.chosen, self.timings = None, {}
 
+    def prepare(self, name):
+        """Per-candidate context state: the pipelined form keeps SIDE_SMS SMs free of the persistent GEMM for the side stream."""
+        from rust_ascend_b200.runtime import _check
+        import ctypes as C
+        limit = self.sm_count - SIDE_SMS if name == PIPELINED else 0
+        _check(self.client._lib.rb_set_sm_limit(self.client._ctx, C.c_int32(limit)))
+
+    def drain(self):
+        """Joins the side stream: after it, every step enqueued so far is complete in the compute stream's order."""
+        from rust_ascend_b200.runtime import _check
+        import ctypes as C
+        for slot, used in enumerate(getattr(self, "_slot_used", [])):
+            if used:
+                _check(self.client._lib.rb_aux_wait(self.client._ctx, C.c_uint32(slot)))
+
     def choose(self):
-        for name, (fn, _) in self.candidates.items():
-            for i in range(max(3, self.args.warmup)):
-                fn(i)
-            self.client.sync(); self.dist.barrier()
+        self.errors = {}
+        for name, (fn, _) in list(self.candidates.items()):
+            try:
+                self.prepare(name)
+                for i in range(max(4, self.args.warmup)):
+                    fn(i)
+                self.drain()
+                self.client.sync()
+                failed = 0.0
+            except Exception as error:       # a form that does not run on this machine is left out; the others are still timed
+                self.errors[name] = f"{type(error).__name__}: {error}"
+                self.client.take_errors()
+                failed = 1.0
+            # every rank must agree on whether the form is timed (the timed loop exchanges data)
+            if max_over_ranks(self.dist, failed) > 0:
+                self.candidates.pop(name)
+                self._slot_used = [False] * PIPE_DEPTH
+                continue
+            self.dist.barrier()
             self.client.start_profile()
             for i in range(20):
                 fn(i)
+            self.drain()
             self.timings[name] = max_over_ranks(self.dist, self.client.end_profile() / 20)
         self.chosen = min(self.timings, key=self.timings.get)
+        self.prepare(self.chosen)
         return self.candidates[self.chosen]
 
     def result(self, i):
-        """Device tensor that holds Y after step i."""
+        """Device tensor that holds Y after step i (and drain())."""
+        if self.chosen == PIPELINED:
+            return self.pipe[i % PIPE_DEPTH].gathered()
         return self.exchange.gathered() if self.chosen.startswith("fused") else None
-
 
 
 def peaks():
@@ -271,6 +335,8 @@ def run_ours(args):
         step, launches_per_step = exchange.choose()
     for i in range(args.warmup):
         step(i)
+    if exchange is not None:
+        exchange.drain()
     client.sync()
     if dist is not None:
         dist.barrier()
@@ -280,6 +346,8 @@ def run_ours(args):
     client.start_profile()
     for i in range(args.steps):
         step(i)
+    if exchange is not None:
+        exchange.drain()
     total_ms = client.end_profile()
     clocks = sampler.stop()
     gpu_launches = client.stats()["launches"] - launches_before
@@ -322,6 +390,7 @@ def run_ours(args):
             st = sets[i % SETS]
             client.write(st[0].handle, hx)
             step(i)
+            exchange.drain()
             out = exchange.result(i) or st[3]
             client.read_into(out.handle, hy, out.offset)
         for i in range(3):
@@ -335,6 +404,9 @@ def run_ours(args):
         e2e_note = ("every rank uploads its K shard of X (rb_write), runs the row-parallel step and reads the whole Y back (rb_read) inside every timed step; "
                     "W and bias stay resident as module parameters")
     e2e_value = world * FLOPS_PER_STEP / e2e_s / 1e12
+    if exchange is not None:
+        exchange.drain()
+        exchange.prepare(None)        # the secondary measurements start from the default context state (all SMs)
 
     kernel_tflops = FLOPS_PER_STEP / (ms_per_step * 1e-3) / 1e12
     sustained = total_ms > 1000.0
@@ -354,7 +426,8 @@ def run_ours(args):
     }
     if exchange is not None:
         line["exchange"] = {"chosen": exchange.chosen, "us_per_step_in_warm_up": {k: v * 1e3 for k, v in exchange.timings.items()},
-                            "bytes_per_rank_and_step": M * N * 2, "fused_error": getattr(exchange, "fused_error", None)}
+                            "bytes_per_rank_and_step": M * N * 2, "fused_error": getattr(exchange, "fused_error", None),
+                            "forms_left_out": getattr(exchange, "errors", None) or None}
         line["roofline"]["note"] = "the step is one 4096^3 GEMM per GPU plus the exchange of its result; achieved counts the GEMM's flops over the whole step"
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         import oracle as orc

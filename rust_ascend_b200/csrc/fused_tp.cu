@@ -474,6 +474,9 @@ constexpr int PUSH_MAXV = 4;        // 16-byte vectors per thread: width <= 256 
 // residual stream, store the new residual row, normalise, and store the row into every rank's activation buffer.
 // v[i][0..8) is the FP32 sum of 16-byte vector i * PUSH_THREADS + threadIdx.x of the row.  Called by all threads of the block.
 // xin[i] is the same vector of the residual stream's row (read when p.x_in is set).
+// SYNC_BEFORE_RED: a block-wide barrier separates this row's write of the reduction scratch from the previous row's reads; a
+// caller whose own loop already has a barrier between the rows passes false.
+template <bool SYNC_BEFORE_RED>
 __device__ __forceinline__ void push_row(const PushParams& p, uint32_t row, const uint4 (&xin)[PUSH_MAXV], float (&v)[PUSH_MAXV][8], const bool (&have)[PUSH_MAXV], float* red) {
     if (p.partials) {
 #pragma unroll
@@ -526,7 +529,7 @@ __device__ __forceinline__ void push_row(const PushParams& p, uint32_t row, cons
         for (int j = 0; j < 8; ++j) acc = acc + __fmul_rn(v[i][j], v[i][j]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    __syncthreads();
+    if (SYNC_BEFORE_RED) __syncthreads();
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
     __syncthreads();
     float sum = red[0];
@@ -600,7 +603,7 @@ __global__ void __launch_bounds__(PUSH_THREADS) reduce_norm_push_kernel(const Pu
 #pragma unroll
             for (int i = 0; i < PUSH_MAXV; ++i) if (have[i]) xin[i] = src[i * PUSH_THREADS + threadIdx.x];
         }
-        push_row(p, row, xin, v, have, red);
+        push_row<true>(p, row, xin, v, have, red);
     }
     push_announce(p, &last);
 }
@@ -649,9 +652,9 @@ __global__ void __launch_bounds__(PUSH_THREADS) pull_reduce_norm_push_kernel(con
     uint32_t landed = 0;                 // rows whose copies are known to have completed
     for (uint32_t it = 0; it < my_rows; ++it) {
         const uint32_t st = it % p.stages, row = blockIdx.x + it * gridDim.x;
-        ok = mbar_wait(&full[st], (it / p.stages) & 1, abort_word);
-        if (!__syncthreads_and(ok)) { ok = false; break; }
-        landed = it + 1;
+        // every thread waits for the row itself (no barrier needed before reading it); a thread whose wait ran out has raised
+        // the abort word, which all threads read after the barrier below
+        mbar_wait(&full[st], (it / p.stages) & 1, abort_word);
         float v[PUSH_MAXV][8];
         bool have[PUSH_MAXV];
 #pragma unroll
@@ -679,9 +682,11 @@ __global__ void __launch_bounds__(PUSH_THREADS) pull_reduce_norm_push_kernel(con
 #pragma unroll
             for (int i = 0; i < PUSH_MAXV; ++i) if (have[i]) xin[i] = src[i * PUSH_THREADS + threadIdx.x];
         }
-        __syncthreads();                 // every thread has read the stage: it may be filled again
+        __syncthreads();                 // every thread has read the stage: it may be filled again (also orders the rows' uses of `red`)
+        if (*abort_word) { ok = false; break; }
+        landed = it + 1;
         if (threadIdx.x == 0 && it + p.stages < my_rows) fetch(it + p.stages);
-        push_row(p, row, xin, v, have, red);
+        push_row<false>(p, row, xin, v, have, red);
     }
     if (!ok) {
         // A copy did not arrive within the bound (a peer's memory went away): raise the status word, give the copies that
@@ -810,12 +815,14 @@ int32_t reduce_norm_push_impl(rb_ctx* ctx, const rb_tensor* staging, const rb_te
     // Beside the compute stream's persistent GEMMs this kernel gets the SMs they leave free; alone it gets them all.
     const int sms = ctx->sm_limit > 0 ? (aux_active(ctx) ? ctx->sm_count - ctx->sm_limit : ctx->sm_limit) : ctx->sm_count;
     if (pulls) {
-        // every block keeps up to PULL_STAGES rows of (world partial products + the residual row) in flight in shared memory;
-        // as many blocks per SM as that leaves room for, so that the stores of one row overlap the sum of another
+        // Every block keeps up to three rows of (world partial products + the residual row) in flight in shared memory, and an
+        // SM takes as many blocks as fit, so that the stores of one row overlap the sum of another.  (One block per SM with
+        // eight rows in flight was measured too: per-block throughput, not bytes in flight, is the limit; a step of the
+        // pipelined row-parallel Linear at two ranks took 229 us instead of 128-167 us.)
         const uint64_t stage_bytes = (uint64_t)(world + (x_in ? 1 : 0)) * width * 2;
         const uint64_t budget = 222 * 1024;
         uint32_t stages = (uint32_t)(budget / stage_bytes);
-        if (stages > (uint32_t)PULL_STAGES) stages = PULL_STAGES;
+        if (stages > 3u) stages = 3u;
         if (stages == 0) return fail(RB_INVALID_TENSOR, "pull form: one row of every rank's partial product (%llu bytes) does not fit shared memory", (unsigned long long)stage_bytes);
         p.stages = stages;
         const uint32_t smem = (uint32_t)(stages * stage_bytes + 128);
