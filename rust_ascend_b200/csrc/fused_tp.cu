@@ -639,15 +639,21 @@ __global__ void __launch_bounds__(PUSH_THREADS) pull_reduce_norm_push_kernel(con
     __syncthreads();
     if (step_lost) return;
     const uint32_t my_rows = blockIdx.x < p.rows ? (p.rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    auto fetch = [&](uint32_t it) {      // one thread: row number `it` of this block into stage it % p.stages
-        const uint32_t st = it % p.stages, row = blockIdx.x + it * gridDim.x;
-        mbar_expect_tx(&full[st], stage_bytes);
-        for (uint32_t s = 0; s < p.partials; ++s)
+    // Row number `it` of this block into stage it % stages: thread 0 arms the barrier with the stage's byte count (arm), then,
+    // behind a block-wide barrier, thread s issues the copy of source s (copy), so that the issue cost of world + 1 copies is
+    // not one thread's.
+    auto arm = [&](uint32_t it) { mbar_expect_tx(&full[it % p.stages], stage_bytes); };
+    auto copy = [&](uint32_t it) {
+        const uint32_t st = it % p.stages, row = blockIdx.x + it * gridDim.x, s = threadIdx.x;
+        if (s < p.partials)
             bulk_load(smem + (size_t)st * stage_bytes + (size_t)s * row_bytes, p.pull[s] + (size_t)row * p.width, row_bytes, &full[st]);
-        if (p.x_in) bulk_load(smem + (size_t)st * stage_bytes + (size_t)p.partials * row_bytes, p.x_in + (size_t)row * p.width, row_bytes, &full[st]);
+        else if (s == p.partials && p.x_in)
+            bulk_load(smem + (size_t)st * stage_bytes + (size_t)s * row_bytes, p.x_in + (size_t)row * p.width, row_bytes, &full[st]);
     };
     if (threadIdx.x == 0)
-        for (uint32_t it = 0; it < my_rows && it < p.stages; ++it) fetch(it);
+        for (uint32_t it = 0; it < my_rows && it < p.stages; ++it) arm(it);
+    __syncthreads();
+    for (uint32_t it = 0; it < my_rows && it < p.stages; ++it) copy(it);
     bool ok = true;
     uint32_t landed = 0;                 // rows whose copies are known to have completed
     for (uint32_t it = 0; it < my_rows; ++it) {
@@ -682,10 +688,11 @@ __global__ void __launch_bounds__(PUSH_THREADS) pull_reduce_norm_push_kernel(con
 #pragma unroll
             for (int i = 0; i < PUSH_MAXV; ++i) if (have[i]) xin[i] = src[i * PUSH_THREADS + threadIdx.x];
         }
+        if (threadIdx.x == 0 && it + p.stages < my_rows) arm(it + p.stages);   // this phase of the barrier is over: arm the next
         __syncthreads();                 // every thread has read the stage: it may be filled again (also orders the rows' uses of `red`)
         if (*abort_word) { ok = false; break; }
         landed = it + 1;
-        if (threadIdx.x == 0 && it + p.stages < my_rows) fetch(it + p.stages);
+        if (it + p.stages < my_rows) copy(it + p.stages);
         push_row<false>(p, row, xin, v, have, red);
     }
     if (!ok) {
