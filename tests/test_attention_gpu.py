@@ -275,3 +275,26 @@ def test_fp32_contract_with_fused_rotary(client, oracle):
     tk = np.broadcast_to(cos[:n], (b, hkv, n, 64)), np.broadcast_to(sin[:n], (b, hkv, n, 64))
     qr = oracle.bf16(oracle.rotary(oracle.bf16(q), tq[0], tq[1], "split_half")); kr = oracle.bf16(oracle.rotary(oracle.bf16(k), tk[0], tk[1], "split_half"))
     check_bf16(client.read(out), oracle.attention(qr, kr, v, SCALE, causal=True))
+
+
+def test_more_steps_per_cta_than_the_item_table_holds(client, oracle):
+    """With one SM a single CTA walks every work item: 600 (batch, head) pairs of one 256-row item each are more steps than
+    the 512 the kernel tabulates in shared memory, so the last ones are computed by the late-item function.  The result must
+    be the one the whole GPU computes (same bits: an item's arithmetic does not depend on which CTA runs it) and match the
+    oracle on sampled heads."""
+    import ctypes as C
+    from rust_ascend_b200.runtime import _check
+    rng = np.random.default_rng(23)
+    b, h, s = 6, 100, 256
+    q, k, v = (r16(rng.standard_normal((b, h, s, 128), dtype=np.float32)) for _ in range(3))
+    dq, dk, dv = up16(client, q), up16(client, k), up16(client, v)
+    whole = bf16_bits_to_f32(client.read(RT.attention(client, dq, dk, dv, 128 ** -0.5, causal=True)))
+    _check(client._lib.rb_set_sm_limit(client._ctx, C.c_int32(1)))
+    try:
+        one = bf16_bits_to_f32(client.read(RT.attention(client, dq, dk, dv, 128 ** -0.5, causal=True)))
+    finally:
+        _check(client._lib.rb_set_sm_limit(client._ctx, C.c_int32(0)))
+    np.testing.assert_array_equal(one, whole)
+    for bi, hi in ((0, 0), (5, 99), (3, 57)):          # (5, 99) is among the last items in any order
+        want = oracle.attention(q[bi:bi + 1, hi:hi + 1], k[bi:bi + 1, hi:hi + 1], v[bi:bi + 1, hi:hi + 1], 128 ** -0.5, causal=True)
+        check_bf16(one[bi:bi + 1, hi:hi + 1], want)
