@@ -41,6 +41,8 @@ def workload_config(world: int) -> dict:
 
 
 PIPELINED = "fused, pipelined: plain GEMM; the owner-side pull kernel of step i runs on the side stream beside the GEMM of step i+1"
+COPIED = "fused: plain GEMM, device-to-device copies (copy engines) gather the partial products and the summed rows, local owner-side kernel"
+COPIED_PIPELINED = "fused, pipelined: plain GEMM; the copies and the local owner-side kernel of step i run on the side stream beside the GEMM of step i+1"
 SIDE_SMS = int(os.environ.get("RUDA_BENCH_SIDE_SMS", "32"))      # SMs the pipelined form keeps free of the GEMM for the side stream
 PIPE_DEPTH = int(os.environ.get("RUDA_BENCH_PIPE_DEPTH", "2"))    # exchanges in flight in the pipelined form (2 or 4: divides the operand sets)
 
@@ -112,6 +114,35 @@ class RowParallelHeadline:
                 _check(lib.rb_aux_end(client._ctx, C.c_uint32(slot)))
                 self._slot_used[slot] = True
             self.candidates[PIPELINED] = (pipelined, 5)
+            # copy form, pipelined the same way; its transfers use no SM, so the GEMM keeps all of them
+            self.copy_pipe = [FusedExchange(client, control, M, N, dma=True) for _ in range(PIPE_DEPTH)]
+            cowns = [e.own_partial()._c() for e in self.copy_pipe]
+            keep.append(cowns)
+            copy_gemms = [(client._ctx, C.byref(k[0]), C.byref(k[1]), C.c_int32(0), C.c_int32(1), C.byref(k[2]) if rank == 0 else None, None,
+                           C.c_int32(1 if rank == 0 else 0), C.byref(cowns[i % PIPE_DEPTH])) for i, k in enumerate(pd)]
+            copy_args = [(e.signal_args(keep, SCATTER), e.wait_args(SCATTER, 1, keep), e.dma_reduce_calls(None, None, 1e-5, None, keep),
+                          e.wait_args(GATHER, 1, keep), e.dma_gather_calls(keep)) for e in self.copy_pipe]
+            self.copy_kernels = 4 + 1                    # GEMM, two signals, two waits ... the copies are not kernels
+
+            def copied(i, fork=True):
+                slot = i % PIPE_DEPTH
+                announce_c, wait_sc, reduce_c, wait_gc, gather_c = copy_args[slot]
+                if fork and self._slot_used[slot]:
+                    _check(lib.rb_aux_wait(client._ctx, C.c_uint32(slot)))
+                _check(lib.rb_gemm(*copy_gemms[i % SETS])); _check(lib.rb_peer_signal(*announce_c))
+                if fork:
+                    _check(lib.rb_aux_begin(client._ctx))
+                _check(lib.rb_peer_wait(*wait_sc))
+                for name, a in reduce_c:
+                    _check(getattr(lib, name)(*a))
+                _check(lib.rb_peer_wait(*wait_gc))
+                for name, a in gather_c:
+                    _check(getattr(lib, name)(*a))
+                if fork:
+                    _check(lib.rb_aux_end(client._ctx, C.c_uint32(slot)))
+                    self._slot_used[slot] = True
+            self.candidates[COPIED] = (lambda i: copied(i, False), 6)
+            self.candidates[COPIED_PIPELINED] = (copied, 6)
         except Exception as error:           # peer memory unavailable: the NCCL form still runs
             self.fused_error = f"{type(error).__name__}: {error}"
         comm = NcclCommunicator.initialize(control, client)
@@ -175,6 +206,8 @@ class RowParallelHeadline:
         """Device tensor that holds Y after step i (and drain())."""
         if self.chosen == PIPELINED:
             return self.pipe[i % PIPE_DEPTH].gathered()
+        if self.chosen in (COPIED, COPIED_PIPELINED):
+            return self.copy_pipe[i % PIPE_DEPTH].gathered()
         return self.exchange.gathered() if self.chosen.startswith("fused") else None
 
 
@@ -830,6 +863,12 @@ def decoder_candidates(world: int, sequences: int = 8, fused: bool = False):
             out.append(dict(overlap, tp=world, fused=True, overlap_exchange=True, pull_exchange=True, nccl_max_ctas=0, micro_batches=4))
         for sms in (NCCL_CTAS // 2, NCCL_CTAS * 3 // 2, 2 * NCCL_CTAS):
             out.append(dict(overlap, tp=world, fused=True, overlap_exchange=True, pull_exchange=True, nccl_max_ctas=0, sms_left_to_nccl=sms))
+        # copy form: device-to-device copies move the data (copy engines), only the owner-side arithmetic is a kernel, and the
+        # GEMMs beside it keep every SM
+        out.append(dict(plain, tp=world, fused=True, dma_exchange=True))
+        for n in (2, 4):
+            if sequences % n == 0 and (sequences // n * 2048) % (128 * world) == 0:
+                out.append(dict(plain, tp=world, fused=True, dma_exchange=True, overlap_exchange=True, micro_batches=n))
     tp = world // 2
     while tp >= 1:
         per_group = sequences * tp // world
@@ -901,10 +940,11 @@ def decoder_extra(client, pk, rank, world, dist, sink, candidates, results):
             models.clear()
             models[key] = TensorParallelDecoder(client, cfg, per_group, seq, comm=comm, rank=tp_rank, world=tp, micro_batches=cand["micro_batches"],
                                                sm_reserve=cand["sms_left_to_nccl"], use_graph=True, fused=cand.get("fused", False),
-                                               overlap_exchange=cand.get("overlap_exchange", False), pull_exchange=cand.get("pull_exchange", False))
+                                               overlap_exchange=cand.get("overlap_exchange", False), pull_exchange=cand.get("pull_exchange", False),
+                                               dma_exchange=cand.get("dma_exchange", False))
         else:
             models[key].configure(comm, cand["micro_batches"], cand["sms_left_to_nccl"], True, cand.get("fused", False), cand.get("overlap_exchange", False),
-                                 cand.get("pull_exchange", False))
+                                 cand.get("pull_exchange", False), cand.get("dma_exchange", False))
         model = models[key]
         model.forward(tokens[first:first + per_group])
         for _ in range(2):
@@ -921,11 +961,12 @@ def decoder_extra(client, pk, rank, world, dist, sink, candidates, results):
         if tp == 1 and cand["micro_batches"] > 1:
             label += f", in {cand['micro_batches']} groups of sequences one after the other"
         if cand.get("fused"):
-            label += (", partial products pulled by the owner-side kernel" if cand.get("pull_exchange") else ", exchange fused into the kernels") \
+            label += (", exchange by device-to-device copies and a local owner-side kernel" if cand.get("dma_exchange") else
+                      ", partial products pulled by the owner-side kernel" if cand.get("pull_exchange") else ", exchange fused into the kernels") \
                 + (" and overlapped on the side stream" if cand.get("overlap_exchange") else "")
             if cand["micro_batches"] > 2:
                 label += f", {cand['micro_batches']} micro batches"
-            if cand.get("overlap_exchange") and cand["sms_left_to_nccl"] != NCCL_CTAS:
+            if cand.get("overlap_exchange") and cand["sms_left_to_nccl"] != NCCL_CTAS and not cand.get("dma_exchange"):
                 label += f", {cand['sms_left_to_nccl']} SMs left to the side stream"
         results.append(dict(cand, parallelism=label, ms_per_forward=ms, launches_per_forward=model.launches_per_forward,
                             all_reduces_per_forward=model.collectives_per_forward, fused_exchanges_per_forward=model.fused_exchanges_per_forward))

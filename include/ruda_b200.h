@@ -409,6 +409,14 @@ RB_API int32_t rb_reduce_norm_push(rb_ctx* ctx, const rb_tensor* staging, const 
 RB_API int32_t rb_reduce_norm_push_pull(rb_ctx* ctx, const rb_tensor* const* partials, const rb_tensor* x_in, const rb_tensor* weight,
                                         double epsilon, const rb_tensor* x_out, uint32_t rank, uint32_t world,
                                         const rb_tensor* const* destinations, const rb_tensor* const* flags, const rb_tensor* done);
+/* The owner-side arithmetic alone, for an exchange whose transfers are device-to-device copies (rb_copy between mapped peer
+ * buffers: copy engines, no SM): sums the `world` partial products gathered in `staging` (BF16 [world, rows, width], local) in
+ * rank order in FP32, rounds once to BF16, adds the residual x_in, stores the new residual to x_out, applies RMSNorm with
+ * `weight` (NULL: none) and writes the rows to `out` (BF16 [rows, width], local), with the bits rb_reduce_norm_push produces.
+ * `done` is two zeroed INT32 words of local scratch.  Stands where the reference runs rms_norm (runtime/mod.rs:405-408) on the
+ * result of all_reduce (src/distributed.rs:139-156). */
+RB_API int32_t rb_reduce_norm_rows(rb_ctx* ctx, const rb_tensor* staging, const rb_tensor* x_in, const rb_tensor* weight, double epsilon,
+                                   const rb_tensor* x_out, const rb_tensor* out, const rb_tensor* done);
 
 /* ---- collectives: NCCL over NVLink 5 / NVSwitch in place of HCCL ----------------------------------------------- */
 typedef struct rb_comm rb_comm;

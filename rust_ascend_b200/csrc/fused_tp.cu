@@ -765,11 +765,14 @@ int32_t resolve_flags(rb_ctx* ctx, const rb_tensor* t, uint32_t world, const cha
 // Host side of both forms of the owner-side step.  `staging` (push form: [world, rows, width] in local memory, written by the
 // scatter GEMMs of all ranks) or `pulls` (pull form: every rank's [world * rows, width] partial product, peers' memory mapped
 // here) names the partials; neither means "no partials, normalise the residual stream only".
+// `local_out` (with destinations and flags null) selects the form that keeps everything on this GPU: the rows go to local_out
+// [rows, width] only and the closing announcement lands in word 1 of `done`.
 int32_t reduce_norm_push_impl(rb_ctx* ctx, const rb_tensor* staging, const rb_tensor* const* pulls, const rb_tensor* x_in, const rb_tensor* weight,
                               double epsilon, const rb_tensor* x_out, uint32_t rank, uint32_t world, const rb_tensor* const* destinations,
-                              const rb_tensor* const* flags, const rb_tensor* done) {
+                              const rb_tensor* const* flags, const rb_tensor* done, const rb_tensor* local_out = nullptr) {
     RB_TRY(check_ctx(ctx));
-    if (world < 1 || world > MAX_PEERS || rank >= world || !destinations || !flags) return fail(RB_INVALID_TENSOR, "reduce+norm+push needs 1..%d ranks and their activation and flag tensors", MAX_PEERS);
+    if (world < 1 || world > MAX_PEERS || rank >= world || (!local_out && (!destinations || !flags)))
+        return fail(RB_INVALID_TENSOR, "reduce+norm+push needs 1..%d ranks and their activation and flag tensors", MAX_PEERS);
     void *ps = nullptr, *pxi = nullptr, *pxo = nullptr, *pw = nullptr, *pd = nullptr;
     RB_TRY(resolve(ctx, staging, "reduce+norm+push staging area", &ps, true)); RB_TRY(resolve(ctx, x_in, "reduce+norm+push residual", &pxi, true));
     RB_TRY(resolve(ctx, x_out, "reduce+norm+push residual output", &pxo, true)); RB_TRY(resolve(ctx, weight, "reduce+norm+push weight", &pw, true));
@@ -791,7 +794,7 @@ int32_t reduce_norm_push_impl(rb_ctx* ctx, const rb_tensor* staging, const rb_te
     for (const rb_tensor* t : {x_in, x_out})
         if (t && (t->rank != 2 || t->dtype != RB_BF16 || t->shape[0] != rows || t->shape[1] != width)) return fail(RB_INVALID_TENSOR, "residual stream is BF16 [rows, width]");
     if (weight && (weight->dtype != RB_BF16 || elements(weight) != width)) return fail(RB_INVALID_TENSOR, "RMSNorm weight is BF16 [width]");
-    if (done->dtype != RB_I32 || elements(done) < 1) return fail(RB_INVALID_TENSOR, "block counter is one INT32 word");
+    if (done->dtype != RB_I32 || elements(done) < (local_out ? 2u : 1u)) return fail(RB_INVALID_TENSOR, "block counter is one INT32 word (two for the local form)");
     if (rows == 0 || width == 0 || width % 8 || width > (uint64_t)PUSH_THREADS * PUSH_MAXV * 8 || rows > 0x7fffffffull)
         return fail(RB_INVALID_TENSOR, "reduce+norm+push needs a positive width that is a multiple of 8 and at most 8192");
     PushParams p{};
@@ -800,7 +803,16 @@ int32_t reduce_norm_push_impl(rb_ctx* ctx, const rb_tensor* staging, const rb_te
     p.eps = (float)epsilon; p.rows = (uint32_t)rows; p.width = (uint32_t)width; p.world = world; p.dst_row0 = (uint64_t)rank * rows;
     p.done = static_cast<uint32_t*>(pd);
     RB_TRY(kernel_status_word(ctx, &p.status));
-    for (uint32_t d = 0; d < world; ++d) {
+    if (local_out) {
+        void* po = nullptr;
+        RB_TRY(resolve(ctx, local_out, "reduce+norm output rows", &po));
+        if (local_out->dtype != RB_BF16 || local_out->rank != 2 || local_out->shape[0] != rows || local_out->shape[1] != width)
+            return fail(RB_INVALID_TENSOR, "output rows are BF16 [rows, width]");
+        p.world = 1; p.dst_row0 = 0;
+        p.dst[0] = static_cast<bf*>(po);
+        p.flag[0] = p.done + 1;
+    }
+    for (uint32_t d = 0; d < world && !local_out; ++d) {
         void* pdst = nullptr; uint32_t* pf = nullptr;
         RB_TRY(resolve(ctx, destinations[d], "reduce+norm+push destination", &pdst));
         RB_TRY(resolve_flags(ctx, flags[d], world, "reduce+norm+push flags", &pf));
@@ -958,6 +970,13 @@ int32_t rb_reduce_norm_push(rb_ctx* ctx, const rb_tensor* staging, const rb_tens
                             const rb_tensor* x_out, uint32_t rank, uint32_t world, const rb_tensor* const* destinations,
                             const rb_tensor* const* flags, const rb_tensor* done) {
     return reduce_norm_push_impl(ctx, staging, nullptr, x_in, weight, epsilon, x_out, rank, world, destinations, flags, done);
+}
+
+int32_t rb_reduce_norm_rows(rb_ctx* ctx, const rb_tensor* staging, const rb_tensor* x_in, const rb_tensor* weight, double epsilon,
+                            const rb_tensor* x_out, const rb_tensor* out, const rb_tensor* done) {
+    if (!staging || !out) return fail(RB_NULL_HANDLE, "reduce+norm of local rows needs the gathered partial products and an output");
+    if (staging->rank != 3 || staging->shape[0] < 1 || staging->shape[0] > (uint64_t)MAX_PEERS) return fail(RB_INVALID_TENSOR, "staging area is BF16 [world, rows, width]");
+    return reduce_norm_push_impl(ctx, staging, nullptr, x_in, weight, epsilon, x_out, 0, (uint32_t)staging->shape[0], nullptr, nullptr, done, out);
 }
 
 int32_t rb_reduce_norm_push_pull(rb_ctx* ctx, const rb_tensor* const* partials, const rb_tensor* x_in, const rb_tensor* weight, double epsilon,

@@ -21,6 +21,8 @@ residual stream (which is then sharded by rows), normalises and pushes the resul
 `overlap_exchange=True` moves the owner-side step to a side stream under the other micro batch's GEMMs.
 `pull_exchange=True` keeps the row-parallel GEMMs plain (each rank writes its partial product locally and announces it) and
 lets the owner-side step fetch the partial products itself, so that all link traffic is on the side stream.
+`dma_exchange=True` moves the data of the exchange with device-to-device copies (copy engines) and keeps only the owner-side
+arithmetic as a kernel, so that the exchange costs the GEMMs beside it no SMs.
 """
 from __future__ import annotations
 
@@ -162,7 +164,7 @@ class TensorParallelDecoder:
 
     def __init__(self, client: ComputeClient, cfg: LlamaConfig, batch: int, seq: int, comm=None, rank: int = 0, world: int = 1,
                  seed: int = 0, exact_weights: bool = False, micro_batches: int = 1, sm_reserve: int = 0, use_graph: bool = False,
-                 fused: bool = False, overlap_exchange: bool = False, pull_exchange: bool = False):
+                 fused: bool = False, overlap_exchange: bool = False, pull_exchange: bool = False, dma_exchange: bool = False):
         if world > 1 and comm is None:
             raise InvalidTensor("a communicator is required for tensor parallelism")
         if cfg.head_dim != 128:
@@ -206,10 +208,10 @@ class TensorParallelDecoder:
         self.scale = 1.0 / float(np.sqrt(d))
         self._graph = None
         self._exchanges, self._peer_h, self._x_own = [], None, None
-        self.configure(comm, micro_batches, sm_reserve, use_graph, fused, overlap_exchange, pull_exchange)
+        self.configure(comm, micro_batches, sm_reserve, use_graph, fused, overlap_exchange, pull_exchange, dma_exchange)
 
     def configure(self, comm, micro_batches: int = 1, sm_reserve: int = 0, use_graph: bool = False, fused: bool = False,
-                  overlap_exchange: bool = False, pull_exchange: bool = False) -> None:
+                  overlap_exchange: bool = False, pull_exchange: bool = False, dma_exchange: bool = False) -> None:
         """(Re)builds the launch plan, and the recorded graph if asked for, on the weights and buffers already resident.
         Lets a caller compare schedules (micro batches, SMs left to NCCL, communicators with different CTA limits)
         without loading the model again."""
@@ -221,7 +223,8 @@ class TensorParallelDecoder:
             raise InvalidTensor("fused exchange needs a communicator with a control plane and micro batches of a multiple of 128 * world tokens")
         self.close()
         self.comm, self.micro, self.fused, self.overlap_exchange = comm, micro_batches, fused, bool(fused and overlap_exchange)
-        self.pull_exchange = bool(fused and pull_exchange)
+        self.dma_exchange = bool(fused and dma_exchange)
+        self.pull_exchange = bool(fused and pull_exchange) or self.dma_exchange     # both keep the row-parallel GEMMs plain
         self._keep = []          # ctypes structures referenced by the plan
         self._steps = []         # (function, argument tuple)
         self.launches_per_forward = 0
@@ -347,7 +350,7 @@ class TensorParallelDecoder:
         rows = tm // self.world                    # rows of it this rank owns
         control = self.comm.control
         self._peer_h = PeerBuffer(c, control, self.tokens * hidden * 2)
-        self._exchanges = [FusedExchange(c, control, tm, hidden, activations=self._peer_h, activation_offset=mb * tm * hidden * 2, pull=self.pull_exchange)
+        self._exchanges = [FusedExchange(c, control, tm, hidden, activations=self._peer_h, activation_offset=mb * tm * hidden * 2, pull=self.pull_exchange, dma=self.dma_exchange)
                            for mb in range(n)]
         self._x_own = c.tensor((n, rows, hidden), DType.BF16)
         eps = cfg.eps
@@ -356,6 +359,7 @@ class TensorParallelDecoder:
         def x_own(mb):
             return TensorBuffer(self._x_own.handle, (rows, hidden), DType.BF16, None, offset=mb * rows * hidden * 2)
 
+        rows_pushed_by_copy = [False] * n        # copy form: the micro batch's last owner-side step left its rows with the owners
         for step in fused_schedule(cfg.layers, n, self.overlap_exchange):
             kind = step[0]
             if kind in ("aux_begin", "aux_end", "aux_wait"):   # fork to / join from the side stream; the slot is the micro batch
@@ -377,12 +381,19 @@ class TensorParallelDecoder:
                 self._op("rb_peer_wait", *ex.wait_args(SCATTER, ex.scatter_count, keep))
             elif kind == "wait_gather":
                 self._op("rb_peer_wait", *ex.wait_args(GATHER, 1, keep))
+                if self.dma_exchange and rows_pushed_by_copy[mb]:      # the owners announced their rows: fetch them
+                    for name, args in ex.dma_gather_calls(keep):
+                        self._op(name, *args, kernel=False)
             elif kind == "push":
                 _, _, layer, which = step
                 lw = self.layers[layer] if layer < cfg.layers else None
                 weight = self.final_norm if lw is None else (lw["norm1"] if which == 0 else lw["norm2"])
                 very_first = layer == 0 and which == 0     # nothing staged yet: normalise the embedding rows
-                if self.pull_exchange and not very_first:
+                rows_pushed_by_copy[mb] = self.dma_exchange and not very_first
+                if self.dma_exchange and not very_first:
+                    for name, args in ex.dma_reduce_calls(x_own(mb), weight, eps, x_own(mb), keep):
+                        self._op(name, *args, kernel=name != "rb_copy")
+                elif self.pull_exchange and not very_first:
                     self._op("rb_reduce_norm_push_pull", *ex.pull_args(x_own(mb), weight, eps, x_own(mb), keep))
                 else:
                     self._op("rb_reduce_norm_push", *ex.push_args(not very_first, x_own(mb), weight, eps, None if very_first else x_own(mb), keep))

@@ -15,6 +15,11 @@ buffer of its own that the others have mapped, announces it (`rb_peer_signal`), 
 (`rb_reduce_norm_push_pull`) fetches its rows of every partial product itself.  All link traffic then belongs to the
 owner-side kernel, which can run on a few SMs beside another micro batch's GEMMs, and the GEMM is never held up by the link.
 
+The copy form (`FusedExchange(..., dma=True)`) moves the data with device-to-device copies between the mapped buffers
+(`rb_copy`: copy engines, no SM at all): every rank copies its rows of every partial product into a local staging area, runs
+the owner-side arithmetic locally (`rb_reduce_norm_rows`), announces its rows, and copies the other ranks' finished rows into
+its own activation buffer.  Beside another micro batch's GEMMs it costs them no SMs except for the short local kernel.
+
 `FusedExchange` owns the buffers and flags of one stream of such projections; `row_parallel_linear_allreduce` is the
 all-reduce-equivalent composition (the entry the reference-shaped API asks for), and `decoder.TensorParallelDecoder` uses the
 pieces directly so that the residual stream stays sharded by rows between projections.
@@ -110,7 +115,7 @@ class FusedExchange:
     `activations` (a PeerBuffer holding at least tokens*hidden BF16 at `activation_offset`) receives the gathered rows."""
 
     def __init__(self, client: ComputeClient, control, tokens: int, hidden: int, activations: PeerBuffer | None = None,
-                 activation_offset: int = 0, pull: bool = False):
+                 activation_offset: int = 0, pull: bool = False, dma: bool = False):
         self.client, self.control = client, control
         self.rank, self.world = control.rank, control.world_size
         self.tokens, self.hidden = int(tokens), int(hidden)
@@ -118,10 +123,13 @@ class FusedExchange:
         if self.signals == 0 or hidden % 64:
             raise InvalidTensor("fused exchange needs tokens a multiple of 128 * world and hidden a multiple of 64")
         self.rows = tokens // self.world
-        self.pull = bool(pull)
-        # push form: a staging area the peers' GEMMs store into; pull form: this rank's whole partial product, read by the peers
+        self.dma = bool(dma)
+        self.pull = bool(pull) or self.dma
+        # push form: a staging area the peers' GEMMs store into; pull and copy forms: this rank's whole partial product, read by
+        # the peers; copy form: also a local staging area that the copies fill
         self.staging = None if self.pull else PeerBuffer(client, control, self.world * self.rows * hidden * 2)
         self.partial = PeerBuffer(client, control, tokens * hidden * 2) if self.pull else None
+        self.local_staging = client.tensor((self.world, self.rows, hidden), DType.BF16) if self.dma else None
         self.flags = PeerBuffer(client, control, 256)
         self._own_activations = activations is None
         self.activations = activations or PeerBuffer(client, control, tokens * hidden * 2)
@@ -146,7 +154,44 @@ class FusedExchange:
         return self.flags.view(self.rank, (FLAG_WORDS,), DType.I32, group * FLAG_WORDS * 4)
 
     def done_word(self) -> TensorBuffer:
-        return self.flags.view(self.rank, (1,), DType.I32, 3 * FLAG_WORDS * 4)
+        return self.flags.view(self.rank, (2,), DType.I32, 3 * FLAG_WORDS * 4)
+
+    # -- copy form: the call list of the owner-side step and of the gather, as (entry point name, argument tuple) ----------
+    def _row_bytes(self) -> int:
+        return self.rows * self.hidden * 2
+
+    def dma_reduce_calls(self, x_in, weight, eps: float, x_out, keep: list):
+        """After the wait for every rank's partial product: fetch this rank's rows of all of them, reduce + normalise locally
+        into this rank's rows of its own activation buffer, announce them."""
+        ctx, calls = self.client._ctx, []
+
+        def ref(t):
+            if t is None:
+                return None
+            c = t._c()
+            keep.append(c)
+            return C.byref(c)
+        for src in range(self.world):
+            theirs = self.partial.view(src, (self.rows, self.hidden), DType.BF16, self.rank * self._row_bytes())
+            slot = TensorBuffer(self.local_staging.handle, (self.rows, self.hidden), DType.BF16, None, offset=src * self._row_bytes())
+            calls.append(("rb_copy", (ctx, ref(theirs), ref(slot))))
+        mine = self.activations.view(self.rank, (self.rows, self.hidden), DType.BF16, self.activation_offset + self.rank * self._row_bytes())
+        calls.append(("rb_reduce_norm_rows", (ctx, ref(self.local_staging), ref(x_in), ref(weight), C.c_double(eps), ref(x_out), ref(mine), ref(self.done_word()))))
+        calls.append(("rb_peer_signal", self.signal_args(keep, GATHER)))
+        return calls
+
+    def dma_gather_calls(self, keep: list):
+        """After the wait for every rank's announcement: copy the other ranks' finished rows into this rank's activation buffer."""
+        ctx, calls = self.client._ctx, []
+        for src in range(self.world):
+            if src == self.rank:
+                continue
+            off = self.activation_offset + src * self._row_bytes()
+            a = self.activations.view(src, (self.rows, self.hidden), DType.BF16, off)._c()
+            b = self.activations.view(self.rank, (self.rows, self.hidden), DType.BF16, off)._c()
+            keep.extend([a, b])
+            calls.append(("rb_copy", (ctx, C.byref(a), C.byref(b))))
+        return calls
 
     def activation_views(self):
         return [self.activations.view(d, (self.tokens, self.hidden), DType.BF16, self.activation_offset) for d in range(self.world)]
@@ -225,13 +270,21 @@ class FusedExchange:
         _check(self.client._lib.rb_peer_wait(*self.wait_args(SCATTER, self.scatter_count, self._keep)))
 
     def reduce_norm_push(self, x_in=None, weight=None, eps: float = 1e-5, x_out=None, use_staging: bool = True) -> None:
-        if self.pull and use_staging:
+        if self.dma and use_staging:
+            for name, args in self.dma_reduce_calls(x_in, weight, eps, x_out, self._keep):
+                _check(getattr(self.client._lib, name)(*args))
+        elif self.pull and use_staging:
             _check(self.client._lib.rb_reduce_norm_push_pull(*self.pull_args(x_in, weight, eps, x_out, self._keep)))
         else:
             _check(self.client._lib.rb_reduce_norm_push(*self.push_args(use_staging and not self.pull, x_in, weight, eps, x_out, self._keep)))
 
-    def wait_gather(self) -> None:
+    def wait_gather(self, after_push_form: bool = False) -> None:
+        """Waits for every rank's rows.  In the copy form the rows are then fetched; `after_push_form` says that the step
+        before was a plain rb_reduce_norm_push (rows already stored here by their owners)."""
         _check(self.client._lib.rb_peer_wait(*self.wait_args(GATHER, 1, self._keep)))
+        if self.dma and not after_push_form:
+            for name, args in self.dma_gather_calls(self._keep):
+                _check(getattr(self.client._lib, name)(*args))
 
     def barrier(self) -> None:
         """All ranks have finished everything enqueued before this point (stream-ordered, no host involvement)."""
@@ -244,6 +297,7 @@ class FusedExchange:
         for buf in ([self.activations] if self._own_activations else []) + [self.flags, self.staging, self.partial]:
             if buf is not None:
                 buf.close()
+        self.local_staging = None
 
 
 class LocalGroup:

@@ -162,6 +162,28 @@ class EmuLib:
             self._view(flags[d])[rank.value] += 1
         return 0
 
+    def rb_copy(self, ctx, x, y):
+        self._view(y)[...] = self._view(x)
+        return 0
+
+    def rb_reduce_norm_rows(self, ctx, staging, x_in, weight, eps, x_out, out, done):
+        """Copy form: the owner-side arithmetic on partial products already gathered locally; rows stay on this rank."""
+        parts = self._f32(staging)
+        acc = np.zeros(parts.shape[1:], np.float32)
+        for src in range(parts.shape[0]):
+            acc = acc + parts[src]
+        value = bf16r(acc)
+        if x_in is not None:
+            value = bf16r(self._f32(x_in) + value)
+        if x_out is not None:
+            self._store(x_out, value)
+        if weight is not None:
+            r = np.float32(1) / np.sqrt((value.astype(np.float32) ** 2).mean(-1, keepdims=True, dtype=np.float32) + np.float32(eps.value))
+            value = (value * r) * self._f32(weight)
+        from rust_ascend_b200.runtime import f32_to_bf16_bits
+        self._view(out)[...] = f32_to_bf16_bits(value)
+        return 0
+
     def rb_reduce_norm_push_pull(self, ctx, partials, x_in, weight, eps, x_out, rank, world, destinations, flags, done):
         """Pull form: source s is rows [rank * rows, (rank + 1) * rows) of rank s's whole partial product."""
         whole = [self._f32(partials[src]) for src in range(world.value)]
@@ -244,7 +266,8 @@ class EmuComm:
 
 
 @pytest.mark.parametrize("world,micro,overlap,pull", [(1, 1, False, False), (1, 2, True, False), (2, 1, False, False), (2, 2, False, False), (2, 2, True, False),
-                                                      (4, 1, False, False), (1, 1, False, True), (2, 2, True, True), (4, 1, False, True)])
+                                                      (4, 1, False, False), (1, 1, False, True), (2, 2, True, True), (4, 1, False, True),
+                                                      (1, 1, False, "dma"), (2, 2, True, "dma"), (4, 1, False, "dma")])
 def test_fused_plan_computes_the_decoder(monkeypatch, oracle, world, micro, overlap, pull):
     import rust_ascend_b200.fused as fused
     from decoder_reference import forward, full_weights
@@ -276,7 +299,8 @@ def test_fused_plan_computes_the_decoder(monkeypatch, oracle, world, micro, over
     for rank in range(world):
         client = EmuClient(shared, rank, oracle)
         model = TensorParallelDecoder(client, cfg, batch, seq, comm=EmuComm(rank, world), rank=rank, world=world, seed=3, exact_weights=True,
-                                      micro_batches=micro, fused=True, overlap_exchange=overlap, pull_exchange=pull, sm_reserve=16 if overlap else 0)
+                                      micro_batches=micro, fused=True, overlap_exchange=overlap, pull_exchange=pull is True, dma_exchange=pull == "dma",
+                                      sm_reserve=16 if overlap else 0)
         client.write(model.tokens_dev.handle, tokens)
         models.append(model)
     steps = len(models[0]._steps)

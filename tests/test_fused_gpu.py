@@ -75,6 +75,12 @@ def _worker(rank, world, port, results):
     out["pull_linear_scaled"] = bf16_bits_to_f32(client.read(row_parallel_linear_allreduce(px, xs2, ws)))
     client.sync()
     px.close()
+    # copy form: device-to-device copies between the mapped buffers move the data, the owner-side arithmetic runs locally
+    cx = FusedExchange(client, control, x.shape[0], w.shape[0], dma=True)
+    out["copy_linear"] = bf16_bits_to_f32(client.read(row_parallel_linear_allreduce(cx, xs, ws)))
+    out["copy_linear_scaled"] = bf16_bits_to_f32(client.read(row_parallel_linear_allreduce(cx, xs2, ws)))
+    client.sync()
+    cx.close()
     # residual + RMSNorm folded into the owner-side step
     rows = x.shape[0] // world
     resid = np.random.default_rng(5).standard_normal((x.shape[0], w.shape[0])).astype(np.float32)
@@ -95,7 +101,8 @@ def _worker(rank, world, port, results):
     cfg = _cfg()
     tokens = np.random.default_rng(0).integers(0, cfg.vocab, size=(2, 128)).astype(np.int32)
     for name, kwargs in (("nccl", {}), ("fused", {"fused": True}), ("fused_graph", {"fused": True, "use_graph": True}),
-                         ("pull_graph", {"fused": True, "use_graph": True, "pull_exchange": True})):
+                         ("pull_graph", {"fused": True, "use_graph": True, "pull_exchange": True}),
+                         ("copy_graph", {"fused": True, "use_graph": True, "dma_exchange": True})):
         model = TensorParallelDecoder(client, cfg, 2, 128, comm=comm, rank=rank, world=world, seed=3, exact_weights=True, **kwargs)
         model.forward(tokens)
         out[name] = bf16_bits_to_f32(client.read(model.forward()))
@@ -103,7 +110,8 @@ def _worker(rank, world, port, results):
     # overlapped exchange: two micro batches, the owner-side step on the side stream under the other batch's GEMMs
     tokens4 = np.random.default_rng(1).integers(0, cfg.vocab, size=(4, 128)).astype(np.int32)
     for name, kwargs in (("fused4", {"fused": True}), ("fused4_overlap", {"fused": True, "micro_batches": 2, "overlap_exchange": True, "sm_reserve": 16, "use_graph": True}),
-                         ("pull4_overlap", {"fused": True, "micro_batches": 2, "overlap_exchange": True, "pull_exchange": True, "sm_reserve": 16, "use_graph": True})):
+                         ("pull4_overlap", {"fused": True, "micro_batches": 2, "overlap_exchange": True, "pull_exchange": True, "sm_reserve": 16, "use_graph": True}),
+                         ("copy4_overlap", {"fused": True, "micro_batches": 2, "overlap_exchange": True, "dma_exchange": True, "use_graph": True})):
         model = TensorParallelDecoder(client, cfg, 4, 128, comm=comm, rank=rank, world=world, seed=3, exact_weights=True, **kwargs)
         model.forward(tokens4)
         out[name] = bf16_bits_to_f32(client.read(model.forward()))
@@ -147,6 +155,8 @@ def test_two_gpu_fused_exchange(oracle):
         np.testing.assert_array_equal(got, r[0]["fused_linear"])          # every rank holds the same bits
         np.testing.assert_array_equal(r[rank]["pull_linear"], got)        # the pull form sums the same partial products in the same order
         np.testing.assert_array_equal(r[rank]["pull_linear_scaled"], -2.0 * got)   # exact: a power of two scales every BF16 value exactly
+        np.testing.assert_array_equal(r[rank]["copy_linear"], got)
+        np.testing.assert_array_equal(r[rank]["copy_linear_scaled"], -2.0 * got)
         for key in ("nccl_linear_0", "nccl_linear_1"):
             assert np.abs(r[rank][key] - total).max() <= 2.0 ** -7 * np.abs(total).max()
     rows = x.shape[0] // world
@@ -162,15 +172,17 @@ def test_two_gpu_fused_exchange(oracle):
     cfg = _cfg()
     tokens = np.random.default_rng(0).integers(0, cfg.vocab, size=(2, 128)).astype(np.int32)
     want = forward(oracle, cfg, full_weights(cfg, 3), tokens)
-    for name in ("nccl", "fused", "fused_graph", "pull_graph"):
+    for name in ("nccl", "fused", "fused_graph", "pull_graph", "copy_graph"):
         got = np.concatenate([r[0][name], r[1][name]], axis=1)
         err = np.abs(got - want)
         assert err.max() <= 0.04 * np.abs(want).max() and err.mean() <= 0.015 * np.abs(want).mean() + 1e-4, (name, err.max(), err.mean())
     np.testing.assert_array_equal(r[0]["fused"], r[0]["fused_graph"])
     np.testing.assert_array_equal(r[0]["fused"], r[0]["pull_graph"])
+    np.testing.assert_array_equal(r[0]["fused"], r[0]["copy_graph"])
     for rank in range(world):      # the schedule changes, the arithmetic does not
         assert np.abs(r[rank]["fused4"] - r[rank]["fused4_overlap"]).max() <= 2.0 ** -7 * np.abs(r[rank]["fused4"]).max()
         assert np.abs(r[rank]["fused4"] - r[rank]["pull4_overlap"]).max() <= 2.0 ** -7 * np.abs(r[rank]["fused4"]).max()
+        assert np.abs(r[rank]["fused4"] - r[rank]["copy4_overlap"]).max() <= 2.0 ** -7 * np.abs(r[rank]["fused4"]).max()
 
 
 def test_single_gpu_fused_exchange(client, oracle):
@@ -195,6 +207,10 @@ def test_single_gpu_fused_exchange(client, oracle):
         for _ in range(2):
             np.testing.assert_array_equal(bf16_bits_to_f32(client.read(row_parallel_linear_allreduce(px, xs, ws))), got)
         px.close()
+        cx = FusedExchange(client, SingleControl(), x.shape[0], w.shape[0], dma=True)
+        for _ in range(2):
+            np.testing.assert_array_equal(bf16_bits_to_f32(client.read(row_parallel_linear_allreduce(cx, xs, ws))), got)
+        cx.close()
         # the scatter GEMM runs on CTA pairs for these sizes; single CTAs must give the same bits
         os.environ["RUDA_GEMM_PAIRS"] = "0"
         try:
@@ -217,7 +233,8 @@ def test_single_gpu_fused_exchange(client, oracle):
         tokens = np.random.default_rng(0).integers(0, cfg.vocab, size=(4, 128)).astype(np.int32)
         want_logits = forward(oracle, cfg, full_weights(cfg, 3), tokens)
         for kwargs in ({}, {"use_graph": True}, {"micro_batches": 2, "overlap_exchange": True, "sm_reserve": 16, "use_graph": True},
-                       {"pull_exchange": True, "use_graph": True}, {"micro_batches": 2, "overlap_exchange": True, "pull_exchange": True, "sm_reserve": 16, "use_graph": True}):
+                       {"pull_exchange": True, "use_graph": True}, {"micro_batches": 2, "overlap_exchange": True, "pull_exchange": True, "sm_reserve": 16, "use_graph": True},
+                       {"dma_exchange": True, "use_graph": True}, {"micro_batches": 2, "overlap_exchange": True, "dma_exchange": True, "use_graph": True}):
             model = TensorParallelDecoder(client, cfg, 4, 128, comm=LocalGroup(), seed=3, exact_weights=True, fused=True, **kwargs)
             model.forward(tokens)
             got = bf16_bits_to_f32(client.read(model.forward()))
