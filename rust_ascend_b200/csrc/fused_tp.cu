@@ -834,18 +834,26 @@ int32_t reduce_norm_push_impl(rb_ctx* ctx, const rb_tensor* staging, const rb_te
     // Beside the compute stream's persistent GEMMs this kernel gets the SMs they leave free; alone it gets them all.
     const int sms = ctx->sm_limit > 0 ? (aux_active(ctx) ? ctx->sm_count - ctx->sm_limit : ctx->sm_limit) : ctx->sm_count;
     if (pulls) {
-        // Every block keeps up to three rows of (world partial products + the residual row) in flight in shared memory, and an
-        // SM takes as many blocks as fit, so that the stores of one row overlap the sum of another.  (One block per SM with
-        // eight rows in flight was measured too: per-block throughput, not bytes in flight, is the limit; a step of the
-        // pipelined row-parallel Linear at two ranks took 229 us instead of 128-167 us.)
+        // Rows of (world partial products + the residual row) in flight in shared memory are what hides the latency of the
+        // remote reads, and blocks per SM are what does the sums and the stores: a block of 256 threads takes about 0.7 us per
+        // row.  Where two blocks with two rows each fit an SM, that split is taken (as many such blocks as fit); where they do
+        // not (eight ranks: 72 KiB per row set), one block keeps up to three rows in flight.  (One block per SM with eight rows
+        // in flight was measured too: a step of the pipelined row-parallel Linear at two ranks took 229 us instead of 128-167.)
         const uint64_t stage_bytes = (uint64_t)(world + (x_in ? 1 : 0)) * width * 2;
         const uint64_t budget = 222 * 1024;
-        uint32_t stages = (uint32_t)(budget / stage_bytes);
-        if (stages > 3u) stages = 3u;
+        uint32_t stages;
+        uint64_t per_sm;
+        if (4 * stage_bytes + 2 * 1152 <= budget) {
+            stages = 2;
+            per_sm = budget / (2 * stage_bytes + 1152);
+        } else {
+            stages = (uint32_t)(budget / stage_bytes);
+            if (stages > 3u) stages = 3u;
+            per_sm = 1;
+        }
         if (stages == 0) return fail(RB_INVALID_TENSOR, "pull form: one row of every rank's partial product (%llu bytes) does not fit shared memory", (unsigned long long)stage_bytes);
         p.stages = stages;
         const uint32_t smem = (uint32_t)(stages * stage_bytes + 128);
-        uint64_t per_sm = budget / (smem + 1024);
         per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
         static std::once_flag once;
         static cudaError_t configured = cudaSuccess;
