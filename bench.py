@@ -41,6 +41,8 @@ def workload_config(world: int) -> dict:
 
 
 PIPELINED = "fused, pipelined: plain GEMM; the owner-side pull kernel of step i runs on the side stream beside the GEMM of step i+1"
+PUSHED_PIPELINED = "fused, pipelined: plain GEMM; a scatter kernel (posted stores) and the owner-side sum + push of step i run on the side stream beside the GEMM of step i+1"
+PUSH_SIDE_SMS = int(os.environ.get("RUDA_BENCH_PUSH_SIDE_SMS", "16"))
 COPIED = "fused: plain GEMM, device-to-device copies (copy engines) gather the partial products and the summed rows, local owner-side kernel"
 COPIED_PIPELINED = "fused, pipelined: plain GEMM; the copies and the local owner-side kernel of step i run on the side stream beside the GEMM of step i+1"
 SIDE_SMS = int(os.environ.get("RUDA_BENCH_SIDE_SMS", "32"))      # SMs the pipelined form keeps free of the GEMM for the side stream
@@ -114,6 +116,27 @@ class RowParallelHeadline:
                 _check(lib.rb_aux_end(client._ctx, C.c_uint32(slot)))
                 self._slot_used[slot] = True
             self.candidates[PIPELINED] = (pipelined, 5)
+            # side-scatter form, pipelined the same way: scatter kernel (posted stores), owner-side sum + push, all on the side stream
+            self.push_pipe = [FusedExchange(client, control, M, N, side_scatter=True) for _ in range(PIPE_DEPTH)]
+            powns = [e.own_partial()._c() for e in self.push_pipe]
+            keep.append(powns)
+            push_gemms = [(client._ctx, C.byref(k[0]), C.byref(k[1]), C.c_int32(0), C.c_int32(1), C.byref(k[2]) if rank == 0 else None, None,
+                           C.c_int32(1 if rank == 0 else 0), C.byref(powns[i % PIPE_DEPTH])) for i, k in enumerate(pd)]
+            push_args = [(e.scatter_rows_args(keep), e.wait_args(SCATTER, 1, keep), e.push_args(True, None, None, 1e-5, None, keep), e.wait_args(GATHER, 1, keep))
+                         for e in self.push_pipe]
+
+            def pushed(i):
+                slot = i % PIPE_DEPTH
+                rows_p, wait_sp, push_p, wait_gp = push_args[slot]
+                if self._slot_used[slot]:
+                    _check(lib.rb_aux_wait(client._ctx, C.c_uint32(slot)))
+                _check(lib.rb_gemm(*push_gemms[i % SETS]))
+                _check(lib.rb_aux_begin(client._ctx))
+                _check(lib.rb_scatter_rows(*rows_p)); _check(lib.rb_peer_wait(*wait_sp))
+                _check(lib.rb_reduce_norm_push(*push_p)); _check(lib.rb_peer_wait(*wait_gp))
+                _check(lib.rb_aux_end(client._ctx, C.c_uint32(slot)))
+                self._slot_used[slot] = True
+            self.candidates[PUSHED_PIPELINED] = (pushed, 5)
             # copy form, pipelined the same way; its transfers use no SM, so the GEMM keeps all of them
             self.copy_pipe = [FusedExchange(client, control, M, N, dma=True) for _ in range(PIPE_DEPTH)]
             cowns = [e.own_partial()._c() for e in self.copy_pipe]
@@ -162,7 +185,7 @@ class RowParallelHeadline:
         """Per-candidate context state: the pipelined form keeps SIDE_SMS SMs free of the persistent GEMM for the side stream."""
         from rust_ascend_b200.runtime import _check
         import ctypes as C
-        limit = self.sm_count - SIDE_SMS if name == PIPELINED else 0
+        limit = self.sm_count - SIDE_SMS if name == PIPELINED else (self.sm_count - PUSH_SIDE_SMS if name == PUSHED_PIPELINED else 0)
         _check(self.client._lib.rb_set_sm_limit(self.client._ctx, C.c_int32(limit)))
 
     def drain(self):
@@ -206,6 +229,8 @@ class RowParallelHeadline:
         """Device tensor that holds Y after step i (and drain())."""
         if self.chosen == PIPELINED:
             return self.pipe[i % PIPE_DEPTH].gathered()
+        if self.chosen == PUSHED_PIPELINED:
+            return self.push_pipe[i % PIPE_DEPTH].gathered()
         if self.chosen in (COPIED, COPIED_PIPELINED):
             return self.copy_pipe[i % PIPE_DEPTH].gathered()
         return self.exchange.gathered() if self.chosen.startswith("fused") else None
@@ -863,6 +888,10 @@ def decoder_candidates(world: int, sequences: int = 8, fused: bool = False):
             out.append(dict(overlap, tp=world, fused=True, overlap_exchange=True, pull_exchange=True, nccl_max_ctas=0, micro_batches=4))
         for sms in (NCCL_CTAS // 2, NCCL_CTAS * 3 // 2, 2 * NCCL_CTAS):
             out.append(dict(overlap, tp=world, fused=True, overlap_exchange=True, pull_exchange=True, nccl_max_ctas=0, sms_left_to_nccl=sms))
+        # side-scatter form: plain GEMMs, the rows go to their owners by a kernel of posted stores (on the side stream when overlapped)
+        out.append(dict(plain, tp=world, fused=True, side_scatter=True))
+        for sms in (NCCL_CTAS // 2, NCCL_CTAS, NCCL_CTAS * 3 // 2):
+            out.append(dict(overlap, tp=world, fused=True, overlap_exchange=True, side_scatter=True, nccl_max_ctas=0, sms_left_to_nccl=sms))
         # copy form: device-to-device copies move the data (copy engines), only the owner-side arithmetic is a kernel, and the
         # GEMMs beside it keep every SM
         out.append(dict(plain, tp=world, fused=True, dma_exchange=True))
@@ -941,10 +970,10 @@ def decoder_extra(client, pk, rank, world, dist, sink, candidates, results):
             models[key] = TensorParallelDecoder(client, cfg, per_group, seq, comm=comm, rank=tp_rank, world=tp, micro_batches=cand["micro_batches"],
                                                sm_reserve=cand["sms_left_to_nccl"], use_graph=True, fused=cand.get("fused", False),
                                                overlap_exchange=cand.get("overlap_exchange", False), pull_exchange=cand.get("pull_exchange", False),
-                                               dma_exchange=cand.get("dma_exchange", False))
+                                               dma_exchange=cand.get("dma_exchange", False), side_scatter=cand.get("side_scatter", False))
         else:
             models[key].configure(comm, cand["micro_batches"], cand["sms_left_to_nccl"], True, cand.get("fused", False), cand.get("overlap_exchange", False),
-                                 cand.get("pull_exchange", False), cand.get("dma_exchange", False))
+                                 cand.get("pull_exchange", False), cand.get("dma_exchange", False), cand.get("side_scatter", False))
         model = models[key]
         model.forward(tokens[first:first + per_group])
         for _ in range(2):
@@ -962,6 +991,7 @@ def decoder_extra(client, pk, rank, world, dist, sink, candidates, results):
             label += f", in {cand['micro_batches']} groups of sequences one after the other"
         if cand.get("fused"):
             label += (", exchange by device-to-device copies and a local owner-side kernel" if cand.get("dma_exchange") else
+                      ", rows scattered to their owners by a kernel of posted stores" if cand.get("side_scatter") else
                       ", partial products pulled by the owner-side kernel" if cand.get("pull_exchange") else ", exchange fused into the kernels") \
                 + (" and overlapped on the side stream" if cand.get("overlap_exchange") else "")
             if cand["micro_batches"] > 2:

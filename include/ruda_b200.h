@@ -417,6 +417,14 @@ RB_API int32_t rb_reduce_norm_push_pull(rb_ctx* ctx, const rb_tensor* const* par
  * result of all_reduce (src/distributed.rs:139-156). */
 RB_API int32_t rb_reduce_norm_rows(rb_ctx* ctx, const rb_tensor* staging, const rb_tensor* x_in, const rb_tensor* weight, double epsilon,
                                    const rb_tensor* x_out, const rb_tensor* out, const rb_tensor* done);
+/* The reduce-scatter half of the exchange as a kernel of its own, for a row-parallel Linear that ran as a plain rb_gemm: every
+ * row of `partial` (BF16 [world * rows, width], local) is stored into slot [rank] of the staging area of the rank that owns
+ * it (staging[o]: BF16 [world, rows, width], rank o's memory), then 1 is added to word [rank] of every flags[o].  Only posted
+ * stores cross the link.  Followed by rb_peer_wait(count 1) and rb_reduce_norm_push it is the scatter form with the transfer
+ * moved out of the GEMM, e.g. onto the side stream; same bits.  `done` is one zeroed INT32 word of local scratch.  Stands where
+ * the reference runs reduce_scatter (src/distributed.rs:139-156 splits all_reduce the same way). */
+RB_API int32_t rb_scatter_rows(rb_ctx* ctx, const rb_tensor* partial, uint32_t rank, uint32_t world, const rb_tensor* const* staging,
+                               const rb_tensor* const* flags, const rb_tensor* done);
 
 /* ---- collectives: NCCL over NVLink 5 / NVSwitch in place of HCCL ----------------------------------------------- */
 typedef struct rb_comm rb_comm;

@@ -450,6 +450,49 @@ __global__ void __launch_bounds__(32) peer_signal_kernel(const SignalParams p) {
     if (threadIdx.x < p.world) signal_release_sys(p.flag[threadIdx.x]);
 }
 
+// The scatter as a kernel of its own, for a row-parallel Linear that ran as a plain GEMM: every row of the local partial
+// product goes to slot [this rank] of the staging area of the rank that owns it.  All link traffic is posted stores (16 bytes
+// per thread, a warp covers 512 contiguous bytes), which a few SMs keep flowing without holding anything in flight the way
+// remote reads must.  Blocks walk the rows starting with the owner after this rank, so the ranks write to different owners at
+// any moment.  The last block to finish tells every owner once.
+struct ScatterRowsParams {
+    const bf* src;                  // [world * rows, width] local
+    uint32_t rows, width, world, rank;
+    bf* dst[MAX_PEERS];             // owner o's staging slot for this rank: [rows, width]
+    uint32_t* flag[MAX_PEERS];      // owner o's flag word for this rank
+    uint32_t* done;                 // local block counter, zero between launches
+    const uint32_t* status;
+};
+
+__global__ void __launch_bounds__(256) scatter_rows_kernel(const ScatterRowsParams p) {
+    __shared__ bool last;
+    __shared__ uint32_t step_lost;
+    if (threadIdx.x == 0) step_lost = *reinterpret_cast<const volatile uint32_t*>(p.status);
+    __syncthreads();
+    if (step_lost) return;
+    const uint32_t vecs = p.width / 8, total = p.rows * p.world;
+    const uint32_t first = ((p.rank + 1) % p.world) * p.rows;      // rotation of the row order
+    for (uint32_t i = blockIdx.x; i < total; i += gridDim.x) {
+        uint32_t row = i + first; if (row >= total) row -= total;
+        const uint32_t owner = row / p.rows, local = row - owner * p.rows;
+        const uint4* src = reinterpret_cast<const uint4*>(p.src + (size_t)row * p.width);
+        uint4* dst = reinterpret_cast<uint4*>(p.dst[owner] + (size_t)local * p.width);
+        for (uint32_t vi = threadIdx.x; vi < vecs; vi += 256) dst[vi] = __ldcs(src + vi);
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t ticket = atomicAdd(p.done, 1u);
+        __threadfence_system();
+        last = ticket == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (last) {
+        if (threadIdx.x == 0) *p.done = 0;
+        if (threadIdx.x < p.world) signal_release_sys(p.flag[threadIdx.x]);
+    }
+}
+
 struct PushParams {
     const bf* staging;              // [partials, rows, width] or null
     const bf* pull[MAX_PEERS];      // pull form: rank s's partial product, at the first of the rows this rank owns ([rows, width])
@@ -476,17 +519,17 @@ constexpr int PUSH_MAXV = 4;        // 16-byte vectors per thread: width <= 256 
 // xin[i] is the same vector of the residual stream's row (read when p.x_in is set).
 // SYNC_BEFORE_RED: a block-wide barrier separates this row's write of the reduction scratch from the previous row's reads; a
 // caller whose own loop already has a barrier between the rows passes false.
-template <bool SYNC_BEFORE_RED>
-__device__ __forceinline__ void push_row(const PushParams& p, uint32_t row, const uint4 (&xin)[PUSH_MAXV], float (&v)[PUSH_MAXV][8], const bool (&have)[PUSH_MAXV], float* red) {
+template <bool SYNC_BEFORE_RED, int NV>
+__device__ __forceinline__ void push_row(const PushParams& p, uint32_t row, const uint4 (&xin)[NV], float (&v)[NV][8], const bool (&have)[NV], float* red) {
     if (p.partials) {
 #pragma unroll
-        for (int i = 0; i < PUSH_MAXV; ++i)
+        for (int i = 0; i < NV; ++i)
 #pragma unroll
             for (int j = 0; j < 8; ++j) v[i][j] = __bfloat162float(__float2bfloat16_rn(v[i][j]));
     }
     if (p.x_in) {
 #pragma unroll
-        for (int i = 0; i < PUSH_MAXV; ++i) if (have[i]) {
+        for (int i = 0; i < NV; ++i) if (have[i]) {
             const uint4 w = xin[i];
             const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&w);
 #pragma unroll
@@ -501,7 +544,7 @@ __device__ __forceinline__ void push_row(const PushParams& p, uint32_t row, cons
     if (p.x_out) {
         uint4* dstx = reinterpret_cast<uint4*>(p.x_out + (size_t)row * p.width);
 #pragma unroll
-        for (int i = 0; i < PUSH_MAXV; ++i) if (have[i]) {
+        for (int i = 0; i < NV; ++i) if (have[i]) {
             uint4 w; __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&w);
 #pragma unroll
             for (int j = 0; j < 4; ++j) h2[j] = __floats2bfloat162_rn(v[i][2 * j], v[i][2 * j + 1]);
@@ -511,7 +554,7 @@ __device__ __forceinline__ void push_row(const PushParams& p, uint32_t row, cons
     if (!p.weight) {
         // plain all-reduce: the reduced rows themselves go to every destination
 #pragma unroll
-        for (int i = 0; i < PUSH_MAXV; ++i) if (have[i]) {
+        for (int i = 0; i < NV; ++i) if (have[i]) {
             const uint32_t vi = i * PUSH_THREADS + threadIdx.x;
             uint4 o; __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
@@ -524,7 +567,7 @@ __device__ __forceinline__ void push_row(const PushParams& p, uint32_t row, cons
     // RMSNorm (row_programs.rs:144-151): r = rsqrt(mean(x^2) + eps); y = (x * r) * w
     float acc = 0.f;
 #pragma unroll
-    for (int i = 0; i < PUSH_MAXV; ++i)
+    for (int i = 0; i < NV; ++i)
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc = acc + __fmul_rn(v[i][j], v[i][j]);
 #pragma unroll
@@ -537,7 +580,7 @@ __device__ __forceinline__ void push_row(const PushParams& p, uint32_t row, cons
     for (int w = 1; w < PUSH_THREADS / 32; ++w) sum += red[w];
     const float r = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum, (float)p.width), p.eps)));
 #pragma unroll
-    for (int i = 0; i < PUSH_MAXV; ++i) if (have[i]) {
+    for (int i = 0; i < NV; ++i) if (have[i]) {
         const uint32_t vi = i * PUSH_THREADS + threadIdx.x;
         const uint4 ww = __ldg(reinterpret_cast<const uint4*>(p.weight) + vi);
         const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&ww);
@@ -603,7 +646,7 @@ __global__ void __launch_bounds__(PUSH_THREADS) reduce_norm_push_kernel(const Pu
 #pragma unroll
             for (int i = 0; i < PUSH_MAXV; ++i) if (have[i]) xin[i] = src[i * PUSH_THREADS + threadIdx.x];
         }
-        push_row<true>(p, row, xin, v, have, red);
+        push_row<true, PUSH_MAXV>(p, row, xin, v, have, red);
     }
     push_announce(p, &last);
 }
@@ -621,7 +664,8 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* src, uint3
                  ::"r"(smem_u32(smem_dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 
-__global__ void __launch_bounds__(PUSH_THREADS) pull_reduce_norm_push_kernel(const PushParams p) {
+template <int NV>      // 16-byte vectors per thread: 2 for rows of up to 4096 values, else NV
+__global__ void __launch_bounds__(PUSH_THREADS, 3) pull_reduce_norm_push_kernel(const PushParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
     __shared__ uint64_t full[PULL_STAGES];
@@ -661,39 +705,44 @@ __global__ void __launch_bounds__(PUSH_THREADS) pull_reduce_norm_push_kernel(con
         // every thread waits for the row itself (no barrier needed before reading it); a thread whose wait ran out has raised
         // the abort word, which all threads read after the barrier below
         mbar_wait(&full[st], (it / p.stages) & 1, abort_word);
-        float v[PUSH_MAXV][8];
-        bool have[PUSH_MAXV];
+        float v[NV][8];
+        bool have[NV];
 #pragma unroll
-        for (int i = 0; i < PUSH_MAXV; ++i) {
+        for (int i = 0; i < NV; ++i) {
             const uint32_t vi = i * PUSH_THREADS + threadIdx.x;
             have[i] = vi < vecs;
 #pragma unroll
             for (int j = 0; j < 8; ++j) v[i][j] = 0.f;
         }
-        // fixed rank order, FP32: every rank computes bit-identical sums for the rows it owns
-        for (uint32_t s = 0; s < p.partials; ++s) {
-            const uint4* src = reinterpret_cast<const uint4*>(smem + (size_t)st * stage_bytes + (size_t)s * row_bytes);
+        // fixed rank order, FP32: every rank computes bit-identical sums for the rows it owns.  Per vector, the loads of all
+        // sources are issued before the first add, so that their shared-memory latencies overlap.
+        const uint8_t* stage = smem + (size_t)st * stage_bytes;
 #pragma unroll
-            for (int i = 0; i < PUSH_MAXV; ++i) if (have[i]) {
-                const uint4 w = src[i * PUSH_THREADS + threadIdx.x];
-                const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&w);
+        for (int i = 0; i < NV; ++i) if (have[i]) {
+            uint4 w[MAX_PEERS];
+#pragma unroll
+            for (int s = 0; s < MAX_PEERS; ++s)
+                if ((uint32_t)s < p.partials) w[s] = reinterpret_cast<const uint4*>(stage + (size_t)s * row_bytes)[i * PUSH_THREADS + threadIdx.x];
+#pragma unroll
+            for (int s = 0; s < MAX_PEERS; ++s) if ((uint32_t)s < p.partials) {
+                const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&w[s]);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) { float2 f = __bfloat1622float2(h2[j]); v[i][2 * j] += f.x; v[i][2 * j + 1] += f.y; }
             }
         }
         // the residual row moves to registers before the stage is handed back
-        uint4 xin[PUSH_MAXV];
+        uint4 xin[NV];
         if (p.x_in) {
             const uint4* src = reinterpret_cast<const uint4*>(smem + (size_t)st * stage_bytes + (size_t)p.partials * row_bytes);
 #pragma unroll
-            for (int i = 0; i < PUSH_MAXV; ++i) if (have[i]) xin[i] = src[i * PUSH_THREADS + threadIdx.x];
+            for (int i = 0; i < NV; ++i) if (have[i]) xin[i] = src[i * PUSH_THREADS + threadIdx.x];
         }
         if (threadIdx.x == 0 && it + p.stages < my_rows) arm(it + p.stages);   // this phase of the barrier is over: arm the next
         __syncthreads();                 // every thread has read the stage: it may be filled again (also orders the rows' uses of `red`)
         if (*abort_word) { ok = false; break; }
         landed = it + 1;
         if (it + p.stages < my_rows) copy(it + p.stages);
-        push_row<false>(p, row, xin, v, have, red);
+        push_row<false, NV>(p, row, xin, v, have, red);
     }
     if (!ok) {
         // A copy did not arrive within the bound (a peer's memory went away): raise the status word, give the copies that
@@ -857,10 +906,14 @@ int32_t reduce_norm_push_impl(rb_ctx* ctx, const rb_tensor* staging, const rb_te
         per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
         static std::once_flag once;
         static cudaError_t configured = cudaSuccess;
-        std::call_once(once, [] { configured = cudaFuncSetAttribute(pull_reduce_norm_push_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 222 * 1024 + 128); });
+        std::call_once(once, [] {
+            configured = cudaFuncSetAttribute(pull_reduce_norm_push_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 222 * 1024 + 128);
+            if (configured == cudaSuccess) configured = cudaFuncSetAttribute(pull_reduce_norm_push_kernel<PUSH_MAXV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 222 * 1024 + 128);
+        });
         if (configured != cudaSuccess) return fail(RB_STATUS, "cudaFuncSetAttribute(pull reduce+norm+push) failed with CUDA status %d (%s)", (int)configured, cudaGetErrorString(configured));
         const uint64_t cap = (uint64_t)(sms > 0 ? sms : 1) * per_sm;
-        pull_reduce_norm_push_kernel<<<(unsigned)(rows < cap ? rows : cap), PUSH_THREADS, smem, ctx->stream>>>(p);
+        if (width <= (uint64_t)PUSH_THREADS * 2 * 8) pull_reduce_norm_push_kernel<2><<<(unsigned)(rows < cap ? rows : cap), PUSH_THREADS, smem, ctx->stream>>>(p);
+        else pull_reduce_norm_push_kernel<PUSH_MAXV><<<(unsigned)(rows < cap ? rows : cap), PUSH_THREADS, smem, ctx->stream>>>(p);
         return after_launch(ctx, "reduce_norm_push (pull)");
     }
     const uint64_t cap = (uint64_t)(sms > 0 ? sms : 1) * 8;
@@ -972,6 +1025,37 @@ int32_t rb_peer_signal(rb_ctx* ctx, uint32_t rank, uint32_t world, const rb_tens
     }
     peer_signal_kernel<<<1, 32, 0, ctx->stream>>>(p);
     return after_launch(ctx, "peer_signal");
+}
+
+int32_t rb_scatter_rows(rb_ctx* ctx, const rb_tensor* partial, uint32_t rank, uint32_t world, const rb_tensor* const* staging,
+                        const rb_tensor* const* flags, const rb_tensor* done) {
+    RB_TRY(check_ctx(ctx));
+    if (world < 1 || world > MAX_PEERS || rank >= world || !staging || !flags) return fail(RB_INVALID_TENSOR, "row scatter covers 1..%d ranks and needs their staging and flag tensors", MAX_PEERS);
+    void *pp = nullptr, *pd = nullptr;
+    RB_TRY(resolve(ctx, partial, "row scatter partial product", &pp)); RB_TRY(resolve(ctx, done, "row scatter block counter", &pd));
+    if (partial->rank != 2 || partial->dtype != RB_BF16 || partial->shape[0] % world || partial->shape[1] % 8 || partial->shape[0] == 0 || partial->shape[0] > 0x7fffffffull)
+        return fail(RB_INVALID_TENSOR, "row scatter takes a BF16 [world * rows, width] partial product with a width that is a multiple of 8");
+    if (done->dtype != RB_I32 || elements(done) < 1) return fail(RB_INVALID_TENSOR, "block counter is one INT32 word");
+    ScatterRowsParams p{};
+    p.src = static_cast<const bf*>(pp);
+    p.rows = (uint32_t)(partial->shape[0] / world); p.width = (uint32_t)partial->shape[1]; p.world = world; p.rank = rank;
+    p.done = static_cast<uint32_t*>(pd);
+    { uint32_t* st = nullptr; RB_TRY(kernel_status_word(ctx, &st)); p.status = st; }
+    for (uint32_t o = 0; o < world; ++o) {
+        void* ps = nullptr; uint32_t* pf = nullptr;
+        RB_TRY(resolve(ctx, staging[o], "row scatter staging area", &ps));
+        RB_TRY(resolve_flags(ctx, flags[o], world, "row scatter flags", &pf));
+        const rb_tensor* t = staging[o];
+        if (t->dtype != RB_BF16 || t->rank != 3 || t->shape[0] != world || t->shape[1] != p.rows || t->shape[2] != p.width)
+            return fail(RB_INVALID_TENSOR, "staging areas are BF16 [world, rows, width]");
+        p.dst[o] = static_cast<bf*>(ps) + (uint64_t)rank * p.rows * p.width;
+        p.flag[o] = pf + rank;
+    }
+    // Beside the compute stream's persistent GEMMs this kernel gets the SMs they leave free; alone it gets them all.
+    const int sms = ctx->sm_limit > 0 ? (aux_active(ctx) ? ctx->sm_count - ctx->sm_limit : ctx->sm_limit) : ctx->sm_count;
+    const uint64_t cap = (uint64_t)(sms > 0 ? sms : 1) * 8, total = (uint64_t)p.rows * world;
+    scatter_rows_kernel<<<(unsigned)(total < cap ? total : cap), 256, 0, ctx->stream>>>(p);
+    return after_launch(ctx, "scatter_rows");
 }
 
 int32_t rb_reduce_norm_push(rb_ctx* ctx, const rb_tensor* staging, const rb_tensor* x_in, const rb_tensor* weight, double epsilon,

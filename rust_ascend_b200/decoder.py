@@ -21,6 +21,8 @@ residual stream (which is then sharded by rows), normalises and pushes the resul
 `overlap_exchange=True` moves the owner-side step to a side stream under the other micro batch's GEMMs.
 `pull_exchange=True` keeps the row-parallel GEMMs plain (each rank writes its partial product locally and announces it) and
 lets the owner-side step fetch the partial products itself, so that all link traffic is on the side stream.
+`side_scatter=True` keeps the GEMMs plain and scatters their rows to the owners with a kernel of its own (posted stores), on
+the side stream when the exchange is overlapped.
 `dma_exchange=True` moves the data of the exchange with device-to-device copies (copy engines) and keeps only the owner-side
 arithmetic as a kernel, so that the exchange costs the GEMMs beside it no SMs.
 """
@@ -164,7 +166,8 @@ class TensorParallelDecoder:
 
     def __init__(self, client: ComputeClient, cfg: LlamaConfig, batch: int, seq: int, comm=None, rank: int = 0, world: int = 1,
                  seed: int = 0, exact_weights: bool = False, micro_batches: int = 1, sm_reserve: int = 0, use_graph: bool = False,
-                 fused: bool = False, overlap_exchange: bool = False, pull_exchange: bool = False, dma_exchange: bool = False):
+                 fused: bool = False, overlap_exchange: bool = False, pull_exchange: bool = False, dma_exchange: bool = False,
+                 side_scatter: bool = False):
         if world > 1 and comm is None:
             raise InvalidTensor("a communicator is required for tensor parallelism")
         if cfg.head_dim != 128:
@@ -208,10 +211,10 @@ class TensorParallelDecoder:
         self.scale = 1.0 / float(np.sqrt(d))
         self._graph = None
         self._exchanges, self._peer_h, self._x_own = [], None, None
-        self.configure(comm, micro_batches, sm_reserve, use_graph, fused, overlap_exchange, pull_exchange, dma_exchange)
+        self.configure(comm, micro_batches, sm_reserve, use_graph, fused, overlap_exchange, pull_exchange, dma_exchange, side_scatter)
 
     def configure(self, comm, micro_batches: int = 1, sm_reserve: int = 0, use_graph: bool = False, fused: bool = False,
-                  overlap_exchange: bool = False, pull_exchange: bool = False, dma_exchange: bool = False) -> None:
+                  overlap_exchange: bool = False, pull_exchange: bool = False, dma_exchange: bool = False, side_scatter: bool = False) -> None:
         """(Re)builds the launch plan, and the recorded graph if asked for, on the weights and buffers already resident.
         Lets a caller compare schedules (micro batches, SMs left to NCCL, communicators with different CTA limits)
         without loading the model again."""
@@ -224,6 +227,7 @@ class TensorParallelDecoder:
         self.close()
         self.comm, self.micro, self.fused, self.overlap_exchange = comm, micro_batches, fused, bool(fused and overlap_exchange)
         self.dma_exchange = bool(fused and dma_exchange)
+        self.side_scatter = bool(fused and side_scatter and not pull_exchange and not dma_exchange)
         self.pull_exchange = bool(fused and pull_exchange) or self.dma_exchange     # both keep the row-parallel GEMMs plain
         self._keep = []          # ctypes structures referenced by the plan
         self._steps = []         # (function, argument tuple)
@@ -350,7 +354,7 @@ class TensorParallelDecoder:
         rows = tm // self.world                    # rows of it this rank owns
         control = self.comm.control
         self._peer_h = PeerBuffer(c, control, self.tokens * hidden * 2)
-        self._exchanges = [FusedExchange(c, control, tm, hidden, activations=self._peer_h, activation_offset=mb * tm * hidden * 2, pull=self.pull_exchange, dma=self.dma_exchange)
+        self._exchanges = [FusedExchange(c, control, tm, hidden, activations=self._peer_h, activation_offset=mb * tm * hidden * 2, pull=self.pull_exchange, dma=self.dma_exchange, side_scatter=self.side_scatter)
                            for mb in range(n)]
         self._x_own = c.tensor((n, rows, hidden), DType.BF16)
         eps = cfg.eps
@@ -378,6 +382,8 @@ class TensorParallelDecoder:
                 ids = TensorBuffer(self.tokens_dev.handle, (rows,), DType.I32, None, offset=first * 4)
                 self._op("rb_embedding", ctx, self._t(self.embedding), self._t(ids), self._t(x_own(mb)))
             elif kind == "wait_scatter":
+                if self.side_scatter:        # the transfer of the GEMM's rows starts here: on the side stream when the exchange is forked
+                    self._op("rb_scatter_rows", *ex.scatter_rows_args(keep))
                 self._op("rb_peer_wait", *ex.wait_args(SCATTER, ex.scatter_count, keep))
             elif kind == "wait_gather":
                 self._op("rb_peer_wait", *ex.wait_args(GATHER, 1, keep))
@@ -412,7 +418,9 @@ class TensorParallelDecoder:
             elif kind == "scatter":
                 lw = self.layers[step[2]]
                 a = self._rows(self.attn, mb) if step[3] == "wo" else self._rows(self.ffn_act, mb)
-                if self.pull_exchange:
+                if self.side_scatter:
+                    self._gemm(a, lw[step[3]], ex.own_partial())
+                elif self.pull_exchange:
                     self._gemm(a, lw[step[3]], ex.own_partial())
                     self._op("rb_peer_signal", *ex.signal_args(keep, SCATTER))
                 else:

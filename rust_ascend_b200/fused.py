@@ -15,6 +15,11 @@ buffer of its own that the others have mapped, announces it (`rb_peer_signal`), 
 (`rb_reduce_norm_push_pull`) fetches its rows of every partial product itself.  All link traffic then belongs to the
 owner-side kernel, which can run on a few SMs beside another micro batch's GEMMs, and the GEMM is never held up by the link.
 
+The side-scatter form (`FusedExchange(..., side_scatter=True)`) also keeps the GEMM plain, and moves its result to the owners'
+staging areas with a kernel of its own (`rb_scatter_rows`: posted stores only, which a few SMs keep flowing); the owner-side
+step is then the one of the scatter form.  Every transfer of the exchange can so run on the side stream, and nothing has to be
+held in flight on an SM the way remote reads must.
+
 The copy form (`FusedExchange(..., dma=True)`) moves the data with device-to-device copies between the mapped buffers
 (`rb_copy`: copy engines, no SM at all): every rank copies its rows of every partial product into a local staging area, runs
 the owner-side arithmetic locally (`rb_reduce_norm_rows`), announces its rows, and copies the other ranks' finished rows into
@@ -115,7 +120,7 @@ class FusedExchange:
     `activations` (a PeerBuffer holding at least tokens*hidden BF16 at `activation_offset`) receives the gathered rows."""
 
     def __init__(self, client: ComputeClient, control, tokens: int, hidden: int, activations: PeerBuffer | None = None,
-                 activation_offset: int = 0, pull: bool = False, dma: bool = False):
+                 activation_offset: int = 0, pull: bool = False, dma: bool = False, side_scatter: bool = False):
         self.client, self.control = client, control
         self.rank, self.world = control.rank, control.world_size
         self.tokens, self.hidden = int(tokens), int(hidden)
@@ -124,6 +129,8 @@ class FusedExchange:
             raise InvalidTensor("fused exchange needs tokens a multiple of 128 * world and hidden a multiple of 64")
         self.rows = tokens // self.world
         self.dma = bool(dma)
+        self.side_scatter = bool(side_scatter) and not (pull or dma)
+        self.local_partial = client.tensor((tokens, hidden), DType.BF16) if self.side_scatter else None
         self.pull = bool(pull) or self.dma
         # push form: a staging area the peers' GEMMs store into; pull and copy forms: this rank's whole partial product, read by
         # the peers; copy form: also a local staging area that the copies fill
@@ -144,8 +151,17 @@ class FusedExchange:
         return [self.partial.view(r, (self.tokens, self.hidden), DType.BF16) for r in range(self.world)]
 
     def own_partial(self) -> TensorBuffer:
-        """Pull form: where this rank's row-parallel GEMM writes its partial product [tokens, hidden]."""
+        """Where this rank's plain row-parallel GEMM writes its partial product [tokens, hidden] (every form but the scatter GEMM)."""
+        if self.side_scatter:
+            return self.local_partial
         return self.partial.view(self.rank, (self.tokens, self.hidden), DType.BF16)
+
+    def scatter_rows_args(self, keep: list):
+        """Arguments of rb_scatter_rows (side-scatter form)."""
+        sp, sd = self.local_partial._c(), self.done_word()._c()
+        keep.extend([sp, sd])
+        return (self.client._ctx, C.byref(sp), C.c_uint32(self.rank), C.c_uint32(self.world), tensor_array(self.staging_views(), keep),
+                tensor_array(self.flag_views(SCATTER), keep), C.byref(sd))
 
     def flag_views(self, group: int):
         return [self.flags.view(d, (FLAG_WORDS,), DType.I32, group * FLAG_WORDS * 4) for d in range(self.world)]
@@ -251,14 +267,19 @@ class FusedExchange:
     def scatter_count(self) -> int:
         """What every peer adds to this rank's SCATTER flag words per projection: the slices its scatter GEMM stores here, or one
         announcement of its finished partial product in the pull form."""
-        return 1 if self.pull else self.signals
+        return 1 if self.pull or self.side_scatter else self.signals
 
     # -- eager calls ---------------------------------------------------------------------------------------------
     def gemm_scatter(self, a: TensorBuffer, w: TensorBuffer) -> None:
         """Partial product a [tokens, K/world] x w [hidden, K/world]^T: scattered to the owners' staging areas, or (pull form)
         written to this rank's partial-product buffer by the plain GEMM and announced to every rank."""
         lib = self.client._lib
-        if self.pull:
+        if self.side_scatter:
+            sa, sw, so = a._c(), w._c(), self.own_partial()._c()
+            self._keep.extend([sa, sw, so])
+            _check(lib.rb_gemm(self.client._ctx, C.byref(sa), C.byref(sw), C.c_int32(0), C.c_int32(1), None, None, C.c_int32(0), C.byref(so)))
+            _check(lib.rb_scatter_rows(*self.scatter_rows_args(self._keep)))
+        elif self.pull:
             sa, sw, so = a._c(), w._c(), self.own_partial()._c()
             self._keep.extend([sa, sw, so])
             _check(lib.rb_gemm(self.client._ctx, C.byref(sa), C.byref(sw), C.c_int32(0), C.c_int32(1), None, None, C.c_int32(0), C.byref(so)))
@@ -297,7 +318,7 @@ class FusedExchange:
         for buf in ([self.activations] if self._own_activations else []) + [self.flags, self.staging, self.partial]:
             if buf is not None:
                 buf.close()
-        self.local_staging = None
+        self.local_staging = self.local_partial = None
 
 
 class LocalGroup:

@@ -162,6 +162,14 @@ class EmuLib:
             self._view(flags[d])[rank.value] += 1
         return 0
 
+    def rb_scatter_rows(self, ctx, partial, rank, world, staging, flags, done):
+        part = self._view(partial)
+        rows = part.shape[0] // world.value
+        for owner in range(world.value):
+            self._view(staging[owner])[rank.value] = part[owner * rows:(owner + 1) * rows]
+            self._view(flags[owner])[rank.value] += 1
+        return 0
+
     def rb_copy(self, ctx, x, y):
         self._view(y)[...] = self._view(x)
         return 0
@@ -267,7 +275,8 @@ class EmuComm:
 
 @pytest.mark.parametrize("world,micro,overlap,pull", [(1, 1, False, False), (1, 2, True, False), (2, 1, False, False), (2, 2, False, False), (2, 2, True, False),
                                                       (4, 1, False, False), (1, 1, False, True), (2, 2, True, True), (4, 1, False, True),
-                                                      (1, 1, False, "dma"), (2, 2, True, "dma"), (4, 1, False, "dma")])
+                                                      (1, 1, False, "dma"), (2, 2, True, "dma"), (4, 1, False, "dma"),
+                                                      (1, 1, False, "side"), (2, 2, True, "side"), (2, 2, False, "side"), (4, 1, False, "side")])
 def test_fused_plan_computes_the_decoder(monkeypatch, oracle, world, micro, overlap, pull):
     import rust_ascend_b200.fused as fused
     from decoder_reference import forward, full_weights
@@ -299,7 +308,7 @@ def test_fused_plan_computes_the_decoder(monkeypatch, oracle, world, micro, over
     for rank in range(world):
         client = EmuClient(shared, rank, oracle)
         model = TensorParallelDecoder(client, cfg, batch, seq, comm=EmuComm(rank, world), rank=rank, world=world, seed=3, exact_weights=True,
-                                      micro_batches=micro, fused=True, overlap_exchange=overlap, pull_exchange=pull is True, dma_exchange=pull == "dma",
+                                      micro_batches=micro, fused=True, overlap_exchange=overlap, pull_exchange=pull is True, dma_exchange=pull == "dma", side_scatter=pull == "side",
                                       sm_reserve=16 if overlap else 0)
         client.write(model.tokens_dev.handle, tokens)
         models.append(model)

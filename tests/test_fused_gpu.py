@@ -75,6 +75,12 @@ def _worker(rank, world, port, results):
     out["pull_linear_scaled"] = bf16_bits_to_f32(client.read(row_parallel_linear_allreduce(px, xs2, ws)))
     client.sync()
     px.close()
+    # side-scatter form: plain GEMM, then a kernel of posted stores takes the rows to their owners
+    sx = FusedExchange(client, control, x.shape[0], w.shape[0], side_scatter=True)
+    out["side_linear"] = bf16_bits_to_f32(client.read(row_parallel_linear_allreduce(sx, xs, ws)))
+    out["side_linear_scaled"] = bf16_bits_to_f32(client.read(row_parallel_linear_allreduce(sx, xs2, ws)))
+    client.sync()
+    sx.close()
     # copy form: device-to-device copies between the mapped buffers move the data, the owner-side arithmetic runs locally
     cx = FusedExchange(client, control, x.shape[0], w.shape[0], dma=True)
     out["copy_linear"] = bf16_bits_to_f32(client.read(row_parallel_linear_allreduce(cx, xs, ws)))
@@ -111,7 +117,8 @@ def _worker(rank, world, port, results):
     tokens4 = np.random.default_rng(1).integers(0, cfg.vocab, size=(4, 128)).astype(np.int32)
     for name, kwargs in (("fused4", {"fused": True}), ("fused4_overlap", {"fused": True, "micro_batches": 2, "overlap_exchange": True, "sm_reserve": 16, "use_graph": True}),
                          ("pull4_overlap", {"fused": True, "micro_batches": 2, "overlap_exchange": True, "pull_exchange": True, "sm_reserve": 16, "use_graph": True}),
-                         ("copy4_overlap", {"fused": True, "micro_batches": 2, "overlap_exchange": True, "dma_exchange": True, "use_graph": True})):
+                         ("copy4_overlap", {"fused": True, "micro_batches": 2, "overlap_exchange": True, "dma_exchange": True, "use_graph": True}),
+                         ("side4_overlap", {"fused": True, "micro_batches": 2, "overlap_exchange": True, "side_scatter": True, "sm_reserve": 16, "use_graph": True})):
         model = TensorParallelDecoder(client, cfg, 4, 128, comm=comm, rank=rank, world=world, seed=3, exact_weights=True, **kwargs)
         model.forward(tokens4)
         out[name] = bf16_bits_to_f32(client.read(model.forward()))
@@ -155,6 +162,8 @@ def test_two_gpu_fused_exchange(oracle):
         np.testing.assert_array_equal(got, r[0]["fused_linear"])          # every rank holds the same bits
         np.testing.assert_array_equal(r[rank]["pull_linear"], got)        # the pull form sums the same partial products in the same order
         np.testing.assert_array_equal(r[rank]["pull_linear_scaled"], -2.0 * got)   # exact: a power of two scales every BF16 value exactly
+        np.testing.assert_array_equal(r[rank]["side_linear"], got)
+        np.testing.assert_array_equal(r[rank]["side_linear_scaled"], -2.0 * got)
         np.testing.assert_array_equal(r[rank]["copy_linear"], got)
         np.testing.assert_array_equal(r[rank]["copy_linear_scaled"], -2.0 * got)
         for key in ("nccl_linear_0", "nccl_linear_1"):
@@ -183,6 +192,7 @@ def test_two_gpu_fused_exchange(oracle):
         assert np.abs(r[rank]["fused4"] - r[rank]["fused4_overlap"]).max() <= 2.0 ** -7 * np.abs(r[rank]["fused4"]).max()
         assert np.abs(r[rank]["fused4"] - r[rank]["pull4_overlap"]).max() <= 2.0 ** -7 * np.abs(r[rank]["fused4"]).max()
         assert np.abs(r[rank]["fused4"] - r[rank]["copy4_overlap"]).max() <= 2.0 ** -7 * np.abs(r[rank]["fused4"]).max()
+        assert np.abs(r[rank]["fused4"] - r[rank]["side4_overlap"]).max() <= 2.0 ** -7 * np.abs(r[rank]["fused4"]).max()
 
 
 def test_single_gpu_fused_exchange(client, oracle):
@@ -207,6 +217,10 @@ def test_single_gpu_fused_exchange(client, oracle):
         for _ in range(2):
             np.testing.assert_array_equal(bf16_bits_to_f32(client.read(row_parallel_linear_allreduce(px, xs, ws))), got)
         px.close()
+        sx = FusedExchange(client, SingleControl(), x.shape[0], w.shape[0], side_scatter=True)
+        for _ in range(2):
+            np.testing.assert_array_equal(bf16_bits_to_f32(client.read(row_parallel_linear_allreduce(sx, xs, ws))), got)
+        sx.close()
         cx = FusedExchange(client, SingleControl(), x.shape[0], w.shape[0], dma=True)
         for _ in range(2):
             np.testing.assert_array_equal(bf16_bits_to_f32(client.read(row_parallel_linear_allreduce(cx, xs, ws))), got)
@@ -234,7 +248,8 @@ def test_single_gpu_fused_exchange(client, oracle):
         want_logits = forward(oracle, cfg, full_weights(cfg, 3), tokens)
         for kwargs in ({}, {"use_graph": True}, {"micro_batches": 2, "overlap_exchange": True, "sm_reserve": 16, "use_graph": True},
                        {"pull_exchange": True, "use_graph": True}, {"micro_batches": 2, "overlap_exchange": True, "pull_exchange": True, "sm_reserve": 16, "use_graph": True},
-                       {"dma_exchange": True, "use_graph": True}, {"micro_batches": 2, "overlap_exchange": True, "dma_exchange": True, "use_graph": True}):
+                       {"dma_exchange": True, "use_graph": True}, {"micro_batches": 2, "overlap_exchange": True, "dma_exchange": True, "use_graph": True},
+                       {"side_scatter": True, "use_graph": True}, {"micro_batches": 2, "overlap_exchange": True, "side_scatter": True, "sm_reserve": 16, "use_graph": True}):
             model = TensorParallelDecoder(client, cfg, 4, 128, comm=LocalGroup(), seed=3, exact_weights=True, fused=True, **kwargs)
             model.forward(tokens)
             got = bf16_bits_to_f32(client.read(model.forward()))
