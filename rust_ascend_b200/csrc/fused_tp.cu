@@ -665,7 +665,7 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* src, uint3
 }
 
 template <int NV>      // 16-byte vectors per thread: 2 for rows of up to 4096 values, else NV
-__global__ void __launch_bounds__(PUSH_THREADS, 3) pull_reduce_norm_push_kernel(const PushParams p) {
+__global__ void __launch_bounds__(PUSH_THREADS) pull_reduce_norm_push_kernel(const PushParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
     __shared__ uint64_t full[PULL_STAGES];
@@ -714,18 +714,13 @@ __global__ void __launch_bounds__(PUSH_THREADS, 3) pull_reduce_norm_push_kernel(
 #pragma unroll
             for (int j = 0; j < 8; ++j) v[i][j] = 0.f;
         }
-        // fixed rank order, FP32: every rank computes bit-identical sums for the rows it owns.  Per vector, the loads of all
-        // sources are issued before the first add, so that their shared-memory latencies overlap.
-        const uint8_t* stage = smem + (size_t)st * stage_bytes;
+        // fixed rank order, FP32: every rank computes bit-identical sums for the rows it owns
+        for (uint32_t s = 0; s < p.partials; ++s) {
+            const uint4* src = reinterpret_cast<const uint4*>(smem + (size_t)st * stage_bytes + (size_t)s * row_bytes);
 #pragma unroll
-        for (int i = 0; i < NV; ++i) if (have[i]) {
-            uint4 w[MAX_PEERS];
-#pragma unroll
-            for (int s = 0; s < MAX_PEERS; ++s)
-                if ((uint32_t)s < p.partials) w[s] = reinterpret_cast<const uint4*>(stage + (size_t)s * row_bytes)[i * PUSH_THREADS + threadIdx.x];
-#pragma unroll
-            for (int s = 0; s < MAX_PEERS; ++s) if ((uint32_t)s < p.partials) {
-                const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&w[s]);
+            for (int i = 0; i < NV; ++i) if (have[i]) {
+                const uint4 w = src[i * PUSH_THREADS + threadIdx.x];
+                const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&w);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) { float2 f = __bfloat1622float2(h2[j]); v[i][2 * j] += f.x; v[i][2 * j + 1] += f.y; }
             }
@@ -883,26 +878,19 @@ int32_t reduce_norm_push_impl(rb_ctx* ctx, const rb_tensor* staging, const rb_te
     // Beside the compute stream's persistent GEMMs this kernel gets the SMs they leave free; alone it gets them all.
     const int sms = ctx->sm_limit > 0 ? (aux_active(ctx) ? ctx->sm_count - ctx->sm_limit : ctx->sm_limit) : ctx->sm_count;
     if (pulls) {
-        // Rows of (world partial products + the residual row) in flight in shared memory are what hides the latency of the
-        // remote reads, and blocks per SM are what does the sums and the stores: a block of 256 threads takes about 0.7 us per
-        // row.  Where two blocks with two rows each fit an SM, that split is taken (as many such blocks as fit); where they do
-        // not (eight ranks: 72 KiB per row set), one block keeps up to three rows in flight.  (One block per SM with eight rows
-        // in flight was measured too: a step of the pipelined row-parallel Linear at two ranks took 229 us instead of 128-167.)
+        // Every block keeps up to three rows of (world partial products + the residual row) in flight in shared memory, and an
+        // SM takes as many blocks as fit, so that the stores of one row overlap the sum of another.  Measured against it at two
+        // ranks and kept out: one block per SM with eight rows in flight (a pipelined Linear step took 229 us instead of
+        // 128-167); two rows per block and more blocks, with the loads of all sources issued before the adds (the unpipelined
+        // Linear step took 185 us instead of 172, the decoder forward 28.7 ms instead of 27.4-28.1).
         const uint64_t stage_bytes = (uint64_t)(world + (x_in ? 1 : 0)) * width * 2;
         const uint64_t budget = 222 * 1024;
-        uint32_t stages;
-        uint64_t per_sm;
-        if (4 * stage_bytes + 2 * 1152 <= budget) {
-            stages = 2;
-            per_sm = budget / (2 * stage_bytes + 1152);
-        } else {
-            stages = (uint32_t)(budget / stage_bytes);
-            if (stages > 3u) stages = 3u;
-            per_sm = 1;
-        }
+        uint32_t stages = (uint32_t)(budget / stage_bytes);
+        if (stages > 3u) stages = 3u;
         if (stages == 0) return fail(RB_INVALID_TENSOR, "pull form: one row of every rank's partial product (%llu bytes) does not fit shared memory", (unsigned long long)stage_bytes);
         p.stages = stages;
         const uint32_t smem = (uint32_t)(stages * stage_bytes + 128);
+        uint64_t per_sm = budget / (smem + 1024);
         per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
         static std::once_flag once;
         static cudaError_t configured = cudaSuccess;
