@@ -886,8 +886,11 @@ def decoder_candidates(world: int, sequences: int = 8, fused: bool = False):
                 dict(overlap, tp=world, fused=True, overlap_exchange=True, pull_exchange=True, nccl_max_ctas=0)]
         if sequences % 4 == 0 and (sequences // 4 * 2048) % (128 * world) == 0:
             out.append(dict(overlap, tp=world, fused=True, overlap_exchange=True, pull_exchange=True, nccl_max_ctas=0, micro_batches=4))
-        for sms in (NCCL_CTAS // 2, NCCL_CTAS * 3 // 2, 2 * NCCL_CTAS):
+        for sms in (NCCL_CTAS // 2, NCCL_CTAS * 5 // 4, NCCL_CTAS * 3 // 2, NCCL_CTAS * 7 // 4, 2 * NCCL_CTAS):
             out.append(dict(overlap, tp=world, fused=True, overlap_exchange=True, pull_exchange=True, nccl_max_ctas=0, sms_left_to_nccl=sms))
+        if sequences % 4 == 0 and (sequences // 4 * 2048) % (128 * world) == 0:
+            out.append(dict(overlap, tp=world, fused=True, overlap_exchange=True, pull_exchange=True, nccl_max_ctas=0, micro_batches=4,
+                            sms_left_to_nccl=NCCL_CTAS * 3 // 2))
         # side-scatter form: plain GEMMs, the rows go to their owners by a kernel of posted stores (on the side stream when overlapped)
         out.append(dict(plain, tp=world, fused=True, side_scatter=True))
         for sms in (NCCL_CTAS // 2, NCCL_CTAS, NCCL_CTAS * 3 // 2):

@@ -32,7 +32,7 @@ def test_fused_candidates_are_added_on_request():
     import bench
     extra = [c for c in bench.decoder_candidates(8, fused=True) if c.get("fused")]
     assert [(c["tp"], c["micro_batches"], c.get("overlap_exchange", False), c.get("pull_exchange", False)) for c in extra if not c.get("dma_exchange") and not c.get("side_scatter")] == [
-        (8, 1, False, False), (8, 2, True, False), (8, 1, False, True), (8, 2, True, True), (8, 4, True, True), (8, 2, True, True), (8, 2, True, True), (8, 2, True, True)]
+        (8, 1, False, False), (8, 2, True, False), (8, 1, False, True), (8, 2, True, True), (8, 4, True, True)] + [(8, 2, True, True)] * 5 + [(8, 4, True, True)]
     assert [(c["micro_batches"], c.get("overlap_exchange", False), c["sms_left_to_nccl"]) for c in extra if c.get("dma_exchange")] == [(1, False, 0), (2, True, 0), (4, True, 0)]
     assert [(c["micro_batches"], c.get("overlap_exchange", False), c["sms_left_to_nccl"]) for c in extra if c.get("side_scatter")] == [(1, False, 0), (2, True, 8), (2, True, 16), (2, True, 24)]
     assert all(c["nccl_max_ctas"] == 0 for c in extra)                  # NCCL is not on this path
