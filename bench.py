@@ -258,6 +258,9 @@ class ClockSampler(threading.Thread):
             self.nv = pynvml
             self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
             self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            # built here, not in run(): scanning the module's names takes the interpreter lock for milliseconds, and the thread
+            # starts together with the timed region, whose launches come from the main thread
+            self.names = {getattr(pynvml, k): k for k in dir(pynvml) if k.startswith("nvmlClocksThrottleReason") or k.startswith("nvmlClocksEventReason")}
             self.ok = True
         except Exception:  # NVML unavailable: the bench still runs, clocks are reported as null
             self.ok = False
@@ -265,8 +268,7 @@ class ClockSampler(threading.Thread):
     def run(self):
         if not self.ok:
             return
-        nv = self.nv
-        names = {getattr(nv, k): k for k in dir(nv) if k.startswith("nvmlClocksThrottleReason") or k.startswith("nvmlClocksEventReason")}
+        nv, names = self.nv, self.names
         while not self._stop_flag.is_set():
             try:
                 self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
