@@ -188,6 +188,14 @@ class RowParallelHeadline:
         limit = self.sm_count - SIDE_SMS if name == PIPELINED else (self.sm_count - PUSH_SIDE_SMS if name == PUSHED_PIPELINED else 0)
         _check(self.client._lib.rb_set_sm_limit(self.client._ctx, C.c_int32(limit)))
 
+    def align(self):
+        """Enqueues a barrier between the GPUs on the compute stream (flag words over peer memory, no host involvement), so that
+        the timed region starts on every GPU within microseconds: the host-side barrier before it leaves the ranks up to a
+        millisecond apart, which a timed region of a few milliseconds whose steps exchange data would count as step time."""
+        exchange = getattr(self, "exchange", None)
+        if exchange is not None and not getattr(self, "fused_error", None):
+            exchange.barrier()
+
     def drain(self):
         """Joins the side stream: after it, every step enqueued so far is complete in the compute stream's order."""
         from rust_ascend_b200.runtime import _check
@@ -216,6 +224,7 @@ class RowParallelHeadline:
                 self._slot_used = [False] * PIPE_DEPTH
                 continue
             self.dist.barrier()
+            self.align()
             self.client.start_profile()
             for i in range(20):
                 fn(i)
@@ -402,6 +411,8 @@ def run_ours(args):
         dist.barrier()
     sampler = ClockSampler(local)
     sampler.start()
+    if exchange is not None:
+        exchange.align()
     launches_before = client.stats()["launches"]
     client.start_profile()
     for i in range(args.steps):
