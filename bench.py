@@ -998,6 +998,8 @@ def decoder_extra(client, pk, rank, world, dist, sink, candidates, results):
         if dist is not None:
             dist.barrier()
         steps = 6
+        if getattr(model, "_exchanges", None):      # fused forms: the GPUs start the timed forwards together (see RowParallelHeadline.align)
+            model._exchanges[0].barrier()
         client.start_profile()
         for _ in range(steps):
             model.forward()
